@@ -1,0 +1,149 @@
+/*
+ * lsg.h — C ABI of the B200 (sm_100a) quantized-GEMM library.
+ *
+ * Every entry point takes plain pointers and sizes, launches asynchronously on
+ * the CUDA stream it is given (a cudaStream_t passed as void*), never
+ * allocates or frees device memory unless its comment says so, and returns an
+ * lsg_status (0 on success, negative on error).  The text of the last error of
+ * the calling thread is available from lsg_last_error().  No C++ exception
+ * crosses this boundary.
+ *
+ * Each declaration cites the interface of the reference project
+ * (kkontosis/LayerStoRmGemmKernels, paths relative to its root) that it
+ * replaces.
+ */
+#ifndef LSG_H_
+#define LSG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LSG_API __attribute__((visibility("default")))
+#else
+#define LSG_API
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* Status codes                                                             */
+/* ------------------------------------------------------------------------ */
+typedef enum lsg_status {
+    LSG_OK = 0,
+    LSG_ERR_INVALID = -1,     /* bad argument (shape, divisibility, null pointer) */
+    LSG_ERR_UNSUPPORTED = -2, /* type / dtype / mode not implemented             */
+    LSG_ERR_WORKSPACE = -3,   /* workspace missing or too small                  */
+    LSG_ERR_CUDA = -4,        /* a CUDA runtime call failed                      */
+    LSG_ERR_ALIGNMENT = -5,   /* a pointer is not aligned as required            */
+    LSG_ERR_DEVICE_WAIT = -6  /* a kernel gave up on a bounded device-side wait  */
+} lsg_status;
+
+/* Last error message of the calling thread ("" when none). */
+LSG_API const char* lsg_last_error(void);
+
+/* Library version string. */
+LSG_API const char* lsg_version(void);
+
+/* Reads and clears the device-side status word of the current device.  Kernels
+ * that wait on an mbarrier do so with a time limit; when the limit runs out
+ * they record a non-zero code here and return instead of spinning.  This call
+ * synchronizes the device.  *code receives 0 when no kernel reported. */
+LSG_API int lsg_device_status(int* code);
+
+/* ------------------------------------------------------------------------ */
+/* GGUF weight types                                                        */
+/* ids 0..6 replace: enum class GgufType,                                   */
+/*   csrc/sm120/gemm/gguf/gguf_dequant_gemm.h:23-31                         */
+/* id 7 (Q4_0) has no counterpart in the reference; it is appended so the   */
+/* reference ids keep their meaning.                                        */
+/* ------------------------------------------------------------------------ */
+typedef enum lsg_gguf_type {
+    LSG_GGUF_Q2_K = 0,
+    LSG_GGUF_Q3_K = 1,
+    LSG_GGUF_Q4_K = 2,
+    LSG_GGUF_Q5_K = 3,
+    LSG_GGUF_Q6_K = 4,
+    LSG_GGUF_Q8_0 = 5,
+    LSG_GGUF_MXFP4 = 6,
+    LSG_GGUF_Q4_0 = 7
+} lsg_gguf_type;
+
+typedef enum lsg_dtype {
+    LSG_DTYPE_BF16 = 0, /* what the reference always writes */
+    LSG_DTYPE_F32 = 1,  /* extension: un-rounded accumulator, for parity checks */
+    LSG_DTYPE_F16 = 2
+} lsg_dtype;
+
+/* Values per packed block (32 or 256); 0 for an unknown type.
+ * Replaces gguf_block_values, csrc/sm120/gemm/gguf/gguf_dequant_gemm.cu:292-294 */
+LSG_API int lsg_gguf_block_values(int type);
+
+/* Bytes per packed block; 0 for an unknown type.
+ * Replaces gguf_block_bytes, csrc/sm120/gemm/gguf/gguf_dequant_gemm.cu:296-307 */
+LSG_API int lsg_gguf_block_bytes(int type);
+
+/* ------------------------------------------------------------------------ */
+/* Q8_1 activation quantizer                                                */
+/* ------------------------------------------------------------------------ */
+
+/* bf16 x[M,K] -> M*(K/32) blocks of 36 bytes {fp16 d, fp16 sum, int8 q[32]}.
+ * K must be a multiple of 32.  Bit-exact with the reference kernel.
+ * Replaces gguf_quantize_q8_1_cuda, csrc/sm120/gemm/gguf/gguf_mmvq.cu:124-128
+ * (kernel quantize_bf16_to_q8_1, same file :42-63). */
+LSG_API int lsg_quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* GGUF mmvq: C[M,N] = Q8_1(A[M,K]) . decode(B[N,K])^T  (decode GEMV)       */
+/* ------------------------------------------------------------------------ */
+
+/* Mirrors struct GgufMmvqParams, csrc/sm120/gemm/gguf/gguf_mmvq.h:21-27,
+ * plus out_dtype. */
+typedef struct lsg_gguf_mmvq_params {
+    int M, N, K;
+    const void* A; /* [M,K] bf16, row-major, device                      */
+    const void* B; /* [N,(K/QK)*block_bytes] packed weight, 16-B aligned */
+    void* C;       /* [M,N] out_dtype, row-major, device                 */
+    int type;      /* lsg_gguf_type                                      */
+    int out_dtype; /* lsg_dtype: BF16 (reference behaviour) or F32       */
+} lsg_gguf_mmvq_params;
+
+/* Bytes of caller-provided scratch for the quantized activation:
+ * M*(K/32)*36.  Replaces gguf_mmvq_workspace_bytes,
+ * csrc/sm120/gemm/gguf/gguf_mmvq.cu:120-122. */
+LSG_API size_t lsg_gguf_mmvq_workspace_bytes(int M, int K);
+
+/* Quantizes A to Q8_1 into `workspace`, then runs the integer mat-vec.
+ * Any M >= 1 (rows are processed eight at a time).  K must be a multiple of
+ * the type's block size.  Replaces launch_gguf_mmvq,
+ * csrc/sm120/gemm/gguf/gguf_mmvq.cu:130-152. */
+LSG_API int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* Same mat-vec on activations that are already Q8_1 blocks (M*(K/32)*36 bytes
+ * at xq).  p->A is ignored.  Exposed so that several projections sharing one
+ * input quantize it once; no counterpart in the reference API (its kernel
+ * gguf_mmvq_kernel, gguf_mmvq.cu:69-101, is file-local). */
+LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* GGUF dequant GEMM (lossless-activation golden strategy)                  */
+/* ------------------------------------------------------------------------ */
+
+/* C[M,N] = A[M,K] (bf16) . dequant(B)^T with fp32 accumulation.
+ * Replaces launch_gguf_dequant_gemm,
+ * csrc/sm120/gemm/gguf/gguf_dequant_gemm.cu:309-325
+ * (params struct gguf_dequant_gemm.h:33-39). */
+LSG_API int lsg_gguf_dequant_gemm(const lsg_gguf_mmvq_params* p, void* stream);
+
+/* Expands packed blocks to fp32: out[n_blocks * block_values].  Test helper;
+ * replaces the per-type dequant_*_block device functions of csrc/formats/. */
+LSG_API int lsg_gguf_dequant_blocks(const void* packed, float* out, int type, long long n_blocks,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LSG_H_ */

@@ -1,0 +1,93 @@
+"""ctypes view of the C ABI declared in include/lsg.h.
+
+The shared library is the product; this module only loads it and turns status
+codes into exceptions.  There is no CPU fallback: if liblsg_b200.so is missing
+or does not load, importing this module raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liblsg_b200.so")
+
+# lsg_gguf_type ids (ids 0..6 are the reference's GgufType values)
+Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_0, MXFP4, Q4_0 = range(8)
+GGUF_TYPES = {"Q2_K": Q2_K, "Q3_K": Q3_K, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K,
+              "Q8_0": Q8_0, "MXFP4": MXFP4, "Q4_0": Q4_0}
+BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q8_0: 34, MXFP4: 17, Q4_0: 18}
+BLOCK_VALUES = {Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256, Q8_0: 32, MXFP4: 32, Q4_0: 32}
+
+DTYPE_BF16, DTYPE_F32, DTYPE_F16 = 0, 1, 2
+
+LSG_OK = 0
+LSG_ERR_INVALID = -1
+LSG_ERR_UNSUPPORTED = -2
+LSG_ERR_WORKSPACE = -3
+LSG_ERR_CUDA = -4
+LSG_ERR_ALIGNMENT = -5
+LSG_ERR_DEVICE_WAIT = -6
+
+
+class LsgError(RuntimeError):
+    """A C-ABI call returned a negative status.  `.code` holds it."""
+
+    def __init__(self, code, message):
+        super().__init__(f"lsg status {code}: {message}")
+        self.code = code
+
+
+class LsgInvalidArgument(LsgError, ValueError):
+    """LSG_ERR_INVALID: where the reference's launchers throw std::invalid_argument."""
+
+
+class GgufMmvqParams(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("C", ctypes.c_void_p),
+                ("type", ctypes.c_int), ("out_dtype", ctypes.c_int)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m layerstormgemmkernels_b200.build` "
+            "(there is no CPU fallback)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, ci, sz, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_longlong
+    sigs = {
+        "lsg_last_error": (ctypes.c_char_p, []),
+        "lsg_version": (ctypes.c_char_p, []),
+        "lsg_device_status": (ci, [ctypes.POINTER(ci)]),
+        "lsg_gguf_block_values": (ci, [ci]),
+        "lsg_gguf_block_bytes": (ci, [ci]),
+        "lsg_quantize_q8_1": (ci, [vp, vp, ci, ci, vp]),
+        "lsg_gguf_mmvq_workspace_bytes": (sz, [ci, ci]),
+        "lsg_gguf_mmvq": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
+        "lsg_gguf_mmvq_q8_1": (ci, [ctypes.POINTER(GgufMmvqParams), vp, vp]),
+        "lsg_gguf_dequant_gemm": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
+        "lsg_gguf_dequant_blocks": (ci, [vp, vp, ci, ll, vp]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib, sorted(sigs)
+
+
+lib, EXPORTS = _load()
+
+
+def check(status):
+    """Raises the exception matching a negative lsg_status."""
+    if status == LSG_OK:
+        return
+    msg = lib.lsg_last_error().decode("utf-8", "replace")
+    if status == LSG_ERR_INVALID:
+        raise LsgInvalidArgument(status, msg)
+    raise LsgError(status, msg)
+
+
+def device_status():
+    """Reads and clears the device-side status word (synchronizes the device)."""
+    code = ctypes.c_int(0)
+    check(lib.lsg_device_status(ctypes.byref(code)))
+    return code.value

@@ -1,0 +1,183 @@
+// Shared host/device helpers for the sm_100a kernels: status plumbing, bounded
+// mbarrier waits, 1-D bulk (TMA) copies, programmatic-dependent-launch hooks.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/lsg.h"
+
+namespace lsg {
+
+// ---------------------------------------------------------------------------
+// Host: error text + status helpers (defined in capi.cu)
+// ---------------------------------------------------------------------------
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+// Address of the per-device status word kernels report bounded-wait failures to.
+unsigned int* device_status_word();
+int sm_count();
+
+#define LSG_CUDA_TRY(expr)                                        \
+    do {                                                          \
+        cudaError_t e__ = (expr);                                 \
+        if (e__ != cudaSuccess) return ::lsg::cuda_fail(e__, #expr); \
+    } while (0)
+
+// Device status codes written to the status word.
+enum : unsigned int {
+    kDevOk = 0,
+    kDevWaitFull = 1,   // consumer gave up waiting for a bulk copy to land
+    kDevWaitEmpty = 2,  // producer gave up waiting for a stage to be released
+    kDevWaitMma = 3,    // epilogue gave up waiting for tensor-core completion
+    kDevWaitTmem = 4,
+};
+
+#if defined(__CUDACC__)
+
+// ---------------------------------------------------------------------------
+// Device: small PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+    // Makes barrier initialisation visible to the async (TMA) proxy.
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Time limit of every device-side wait.  Nothing in these kernels legitimately
+// waits longer than a few microseconds; two seconds only ever elapses when a
+// copy or an MMA was mis-issued, and then the kernel reports and returns.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Waits for the phase with the given parity to complete.  Returns false (after
+// recording `code` in *status) when the time limit runs out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  unsigned int* status, unsigned int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (status) atomicCAS(status, 0u, code);
+            return false;
+        }
+    }
+}
+
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`.
+// src, dst 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Same with an L2 eviction-priority hint (weights are streamed once).
+__device__ __forceinline__ void bulk_g2s_hint(void* dst_smem, const void* src_gmem,
+                                              uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start its
+// prologue now / wait until the previous kernel's memory is visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_prior() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// dp4a with unsigned first operand (u8 x s8 -> s32).
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ float fp16_bits_to_float(uint32_t h) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
+}
+
+#endif  // __CUDACC__
+
+// Launch helper: plain or with the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace lsg

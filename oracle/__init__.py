@@ -1,0 +1,97 @@
+"""CPU oracle (test infrastructure): ctypes loader for oracle/liblsg_oracle.so.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liblsg_oracle.so")
+
+
+def build(force=False):
+    """Compiles the C restatement with gcc (seconds)."""
+    srcs = [os.path.join(_HERE, n) for n in ("lsg_oracle.c", "lsg_oracle_quant.c", "Makefile")]
+    if (not force and os.path.exists(LIB_PATH)
+            and all(os.path.getmtime(LIB_PATH) >= os.path.getmtime(s) for s in srcs)):
+        return LIB_PATH
+    subprocess.run(["make", "-C", _HERE, "-B", "liblsg_oracle.so"], check=True,
+                   capture_output=True)
+    return LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.oracle_f16_to_f32.restype = ctypes.c_float
+        _lib.oracle_f16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib.oracle_f32_to_f16.restype = ctypes.c_uint16
+        _lib.oracle_f32_to_f16.argtypes = [ctypes.c_float]
+    return _lib
+
+
+def _ptr(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _u8(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.uint8
+    return a
+
+
+def block_values(t):
+    return lib().oracle_block_values(int(t))
+
+
+def block_bytes(t):
+    return lib().oracle_block_bytes(int(t))
+
+
+def quantize_q8_1(x_bf16_bits):
+    """x_bf16_bits: uint16 [M,K] (raw bf16).  Returns uint8 [M, K/32, 36]."""
+    x = np.ascontiguousarray(x_bf16_bits, dtype=np.uint16)
+    M, K = x.shape
+    out = np.zeros((M, K // 32, 36), dtype=np.uint8)
+    lib().oracle_quantize_q8_1(_ptr(x), _ptr(out), ctypes.c_int(M), ctypes.c_int(K))
+    return out
+
+
+def dequant(t, packed):
+    """packed: uint8 [N, row_bytes].  Returns float32 [N, K]."""
+    p = _u8(packed)
+    N = p.shape[0]
+    nblk = p.shape[1] // block_bytes(t)
+    out = np.zeros((N, nblk * block_values(t)), dtype=np.float32)
+    lib().oracle_dequant_blocks(ctypes.c_int(int(t)), _ptr(p), ctypes.c_long(N * nblk), _ptr(out))
+    return out
+
+
+def mmvq(t, xq, W, K):
+    """Integer mat-vec in double precision.  xq uint8 [M,K/32,36]; W uint8 [N,row_bytes]."""
+    xq = _u8(xq)
+    W = _u8(W)
+    M, N = xq.shape[0], W.shape[0]
+    out = np.zeros((M, N), dtype=np.float64)
+    lib().oracle_mmvq(ctypes.c_int(int(t)), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                      _ptr(xq), _ptr(W), _ptr(out))
+    return out
+
+
+def dequant_gemm(t, a_bf16_bits, W, K):
+    a = np.ascontiguousarray(a_bf16_bits, dtype=np.uint16)
+    W = _u8(W)
+    M, N = a.shape[0], W.shape[0]
+    out = np.zeros((M, N), dtype=np.float64)
+    lib().oracle_dequant_gemm(ctypes.c_int(int(t)), ctypes.c_int(M), ctypes.c_int(N),
+                              ctypes.c_int(K), _ptr(a), _ptr(W), _ptr(out))
+    return out

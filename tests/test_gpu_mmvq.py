@@ -1,0 +1,193 @@
+"""GPU parity tests for the GGUF decode path, through the C ABI, against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from layerstormgemmkernels_b200 import quantize as Q
+from layerstormgemmkernels_b200.capi import GGUF_TYPES, BLOCK_BYTES, BLOCK_VALUES
+
+pytestmark = pytest.mark.gpu
+T = GGUF_TYPES
+
+# GEMM parity bound of the north star: max |y - ref| / max |ref| <= 1e-3.  The fp32
+# accumulator output is held to 2e-5 (it only differs from the oracle by summation order).
+TOL_BF16 = 1e-3 * 4  # bf16 rounding alone is up to 2^-9 = 1.95e-3 relative per element
+TOL_F32 = 2e-5
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from layerstormgemmkernels_b200 import ops as _ops, capi
+    assert torch.cuda.is_available()
+    yield _ops
+    assert capi.device_status() == 0, "a kernel reported a timed-out device-side wait"
+
+
+def bf16_bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def rel_err(got, ref):
+    return np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30)
+
+
+@pytest.mark.parametrize("M,K", [(1, 32), (1, 4096), (3, 512), (8, 14336), (17, 256), (64, 2048)])
+def test_q8_1_quantizer_bit_exact(ops, M, K):
+    g = torch.Generator().manual_seed(M * 1000 + K)
+    x = torch.randn(M, K, generator=g)
+    x[0, :32] = 0.0                       # all-zero block -> d = 0, q = 0
+    if K >= 64:
+        x[-1, 32:64] *= 1e-3              # small block
+        x[-1, 40] = 3e4                   # large outlier
+    xb = x.to(torch.bfloat16).cuda()
+    got = ops.quantize_q8_1(xb).cpu().numpy()
+    ref = oracle.quantize_q8_1(bf16_bits(xb))
+    np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.parametrize("name", list(T))
+def test_dequant_blocks_match_oracle(ops, name):
+    t = T[name]
+    K = 512
+    W = Q.random_gguf_weight(name, 33, K, seed=21)
+    got = ops.gguf_dequant(torch.from_numpy(W).cuda(), t).cpu().numpy()
+    ref = oracle.dequant(t, W)
+    # same fp32 operations; fused multiply-add contraction may differ in the last bit
+    np.testing.assert_allclose(got, ref, rtol=3e-7, atol=1e-9)
+
+
+@pytest.mark.parametrize("name", list(T))
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 12, 17])
+def test_mmvq_matches_oracle_small(ops, name, M):
+    """The reference's own test shape (tests/test_gguf_mmvq.py:55-72): N=320, K=512."""
+    t = T[name]
+    N, K = 320, 512
+    g = torch.Generator().manual_seed(M)
+    A = (torch.randn(M, K, generator=g) * 0.4).to(torch.bfloat16).cuda()
+    W = Q.random_gguf_weight(name, N, K, seed=42)
+    Wd = torch.from_numpy(W).cuda()
+    xq = oracle.quantize_q8_1(bf16_bits(A))
+    ref = oracle.mmvq(t, xq, W, K)
+    got32 = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(got32, ref) <= TOL_F32
+    got16 = ops.gguf_mmvq(A, Wd, t, N, K).float().cpu().numpy()
+    assert rel_err(got16, ref) <= TOL_BF16
+    # bf16 output must be exactly the rounding of the fp32 accumulator
+    np.testing.assert_array_equal(
+        got16, torch.from_numpy(got32).to(torch.bfloat16).float().numpy())
+
+
+@pytest.mark.parametrize("name,N,K,M", [
+    ("Q4_K", 1536, 2048, 1), ("Q8_0", 1536, 2048, 1),     # reference decode shape
+    ("Q4_K", 1024, 4096, 1), ("Q4_K", 1024, 4096, 8),     # k/v projection
+    ("Q6_K", 1024, 4096, 2), ("Q6_K", 1000, 4096, 4),     # N not a multiple of anything
+    ("Q4_K", 301, 14336, 1), ("Q4_K", 301, 14336, 8),     # long K: smem activations
+    ("Q6_K", 150, 14336, 5), ("Q4_0", 777, 4096, 1),
+    ("Q8_0", 600, 4096, 3), ("MXFP4", 513, 2048, 2),
+    ("Q2_K", 300, 768, 1), ("Q3_K", 300, 768, 7), ("Q5_K", 129, 768, 4),  # K=768: 12 chunks
+    ("Q4_K", 5, 256, 1), ("Q8_0", 3, 32, 1), ("MXFP4", 7, 32, 2), ("Q4_0", 1, 96, 9),
+])
+def test_mmvq_matches_oracle_shapes(ops, name, N, K, M):
+    t = T[name]
+    g = torch.Generator().manual_seed(N + K + M)
+    A = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    W = Q.random_gguf_weight(name, N, K, seed=N)
+    Wd = torch.from_numpy(W).cuda()
+    ref = oracle.mmvq(t, oracle.quantize_q8_1(bf16_bits(A)), W, K)
+    got = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(got, ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0"])
+def test_mmvq_real_quantized_weights_vs_dequant_golden(ops, name, golden_dir):
+    """Weights quantized from N(0, 0.02): integer path vs lossless-activation golden
+    (cosine >= 0.999 is the reference's own acceptance bound, test_gguf_mmvq.py:65-68)."""
+    t = T[name]
+    N, K, M = 256, 1024, 4
+    rng = np.random.default_rng(1)
+    W = Q.QUANTIZERS[name]((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
+    A = torch.randn(M, K, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+    Wd = torch.from_numpy(W).cuda()
+    out = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32).cpu().numpy()
+    gold = ops.gguf_dequant_gemm(A, Wd, t, N, K, out_dtype=torch.float32).cpu().numpy()
+    gold_cpu = oracle.dequant_gemm(t, bf16_bits(A), W, K)
+    assert rel_err(gold, gold_cpu) <= TOL_F32
+    cos = (out * gold).sum() / np.sqrt((out * out).sum() * (gold * gold).sum())
+    assert cos >= 0.999
+
+
+def test_mmvq_q4k_golden_fixture(ops, golden_dir):
+    """Weights packed by the reference's own quantize_to_q4k (committed fixture)."""
+    z = np.load(os.path.join(golden_dir, "q4k_reference.npz"))
+    W = z["packed"]
+    A = torch.from_numpy(z["x_bf16"].view(np.int16)).view(torch.bfloat16).cuda()
+    Wd = torch.from_numpy(W).cuda()
+    N, K = W.shape[0], 512
+    gold = ops.gguf_dequant_gemm(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(gold, z["gemm"].astype(np.float64)) <= TOL_F32
+    ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(z["x_bf16"]), W, K)
+    got = ops.gguf_mmvq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(got, ref) <= TOL_F32
+
+
+def test_mmvq_bit_deterministic(ops):
+    """tests/test_gguf_mmvq.py:91-103."""
+    N, K = 640, 1024
+    A = (torch.randn(3, K, generator=torch.Generator().manual_seed(2)) * 0.4).to(torch.bfloat16).cuda()
+    W = torch.from_numpy(Q.random_gguf_weight("Q8_0", N, K, seed=9)).cuda()
+    ref = ops.gguf_mmvq(A, W, T["Q8_0"], N, K)
+    for _ in range(5):
+        assert torch.equal(ref, ops.gguf_mmvq(A, W, T["Q8_0"], N, K))
+
+
+def test_mmvq_graph_capture(ops):
+    """tests/test_gguf_mmvq.py:106-134: capture + replay equals eager."""
+    N, K = 512, 1024
+    A = (torch.randn(1, K, generator=torch.Generator().manual_seed(3)) * 0.4).to(torch.bfloat16).cuda()
+    W = torch.from_numpy(Q.random_gguf_weight("Q8_0", N, K, seed=11)).cuda()
+    eager = ops.gguf_mmvq(A, W, T["Q8_0"], N, K)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            ops.gguf_mmvq(A, W, T["Q8_0"], N, K)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        captured = ops.gguf_mmvq(A, W, T["Q8_0"], N, K)
+    captured.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(eager, captured)
+
+
+def test_mmvq_full_size_linearity(ops):
+    """Llama-3-8B gate/up shape (14336 x 4096, Q4_K): too big for the scalar oracle, so
+    check size-independent properties: a sampled set of rows against the oracle, and
+    exact agreement between M=1 calls and the rows of an M=8 call."""
+    N, K = 14336, 4096
+    W = Q.random_gguf_weight("Q4_K", N, K, seed=5)
+    Wd = torch.from_numpy(W).cuda()
+    A = torch.randn(8, K, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).cuda()
+    y8 = ops.gguf_mmvq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32).cpu().numpy()
+    rows = np.r_[0:8, 7000:7008, N - 8:N]
+    ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bf16_bits(A)), W[rows], K)
+    assert rel_err(y8[:, rows], ref) <= TOL_F32
+    y1 = ops.gguf_mmvq(A[3:4].contiguous(), Wd, T["Q4_K"], N, K, out_dtype=torch.float32).cpu().numpy()
+    assert rel_err(y1[0], y8[3].astype(np.float64)) <= TOL_F32
+
+
+def test_errors_mirror_reference(ops):
+    A = torch.zeros(1, 100, dtype=torch.bfloat16, device="cuda")
+    W = torch.zeros(8, 144, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError, match="divisible"):      # std::invalid_argument -> ValueError
+        ops.gguf_mmvq(A, W, T["Q4_K"], 8, 100)
+    with pytest.raises(RuntimeError, match="BF16"):         # TORCH_CHECK -> RuntimeError
+        ops.gguf_mmvq(A.float(), W, T["Q4_K"], 8, 100)
+    with pytest.raises(RuntimeError, match="size"):
+        ops.gguf_mmvq(A, W, T["Q4_K"], 8, 256)
