@@ -313,7 +313,12 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         const uint32_t slab = smem_u32(ring + static_cast<size_t>(s) * a.stage_bytes) +
                               static_cast<uint32_t>(src_b & 15);
 
-        for (int g = warp * RPP; g < nrows; g += n_cons_warps * RPP) {
+        // Row groups are dealt to warps round-robin across the whole row range of the
+        // CTA (not per slab), so that short slabs still keep every warp busy.
+        const int groups_per_slab = (a.slab_rows + RPP - 1) / RPP;
+        const int first_group = i * groups_per_slab;
+        const int my_first = (warp + n_cons_warps - first_group % n_cons_warps) % n_cons_warps;
+        for (int g = my_first * RPP; g < nrows; g += n_cons_warps * RPP) {
             int rloc[RW];
             uint32_t raddr[RW];
 #pragma unroll

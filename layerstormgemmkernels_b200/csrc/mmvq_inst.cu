@@ -15,7 +15,7 @@ constexpr int T = LSG_MMVQ_TYPE;
 constexpr int kConsumerWarps = 15;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kSmemCap = 227 * 1024;
-constexpr int kStageTarget = 16 * 1024;
+constexpr int kStageTarget = 24 * 1024;
 
 template <int MT, int RW, int L, int XREG>
 int launch_variant(const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
