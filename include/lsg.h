@@ -128,6 +128,17 @@ LSG_API int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace, size_t
  * gguf_mmvq_kernel, gguf_mmvq.cu:69-101, is file-local). */
 LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, void* stream);
 
+/* Launch geometry of the mmvq kernels, process-wide: consumer warps per CTA
+ * (1..15), CTAs of one launch per SM, KiB per pipeline stage, and how many CTAs
+ * (of this and of neighbouring launches in the stream) split an SM's shared
+ * memory.  An argument <= 0 keeps the current value; skip_math < 0 keeps it,
+ * 1 makes kernels stream the weights without doing the arithmetic (bandwidth
+ * measurements only - outputs are then zeros).  Results do not depend on the
+ * geometry.  No counterpart in the reference (its grid is fixed: one CTA per
+ * output channel, gguf_mmvq.cu:104-112). */
+LSG_API int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_kib,
+                                int smem_share, int skip_math);
+
 /* ------------------------------------------------------------------------ */
 /* GGUF dequant GEMM (lossless-activation golden strategy)                  */
 /* ------------------------------------------------------------------------ */

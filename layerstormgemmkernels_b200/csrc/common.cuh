@@ -74,22 +74,25 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
+    // The third operand is a suspend-time hint in nanoseconds: the thread sleeps in
+    // hardware until the phase completes or the hint runs out, instead of polling
+    // and taking issue slots from the warps that have work.
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
         : "memory");
     return ok != 0;
 }
 
 // Time limit of every device-side wait.  Nothing in these kernels legitimately
-// waits longer than a few microseconds; two seconds only ever elapses when a
+// waits longer than a few microseconds; 0.2 s only ever elapses when a
 // copy or an MMA was mis-issued, and then the kernel reports and returns.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr uint64_t kWaitLimitNs = 200000000ull;
 
 // Waits for the phase with the given parity to complete.  Returns false (after
 // recording `code` in *status) when the time limit runs out.
@@ -99,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 16; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
         }
         if (global_timer_ns() - t0 > kWaitLimitNs) {

@@ -4,20 +4,48 @@
 #include "mmvq.cuh"
 #include "host.h"
 
+#include <stdlib.h>
+
 namespace lsg {
 
 namespace {
 
+// Process-wide launch geometry.  Defaults suit decode on a 148-SM B200; the
+// environment (LSG_MMVQ_WARPS / _CTAS / _STAGE_KB / _SHARE) or lsg_mmvq_set_tuning
+// override them.
+MmvqTune& tuning() {
+    static MmvqTune t = [] {
+        MmvqTune v{7, 1, 16, 2, 0};
+        if (const char* e = getenv("LSG_MMVQ_WARPS")) v.warps = atoi(e);
+        if (const char* e = getenv("LSG_MMVQ_CTAS")) v.ctas = atoi(e);
+        if (const char* e = getenv("LSG_MMVQ_STAGE_KB")) v.stage_kb = atoi(e);
+        if (const char* e = getenv("LSG_MMVQ_SHARE")) v.share = atoi(e);
+        if (getenv("LSG_MMVQ_SKIP")) v.skip_math = 1;
+        return v;
+    }();
+    return t;
+}
+
+MmvqTune sane_tuning() {
+    MmvqTune v = tuning();
+    v.warps = v.warps < 1 ? 1 : (v.warps > 15 ? 15 : v.warps);
+    v.ctas = v.ctas < 1 ? 1 : (v.ctas > 8 ? 8 : v.ctas);
+    v.share = v.share < 1 ? 1 : (v.share > 8 ? 8 : v.share);
+    v.stage_kb = v.stage_kb < 1 ? 1 : (v.stage_kb > 96 ? 96 : v.stage_kb);
+    return v;
+}
+
 int dispatch_launch(int type, const MmvqArgs& a, cudaStream_t s, bool pdl) {
+    const MmvqTune tn = sane_tuning();
     switch (type) {
-        case 0: return mmvq_launch_t0(a, s, pdl);
-        case 1: return mmvq_launch_t1(a, s, pdl);
-        case 2: return mmvq_launch_t2(a, s, pdl);
-        case 3: return mmvq_launch_t3(a, s, pdl);
-        case 4: return mmvq_launch_t4(a, s, pdl);
-        case 5: return mmvq_launch_t5(a, s, pdl);
-        case 6: return mmvq_launch_t6(a, s, pdl);
-        case 7: return mmvq_launch_t7(a, s, pdl);
+        case 0: return mmvq_launch_t0(a, tn, s, pdl);
+        case 1: return mmvq_launch_t1(a, tn, s, pdl);
+        case 2: return mmvq_launch_t2(a, tn, s, pdl);
+        case 3: return mmvq_launch_t3(a, tn, s, pdl);
+        case 4: return mmvq_launch_t4(a, tn, s, pdl);
+        case 5: return mmvq_launch_t5(a, tn, s, pdl);
+        case 6: return mmvq_launch_t6(a, tn, s, pdl);
+        case 7: return mmvq_launch_t7(a, tn, s, pdl);
     }
     return fail(LSG_ERR_UNSUPPORTED, "gguf_mmvq: unknown type %d", type);
 }
@@ -99,7 +127,7 @@ extern "C" int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq,
     int rc = check_gemm_params("gguf_mmvq", p);
     if (rc != LSG_OK) return rc;
     return mmvq_q8_1(p->type, p->M, p->N, p->K, p->B, xq, p->C, p->N,
-                     p->out_dtype == LSG_DTYPE_F32, static_cast<cudaStream_t>(stream), false);
+                     p->out_dtype == LSG_DTYPE_F32, static_cast<cudaStream_t>(stream), true);
 }
 
 extern "C" int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace,
@@ -116,4 +144,15 @@ extern "C" int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace,
     if (rc != LSG_OK) return rc;
     return mmvq_q8_1(p->type, p->M, p->N, p->K, p->B, workspace, p->C, p->N,
                      p->out_dtype == LSG_DTYPE_F32, s, true);
+}
+
+extern "C" int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_kib,
+                                   int smem_share, int skip_math) {
+    MmvqTune& t = tuning();
+    if (consumer_warps > 0) t.warps = consumer_warps;
+    if (ctas_per_sm > 0) t.ctas = ctas_per_sm;
+    if (stage_kib > 0) t.stage_kb = stage_kib;
+    if (smem_share > 0) t.share = smem_share;
+    if (skip_math >= 0) t.skip_math = skip_math ? 1 : 0;
+    return LSG_OK;
 }

@@ -11,12 +11,11 @@
 //     contiguous in memory, so a slab is one perfectly coalesced transfer
 //     whatever the block size (17..210 bytes) - tracked by mbarriers;
 //   * the Q8_1 activations are re-laid once per CTA into a planar,
-//     bank-conflict-free shared-memory image with per-group sums, and for a
-//     single row with short K they stay in registers for the whole kernel;
-//   * consumer warps take `L` lanes per weight row (a whole warp for long
-//     rows), decode chunks with packed-nibble tricks, dp4a against the
-//     activations, and reduce with a halving butterfly that folds several
-//     (row, batch-row) results per shuffle;
+//     bank-conflict-free shared-memory image with per-group sums;
+//   * consumer warps take `L` lanes per weight row (4..32, by row length),
+//     each lane decoding whole super-blocks (mmvq_decode.cuh) and dp4a-ing
+//     them against the activations, and reduce with a halving butterfly that
+//     folds several (row, batch-row) results per shuffle;
 //   * the weight stream starts before griddepcontrol.wait, so under
 //     programmatic dependent launch it overlaps the activation quantizer.
 //
@@ -26,6 +25,7 @@
 
 #include "common.cuh"
 #include "formats.cuh"
+#include "mmvq_decode.cuh"
 
 namespace lsg {
 
@@ -44,6 +44,17 @@ struct MmvqArgs {
     int stages;               // ring depth
     int stage_bytes;          // bytes reserved per stage (multiple of 128)
     int x_bytes;              // bytes of the activation image (multiple of 128)
+    int debug_skip;           // tuning aid: 1 = consumers skip the math
+    int cons_warps;           // consumer warps per CTA (block = 32 * (cons_warps + 1))
+};
+
+// Launch geometry knobs (see lsg_mmvq_set_tuning in lsg.h).
+struct MmvqTune {
+    int warps;      // consumer warps per CTA, 1..15
+    int ctas;       // CTAs of one launch per SM
+    int stage_kb;   // target bytes per pipeline stage, in KiB
+    int share;      // CTAs (of this and neighbouring launches) sharing an SM's shared memory
+    int skip_math;  // measurement aid: stream the weights but skip the arithmetic
 };
 
 // Per-type entry points, one translation unit each (mmvq_inst.cu).
@@ -51,112 +62,69 @@ struct MmvqArgs {
 #define LSG_CAT(a, b) LSG_CAT2(a, b)
 #define MMVQ_FN(name) LSG_CAT(LSG_CAT(mmvq_, name), LSG_CAT(_t, LSG_MMVQ_TYPE))
 #define LSG_DECLARE_MMVQ(id)                                         \
-    int mmvq_launch_t##id(MmvqArgs a, cudaStream_t stream, bool pdl); \
+    int mmvq_launch_t##id(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pdl); \
     int mmvq_max_rows_t##id(int K);
 LSG_DECLARE_MMVQ(0) LSG_DECLARE_MMVQ(1) LSG_DECLARE_MMVQ(2) LSG_DECLARE_MMVQ(3)
 LSG_DECLARE_MMVQ(4) LSG_DECLARE_MMVQ(5) LSG_DECLARE_MMVQ(6) LSG_DECLARE_MMVQ(7)
 
 #if defined(__CUDACC__)
 
-// Sizes of the activation image in shared memory, per activation row.
-template <ChunkShape S> __host__ __device__ constexpr int x_row_bytes(int K) {
-    // int8 values + fp32 d per 32 + fp32 d*sum per 32 (kPair/kBlock) or per 16 (kQuad)
-    // rounded up so that every row image starts on a 16-byte boundary
-    return (K + (K / 32) * 4 + (S == kQuad ? (K / 16) * 4 : (K / 32) * 4) + 15) & ~15;
+// Bytes of one batch row's activation image.
+template <int T> __host__ __device__ constexpr int x_row_bytes(int K) {
+    return (K + (K / 32) * 4 + Mmvq<T>::NS * (K / Mmvq<T>::UV) * 4 + 15) & ~15;
 }
 
 // ---------------------------------------------------------------------------
-// Activation image: build (once per CTA) and read (per chunk)
+// Activation image: Q8_1 blocks from global memory -> planar layout described
+// in mmvq_decode.cuh.  One thread per Q8_1 block.
 // ---------------------------------------------------------------------------
-// Layout of one row: [planes of 16-byte units][d per 32-block][s].
-//   kPair : 4 planes; unit (plane j, chunk c) = values 64c+16j ..  ; s per 32-block
-//   kQuad : 4 planes; unit (plane q, chunk c=4sb+2ip+h) = values 256sb+128ip+32q+16h .. ;
-//           s per (chunk, quad)
-//   kBlock: 2 planes; unit (plane j, chunk c) = values 32c+16j .. ; s per 32-block
-template <ChunkShape S>
+template <int T>
 __device__ __forceinline__ void build_x_image(uint8_t* img, const uint8_t* __restrict__ xq,
                                               int M, int K, int tid, int nthreads) {
+    using D = Mmvq<T>;
+    constexpr int UVB = D::UV / 32;  // Q8_1 blocks per unit
     const int nb = K / 32;
-    const int C = (S == kBlock) ? nb : K / 64;
-    const int rowb = x_row_bytes<S>(K);
+    const int U = K / D::UV;
+    const int rowb = x_row_bytes<T>(K);
     for (int idx = tid; idx < M * nb; idx += nthreads) {
         const int m = idx / nb, b = idx - m * nb;
         const uint32_t* src = reinterpret_cast<const uint32_t*>(xq + static_cast<size_t>(idx) * kQ8_1Bytes);
-        const uint32_t ds = __ldg(src);
-        const float d = fp16_bits_to_float(ds);
-        uint4 u[2];
-        u[0] = make_uint4(__ldg(src + 1), __ldg(src + 2), __ldg(src + 3), __ldg(src + 4));
-        u[1] = make_uint4(__ldg(src + 5), __ldg(src + 6), __ldg(src + 7), __ldg(src + 8));
+        const float d = fp16_bits_to_float(__ldg(src));
+        uint4 q[2];
+        q[0] = make_uint4(__ldg(src + 1), __ldg(src + 2), __ldg(src + 3), __ldg(src + 4));
+        q[1] = make_uint4(__ldg(src + 5), __ldg(src + 6), __ldg(src + 7), __ldg(src + 8));
         int sum[2];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-            int s = __dp4a(static_cast<int>(u[hf].x), 0x01010101, 0);
-            s = __dp4a(static_cast<int>(u[hf].y), 0x01010101, s);
-            s = __dp4a(static_cast<int>(u[hf].z), 0x01010101, s);
-            s = __dp4a(static_cast<int>(u[hf].w), 0x01010101, s);
+            int s = __dp4a(static_cast<int>(q[hf].x), 0x01010101, 0);
+            s = __dp4a(static_cast<int>(q[hf].y), 0x01010101, s);
+            s = __dp4a(static_cast<int>(q[hf].z), 0x01010101, s);
+            s = __dp4a(static_cast<int>(q[hf].w), 0x01010101, s);
             sum[hf] = s;
         }
         uint8_t* row = img + static_cast<size_t>(m) * rowb;
         uint4* planes = reinterpret_cast<uint4*>(row);
-        float* dvec = reinterpret_cast<float*>(row + K);
-        float* svec = dvec + nb;
-        dvec[b] = d;
-        if (S == kPair) {
-            const int c = b >> 1, j = (b & 1) * 2;
-            planes[j * C + c] = u[0];
-            planes[(j + 1) * C + c] = u[1];
-            svec[b] = d * static_cast<float>(sum[0] + sum[1]);
-        } else if (S == kBlock) {
-            planes[b] = u[0];
-            planes[C + b] = u[1];
-            svec[b] = d * static_cast<float>(sum[0] + sum[1]);
-        } else {
-            // block b = 8sb + 4ip + q holds units h = 0, 1 of quad q
-            const int sb = b >> 3, ip = (b >> 2) & 1, q = b & 3;
-            const int c0 = 4 * sb + 2 * ip;
-            planes[q * C + c0] = u[0];
-            planes[q * C + c0 + 1] = u[1];
-            svec[c0 * 4 + q] = d * static_cast<float>(sum[0]);
-            svec[(c0 + 1) * 4 + q] = d * static_cast<float>(sum[1]);
-        }
-    }
-}
-
-template <ChunkShape S>
-__device__ __forceinline__ void load_x_chunk(uint32_t row /*shared addr of the row image*/,
-                                             int K, int c, XChunk<S>& x) {
-    const int nb = K / 32;
-    const int C = (S == kBlock) ? nb : K / 64;
-    const uint32_t dvec = row + K;
-    const uint32_t svec = dvec + nb * 4;
-    if (S == kPair) {
+        uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
+        uint32_t* svec = dvec + nb;
+        const int u = b / UVB, jb = b % UVB;
+        planes[(2 * jb) * U + u] = q[0];
+        planes[(2 * jb + 1) * U + u] = q[1];
+        if (UVB >= 4) dvec[((jb >> 2) * U + u) * 4 + (jb & 3)] = __float_as_uint(d);
+        else dvec[u] = __float_as_uint(d);
+        if (D::SUM == kSumF32Per32) {
+            const uint32_t v = __float_as_uint(d * static_cast<float>(sum[0] + sum[1]));
+            if (UVB >= 4) svec[((jb >> 2) * U + u) * 4 + (jb & 3)] = v;
+            else svec[u] = v;
+        } else if (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint4 v = lds128(row + (j * C + c) * 16);
-            x.qs[4 * j] = v.x; x.qs[4 * j + 1] = v.y; x.qs[4 * j + 2] = v.z; x.qs[4 * j + 3] = v.w;
+            for (int hf = 0; hf < 2; ++hf) {
+                const int e = 2 * jb + hf;  // 16-value group of the unit
+                const uint32_t v = (D::SUM == kSumI32Per16)
+                                       ? static_cast<uint32_t>(sum[hf])
+                                       : __float_as_uint(d * static_cast<float>(sum[hf]));
+                svec[((e >> 2) * U + u) * 4 + (e & 3)] = v;
+            }
         }
-        const uint2 d = lds64(dvec + c * 8), s = lds64(svec + c * 8);
-        x.d[0] = __uint_as_float(d.x); x.d[1] = __uint_as_float(d.y);
-        x.s[0] = __uint_as_float(s.x); x.s[1] = __uint_as_float(s.y);
-    } else if (S == kQuad) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const uint4 v = lds128(row + (q * C + c) * 16);
-            x.qs[4 * q] = v.x; x.qs[4 * q + 1] = v.y; x.qs[4 * q + 2] = v.z; x.qs[4 * q + 3] = v.w;
-        }
-        const uint4 d = lds128(dvec + (c >> 1) * 16), s = lds128(svec + c * 16);
-        x.d[0] = __uint_as_float(d.x); x.d[1] = __uint_as_float(d.y);
-        x.d[2] = __uint_as_float(d.z); x.d[3] = __uint_as_float(d.w);
-        x.s[0] = __uint_as_float(s.x); x.s[1] = __uint_as_float(s.y);
-        x.s[2] = __uint_as_float(s.z); x.s[3] = __uint_as_float(s.w);
-    } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const uint4 v = lds128(row + (j * C + c) * 16);
-            x.qs[4 * j] = v.x; x.qs[4 * j + 1] = v.y; x.qs[4 * j + 2] = v.z; x.qs[4 * j + 3] = v.w;
-        }
-        x.d[0] = __uint_as_float(lds32(dvec + c * 4));
-        x.s[0] = __uint_as_float(lds32(svec + c * 4));
     }
 }
 
@@ -193,27 +161,25 @@ __device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, floa
 
 // ---------------------------------------------------------------------------
 // The kernel
-//   T    : lsg_gguf_type
-//   MT   : activation rows per register pass (1, 2, 4, 8)
-//   RW   : weight rows per lane group per pass (1 or 2)
-//   L    : lanes per weight row (32, 8)
-//   XREG : chunks of the single activation row kept in registers (0 = none)
+//   T  : lsg_gguf_type
+//   MT : batch rows per register pass (1, 2, 4, 8)
+//   RW : weight rows per lane group per pass (1 or 2)
+//   L  : lanes per weight row (4, 8, 16, 32)
 // blockDim.x = 32 * (consumer warps + 1); the last warp is the producer.
 // ---------------------------------------------------------------------------
-template <int T, int MT, int RW, int L, int XREG>
+template <int T, int MT, int RW, int L>
 __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
-    using F = Fmt<T>;
     using D = Mmvq<T>;
-    constexpr ChunkShape S = F::SHAPE;
-    constexpr int CHUNK_VALS = (S == kBlock) ? 32 : 64;
-    constexpr int SUBS = 32 / L;        // lane groups per warp
-    constexpr int RPP = SUBS * RW;      // rows per warp pass
+    constexpr int SUBS = 32 / L;    // lane groups per warp
+    constexpr int RPP = SUBS * RW;  // rows per warp pass
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* x_img = smem;
     uint8_t* ring = smem + a.x_bytes;
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(a.stages) * a.stage_bytes);
     uint64_t* empty = full + kMmvqMaxStages;
+    int* next_group = reinterpret_cast<int*>(empty + kMmvqMaxStages);
+    volatile int* slab_in_stage = next_group + 1;  // which slab each stage was last loaded with
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -225,12 +191,15 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     const int row_begin = static_cast<int>((static_cast<long long>(a.N) * blockIdx.x) / gridDim.x);
     const int row_end = static_cast<int>((static_cast<long long>(a.N) * (blockIdx.x + 1)) / gridDim.x);
     const int n_slabs = (row_end - row_begin + a.slab_rows - 1) / a.slab_rows;
+    const int groups_per_slab = (a.slab_rows + RPP - 1) / RPP;
 
     if (tid == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], n_cons_warps);
+            mbar_init(&empty[s], groups_per_slab);  // one arrival per row group
         }
+        *next_group = 0;
+        for (int s = 0; s < kMmvqMaxStages; ++s) slab_in_stage[s] = -1;
         mbar_fence_init();
     }
     __syncthreads();
@@ -268,6 +237,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                         dst[p - cp_b] = *reinterpret_cast<const uint8_t*>(p);
                 }
                 const uint32_t bytes = static_cast<uint32_t>(cp_e - cp_b);
+                slab_in_stage[s] = i;  // published before the arrive below (release)
                 if (bytes > 0) {
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_g2s_hint(dst, reinterpret_cast<const void*>(cp_b), bytes, &full[s], policy);
@@ -284,82 +254,68 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     // ----------------------------------------------------------------------
     pdl_wait_prior();  // activations (and the output buffer) belong to the stream order
     const int n_cons = n_cons_warps * 32;
-    build_x_image<S>(x_img, a.xq, a.M, a.K, tid, n_cons);
+    build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
     asm volatile("bar.sync 1, %0;" ::"r"(n_cons) : "memory");
 
-    const int C = a.K / CHUNK_VALS;
     const int sub = lane / L;
     const int kl = lane % L;
+    XView xv;
+    xv.rowb = x_row_bytes<T>(a.K);
+    xv.d_off = a.K;
+    xv.s_off = a.K + (a.K / 32) * 4;
+    xv.U = a.K / D::UV;
     const uint32_t x_base = smem_u32(x_img);
-    const int x_rowb = x_row_bytes<S>(a.K);
 
-    XChunk<S> xr[XREG > 0 ? XREG : 1];
-    if constexpr (XREG > 0) {
-#pragma unroll
-        for (int i = 0; i < XREG; ++i) {
-            const int c = kl + L * i;
-            if (c < C) load_x_chunk<S>(x_base, a.K, c, xr[i]);
-        }
-    }
-
+    // Row groups (RPP rows each) are claimed from a CTA-wide queue in row order.  A
+    // warp therefore waits on a stage only when it holds work in it, a short slab
+    // never leaves warps polling, and the tail of the range balances itself.  Which
+    // warp computes a group does not change its result.
     const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.W);
-    for (int i = 0; i < n_slabs; ++i) {
+    const int total_groups = n_slabs * groups_per_slab;
+    for (;;) {
+        int gidx = 0;
+        if (lane == 0) gidx = atomicAdd(next_group, 1);
+        gidx = __shfl_sync(0xffffffffu, gidx, 0);
+        if (gidx >= total_groups) break;
+        const int i = gidx / groups_per_slab;
+        const int g = (gidx - i * groups_per_slab) * RPP;
         const int s = i % a.stages;
-        if (!mbar_wait_bounded(&full[s], (i / a.stages) & 1, a.status, kDevWaitFull)) return;
-
         const int r0 = row_begin + i * a.slab_rows;
         const int nrows = min(a.slab_rows, row_end - r0);
-        const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
-        const uint32_t slab = smem_u32(ring + static_cast<size_t>(s) * a.stage_bytes) +
-                              static_cast<uint32_t>(src_b & 15);
-
-        // Row groups are dealt to warps round-robin across the whole row range of the
-        // CTA (not per slab), so that short slabs still keep every warp busy.
-        const int groups_per_slab = (a.slab_rows + RPP - 1) / RPP;
-        const int first_group = i * groups_per_slab;
-        const int my_first = (warp + n_cons_warps - first_group % n_cons_warps) % n_cons_warps;
-        for (int g = my_first * RPP; g < nrows; g += n_cons_warps * RPP) {
-            int rloc[RW];
+        // Every claim waits for its slab, including the groups past the end of a short
+        // last slab: their arrival below must not fall into the stage's previous phase.
+        // A parity wait alone cannot tell lap n of a stage from lap n-2, and a warp may
+        // claim a group whose slab is more than a ring ahead of the slowest warp; so
+        // first wait until the producer has started loading exactly this slab.
+        if (slab_in_stage[s] != i) {
+            const uint64_t t0 = global_timer_ns();
+            while (slab_in_stage[s] != i) {
+                __nanosleep(64);
+                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    if (a.status) atomicCAS(a.status, 0u, static_cast<unsigned int>(kDevWaitFull));
+                    return;
+                }
+            }
+        }
+        if (!mbar_wait_bounded(&full[s], (i / a.stages) & 1, a.status, kDevWaitFull)) return;
+        if (g < nrows) {
+            const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
+            const uint32_t slab = smem_u32(ring + static_cast<size_t>(s) * a.stage_bytes) +
+                                  static_cast<uint32_t>(src_b & 15);
             uint32_t raddr[RW];
 #pragma unroll
-            for (int r = 0; r < RW; ++r) {
-                rloc[r] = g + sub * RW + r;
-                raddr[r] = slab + static_cast<uint32_t>(min(rloc[r], nrows - 1)) * a.row_bytes;
-            }
+            for (int r = 0; r < RW; ++r)
+                raddr[r] = slab + static_cast<uint32_t>(min(g + sub * RW + r, nrows - 1)) * a.row_bytes;
+
             for (int m0 = 0; m0 < a.M; m0 += MT) {
                 float acc[RW * MT];
 #pragma unroll
                 for (int v = 0; v < RW * MT; ++v) acc[v] = 0.0f;
+                xv.base = x_base + m0 * xv.rowb;
+                xv.mlast = a.M - 1 - m0;
 
-                if constexpr (XREG > 0) {
-#pragma unroll
-                    for (int it = 0; it < XREG; ++it) {
-                        const int c = kl + L * it;
-                        if (c < C) {
-#pragma unroll
-                            for (int r = 0; r < RW; ++r) {
-                                typename D::W w;
-                                D::load(raddr[r], c, w);
-                                acc[r] += D::dot(w, xr[it]);
-                            }
-                        }
-                    }
-                } else {
-                    for (int c = kl; c < C; c += L) {
-                        typename D::W w[RW];
-#pragma unroll
-                        for (int r = 0; r < RW; ++r) D::load(raddr[r], c, w[r]);
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) {
-                            // Rows past M re-read the last row; their results are dropped.
-                            const int mm = min(m0 + m, a.M - 1);
-                            XChunk<S> x;
-                            load_x_chunk<S>(x_base + mm * x_rowb, a.K, c, x);
-#pragma unroll
-                            for (int r = 0; r < RW; ++r) acc[r * MT + m] += D::dot(w[r], x);
-                        }
-                    }
-                }
+                if (!a.debug_skip)
+                    for (int u = kl; u < xv.U; u += L) D::template unit_dot<RW, MT>(raddr, u, xv, acc);
 
                 // Reduce over the L lanes of each group, NVB values at a time.
                 constexpr int NV = RW * MT;
@@ -383,6 +339,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                 }
             }
         }
+        // Every stage collects one arrival per group, real or past the end.
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }

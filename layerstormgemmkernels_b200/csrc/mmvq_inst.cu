@@ -3,6 +3,7 @@
 // geometry for a shape and launches it.
 #include "mmvq.cuh"
 
+
 #ifndef LSG_MMVQ_TYPE
 #error "compile with -DLSG_MMVQ_TYPE=<lsg_gguf_type id>"
 #endif
@@ -12,14 +13,11 @@ namespace lsg {
 namespace {
 
 constexpr int T = LSG_MMVQ_TYPE;
-constexpr int kConsumerWarps = 15;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kSmemCap = 227 * 1024;
-constexpr int kStageTarget = 24 * 1024;
 
-template <int MT, int RW, int L, int XREG>
+template <int MT, int RW, int L>
 int launch_variant(const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
-    auto kernel = mmvq_kernel<T, MT, RW, L, XREG>;
+    auto kernel = mmvq_kernel<T, MT, RW, L>;
     static bool configured[64] = {};
     int dev = 0;
     LSG_CUDA_TRY(cudaGetDevice(&dev));
@@ -28,16 +26,33 @@ int launch_variant(const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream
                                           kSmemCap));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    LSG_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3(kThreads), smem, stream, pdl, a));
+    LSG_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3((a.cons_warps + 1) * 32), smem, stream, pdl, a));
     return LSG_OK;
+}
+
+template <int MT, int RW>
+int launch_lanes(int lanes, const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+    switch (lanes) {
+        case 4: return launch_variant<MT, RW, 4>(a, grid, smem, stream, pdl);
+        case 8: return launch_variant<MT, RW, 8>(a, grid, smem, stream, pdl);
+        case 16: return launch_variant<MT, RW, 16>(a, grid, smem, stream, pdl);
+        default: return launch_variant<MT, RW, 32>(a, grid, smem, stream, pdl);
+    }
+}
+
+template <int MT>
+int launch_rows(int rw, int lanes, const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream,
+                bool pdl) {
+    // one weight row per lane group is only built for whole-warp groups (long rows)
+    if (rw == 1 && lanes == 32) return launch_variant<MT, 1, 32>(a, grid, smem, stream, pdl);
+    return launch_lanes<MT, 2>(lanes, a, grid, smem, stream, pdl);
 }
 
 }  // namespace
 
-// Largest number of activation rows one launch can hold in shared memory.
+// Largest number of batch rows one launch can hold in shared memory.
 int MMVQ_FN(max_rows)(int K) {
-    constexpr ChunkShape S = Fmt<T>::SHAPE;
-    const int per_row = x_row_bytes<S>(K);
+    const int per_row = x_row_bytes<T>(K);
     const int row_bytes = (K / Fmt<T>::VALS) * Fmt<T>::BYTES;
     // leave room for two stages of at least one weight row each
     const int ring_min = 2 * (((row_bytes + 47 + 127) / 128) * 128) + 256;
@@ -45,57 +60,65 @@ int MMVQ_FN(max_rows)(int K) {
     return rows < 1 ? 0 : rows;
 }
 
-int MMVQ_FN(launch)(MmvqArgs a, cudaStream_t stream, bool pdl) {
+int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pdl) {
     using F = Fmt<T>;
-    constexpr ChunkShape S = F::SHAPE;
-    constexpr int CHUNK_VALS = (S == kBlock) ? 32 : 64;
-    constexpr int XR = (S == kBlock) ? 4 : 2;
-
     a.row_bytes = (a.K / F::VALS) * F::BYTES;
-    const int C = a.K / CHUNK_VALS;
-    const int grid = a.N < sm_count() ? a.N : sm_count();
-    const int rows_per_cta = (a.N + grid - 1) / grid;
+    const int U = a.K / Mmvq<T>::UV;
+    a.cons_warps = tn.warps;
+    a.debug_skip = tn.skip_math;
+    a.x_bytes = ((a.M * x_row_bytes<T>(a.K) + 127) / 128) * 128;
+    const int bar_bytes = 2 * kMmvqMaxStages * 8 + 16 + kMmvqMaxStages * 4;
 
-    a.x_bytes = ((a.M * x_row_bytes<S>(a.K) + 127) / 128) * 128;
-    int slab_rows = kStageTarget / a.row_bytes;
-    if (slab_rows < 1) slab_rows = 1;
-    if (slab_rows > rows_per_cta) slab_rows = rows_per_cta;
-    int stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
-    const int bar_bytes = 2 * kMmvqMaxStages * 8;
-    int avail = kSmemCap - a.x_bytes - bar_bytes;
-    while (slab_rows > 1 && 2 * stage_bytes > avail) {
-        slab_rows = (slab_rows + 1) / 2;
-        stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
-    }
-    if (2 * stage_bytes > avail)
-        return fail(LSG_ERR_UNSUPPORTED,
-                    "gguf_mmvq: M=%d rows of K=%d do not fit shared memory with a weight ring",
-                    a.M, a.K);
-    const int n_slabs = (rows_per_cta + slab_rows - 1) / slab_rows;
-    int stages = avail / stage_bytes;
-    if (stages > kMmvqMaxStages) stages = kMmvqMaxStages;
-    if (stages > n_slabs) stages = n_slabs < 2 ? 2 : n_slabs;
-    a.slab_rows = slab_rows;
-    a.stage_bytes = stage_bytes;
-    a.stages = stages;
-    const size_t smem = static_cast<size_t>(a.x_bytes) + static_cast<size_t>(stages) * stage_bytes + bar_bytes;
+    // lanes per weight row: the smallest power of two covering the units of a row
+    int lanes = 4;
+    while (lanes < 32 && lanes < U) lanes *= 2;
 
-    const bool wide = C >= 24;  // a whole warp per weight row
-    if (a.M == 1) {
-        if (wide && C <= 32 * XR) return launch_variant<1, 2, 32, XR>(a, grid, smem, stream, pdl);
-        if (wide) return launch_variant<1, 2, 32, 0>(a, grid, smem, stream, pdl);
-        return launch_variant<1, 2, 8, 0>(a, grid, smem, stream, pdl);
+    // Several CTAs per SM when the activation image leaves room for their rings:
+    // their prologues, tails and pipeline fills then overlap each other and, under
+    // programmatic dependent launch, the neighbouring kernels in the stream.
+    int grid = 0, rw = 2, stages = 0;
+    size_t smem = 0;
+    // `share` = how many CTAs (of this and of neighbouring launches) split an SM's
+    // shared memory; `ctas` = how many of them belong to one launch.
+    for (int share = tn.share > tn.ctas ? tn.share : tn.ctas; share >= 1; --share) {
+        const int ctas = tn.ctas < share ? tn.ctas : share;
+        const int smem_cap = kSmemCap / share - (share > 1 ? 1024 : 0);  // 1 KB per-CTA reserve
+        const int slots = sm_count() * ctas;
+        grid = a.N < slots ? a.N : slots;
+        const int rows_per_cta = (a.N + grid - 1) / grid;
+        // Long rows: one row per lane group, so that the rows resident in the ring
+        // are enough to occupy every consumer warp.
+        rw = (lanes == 32 && a.row_bytes * 2 * tn.warps > (smem_cap * 3) / 4) ? 1 : 2;
+        int slab_rows = tn.stage_kb * 1024 / a.row_bytes;
+        if (slab_rows < 1) slab_rows = 1;
+        if (slab_rows > rows_per_cta) slab_rows = rows_per_cta;
+        int stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
+        const int avail = smem_cap - a.x_bytes - bar_bytes;
+        while (slab_rows > 1 && 2 * stage_bytes > avail) {
+            slab_rows = (slab_rows + 1) / 2;
+            stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
+        }
+        if (2 * stage_bytes > avail) {
+            if (share > 1) continue;
+            return fail(LSG_ERR_UNSUPPORTED,
+                        "gguf_mmvq: M=%d rows of K=%d do not fit shared memory with a weight ring",
+                        a.M, a.K);
+        }
+        const int n_slabs = (rows_per_cta + slab_rows - 1) / slab_rows;
+        stages = avail / stage_bytes;
+        if (stages > kMmvqMaxStages) stages = kMmvqMaxStages;
+        if (stages > n_slabs) stages = n_slabs < 2 ? 2 : n_slabs;
+        a.slab_rows = slab_rows;
+        a.stage_bytes = stage_bytes;
+        a.stages = stages;
+        smem = static_cast<size_t>(a.x_bytes) + static_cast<size_t>(stages) * stage_bytes + bar_bytes;
+        break;
     }
-    if (a.M == 2) {
-        if (wide) return launch_variant<2, 2, 32, 0>(a, grid, smem, stream, pdl);
-        return launch_variant<2, 2, 8, 0>(a, grid, smem, stream, pdl);
-    }
-    if (a.M <= 4) {
-        if (wide) return launch_variant<4, 2, 32, 0>(a, grid, smem, stream, pdl);
-        return launch_variant<4, 2, 8, 0>(a, grid, smem, stream, pdl);
-    }
-    if (wide) return launch_variant<8, 2, 32, 0>(a, grid, smem, stream, pdl);
-    return launch_variant<8, 2, 8, 0>(a, grid, smem, stream, pdl);
+
+    if (a.M == 1) return launch_rows<1>(rw, lanes, a, grid, smem, stream, pdl);
+    if (a.M == 2) return launch_rows<2>(rw, lanes, a, grid, smem, stream, pdl);
+    if (a.M <= 4) return launch_rows<4>(rw, lanes, a, grid, smem, stream, pdl);
+    return launch_rows<8>(rw, lanes, a, grid, smem, stream, pdl);
 }
 
 }  // namespace lsg

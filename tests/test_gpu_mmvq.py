@@ -191,3 +191,32 @@ def test_errors_mirror_reference(ops):
         ops.gguf_mmvq(A.float(), W, T["Q4_K"], 8, 100)
     with pytest.raises(RuntimeError, match="size"):
         ops.gguf_mmvq(A, W, T["Q4_K"], 8, 256)
+
+
+@pytest.mark.parametrize("warps,ctas,stage_kib,share", [
+    (15, 1, 1, 1),     # many warps, tiny stages: claims run laps ahead of the ring
+    (11, 1, 16, 2), (3, 4, 4, 4), (1, 1, 2, 1), (7, 2, 8, 2), (15, 1, 64, 1),
+])
+def test_mmvq_results_do_not_depend_on_launch_geometry(ops, warps, ctas, stage_kib, share):
+    """The pipeline (ring depth, work queue, CTA count) must never change a result."""
+    from layerstormgemmkernels_b200 import capi
+    cases = [("Q4_K", 2000, 4096, 1), ("Q4_K", 500, 14336, 1), ("Q6_K", 1111, 4096, 3),
+             ("Q8_0", 300, 1024, 8), ("Q4_K", 700, 768, 2)]
+    try:
+        for name, N, K, M in cases:
+            t = T[name]
+            A = torch.randn(M, K, generator=torch.Generator().manual_seed(N)).to(torch.bfloat16).cuda()
+            W = Q.random_gguf_weight(name, N, K, seed=K + N)
+            Wd = torch.from_numpy(W).cuda()
+            capi.check(capi.lib.lsg_mmvq_set_tuning(7, 1, 16, 2, 0))
+            base = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32)
+            capi.check(capi.lib.lsg_mmvq_set_tuning(warps, ctas, stage_kib, share, 0))
+            for _ in range(3):
+                got = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32)
+                assert torch.equal(base, got), (name, N, K, M)
+            if name == "Q4_K" and N == 2000:
+                ref = oracle.mmvq(t, oracle.quantize_q8_1(bf16_bits(A)), W, K)
+                assert rel_err(got.cpu().numpy(), ref) <= TOL_F32
+        assert capi.device_status() == 0
+    finally:
+        capi.check(capi.lib.lsg_mmvq_set_tuning(7, 1, 16, 2, 0))
