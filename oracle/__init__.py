@@ -95,3 +95,22 @@ def dequant_gemm(t, a_bf16_bits, W, K):
     lib().oracle_dequant_gemm(ctypes.c_int(int(t)), ctypes.c_int(M), ctypes.c_int(N),
                               ctypes.c_int(K), _ptr(a), _ptr(W), _ptr(out))
     return out
+
+
+# ---------------------------------------------------------------------------
+# The reference's own CUDA kernels, compiled for sm_100a from its sources where they
+# lie (oracle/Makefile target `ref`).  Optional second checker for the GPU tests.
+# ---------------------------------------------------------------------------
+REF_LIB_PATH = os.path.join(_HERE, "_ref", "libref_gguf.so")
+_ref = None
+
+
+def ref_lib():
+    """ctypes handle of oracle/_ref/libref_gguf.so, or None when it has not been built."""
+    global _ref
+    if _ref is None and os.path.exists(REF_LIB_PATH):
+        try:
+            _ref = ctypes.CDLL(REF_LIB_PATH)
+        except OSError:
+            _ref = None
+    return _ref

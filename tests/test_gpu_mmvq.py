@@ -14,7 +14,7 @@ T = GGUF_TYPES
 
 # GEMM parity bound of the north star: max |y - ref| / max |ref| <= 1e-3.  The fp32
 # accumulator output is held to 2e-5 (it only differs from the oracle by summation order).
-TOL_BF16 = 1e-3 * 4  # bf16 rounding alone is up to 2^-9 = 1.95e-3 relative per element
+TOL_BF16 = 2.0 ** -8 + 1e-4  # bf16 rounding alone is up to half an ulp = 2^-8 relative
 TOL_F32 = 2e-5
 
 
