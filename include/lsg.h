@@ -128,6 +128,19 @@ LSG_API int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace, size_t
  * gguf_mmvq_kernel, gguf_mmvq.cu:69-101, is file-local). */
 LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, void* stream);
 
+/* Same operation as lsg_gguf_mmvq for callers that cannot allocate device memory -
+ * a process on a fixed memory plan, a plug-in running inside someone else's runtime,
+ * a decode loop that must never hit cudaMalloc.  The Q8_1 scratch is a device array
+ * built into the library (held by every GPU that loads it, until exit), so only the
+ * inputs and the output are passed.  M * (K/32) * 36 must not exceed
+ * LSG_NOALLOC_MAX_Q8_1_BYTES, otherwise LSG_ERR_WORKSPACE.  The first call on a device
+ * resolves the array's address: make it before any stream capture.  All calls share the
+ * array (nothing in it needs clearing; each call rewrites what it reads), so calls whose
+ * kernels may overlap on the GPU must be ordered by the caller.  This entry point has no
+ * counterpart in the reference, whose launchers always take a caller workspace. */
+#define LSG_NOALLOC_MAX_Q8_1_BYTES 147456
+LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
+
 /* Launch geometry of the mmvq kernels, process-wide: consumer warps per CTA
  * (1..15), CTAs of one launch per SM, KiB per pipeline stage, and how many CTAs
  * (of this and of neighbouring launches in the stream) split an SM's shared

@@ -63,6 +63,7 @@ def _load():
         "lsg_gguf_mmvq_workspace_bytes": (sz, [ci, ci]),
         "lsg_gguf_mmvq": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_gguf_mmvq_q8_1": (ci, [ctypes.POINTER(GgufMmvqParams), vp, vp]),
+        "lsg_gguf_mmvq_noalloc": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_mmvq_set_tuning": (ci, [ci, ci, ci, ci, ci]),
         "lsg_gguf_dequant_gemm": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_gguf_dequant_blocks": (ci, [vp, vp, ci, ll, vp]),
