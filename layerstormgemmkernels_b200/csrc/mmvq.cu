@@ -81,13 +81,13 @@ int check_gemm_params(const char* op, const lsg_gguf_mmvq_params* p) {
 // xq: Q8_1 blocks of all M rows.  ldc: output row stride.  Rows are processed
 // in batches that fit the shared-memory activation image.
 int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void* C, int ldc,
-              int out_f32, cudaStream_t stream, bool pdl) {
+              int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16) {
     if (M == 0 || N == 0) return LSG_OK;
     if (K == 0) return fail(LSG_ERR_INVALID, "gguf_mmvq: K must be positive");
-    if (!W || !xq || !C) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
+    if (!W || (!xq && !A_bf16) || !C) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
     if (reinterpret_cast<uintptr_t>(W) & 15)
         return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq: packed weight must be 16-byte aligned");
-    if (reinterpret_cast<uintptr_t>(xq) & 3)
+    if (!A_bf16 && (reinterpret_cast<uintptr_t>(xq) & 3))
         return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq: Q8_1 buffer must be 4-byte aligned");
     const int max_rows = dispatch_max_rows(type, K);
     if (max_rows < 1)
@@ -100,7 +100,8 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
     for (int m0 = 0; m0 < M; m0 += batch) {
         MmvqArgs a = {};
         a.W = static_cast<const uint8_t*>(W);
-        a.xq = static_cast<const uint8_t*>(xq) + static_cast<size_t>(m0) * xq_row;
+        a.xq = xq ? static_cast<const uint8_t*>(xq) + static_cast<size_t>(m0) * xq_row : nullptr;
+        a.A = A_bf16 ? static_cast<const __nv_bfloat16*>(A_bf16) + static_cast<size_t>(m0) * K : nullptr;
         a.C = static_cast<uint8_t*>(C) + static_cast<size_t>(m0) * ldc * c_elem;
         a.status = device_status_word();
         a.M = (M - m0) < batch ? (M - m0) : batch;
@@ -112,6 +113,14 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
         if (rc != LSG_OK) return rc;
     }
     return LSG_OK;
+}
+
+bool fused_quant_ok(int M, int K, const void* A) {
+    static const long long limit = [] {
+        const char* e = getenv("LSG_MMVQ_FUSED_QUANT_MAX");
+        return e ? atoll(e) : 16384LL;
+    }();
+    return A && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && static_cast<long long>(M) * K <= limit;
 }
 
 }  // namespace lsg
@@ -140,6 +149,11 @@ extern "C" int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace,
         return fail(LSG_ERR_WORKSPACE, "gguf_mmvq: workspace too small (have %zu, need %zu)",
                     workspace ? workspace_bytes : size_t(0), need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Few activation values: every CTA quantizes them itself while its first weights are
+    // in flight, which saves a launch and a dependency.  Otherwise quantize once, here.
+    if (fused_quant_ok(p->M, p->K, p->A))
+        return mmvq_q8_1(p->type, p->M, p->N, p->K, p->B, nullptr, p->C, p->N,
+                         p->out_dtype == LSG_DTYPE_F32, s, true, p->A);
     rc = quantize_q8_1(p->A, workspace, p->M, p->K, s, true);
     if (rc != LSG_OK) return rc;
     return mmvq_q8_1(p->type, p->M, p->N, p->K, p->B, workspace, p->C, p->N,

@@ -33,7 +33,8 @@ constexpr int kMmvqMaxStages = 8;
 
 struct MmvqArgs {
     const uint8_t* W;         // packed weight, 16-byte aligned
-    const uint8_t* xq;        // Q8_1 blocks [M][K/32][36]
+    const uint8_t* xq;        // Q8_1 blocks [M][K/32][36] (used when A is null)
+    const __nv_bfloat16* A;   // bf16 activations [M][K]: quantized inside the kernel when set
     void* C;                  // [M][ldc] bf16 or f32
     unsigned int* status;     // device status word
     int M, N, K;
@@ -122,6 +123,101 @@ __device__ __forceinline__ void build_x_image(uint8_t* img, const uint8_t* __res
                 const uint32_t v = (D::SUM == kSumI32Per16)
                                        ? static_cast<uint32_t>(sum[hf])
                                        : __float_as_uint(d * static_cast<float>(sum[hf]));
+                svec[((e >> 2) * U + u) * 4 + (e & 3)] = v;
+            }
+        }
+    }
+}
+
+// Same image straight from bf16 activations: the Q8_1 quantization of
+// quantize_q8_1_kernel (d = amax/127, q = rn(x/d), d then rounded to fp16) done per CTA,
+// without the round trip through global memory and without a launch of its own.  Four
+// lanes share a 32-value block, eight values each.  Values are identical to the
+// quantizer kernel's: max and the per-element division do not depend on the lane layout,
+// and the block sum of the original values (the only order-dependent field of a Q8_1
+// block) is not used by the mat-vec.
+template <int T>
+__device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bfloat16* __restrict__ A,
+                                                   int M, int K, int tid, int nthreads) {
+    using D = Mmvq<T>;
+    constexpr int UVB = D::UV / 32;
+    const int nb = K / 32;
+    const int U = K / D::UV;
+    const int rowb = x_row_bytes<T>(K);
+    const int total = M * nb * 4;  // tasks of 8 values
+    const int trips = (total + nthreads - 1) / nthreads;
+    constexpr int kBatch = 4;      // loads in flight per thread
+    for (int it0 = 0; it0 < trips; it0 += kBatch) {
+        uint4 raws[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const int idx = (it0 + k) * nthreads + tid;
+            raws[k] = __ldg(reinterpret_cast<const uint4*>(A) + (idx < total ? idx : 0));
+        }
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            if (it0 + k >= trips) break;  // uniform across the CTA
+            const int idx = (it0 + k) * nthreads + tid;
+            const bool live = idx < total;
+            const int task = live ? idx : 0;
+            const uint4 raw = raws[k];
+            float x[8];
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                x[2 * i] = __uint_as_float(w[i] << 16);
+                x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const float d = amax / 127.0f;
+            // q = rn(fl(x / d)) as the reference computes it, without eight IEEE divisions:
+            // x * fl(1/d) is within 2.3e-5 of fl(x/d) for |x/d| <= 127, so rounding it gives
+            // the same integer unless it lies within 1e-4 of a half-integer; only then
+            // (about one value in 5000) is the true quotient formed.
+            const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+            int q[8];
+            int sum8 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float t = x[i] * rcp;
+                int k = __float2int_rn(t);
+                if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x[i] / d);
+                q[i] = k;
+                sum8 += k;
+            }
+            const int sum16 = sum8 + __shfl_xor_sync(0xffffffffu, sum8, 1);
+            const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+            if (!live) continue;
+            uint2 packed;
+            packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
+            packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+            const float dh = __half2float(__float2half(d));  // the mat-vec sees the fp16-rounded scale
+            const int part = task & 3;
+            const int blk = task >> 2;
+            const int m = blk / nb, b = blk - m * nb;
+            uint8_t* row = img + static_cast<size_t>(m) * rowb;
+            uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
+            uint32_t* svec = dvec + nb;
+            const int u = b / UVB, jb = b % UVB;
+            uint2* piece = reinterpret_cast<uint2*>(row + (static_cast<size_t>(2 * jb + (part >> 1)) * U + u) * 16);
+            piece[part & 1] = packed;
+            if (part == 0) {
+                if (UVB >= 4) dvec[((jb >> 2) * U + u) * 4 + (jb & 3)] = __float_as_uint(dh);
+                else dvec[u] = __float_as_uint(dh);
+                if (D::SUM == kSumF32Per32) {
+                    const uint32_t v = __float_as_uint(dh * static_cast<float>(sum32));
+                    if (UVB >= 4) svec[((jb >> 2) * U + u) * 4 + (jb & 3)] = v;
+                    else svec[u] = v;
+                }
+            }
+            if ((part & 1) == 0 && (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16)) {
+                const int e = 2 * jb + (part >> 1);
+                const uint32_t v = (D::SUM == kSumI32Per16) ? static_cast<uint32_t>(sum16)
+                                                            : __float_as_uint(dh * static_cast<float>(sum16));
                 svec[((e >> 2) * U + u) * 4 + (e & 3)] = v;
             }
         }
@@ -254,7 +350,8 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     // ----------------------------------------------------------------------
     pdl_wait_prior();  // activations (and the output buffer) belong to the stream order
     const int n_cons = n_cons_warps * 32;
-    build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
+    if (a.A) build_x_image_bf16<T>(x_img, a.A, a.M, a.K, tid, n_cons);
+    else build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
     asm volatile("bar.sync 1, %0;" ::"r"(n_cons) : "memory");
 
     const int sub = lane / L;
