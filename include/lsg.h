@@ -167,6 +167,55 @@ LSG_API int lsg_gguf_dequant_gemm(const lsg_gguf_mmvq_params* p, void* stream);
 LSG_API int lsg_gguf_dequant_blocks(const void* packed, float* out, int type, long long n_blocks,
                             void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Activation quantizers for the FP8 / NVFP4 paths                          */
+/* ------------------------------------------------------------------------ */
+
+/* Mirrors struct DynamicFp8QuantParams, csrc/smxx/quant/dynamic_fp8_quant.h:25-32. */
+typedef struct lsg_dynamic_fp8_quant_params {
+    int num_tokens;     /* M */
+    int hidden_size;    /* K */
+    const void* input;  /* [M,K] bf16 */
+    void* output;       /* [M,K] e4m3 bytes */
+    void* scales;       /* fp32 [M,ceil(K/128)], or [ceil(K/128),M] when m_major_scales */
+    int m_major_scales;
+} lsg_dynamic_fp8_quant_params;
+
+/* bf16 -> e4m3 with one fp32 scale per (token, 128-column block); bit-exact with the
+ * reference.  Replaces launch_dynamic_fp8_quant,
+ * csrc/smxx/quant/dynamic_fp8_quant.cu:118-147 (kernel :38-112). */
+LSG_API int lsg_dynamic_fp8_quant(const lsg_dynamic_fp8_quant_params* p, void* stream);
+
+/* Mirrors Bf16ToNvfp4GroupedParams (csrc/smxx/quant/bf16_to_nvfp4_grouped.h:15-33) and
+ * SiluMulToNvfp4GroupedParams (silu_mul_to_nvfp4_grouped.h:15-35): `input` is the
+ * activation, or the gate half when `up` is used. */
+typedef struct lsg_nvfp4_grouped_quant_params {
+    const void* input;          /* [T,K] bf16 (gate for the SwiGLU variant)          */
+    const void* up;             /* [T,K] bf16, SwiGLU variant only                   */
+    void* output_packed;        /* [T,K/2] e2m1 pairs, low nibble = even k           */
+    void* output_scales;        /* ue4m3, interleaved 128x4 layout, per-expert       */
+                                /* sections padded to 128 rows; caller zero-fills    */
+    const void* expert_offsets; /* int32 [E+1], device                               */
+    const void* sf_offsets;     /* int32 [E+1], device, in padded rows               */
+    int total_tokens;
+    int num_experts;
+    int K;                      /* multiple of 16 (64 for the GEMM's scale atoms)    */
+    const void* input_scales;   /* optional fp32 [E] per-expert global scales        */
+} lsg_nvfp4_grouped_quant_params;
+
+/* Replaces launch_bf16_to_nvfp4_grouped, csrc/smxx/quant/bf16_to_nvfp4_grouped.cu:99-113. */
+LSG_API int lsg_bf16_to_nvfp4_grouped(const lsg_nvfp4_grouped_quant_params* p, void* stream);
+
+/* Replaces launch_silu_mul_to_nvfp4_grouped,
+ * csrc/smxx/quant/silu_mul_to_nvfp4_grouped.cu:121-139. */
+LSG_API int lsg_silu_mul_to_nvfp4_grouped(const lsg_nvfp4_grouped_quant_params* p, void* stream);
+
+/* sf_offsets[e] = rows of the experts before e, each rounded up to 128, on the device.
+ * Replaces the host loop of the reference's binding, csrc/bindings_python.cu:312-326,
+ * for callers that must not synchronize. */
+LSG_API int lsg_nvfp4_sf_offsets(const int32_t* expert_offsets, int32_t* sf_offsets,
+                                 int num_experts, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,20 @@ class GgufMmvqParams(ctypes.Structure):
                 ("type", ctypes.c_int), ("out_dtype", ctypes.c_int)]
 
 
+class DynamicFp8QuantParams(ctypes.Structure):
+    _fields_ = [("num_tokens", ctypes.c_int), ("hidden_size", ctypes.c_int),
+                ("input", ctypes.c_void_p), ("output", ctypes.c_void_p),
+                ("scales", ctypes.c_void_p), ("m_major_scales", ctypes.c_int)]
+
+
+class Nvfp4GroupedQuantParams(ctypes.Structure):
+    _fields_ = [("input", ctypes.c_void_p), ("up", ctypes.c_void_p),
+                ("output_packed", ctypes.c_void_p), ("output_scales", ctypes.c_void_p),
+                ("expert_offsets", ctypes.c_void_p), ("sf_offsets", ctypes.c_void_p),
+                ("total_tokens", ctypes.c_int), ("num_experts", ctypes.c_int),
+                ("K", ctypes.c_int), ("input_scales", ctypes.c_void_p)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -65,6 +79,10 @@ def _load():
         "lsg_gguf_mmvq_q8_1": (ci, [ctypes.POINTER(GgufMmvqParams), vp, vp]),
         "lsg_gguf_mmvq_noalloc": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_mmvq_set_tuning": (ci, [ci, ci, ci, ci, ci]),
+        "lsg_dynamic_fp8_quant": (ci, [ctypes.POINTER(DynamicFp8QuantParams), vp]),
+        "lsg_bf16_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
+        "lsg_silu_mul_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
+        "lsg_nvfp4_sf_offsets": (ci, [vp, vp, ci, vp]),
         "lsg_gguf_dequant_gemm": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_gguf_dequant_blocks": (ci, [vp, vp, ci, ll, vp]),
     }

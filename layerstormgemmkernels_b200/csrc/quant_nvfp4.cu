@@ -1,0 +1,201 @@
+// Grouped NVFP4 activation quantizers: bf16 rows (already permuted by expert) ->
+// e2m1 codes, two per byte, plus one ue4m3 scale per 16 values written in the
+// 128-row x 4-group interleaved scale-factor layout block-scaled tensor-core GEMMs read.
+//
+// Bit-identical to the reference kernels bf16_to_nvfp4_grouped_kernel
+// (csrc/smxx/quant/bf16_to_nvfp4_grouped.cu:16-97) and silu_mul_to_nvfp4_grouped_kernel
+// (csrc/smxx/quant/silu_mul_to_nvfp4_grouped.cu:26-119), helpers in
+// bf16_to_nvfp4_grouped_detail.cuh:30-92:
+//   scale      = max(amax / (6 * is), 2^-9), stored as ue4m3 (clamped to [0, 480], RN)
+//   code(v)    = sign | #{thresholds .25 .75 1.25 1.75 2.5 3.5 5 that |v| reaches},
+//                v = x * (1 / (ue4m3(scale) * is))       (ties go up in magnitude)
+//   SwiGLU     = bf16( (g * (0.5 * tanhf(0.5 g) + 0.5)) * u ) before quantization
+// One thread per 16-value group (two 16-byte loads, one 8-byte store); a CTA covers up to
+// 256 consecutive groups of one row and resolves the row's expert once.
+#include "common.cuh"
+#include "host.h"
+
+#include <cuda_fp8.h>
+
+namespace lsg {
+
+namespace {
+
+__device__ __forceinline__ int sf_offset_sm1xx(int row, int g, int groups_padded4) {
+    // 512-byte atoms of 128 rows x 4 groups, atoms tiled row-major over (row/128, g/4);
+    // inside an atom: (row % 32) * 16 + ((row % 128) / 32) * 4 + g % 4.
+    const int tiles_g = groups_padded4 >> 2;
+    const int atom = (row >> 7) * tiles_g + (g >> 2);
+    const int r = row & 127;
+    return atom * 512 + (r & 31) * 16 + (r >> 5) * 4 + (g & 3);
+}
+
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+    const float a = fabsf(v);
+    const uint32_t mag = (a >= 0.25f) + (a >= 0.75f) + (a >= 1.25f) + (a >= 1.75f) +
+                         (a >= 2.5f) + (a >= 3.5f) + (a >= 5.0f);
+    return mag | ((v < 0.0f) ? 8u : 0u);
+}
+
+__device__ __forceinline__ float swiglu(float g, float u) {
+    const float silu = g * (0.5f * tanhf(0.5f * g) + 0.5f);
+    return silu * u;
+}
+
+// Which expert owns `row`: the last e with offsets[e] <= row < offsets[e+1].
+__device__ __forceinline__ int expert_of_row(const int32_t* __restrict__ offs, int E, int row) {
+    int lo = 0, hi = E;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (offs[mid + 1] <= row) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(256)
+nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __restrict__ up,
+                           uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                           const int32_t* __restrict__ expert_offsets,
+                           const int32_t* __restrict__ sf_offsets,
+                           const float* __restrict__ input_scales, int T, int E, int K) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    __shared__ int s_info[3];  // expert start, sf base (in groups), expert id
+    const int row = blockIdx.y;
+    const int gpr = K >> 4;
+    if (threadIdx.x == 0) {
+        const int e = expert_of_row(expert_offsets, E, row);
+        s_info[0] = expert_offsets[e];
+        s_info[1] = sf_offsets[e];
+        s_info[2] = e;
+    }
+    __syncthreads();
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= gpr) return;
+    const int e = s_info[2];
+    const int local_row = row - s_info[0];
+    float is = 1.0f;
+    if (input_scales) {
+        const float v = input_scales[e];
+        if (v > 0.0f) is = v;
+    }
+
+    const size_t base = static_cast<size_t>(row) * K + static_cast<size_t>(g) * 16;
+    float x[16];
+    {
+        const uint4* p = reinterpret_cast<const uint4*>(in + base);
+        const uint4 a = __ldg(p), b = __ldg(p + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            x[2 * i] = __uint_as_float(w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    if (SWIGLU) {
+        const uint4* p = reinterpret_cast<const uint4*>(up + base);
+        const uint4 a = __ldg(p), b = __ldg(p + 1);
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float u0 = __uint_as_float(w[i] << 16), u1 = __uint_as_float(w[i] & 0xFFFF0000u);
+            x[2 * i] = __bfloat162float(__float2bfloat16(swiglu(x[2 * i], u0)));
+            x[2 * i + 1] = __bfloat162float(__float2bfloat16(swiglu(x[2 * i + 1], u1)));
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+
+    float scale = amax / (6.0f * is);
+    scale = fmaxf(scale, 0.001953125f);  // 2^-9, the smallest positive ue4m3
+    const float clamped = fminf(fmaxf(scale, 0.0f), 480.0f);
+    const uint32_t sbits = static_cast<uint32_t>(
+        __nv_cvt_float_to_fp8(clamped, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
+    __nv_fp8_e4m3 f8;
+    f8.__x = static_cast<__nv_fp8_storage_t>(sbits);
+    float srepr = static_cast<float>(f8);
+    srepr = fmaxf(srepr, 1e-12f);
+    const int groups_padded4 = (gpr + 3) & ~3;
+    scales[static_cast<size_t>(s_info[1]) * gpr + sf_offset_sm1xx(local_row, g, groups_padded4)] =
+        static_cast<uint8_t>(sbits);
+
+    const float inv = 1.0f / (srepr * is);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= e2m1_code(x[i] * inv) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= e2m1_code(x[8 + i] * inv) << (4 * i);
+    *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (K >> 1) + static_cast<size_t>(g) * 8) =
+        make_uint2(lo, hi);
+}
+
+// sf_offsets[e] = sum over experts before e of their row counts rounded up to 128
+// (the reference computes this on the host: csrc/bindings_python.cu:312-326).
+__global__ void nvfp4_sf_offsets_kernel(const int32_t* __restrict__ expert_offsets,
+                                        int32_t* __restrict__ sf_offsets, int E) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int acc = 0;
+    for (int e = 0; e <= E; ++e) {
+        sf_offsets[e] = acc;
+        if (e < E) acc += ((expert_offsets[e + 1] - expert_offsets[e] + 127) / 128) * 128;
+    }
+}
+
+template <bool SWIGLU>
+int launch_quant(const lsg_nvfp4_grouped_quant_params* p, const char* op, void* stream) {
+    if (!p) return fail(LSG_ERR_INVALID, "%s: null params", op);
+    // the reference returns silently in these two cases (bf16_to_nvfp4_grouped.cu:101-102)
+    if (p->K % 16 != 0) return LSG_OK;
+    if (p->total_tokens <= 0) return LSG_OK;
+    if (!p->input || (SWIGLU && !p->up) || !p->output_packed || !p->output_scales ||
+        !p->expert_offsets || !p->sf_offsets)
+        return fail(LSG_ERR_INVALID, "%s: null pointer in params", op);
+    if ((reinterpret_cast<uintptr_t>(p->input) & 15) || (SWIGLU && (reinterpret_cast<uintptr_t>(p->up) & 15)) ||
+        (reinterpret_cast<uintptr_t>(p->output_packed) & 7))
+        return fail(LSG_ERR_ALIGNMENT, "%s: input must be 16-byte and output 8-byte aligned", op);
+    const int gpr = p->K / 16;
+    const int threads = gpr < 256 ? ((gpr + 31) / 32) * 32 : 256;
+    dim3 grid((gpr + threads - 1) / threads, p->total_tokens);
+    if (p->total_tokens > 65535) {
+        // grid.y limit: fold rows into several launches
+        return fail(LSG_ERR_UNSUPPORTED, "%s: more than 65535 rows per call is not supported", op);
+    }
+    LSG_CUDA_TRY(launch_kernel(nvfp4_grouped_quant_kernel<SWIGLU>, grid, dim3(threads), 0,
+                               static_cast<cudaStream_t>(stream), true,
+                               static_cast<const __nv_bfloat16*>(p->input),
+                               static_cast<const __nv_bfloat16*>(p->up),
+                               static_cast<uint8_t*>(p->output_packed),
+                               static_cast<uint8_t*>(p->output_scales),
+                               static_cast<const int32_t*>(p->expert_offsets),
+                               static_cast<const int32_t*>(p->sf_offsets),
+                               static_cast<const float*>(p->input_scales), p->total_tokens,
+                               p->num_experts, p->K));
+    return LSG_OK;
+}
+
+}  // namespace
+
+}  // namespace lsg
+
+using namespace lsg;
+
+extern "C" int lsg_bf16_to_nvfp4_grouped(const lsg_nvfp4_grouped_quant_params* p, void* stream) {
+    return launch_quant<false>(p, "bf16_to_nvfp4_grouped", stream);
+}
+
+extern "C" int lsg_silu_mul_to_nvfp4_grouped(const lsg_nvfp4_grouped_quant_params* p, void* stream) {
+    return launch_quant<true>(p, "silu_mul_to_nvfp4_grouped", stream);
+}
+
+extern "C" int lsg_nvfp4_sf_offsets(const int32_t* expert_offsets, int32_t* sf_offsets,
+                                    int num_experts, void* stream) {
+    if (num_experts < 0 || !expert_offsets || !sf_offsets)
+        return fail(LSG_ERR_INVALID, "nvfp4_sf_offsets: bad argument");
+    nvfp4_sf_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(expert_offsets,
+                                                                             sf_offsets, num_experts);
+    LSG_CUDA_TRY(cudaGetLastError());
+    return LSG_OK;
+}

@@ -107,3 +107,86 @@ def gguf_dequant(B_packed, type):
     out = torch.empty((N, nblk * capi.BLOCK_VALUES[t]), dtype=torch.float32, device=B_packed.device)
     capi.check(_lib.lsg_gguf_dequant_blocks(_ptr(B_packed), _ptr(out), t, N * nblk, _stream()))
     return out
+
+
+# ---------------------------------------------------------------------------
+# Activation quantizers
+# ---------------------------------------------------------------------------
+def dynamic_fp8_quant(input, m_major_scales=False):
+    """bf16 [M,K] -> (float8_e4m3fn [M,K], fp32 scales [M,ceil(K/128)] or [ceil(K/128),M]).
+
+    Mirrors dynamic_fp8_quant (csrc/bindings_python.cu:32-61).
+    """
+    _require(input.is_cuda, "dynamic_fp8_quant: input must be on CUDA")
+    _require(input.is_contiguous(), "dynamic_fp8_quant: input must be contiguous")
+    _require(input.dim() == 2, "dynamic_fp8_quant: input must be 2D [M, K]")
+    _require(input.dtype == torch.bfloat16, "dynamic_fp8_quant: input must be BF16")
+    M, K = input.shape
+    nb = (K + 127) // 128
+    out = torch.empty((M, K), dtype=torch.float8_e4m3fn, device=input.device)
+    scales = torch.empty((nb, M) if m_major_scales else (M, nb), dtype=torch.float32,
+                         device=input.device)
+    p = capi.DynamicFp8QuantParams(num_tokens=M, hidden_size=K, input=input.data_ptr(),
+                                   output=out.data_ptr(), scales=scales.data_ptr(),
+                                   m_major_scales=1 if m_major_scales else 0)
+    capi.check(_lib.lsg_dynamic_fp8_quant(ctypes.byref(p), _stream()))
+    return out, scales
+
+
+def _nvfp4_grouped(op, fn, x, up, expert_offsets, input_scales):
+    _require(x.is_cuda and x.dtype == torch.bfloat16, f"{op}: input must be BF16 on CUDA")
+    _require(x.dim() == 2 and x.is_contiguous(), f"{op}: input must be contiguous [T, K]")
+    if up is not None:
+        _require(up.is_cuda and up.dtype == torch.bfloat16, f"{op}: up must be BF16 on CUDA")
+        _require(up.dim() == 2 and up.is_contiguous(), f"{op}: up must be contiguous [T, K]")
+        _require(tuple(up.shape) == tuple(x.shape), f"{op}: gate and up must have the same shape")
+    _require(expert_offsets.dim() == 1 and expert_offsets.dtype == torch.int32,
+             f"{op}: expert_offsets must be 1D int32")
+    T, K = x.shape
+    E = expert_offsets.numel() - 1
+    _require(K % 64 == 0, f"{op}: K must be divisible by 64 "
+             "(K/16 groups must align to the 4-group Sm1xx atom)")
+    # As the reference binding: the scale buffer's size depends on the padded row total,
+    # which needs the offsets on the host (one D2H copy when they live on the device).
+    offs_cpu = expert_offsets.cpu().contiguous()
+    _require(int(offs_cpu[E]) == T, f"{op}: expert_offsets must end at total_tokens")
+    counts = (offs_cpu[1:] - offs_cpu[:-1]).to(torch.int64)
+    padded = ((counts + 127) // 128) * 128
+    sf_cpu = torch.zeros(E + 1, dtype=torch.int32)
+    sf_cpu[1:] = torch.cumsum(padded, 0).to(torch.int32)
+    padded_total = int(sf_cpu[E])
+    packed = torch.empty((T, K // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros((padded_total * (K // 16),), dtype=torch.uint8, device=x.device)
+    offs_dev = expert_offsets.contiguous() if expert_offsets.is_cuda else expert_offsets.to(x.device)
+    sf_dev = sf_cpu.to(x.device)
+    isc = None
+    if input_scales is not None:
+        _require(input_scales.is_cuda and input_scales.dtype == torch.float32
+                 and input_scales.numel() == E,
+                 f"{op}: input_scales must be [num_experts] float32 on CUDA")
+        isc = input_scales.contiguous()
+    p = capi.Nvfp4GroupedQuantParams(
+        input=x.data_ptr(), up=up.data_ptr() if up is not None else None,
+        output_packed=packed.data_ptr(), output_scales=scales.data_ptr(),
+        expert_offsets=offs_dev.data_ptr(), sf_offsets=sf_dev.data_ptr(), total_tokens=T,
+        num_experts=E, K=K, input_scales=isc.data_ptr() if isc is not None else None)
+    capi.check(fn(ctypes.byref(p), _stream()))
+    return packed, scales, sf_dev
+
+
+def bf16_to_nvfp4_grouped(input, expert_offsets, input_scales=None):
+    """Grouped bf16 -> NVFP4 activation quantization; returns (packed, scales, sf_offsets).
+
+    Mirrors bf16_to_nvfp4_grouped (csrc/bindings_python.cu:287-358).
+    """
+    return _nvfp4_grouped("bf16_to_nvfp4_grouped", _lib.lsg_bf16_to_nvfp4_grouped, input, None,
+                          expert_offsets, input_scales)
+
+
+def silu_mul_to_nvfp4_grouped(gate, up, expert_offsets, input_scales=None):
+    """Fused SwiGLU + grouped NVFP4 quantization; returns (packed, scales, sf_offsets).
+
+    Mirrors silu_mul_to_nvfp4_grouped (csrc/bindings_python.cu:362-440).
+    """
+    return _nvfp4_grouped("silu_mul_to_nvfp4_grouped", _lib.lsg_silu_mul_to_nvfp4_grouped, gate, up,
+                          expert_offsets, input_scales)

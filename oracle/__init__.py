@@ -114,3 +114,59 @@ def ref_lib():
         except OSError:
             _ref = None
     return _ref
+
+
+# ---------------------------------------------------------------------------
+# FP8 / NVFP4 activation quantizers
+# ---------------------------------------------------------------------------
+def f32_to_e4m3(values):
+    L = lib()
+    L.oracle_f32_to_e4m3.restype = ctypes.c_uint8
+    L.oracle_f32_to_e4m3.argtypes = [ctypes.c_float]
+    v = np.asarray(values, dtype=np.float32).ravel()
+    return np.array([L.oracle_f32_to_e4m3(float(x)) for x in v], dtype=np.uint8)
+
+
+def e4m3_to_f32(bits):
+    L = lib()
+    L.oracle_e4m3_to_f32.restype = ctypes.c_float
+    L.oracle_e4m3_to_f32.argtypes = [ctypes.c_uint8]
+    return np.array([L.oracle_e4m3_to_f32(int(b)) for b in np.asarray(bits).ravel()], dtype=np.float32)
+
+
+def dynamic_fp8_quant(x_bf16_bits, m_major=False):
+    """Returns (e4m3 bytes [M,K], fp32 scales [M,nb] or [nb,M])."""
+    x = np.ascontiguousarray(x_bf16_bits, dtype=np.uint16)
+    M, K = x.shape
+    nb = (K + 127) // 128
+    out = np.zeros((M, K), dtype=np.uint8)
+    scales = np.zeros((nb, M) if m_major else (M, nb), dtype=np.float32)
+    lib().oracle_dynamic_fp8_quant(_ptr(x), _ptr(out), _ptr(scales), ctypes.c_int(M),
+                                   ctypes.c_int(K), ctypes.c_int(1 if m_major else 0))
+    return out, scales
+
+
+def nvfp4_sf_offsets(expert_offsets):
+    offs = np.ascontiguousarray(expert_offsets, dtype=np.int32)
+    E = offs.shape[0] - 1
+    sf = np.zeros(E + 1, dtype=np.int32)
+    lib().oracle_nvfp4_sf_offsets(_ptr(offs), _ptr(sf), ctypes.c_int(E))
+    return sf
+
+
+def bf16_to_nvfp4_grouped(x_bf16_bits, expert_offsets, input_scales=None):
+    """Returns (packed [T,K/2], scales [padded_total*K/16], sf_offsets [E+1])."""
+    x = np.ascontiguousarray(x_bf16_bits, dtype=np.uint16)
+    T, K = x.shape
+    offs = np.ascontiguousarray(expert_offsets, dtype=np.int32)
+    E = offs.shape[0] - 1
+    sf = nvfp4_sf_offsets(offs)
+    packed = np.zeros((T, K // 2), dtype=np.uint8)
+    scales = np.zeros(int(sf[E]) * (K // 16), dtype=np.uint8)
+    isc = None
+    if input_scales is not None:
+        isc = np.ascontiguousarray(input_scales, dtype=np.float32)
+    lib().oracle_bf16_to_nvfp4_grouped(_ptr(x), _ptr(packed), _ptr(scales), _ptr(offs), _ptr(sf),
+                                       _ptr(isc) if isc is not None else None,
+                                       ctypes.c_int(T), ctypes.c_int(E), ctypes.c_int(K))
+    return packed, scales, sf
