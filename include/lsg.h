@@ -153,6 +153,19 @@ LSG_API int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_k
                                 int smem_share, int skip_math);
 
 /* ------------------------------------------------------------------------ */
+/* GGUF mmq: prefill GEMM on the tensor cores                               */
+/* ------------------------------------------------------------------------ */
+
+/* C[M,N] = Q8_1(A) . decode(B)^T for large M through tcgen05 (fp16 operands made from
+ * the Q8_1 round trip of A and the dequantized weight, fp32 accumulation).
+ * Replaces launch_gguf_mmq_mma, csrc/sm120/gemm/gguf/mmq_mma/mmq_mma_dispatch.cu:52-91
+ * (no Python binding of its own in the reference; reached through the grouped operator).
+ * Workspace: lsg_gguf_mmq_workspace_bytes(M, N, K) bytes, 256-byte aligned. */
+LSG_API size_t lsg_gguf_mmq_workspace_bytes(int M, int N, int K);
+LSG_API int lsg_gguf_mmq(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/* ------------------------------------------------------------------------ */
 /* GGUF dequant GEMM (lossless-activation golden strategy)                  */
 /* ------------------------------------------------------------------------ */
 
@@ -166,6 +179,60 @@ LSG_API int lsg_gguf_dequant_gemm(const lsg_gguf_mmvq_params* p, void* stream);
  * replaces the per-type dequant_*_block device functions of csrc/formats/. */
 LSG_API int lsg_gguf_dequant_blocks(const void* packed, float* out, int type, long long n_blocks,
                             void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* GGUF grouped GEMM: one MoE projection over E experts                     */
+/* ------------------------------------------------------------------------ */
+enum { LSG_GGUF_STRATEGY_DEQUANT = 0, LSG_GGUF_STRATEGY_INT = 1 };
+/* replaces enum GgufGroupedStrategy, csrc/sm120/gemm/gguf/gguf_grouped_gemm.h:38-41 */
+enum { LSG_GGUF_FORCE_AUTO = 0, LSG_GGUF_FORCE_MMVQ = 1, LSG_GGUF_FORCE_MMQ = 2,
+       LSG_GGUF_FORCE_HOSTLOOP = 3 };
+/* replaces GgufGroupedIntForce (gguf_grouped_int.h:100-104) and the binding's force
+ * argument (csrc/bindings_python.cu:552,594-602) */
+
+/* Mirrors struct GgufGroupedGemmKernelParams, gguf_grouped_gemm.h:43-55, plus out_dtype. */
+typedef struct lsg_gguf_grouped_gemm_params {
+    int type;                      /* lsg_gguf_type, shared by all experts           */
+    int strategy;                  /* LSG_GGUF_STRATEGY_*                            */
+    int num_experts;
+    int N;                         /* output columns                                 */
+    int K;                         /* input columns                                  */
+    const void* A_base;            /* [total_tokens,K] bf16, rows grouped by expert  */
+    void* D_base;                  /* [total_tokens,N] out_dtype                     */
+    const int32_t* expert_offsets; /* [E+1] cumulative row counts, device            */
+    const void* const* B_ptrs;     /* [E] packed weights, device array of device     */
+                                   /* pointers; a null entry skips that expert       */
+    int out_dtype;
+} lsg_gguf_grouped_gemm_params;
+
+/* Replaces gguf_grouped_gemm_workspace_bytes, gguf_grouped_gemm.cu:28-37.  The layout
+ * differs from the reference's (it also holds this library's segment list), so callers
+ * must size the workspace with this function. */
+LSG_API size_t lsg_gguf_grouped_gemm_workspace_bytes(int total_tokens, int K, int num_experts);
+
+/* Workspace that also holds the fp16 operands of the tensor-core path (N is needed for
+ * that, which the reference's signature does not carry).  With only the smaller workspace
+ * above, calls that would use tensor cores run the grouped mat-vec kernel instead. */
+LSG_API size_t lsg_gguf_grouped_gemm_workspace_bytes_ex(int total_tokens, int K, int num_experts,
+                                                        int N);
+
+/* Replaces launch_gguf_grouped_gemm / _int_forced / _hostloop (gguf_grouped_gemm.cu:40-150).
+ * Rows of experts that are empty or whose weight pointer is null are left untouched.
+ * The Int strategy with force 0..2 never synchronizes with the host. */
+LSG_API int lsg_gguf_grouped_gemm(const lsg_gguf_grouped_gemm_params* p, int total_tokens,
+                                  void* workspace, size_t workspace_bytes, int force, void* stream);
+
+/* Ascending list of the experts that have rows, padded with -1 to `cap` entries.
+ * Replaces build_active_expert_list, gguf_grouped_int.cu:156-187. */
+LSG_API int lsg_build_active_expert_list(const int32_t* expert_offsets, int num_experts, int cap,
+                                         int32_t* active_experts, void* stream);
+
+/* m-tile t -> (expert, first row) for tiles of tile_m rows, padded with (-1, 0) to t_max.
+ * Replaces build_mmq_tile_map, gguf_grouped_int.cu:46-66 (t_max as
+ * gguf_grouped_mmq_tmax, gguf_grouped_int.h:91-95). */
+LSG_API int lsg_build_mmq_tile_map(const int32_t* expert_offsets, int num_experts, int tile_m,
+                                   int t_max, int32_t* tile_expert, int32_t* tile_mstart,
+                                   void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Activation quantizers for the FP8 / NVFP4 paths                          */

@@ -60,6 +60,13 @@ class Nvfp4GroupedQuantParams(ctypes.Structure):
                 ("K", ctypes.c_int), ("input_scales", ctypes.c_void_p)]
 
 
+class GgufGroupedGemmParams(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("strategy", ctypes.c_int), ("num_experts", ctypes.c_int),
+                ("N", ctypes.c_int), ("K", ctypes.c_int), ("A_base", ctypes.c_void_p),
+                ("D_base", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p),
+                ("B_ptrs", ctypes.c_void_p), ("out_dtype", ctypes.c_int)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -83,6 +90,13 @@ def _load():
         "lsg_bf16_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
         "lsg_silu_mul_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
         "lsg_nvfp4_sf_offsets": (ci, [vp, vp, ci, vp]),
+        "lsg_gguf_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci]),
+        "lsg_gguf_grouped_gemm": (ci, [ctypes.POINTER(GgufGroupedGemmParams), ci, vp, sz, ci, vp]),
+        "lsg_build_active_expert_list": (ci, [vp, ci, ci, vp, vp]),
+        "lsg_build_mmq_tile_map": (ci, [vp, ci, ci, ci, vp, vp, vp]),
+        "lsg_gguf_grouped_gemm_workspace_bytes_ex": (sz, [ci, ci, ci, ci]),
+        "lsg_gguf_mmq_workspace_bytes": (sz, [ci, ci, ci]),
+        "lsg_gguf_mmq": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_gguf_dequant_gemm": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_gguf_dequant_blocks": (ci, [vp, vp, ci, ll, vp]),
     }

@@ -1,6 +1,7 @@
 // Host-side entry points shared between translation units.
 #pragma once
 #include <cuda_runtime.h>
+#include <stdint.h>
 #include "../../include/lsg.h"
 
 namespace lsg {
@@ -13,5 +14,18 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
 bool fused_quant_ok(int M, int K, const void* A);
 int dequant_gemm(int type, int M, int N, int K, const void* A, const void* W, void* C, int ldc,
                  int out_f32, cudaStream_t stream);
+
+int build_active_expert_list(const int32_t* offs, int E, int cap, int* active, cudaStream_t s);
+int build_mmq_tile_map(const int32_t* offs, int E, int tile_m, int T_max, int* tile_expert,
+                       int* tile_mstart, cudaStream_t s);
+int build_segment_list(const int32_t* offs, const void* const* B_ptrs, int E, int max_rows,
+                       int max_segments, int* seg, cudaStream_t s);
+
+size_t mmq_scratch_bytes(long long rows, int K, int E, int N);
+int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
+              size_t ws_bytes, cudaStream_t s);
+int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void* const* B_ptrs,
+                const int32_t* expert_offsets, void* D, int out_f32, const int* tile_expert,
+                const int* tile_mstart, int t_max, void* scratch, size_t scratch_bytes, cudaStream_t s);
 
 }  // namespace lsg

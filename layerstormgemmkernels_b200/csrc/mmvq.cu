@@ -66,6 +66,8 @@ int dispatch_max_rows(int type, int K) {
 
 }  // namespace
 
+MmvqTune mmvq_tuning() { return sane_tuning(); }
+
 int check_gemm_params(const char* op, const lsg_gguf_mmvq_params* p) {
     if (!p) return fail(LSG_ERR_INVALID, "%s: null params", op);
     const int qk = gguf_block_values(p->type);

@@ -58,6 +58,8 @@ struct MmvqTune {
     int skip_math;  // measurement aid: stream the weights but skip the arithmetic
 };
 
+MmvqTune mmvq_tuning();  // current process-wide geometry, clamped to valid ranges (mmvq.cu)
+
 // Per-type entry points, one translation unit each (mmvq_inst.cu).
 #define LSG_CAT2(a, b) a##b
 #define LSG_CAT(a, b) LSG_CAT2(a, b)
@@ -256,6 +258,47 @@ __device__ __forceinline__ void store_out(void* C, int out_f32, size_t idx, floa
 }
 
 // ---------------------------------------------------------------------------
+// One row group x MT batch rows: dot every unit of the RW*SUBS rows of the group with
+// the activation image, reduce over the L lanes of each row, store.
+//   raddr   shared addresses of this lane group's RW rows (clamped to the slab)
+//   xv      activation image view; xv.base / xv.mlast already set for this batch tile
+//   rl0     first row of this lane group inside the slab; rows >= nrows are not stored
+//   col0    output column of slab row 0;  mrow0 / mvalid  first output row and how many
+// ---------------------------------------------------------------------------
+template <int T, int MT, int RW, int L>
+__device__ __forceinline__ void group_dot_store(const uint32_t (&raddr)[RW], const XView& xv, int lane,
+                                                int rl0, int nrows, long long col0, int mrow0,
+                                                int mvalid, void* C, int ldc, int out_f32,
+                                                bool skip_math) {
+    using D = Mmvq<T>;
+    const int kl = lane % L;
+    float acc[RW * MT];
+#pragma unroll
+    for (int v = 0; v < RW * MT; ++v) acc[v] = 0.0f;
+    if (!skip_math)
+        for (int u = kl; u < xv.U; u += L) D::template unit_dot<RW, MT>(raddr, u, xv, acc);
+
+    // Reduce over the L lanes of each group, NVB values at a time.
+    constexpr int NV = RW * MT;
+    constexpr int NVB = NV < L ? NV : L;
+#pragma unroll
+    for (int b0 = 0; b0 < NV; b0 += NVB) {
+        float v[NVB];
+#pragma unroll
+        for (int k = 0; k < NVB; ++k) v[k] = acc[b0 + k];
+        reduce_group<NVB, L>(v, lane);
+        constexpr int LPV = L / NVB;  // lanes holding the same value
+        if ((kl % LPV) == 0) {
+            const int vi = b0 + kl / LPV;
+            const int r = vi / MT, m = vi % MT;
+            const int rl = rl0 + r;
+            if (rl < nrows && m < mvalid)
+                store_out(C, out_f32, static_cast<size_t>(mrow0 + m) * ldc + (col0 + rl), v[0]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The kernel
 //   T  : lsg_gguf_type
 //   MT : batch rows per register pass (1, 2, 4, 8)
@@ -405,35 +448,10 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                 raddr[r] = slab + static_cast<uint32_t>(min(g + sub * RW + r, nrows - 1)) * a.row_bytes;
 
             for (int m0 = 0; m0 < a.M; m0 += MT) {
-                float acc[RW * MT];
-#pragma unroll
-                for (int v = 0; v < RW * MT; ++v) acc[v] = 0.0f;
                 xv.base = x_base + m0 * xv.rowb;
                 xv.mlast = a.M - 1 - m0;
-
-                if (!a.debug_skip)
-                    for (int u = kl; u < xv.U; u += L) D::template unit_dot<RW, MT>(raddr, u, xv, acc);
-
-                // Reduce over the L lanes of each group, NVB values at a time.
-                constexpr int NV = RW * MT;
-                constexpr int NVB = NV < L ? NV : L;
-#pragma unroll
-                for (int b0 = 0; b0 < NV; b0 += NVB) {
-                    float v[NVB];
-#pragma unroll
-                    for (int k = 0; k < NVB; ++k) v[k] = acc[b0 + k];
-                    reduce_group<NVB, L>(v, lane);
-                    constexpr int LPV = L / NVB;  // lanes holding the same value
-                    if ((kl % LPV) == 0) {
-                        const int vi = b0 + kl / LPV;
-                        const int r = vi / MT, m = vi % MT;
-                        const int rl = g + sub * RW + r;
-                        if (rl < nrows && m0 + m < a.M) {
-                            store_out(a.C, a.out_f32,
-                                      static_cast<size_t>(m0 + m) * a.ldc + (r0 + rl), v[0]);
-                        }
-                    }
-                }
+                group_dot_store<T, MT, RW, L>(raddr, xv, lane, g + sub * RW, nrows, r0, m0,
+                                              a.M - m0, a.C, a.ldc, a.out_f32, a.debug_skip != 0);
             }
         }
         // Every stage collects one arrival per group, real or past the end.

@@ -1,7 +1,7 @@
 // One translation unit per GGUF type (compiled with -DLSG_MMVQ_TYPE=<id>) so the
 // eight decoders build in parallel.  Picks the kernel variant and the pipeline
 // geometry for a shape and launches it.
-#include "mmvq.cuh"
+#include "mmvq_grouped.cuh"
 
 
 #ifndef LSG_MMVQ_TYPE
@@ -119,6 +119,81 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pd
     if (a.M == 2) return launch_rows<2>(rw, lanes, a, grid, smem, stream, pdl);
     if (a.M <= 4) return launch_rows<4>(rw, lanes, a, grid, smem, stream, pdl);
     return launch_rows<8>(rw, lanes, a, grid, smem, stream, pdl);
+}
+
+namespace {
+
+template <int RW, int L>
+int launch_grouped_variant(const GroupedArgs& a, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+    auto kernel = mmvq_grouped_kernel<T, RW, L>;
+    static bool configured[64] = {};
+    int dev = 0;
+    LSG_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        LSG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemCap));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    LSG_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3((a.cons_warps + 1) * 32), smem, stream, pdl, a));
+    return LSG_OK;
+}
+
+constexpr int kGroupedCtlBytes = 2 * kMmvqMaxStages * 8 + 16 + kMmvqMaxStages * 4 + 3 * kGroupedMaxSlabs * 4;
+constexpr int kGroupedImageBudget = 64 * 1024;  // activation image of one segment
+
+}  // namespace
+
+// Rows of one segment: as many batch rows as fit the image budget (at least 1, at most 64).
+int MMVQ_FN(grouped_max_rows)(int K, const MmvqTune&) {
+    int rows = kGroupedImageBudget / x_row_bytes<T>(K);
+    if (rows > 64) rows = 64;
+    if (rows >= 8) rows &= ~7;
+    return rows < 1 ? 1 : rows;
+}
+
+int MMVQ_FN(grouped_launch)(GroupedArgs a, const MmvqTune& tn, int max_segments, cudaStream_t stream,
+                            bool pdl) {
+    using F = Fmt<T>;
+    a.row_bytes = (a.K / F::VALS) * F::BYTES;
+    a.cons_warps = tn.warps;
+    const int U = a.K / Mmvq<T>::UV;
+    int lanes = 4;
+    while (lanes < 32 && lanes < U) lanes *= 2;
+    const int max_rows = MMVQ_FN(grouped_max_rows)(a.K, tn);
+    a.x_bytes = ((max_rows * x_row_bytes<T>(a.K) + 127) / 128) * 128;
+    const int avail = kSmemCap - a.x_bytes - kGroupedCtlBytes - 128;
+    int slab_rows = tn.stage_kb * 1024 / a.row_bytes;
+    if (slab_rows < 1) slab_rows = 1;
+    if (slab_rows > a.N) slab_rows = a.N;
+    int stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
+    while (slab_rows > 1 && 2 * stage_bytes > avail) {
+        slab_rows = (slab_rows + 1) / 2;
+        stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;
+    }
+    if (2 * stage_bytes > avail)
+        return fail(LSG_ERR_UNSUPPORTED, "gguf_grouped_gemm: K=%d does not fit the shared-memory ring", a.K);
+    int stages = avail / stage_bytes;
+    if (stages > kMmvqMaxStages) stages = kMmvqMaxStages;
+    a.slab_rows = slab_rows;
+    a.stage_bytes = stage_bytes;
+    a.stages = stages;
+    // Enough CTAs that no CTA's slab table can overflow even if every segment is live.
+    const long long v_max = static_cast<long long>(max_segments) * a.N;
+    long long grid = sm_count();
+    const long long per_cta_cap = static_cast<long long>(kGroupedMaxSlabs / 4) * slab_rows;
+    if (v_max / grid > per_cta_cap) grid = (v_max + per_cta_cap - 1) / per_cta_cap;
+    // each segment boundary inside a range adds a slab: bound that too
+    const long long seg_cap = static_cast<long long>(kGroupedMaxSlabs / 4) * a.N;
+    if (v_max / grid > seg_cap) grid = (v_max + seg_cap - 1) / seg_cap;
+    if (grid > 0x7fffffffLL) return fail(LSG_ERR_UNSUPPORTED, "gguf_grouped_gemm: problem too large");
+    const size_t smem = static_cast<size_t>(a.x_bytes) + static_cast<size_t>(stages) * stage_bytes +
+                        kGroupedCtlBytes;
+    switch (lanes) {
+        case 4: return launch_grouped_variant<2, 4>(a, static_cast<int>(grid), smem, stream, pdl);
+        case 8: return launch_grouped_variant<2, 8>(a, static_cast<int>(grid), smem, stream, pdl);
+        case 16: return launch_grouped_variant<2, 16>(a, static_cast<int>(grid), smem, stream, pdl);
+        default: return launch_grouped_variant<2, 32>(a, static_cast<int>(grid), smem, stream, pdl);
+    }
 }
 
 }  // namespace lsg

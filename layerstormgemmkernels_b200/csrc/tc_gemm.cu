@@ -1,0 +1,555 @@
+// Tensor-core path of the GGUF GEMMs on sm_100a: prefill ("mmq") and the grouped MoE
+// GEMM when experts have many rows.
+//
+// Replaces the reference's int8 mma.sync kernels (csrc/sm120/gemm/gguf/mmq_mma/:
+// mmq_kernel_32aligned.cuh:34-169, mmq_kernel_16subblock.cuh:36-155, launchers
+// mmq_mma_dispatch.cu:52-91) and their grouped variants.  The reference multiplies int8
+// tiles and rescales the int32 partial sums every 32 (or 16) values of K in registers:
+//   C += dx[m,c] * (A[n,c] * dot_int8 + B[n,c] * sum qx[m,c]).
+// With tcgen05 the accumulator lives in tensor memory, so a per-chunk rescale would mean
+// draining it 128 times per row of a 4096-wide K.  This path therefore applies the scales
+// BEFORE the multiply: both operands are turned into fp16 once per call,
+//   w16[n,k] = fp16(A*Q + B)          (the weight's dequantized value)
+//   x16[m,k] = fp16(d_x * q_x)        (the Q8_1 round trip of the activation)
+// and one fp16 x fp16 -> fp32 tcgen05.mma sweep over the whole K does the rest.  The
+// products are the same real numbers as the reference's, up to the fp16 rounding of each
+// operand (2^-11 relative, unbiased), which lands far inside the 1e-3 bound.
+//
+// Kernel: persistent, warp-specialised.
+//   warp 4      TMA producer: cp.async.bulk.tensor 2-D loads (128-byte swizzle) of a
+//               128 x 64 activation tile and a 256 x 64 weight tile per stage, 4 stages;
+//   warp 5      MMA issuer: one elected lane issues tcgen05.mma.cta_group::1.kind::f16
+//               (M = 128, N = 256, K = 16) x 4 per stage, commits to the stage's "empty"
+//               barrier, and after the last K block to the accumulator's "full" barrier;
+//   warps 0-3   epilogue: tcgen05.ld of the 128 x 256 fp32 accumulator (each warp its 32
+//               TMEM lanes), conversion, row-masked stores.  Two accumulators (2 x 256 of the
+//               512 TMEM columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+// Work items are (m-tile, n-tile) pairs; m-tiles come either from a dense problem or from
+// the device-built tile map of the grouped problem (routing.cu), so expert routing never
+// touches the host.  Every mbarrier wait is time-limited; after a time-out all roles leave
+// their loops, TMEM is freed, and the status word says so.
+#include "common.cuh"
+#include "formats.cuh"
+#include "host.h"
+
+#include <cuda.h>
+
+namespace lsg {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;   // 16 KB
+constexpr int kBBytes = BN * BK * 2;   // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTcThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kTcSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct TcArgs {
+    void* C;                  // [rows, ldc] bf16 or f32
+    int ldc;
+    int out_f32;
+    int K;
+    int N;                    // columns of one problem (per expert)
+    int n_tiles;              // ceil(N / BN)
+    // dense: m_tiles = ceil(M / BM), tile_expert == nullptr
+    // grouped: m_tiles = T_max, tile map and offsets on the device
+    int m_tiles;
+    int M;                    // dense: rows; grouped: total rows (for clamping)
+    const int* tile_expert;
+    const int* tile_mstart;
+    const int* expert_offsets;
+    unsigned int* status;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address
+    d |= static_cast<uint64_t>(1) << 16;                             // leading byte offset (unused)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                     // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;                             // version
+    d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = 128, N = 256.
+__device__ __forceinline__ constexpr uint32_t idesc_f16(int m, int n) {
+    return (1u << 4)                                  // accumulator format: F32
+           | (0u << 7) | (0u << 10)                   // A, B format: F16
+           | (0u << 15) | (0u << 16)                  // A, B K-major
+           | (static_cast<uint32_t>(n >> 3) << 17)    // N / 8
+           | (static_cast<uint32_t>(m >> 4) << 24);   // M / 16
+}
+
+// ---------------------------------------------------------------------------
+// The GEMM kernel
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* acc_full = empty + kStages;   // [2]
+    uint64_t* acc_empty = acc_full + 2;     // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    pdl_wait_prior();  // operands were produced by the preparation kernels before this one
+
+    const int kblocks = (a.K + BK - 1) / BK;
+    const int total = a.m_tiles * a.n_tiles;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int it = 0;
+            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+                const int t = w % a.m_tiles, j = w / a.m_tiles;
+                int mstart = t * BM, brow0 = j * BN;
+                if (a.tile_expert) {
+                    const int e = a.tile_expert[t];
+                    if (e < 0) continue;
+                    mstart = a.tile_mstart[t];
+                    brow0 = e * a.N + j * BN;
+                }
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages &&
+                        !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1, a.status, kDevWaitEmpty)) {
+                        *abort_flag = 1;
+                        break;
+                    }
+                    uint8_t* sA = smem + s * kStageBytes;
+                    uint8_t* sB = sA + kABytes;
+                    mbar_arrive_expect_tx(&full[s], kStageBytes);
+                    tma_load_2d(sA, &tmA, kb * BK, mstart, &full[s]);
+                    tma_load_2d(sB, &tmB, kb * BK, brow0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BM, BN);
+            int it = 0, tile_i = 0;
+            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+                const int t = w % a.m_tiles;
+                if (a.tile_expert && a.tile_expert[t] < 0) continue;
+                const int ab = tile_i & 1;
+                if (tile_i >= 2 &&
+                    !mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status, kDevWaitTmem)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait_bounded(&full[s], (it / kStages) & 1, a.status, kDevWaitFull)) {
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sA = smem_u32(smem + s * kStageBytes);
+                    const uint64_t adesc = smem_desc_sw128(sA);
+                    const uint64_t bdesc = smem_desc_sw128(sA + kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in
+                        // the (address >> 4) field of the descriptors
+                        tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&empty[s]);  // the stage is free once these MMAs have read it
+                }
+                if (*abort_flag) break;
+                tc_commit(&acc_full[ab]);  // accumulator complete
+                ++tile_i;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (warps 0-3) ----------------------
+        int tile_i = 0;
+        for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+            const int t = w % a.m_tiles, j = w / a.m_tiles;
+            int mstart = t * BM, mend = a.M;
+            if (a.tile_expert) {
+                const int e = a.tile_expert[t];
+                if (e < 0) continue;
+                mstart = a.tile_mstart[t];
+                mend = a.expert_offsets[e + 1];
+            }
+            const int ab = tile_i & 1;
+            // warp-uniform outcome: the tensor-memory loads below need the whole warp
+            const bool landed = __all_sync(0xffffffffu,
+                                           mbar_wait_bounded(&acc_full[ab], (tile_i >> 1) & 1, a.status, kDevWaitMma));
+            if (!landed) {
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const int row = mstart + warp * 32 + lane;
+            const bool row_ok = row < mend;
+            const int n0 = j * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * BN + c, r);
+                if (row_ok && n0 + c < a.N) {
+                    const size_t o = static_cast<size_t>(row) * a.ldc + n0 + c;
+                    const int ncols = min(32, a.N - (n0 + c));
+                    if (a.out_f32) {
+                        float* dst = static_cast<float*>(a.C) + o;
+                        if (ncols == 32 && (a.ldc & 3) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<uint4*>(dst)[q] =
+                                    make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+                            for (int q = 0; q < ncols; ++q) dst[q] = __uint_as_float(r[q]);
+                        }
+                    } else {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.C) + o;
+                        if (ncols == 32 && (a.ldc & 7) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t p[4];
+#pragma unroll
+                                for (int h = 0; h < 4; ++h) {
+                                    const __nv_bfloat162 v = __floats2bfloat162_rn(
+                                        __uint_as_float(r[8 * q + 2 * h]), __uint_as_float(r[8 * q + 2 * h + 1]));
+                                    p[h] = *reinterpret_cast<const uint32_t*>(&v);
+                                }
+                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                            }
+                        } else {
+                            for (int q = 0; q < ncols; ++q) dst[q] = __float2bfloat16_rn(__uint_as_float(r[q]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            ++tile_i;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Operand preparation
+// ---------------------------------------------------------------------------
+// Packed GGUF rows -> fp16 [rows, K].  One thread per block; `row_owner`, when given,
+// skips experts without rows (grouped case).
+template <int T>
+__global__ void weights_to_f16_kernel(const uint8_t* __restrict__ W, const void* const* __restrict__ B_ptrs,
+                                      const int32_t* __restrict__ expert_offsets, __half* __restrict__ out,
+                                      int N, int K, long long n_blocks_per_matrix) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    using F = Fmt<T>;
+    const int e = blockIdx.y;
+    const uint8_t* base = W;
+    if (B_ptrs) {
+        if (expert_offsets[e + 1] - expert_offsets[e] <= 0) return;
+        base = static_cast<const uint8_t*>(B_ptrs[e]);
+        if (!base) return;
+    }
+    const long long b = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (b >= n_blocks_per_matrix) return;
+    float v[F::VALS];
+    dequant_block<T>(base + b * F::BYTES, v);
+    __half* dst = out + (static_cast<long long>(e) * N * K) + b * F::VALS;
+#pragma unroll
+    for (int i = 0; i < F::VALS; i += 8) {
+        uint32_t p[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            const __half2 hv = __floats2half2_rn(v[i + 2 * h], v[i + 2 * h + 1]);
+            p[h] = *reinterpret_cast<const uint32_t*>(&hv);
+        }
+        *reinterpret_cast<uint4*>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+}
+
+// bf16 x[M,K] -> fp16 of the Q8_1 round trip: d_h * rn(x / d) with d = amax/127 per 32
+// values and d_h its fp16 rounding (what the integer paths multiply by).
+__global__ void __launch_bounds__(256)
+x_q8_1_roundtrip_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int lane = threadIdx.x & 31;
+    const long long blk = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (blk >= n_blocks) return;
+    const float xi = __bfloat162float(x[blk * 32 + lane]);
+    float amax = fabsf(xi);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = amax / 127.0f;
+    const int q = (amax == 0.0f) ? 0 : __float2int_rn(xi / d);
+    const float dh = __half2float(__float2half(d));
+    out[blk * 32 + lane] = __float2half(dh * static_cast<float>(q));
+}
+
+// ---------------------------------------------------------------------------
+// Host
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// fp16 matrix [rows, K] row-major -> tensor map with a (BK x box_rows) box, 128 B swizzle.
+int make_map(CUtensorMap* map, const void* base, long long rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(LSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LSG_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+    return LSG_OK;
+}
+
+int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcArgs& a, int max_items, cudaStream_t s) {
+    static bool configured[64] = {};
+    int dev = 0;
+    LSG_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        LSG_CUDA_TRY(cudaFuncSetAttribute(tc_gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    int grid = sm_count();
+    if (grid > max_items) grid = max_items;
+    if (grid < 1) grid = 1;
+    LSG_CUDA_TRY(launch_kernel(tc_gemm_f16_kernel, dim3(grid), dim3(kTcThreads), kTcSmem, s, true, tmA, tmB, a));
+    return LSG_OK;
+}
+
+template <int T>
+int launch_w16(const void* W, const void* const* B_ptrs, const int32_t* offs, __half* out, int E, int N,
+               int K, cudaStream_t s) {
+    const long long nb = static_cast<long long>(N) * (K / Fmt<T>::VALS);
+    dim3 grid(static_cast<unsigned>((nb + 63) / 64), E);
+    LSG_CUDA_TRY(launch_kernel(weights_to_f16_kernel<T>, grid, dim3(64), 0, s, true,
+                               static_cast<const uint8_t*>(W), B_ptrs, offs, out, N, K, nb));
+    return LSG_OK;
+}
+
+int weights_to_f16(int type, const void* W, const void* const* B_ptrs, const int32_t* offs, __half* out,
+                   int E, int N, int K, cudaStream_t s) {
+    switch (type) {
+        case 0: return launch_w16<0>(W, B_ptrs, offs, out, E, N, K, s);
+        case 1: return launch_w16<1>(W, B_ptrs, offs, out, E, N, K, s);
+        case 2: return launch_w16<2>(W, B_ptrs, offs, out, E, N, K, s);
+        case 3: return launch_w16<3>(W, B_ptrs, offs, out, E, N, K, s);
+        case 4: return launch_w16<4>(W, B_ptrs, offs, out, E, N, K, s);
+        case 5: return launch_w16<5>(W, B_ptrs, offs, out, E, N, K, s);
+        case 6: return launch_w16<6>(W, B_ptrs, offs, out, E, N, K, s);
+        case 7: return launch_w16<7>(W, B_ptrs, offs, out, E, N, K, s);
+    }
+    return fail(LSG_ERR_UNSUPPORTED, "gguf mmq: unknown type %d", type);
+}
+
+int x_to_f16(const void* x_bf16, __half* out, long long rows, int K, cudaStream_t s) {
+    const long long nb = rows * (K / 32);
+    if (nb == 0) return LSG_OK;
+    LSG_CUDA_TRY(launch_kernel(x_q8_1_roundtrip_f16_kernel, dim3(static_cast<unsigned>((nb + 7) / 8)), dim3(256),
+                               0, s, true, static_cast<const __nv_bfloat16*>(x_bf16), out, nb));
+    return LSG_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+// Scratch of the tensor-core path: fp16 activations + fp16 weights of E matrices.
+size_t mmq_scratch_bytes(long long rows, int K, int E, int N) {
+    return align256(static_cast<size_t>(rows) * K * 2) + align256(static_cast<size_t>(E) * N * K * 2);
+}
+
+// Dense: C[M,N] = x16 . w16^T.
+int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
+              size_t ws_bytes, cudaStream_t s) {
+    if (M == 0 || N == 0) return LSG_OK;
+    if (K % 8 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_mmq: K must be a multiple of 8");
+    const size_t need = mmq_scratch_bytes(M, K, 1, N);
+    if (!ws || ws_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "gguf_mmq: workspace too small (have %zu, need %zu)",
+                    ws ? ws_bytes : size_t(0), need);
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(LSG_ERR_ALIGNMENT, "gguf_mmq: workspace must be 256-byte aligned");
+    __half* x16 = static_cast<__half*>(ws);
+    __half* w16 = reinterpret_cast<__half*>(static_cast<uint8_t*>(ws) + align256(static_cast<size_t>(M) * K * 2));
+    int rc = x_to_f16(A, x16, M, K, s);
+    if (rc != LSG_OK) return rc;
+    rc = weights_to_f16(type, W, nullptr, nullptr, w16, 1, N, K, s);
+    if (rc != LSG_OK) return rc;
+    CUtensorMap tmA, tmB;
+    rc = make_map(&tmA, x16, M, K, BM);
+    if (rc != LSG_OK) return rc;
+    rc = make_map(&tmB, w16, N, K, BN);
+    if (rc != LSG_OK) return rc;
+    TcArgs a = {};
+    a.C = C; a.ldc = N; a.out_f32 = out_f32; a.K = K; a.N = N;
+    a.n_tiles = (N + BN - 1) / BN;
+    a.m_tiles = (M + BM - 1) / BM;
+    a.M = M;
+    a.status = device_status_word();
+    return launch_tc(tmA, tmB, a, a.m_tiles * a.n_tiles, s);
+}
+
+// Grouped: rows routed by the device-built tile map (tile_m must be BM = 128).
+int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void* const* B_ptrs,
+                const int32_t* expert_offsets, void* D, int out_f32, const int* tile_expert,
+                const int* tile_mstart, int t_max, void* scratch, size_t scratch_bytes, cudaStream_t s) {
+    if (K % 8 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf grouped mmq: K must be a multiple of 8");
+    const size_t need = mmq_scratch_bytes(T, K, E, N);
+    if (!scratch || scratch_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "gguf grouped mmq: scratch too small (have %zu, need %zu)",
+                    scratch ? scratch_bytes : size_t(0), need);
+    __half* x16 = static_cast<__half*>(scratch);
+    __half* w16 = reinterpret_cast<__half*>(static_cast<uint8_t*>(scratch) + align256(static_cast<size_t>(T) * K * 2));
+    int rc = x_to_f16(A, x16, T, K, s);
+    if (rc != LSG_OK) return rc;
+    rc = weights_to_f16(type, nullptr, B_ptrs, expert_offsets, w16, E, N, K, s);
+    if (rc != LSG_OK) return rc;
+    CUtensorMap tmA, tmB;
+    rc = make_map(&tmA, x16, T, K, BM);
+    if (rc != LSG_OK) return rc;
+    rc = make_map(&tmB, w16, static_cast<long long>(E) * N, K, BN);
+    if (rc != LSG_OK) return rc;
+    TcArgs a = {};
+    a.C = D; a.ldc = N; a.out_f32 = out_f32; a.K = K; a.N = N;
+    a.n_tiles = (N + BN - 1) / BN;
+    a.m_tiles = t_max;
+    a.M = T;
+    a.tile_expert = tile_expert;
+    a.tile_mstart = tile_mstart;
+    a.expert_offsets = expert_offsets;
+    a.status = device_status_word();
+    return launch_tc(tmA, tmB, a, a.m_tiles * a.n_tiles, s);
+}
+
+}  // namespace lsg
+
+using namespace lsg;
+
+extern "C" size_t lsg_gguf_mmq_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return mmq_scratch_bytes(M, K, 1, N);
+}
+
+extern "C" int lsg_gguf_mmq(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+    int rc = check_gemm_params("gguf_mmq", p);
+    if (rc != LSG_OK) return rc;
+    if (p->M == 0 || p->N == 0) return LSG_OK;
+    if (!p->A || !p->B || !p->C) return fail(LSG_ERR_INVALID, "gguf_mmq: null pointer");
+    return mmq_dense(p->type, p->M, p->N, p->K, p->A, p->B, p->C, p->out_dtype == LSG_DTYPE_F32, workspace,
+                     workspace_bytes, static_cast<cudaStream_t>(stream));
+}

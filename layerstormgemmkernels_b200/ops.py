@@ -190,3 +190,76 @@ def silu_mul_to_nvfp4_grouped(gate, up, expert_offsets, input_scales=None):
     """
     return _nvfp4_grouped("silu_mul_to_nvfp4_grouped", _lib.lsg_silu_mul_to_nvfp4_grouped, gate, up,
                           expert_offsets, input_scales)
+
+
+# ---------------------------------------------------------------------------
+# Grouped (MoE) GEMM
+# ---------------------------------------------------------------------------
+def gguf_grouped_gemm(A_base, expert_offsets, b_ptrs, type, strategy, N, K, force=0,
+                      out_dtype=torch.bfloat16):
+    """One MoE projection over E experts: rows [offsets[e], offsets[e+1]) of A_base times
+    decode(weight e)^T.  `b_ptrs` is a CUDA int64 tensor of device pointers.
+    strategy: 0 = Dequant, 1 = Int; force: 0 auto, 1 mmvq, 2 mmq, 3 host loop.
+
+    Mirrors gguf_grouped_gemm (csrc/bindings_python.cu:553-604): the output comes from
+    torch.empty, so rows of empty or skipped experts are uninitialised.
+    """
+    _require(A_base.is_cuda and A_base.dtype == torch.bfloat16,
+             "gguf_grouped_gemm: A_base must be BF16 on CUDA")
+    _require(A_base.dim() == 2 and A_base.is_contiguous(),
+             "gguf_grouped_gemm: A_base must be contiguous [T, K]")
+    _require(expert_offsets.is_cuda and expert_offsets.dtype == torch.int32,
+             "gguf_grouped_gemm: expert_offsets must be int32 on CUDA")
+    _require(b_ptrs.is_cuda and b_ptrs.dtype == torch.int64,
+             "gguf_grouped_gemm: b_ptrs must be int64 (device pointers) on CUDA")
+    T = A_base.size(0)
+    E = b_ptrs.numel()
+    _require(expert_offsets.numel() == E + 1,
+             "gguf_grouped_gemm: expert_offsets must be [num_experts+1]")
+    D = torch.empty((T, N), dtype=out_dtype, device=A_base.device)
+    p = capi.GgufGroupedGemmParams(
+        type=int(type), strategy=int(strategy), num_experts=E, N=int(N), K=int(K),
+        A_base=A_base.data_ptr(), D_base=D.data_ptr(), expert_offsets=expert_offsets.data_ptr(),
+        B_ptrs=b_ptrs.data_ptr(),
+        out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+    use_tc = int(strategy) == 1 and int(force) != 3 and E > 0 and (int(force) == 2 or (int(force) == 0 and T // E > 8))
+    ws_bytes = (_lib.lsg_gguf_grouped_gemm_workspace_bytes_ex(T, int(K), E, int(N)) if use_tc
+                else _lib.lsg_gguf_grouped_gemm_workspace_bytes(T, int(K), E))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
+    capi.check(_lib.lsg_gguf_grouped_gemm(ctypes.byref(p), T, _ptr(ws), ws_bytes, int(force), _stream()))
+    return D
+
+
+def build_active_expert_list(expert_offsets, cap):
+    """int32 [cap]: ascending experts with rows, -1 padded (device-side, no sync)."""
+    E = expert_offsets.numel() - 1
+    out = torch.empty((cap,), dtype=torch.int32, device=expert_offsets.device)
+    capi.check(_lib.lsg_build_active_expert_list(_ptr(expert_offsets), E, cap, _ptr(out), _stream()))
+    return out
+
+
+def build_mmq_tile_map(expert_offsets, tile_m, t_max):
+    """(tile_expert, tile_mstart), int32 [t_max] each."""
+    E = expert_offsets.numel() - 1
+    te = torch.empty((t_max,), dtype=torch.int32, device=expert_offsets.device)
+    tm = torch.empty((t_max,), dtype=torch.int32, device=expert_offsets.device)
+    capi.check(_lib.lsg_build_mmq_tile_map(_ptr(expert_offsets), E, tile_m, t_max, _ptr(te), _ptr(tm),
+                                           _stream()))
+    return te, tm
+
+
+def gguf_mmq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
+    """Prefill GEMM on the tensor cores: bf16 A[M,K] @ decode(B)^T -> [M,N] with the
+    integer paths' activation quantization.  The reference reaches its mmq kernels only
+    through gguf_grouped_gemm(..., force=2); this direct entry is an addition."""
+    _require(A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous(),
+             "gguf_mmq: A must be contiguous BF16 [M, K] on CUDA")
+    _require(A.size(1) == K, "gguf_mmq: A.size(1) != K")
+    M = A.size(0)
+    C = torch.empty((M, N), dtype=out_dtype, device=A.device)
+    ws_bytes = _lib.lsg_gguf_mmq_workspace_bytes(M, int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    p = _gemm_params(A, B_packed, C, type, N, K,
+                     capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+    capi.check(_lib.lsg_gguf_mmq(ctypes.byref(p), _ptr(ws), ws_bytes, _stream()))
+    return C
