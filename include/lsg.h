@@ -283,6 +283,73 @@ LSG_API int lsg_silu_mul_to_nvfp4_grouped(const lsg_nvfp4_grouped_quant_params* 
 LSG_API int lsg_nvfp4_sf_offsets(const int32_t* expert_offsets, int32_t* sf_offsets,
                                  int num_experts, void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* NVFP4 grouped GEMM                                                       */
+/* ------------------------------------------------------------------------ */
+
+/* Mirrors struct Nvfp4GroupedGemmParams, csrc/sm120/gemm/grouped_gemm.h:34-57
+ * (problem_sizes is accepted for interface parity; row counts come from expert_offsets). */
+typedef struct lsg_nvfp4_grouped_gemm_params {
+    int num_experts;
+    int N;
+    int K;
+    const void* A_base;            /* [T,K/2] e2m1 pairs, low nibble = even k            */
+    const void* B_base;            /* [E,N,K/2]                                          */
+    void* D_base;                  /* [T,N] output_dtype                                 */
+    const void* scale_A_base;      /* ue4m3, interleaved layout, sections per sf_offsets */
+    const void* scale_B_base;      /* ue4m3, interleaved layout, N*K/16 bytes per expert */
+    const float* alphas;           /* [E]                                                */
+    const int32_t* expert_offsets; /* [E+1]                                              */
+    const int32_t* sf_offsets;     /* [E+1] in padded rows                               */
+    const int32_t* problem_sizes;  /* [E,3] {M_e,N,K}; may be null                       */
+    int output_dtype;              /* LSG_DTYPE_BF16, _F16 (or _F32 as an extension)     */
+    const void* const* B_ptrs;       /* optional [E] per-expert weight pointers          */
+    const void* const* scale_B_ptrs; /* optional [E] per-expert scale pointers           */
+} lsg_nvfp4_grouped_gemm_params;
+
+/* Replaces query_nvfp4_grouped_gemm_workspace_size (nvfp4_grouped_gemm.cu:373-384); needs
+ * the row count because this implementation expands the operands to fp16 in the workspace. */
+LSG_API size_t lsg_nvfp4_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K);
+
+/* Replaces launch_nvfp4_grouped_gemm, nvfp4_grouped_gemm.cu:386-423.  Device-routed (no
+ * host synchronization); rows of empty experts are left untouched. */
+LSG_API int lsg_nvfp4_grouped_gemm(const lsg_nvfp4_grouped_gemm_params* p, int total_tokens,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* fp32 scales [rows, K/16] -> ue4m3 in the interleaved layout (rows padded to 128, groups
+ * to 4; dst must hold lsg_nvfp4_sf_buffer_bytes(rows, K) zero-filled bytes).
+ * Replaces launch_reformat_scales, csrc/smxx/quant/reformat_scales.cu:63-69, and
+ * query_sf_buffer_size_b. */
+LSG_API size_t lsg_nvfp4_sf_buffer_bytes(int rows, int K);
+LSG_API int lsg_nvfp4_reformat_scales(const float* src, void* dst, int rows, int K, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* MoE routing, permutation, combine                                        */
+/* No counterpart in the reference: its grouped operators take rows that are */
+/* already grouped by expert (gguf_grouped_gemm.h:20-24).                   */
+/* ------------------------------------------------------------------------ */
+
+/* p = softmax(logits fp32 [T,E]); top-k (ties to the lower expert id); weights renormalised
+ * to sum 1.  topk_idx int32 [T,k], topk_weights fp32 [T,k].  E <= 1024, k <= 16. */
+LSG_API int lsg_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
+                          int32_t* topk_idx, float* topk_weights, void* stream);
+
+/* Stable grouping of the T*k (token, slot) pairs by expert: expert_offsets int32 [E+1],
+ * perm int32 [T*k] (row -> pair), inv_perm int32 [T*k] (pair -> row).
+ * counts_scratch: int32 [E]. */
+LSG_API int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int top_k, int num_experts,
+                                int32_t* expert_offsets, int32_t* perm, int32_t* inv_perm,
+                                int32_t* counts_scratch, void* stream);
+
+/* out[row,:] = hidden[perm[row] / top_k, :]   (bf16, H multiple of 8). */
+LSG_API int lsg_moe_permute(const void* hidden_bf16, const int32_t* perm, int rows, int top_k, int H,
+                            void* out_bf16, void* stream);
+
+/* out[t,:] = sum over slots s (in order) of topk_weights[t,s] * y[inv_perm[t*k+s], :],
+ * fp32 fused multiply-adds, rounded to bf16. */
+LSG_API int lsg_moe_unpermute(const void* y_bf16, const int32_t* inv_perm, const float* topk_weights,
+                              int num_tokens, int top_k, int H, void* out_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -67,6 +67,16 @@ class GgufGroupedGemmParams(ctypes.Structure):
                 ("B_ptrs", ctypes.c_void_p), ("out_dtype", ctypes.c_int)]
 
 
+class Nvfp4GroupedGemmParams(ctypes.Structure):
+    _fields_ = [("num_experts", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("A_base", ctypes.c_void_p), ("B_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p),
+                ("scale_A_base", ctypes.c_void_p), ("scale_B_base", ctypes.c_void_p),
+                ("alphas", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p),
+                ("sf_offsets", ctypes.c_void_p), ("problem_sizes", ctypes.c_void_p),
+                ("output_dtype", ctypes.c_int), ("B_ptrs", ctypes.c_void_p),
+                ("scale_B_ptrs", ctypes.c_void_p)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -97,6 +107,14 @@ def _load():
         "lsg_gguf_grouped_gemm_workspace_bytes_ex": (sz, [ci, ci, ci, ci]),
         "lsg_gguf_mmq_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_mmq": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
+        "lsg_nvfp4_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci, ci]),
+        "lsg_nvfp4_grouped_gemm": (ci, [ctypes.POINTER(Nvfp4GroupedGemmParams), ci, vp, sz, vp]),
+        "lsg_nvfp4_sf_buffer_bytes": (sz, [ci, ci]),
+        "lsg_nvfp4_reformat_scales": (ci, [vp, vp, ci, ci, vp]),
+        "lsg_moe_route": (ci, [vp, ci, ci, ci, vp, vp, vp]),
+        "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
+        "lsg_moe_permute": (ci, [vp, vp, ci, ci, ci, vp, vp]),
+        "lsg_moe_unpermute": (ci, [vp, vp, vp, ci, ci, ci, vp, vp]),
         "lsg_gguf_dequant_gemm": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_gguf_dequant_blocks": (ci, [vp, vp, ci, ll, vp]),
     }

@@ -230,6 +230,56 @@ __device__ inline void dequant_block<LSG_GGUF_MXFP4>(const uint8_t* __restrict__
 }
 
 // ---------------------------------------------------------------------------
+// 32 consecutive values (chunk c of a block) to fp32: the same arithmetic as
+// dequant_block, one chunk at a time, for kernels that spread a block over 8 threads.
+// ---------------------------------------------------------------------------
+template <int T>
+__device__ inline void dequant_chunk32(const uint8_t* __restrict__ b, int c, float* __restrict__ out) {
+    if (T == LSG_GGUF_Q4_K || T == LSG_GGUF_Q5_K) {
+        const float d = half_at(b), dmin = half_at(b + 2);
+        int sc, mn;
+        k4_scale_min(c, b + 4, sc, mn);
+        const float ds = d * sc, ms = dmin * mn;
+        const int pair = c >> 1, hi = c & 1;
+        const uint8_t* qs = b + (T == LSG_GGUF_Q4_K ? 16 : 48) + pair * 32;
+        for (int l = 0; l < 32; ++l) {
+            int q = hi ? (qs[l] >> 4) : (qs[l] & 0xF);
+            if (T == LSG_GGUF_Q5_K) q += ((b[16 + l] >> c) & 1) << 4;
+            out[l] = ds * q - ms;
+        }
+    } else if (T == LSG_GGUF_Q6_K) {
+        const int ip = c >> 2, quad = c & 3;
+        const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192);
+        const float d = half_at(b + 208);
+        for (int l = 0; l < 32; ++l) {
+            const int ql = b[64 * ip + (quad & 1) * 32 + l];
+            const int nib = (quad >= 2) ? (ql >> 4) : (ql & 0xF);
+            const int h = (b[128 + 32 * ip + l] >> (2 * quad)) & 3;
+            out[l] = d * sc[8 * ip + 2 * quad + l / 16] * (static_cast<int>(nib | (h << 4)) - 32);
+        }
+    } else if (T == LSG_GGUF_Q2_K) {
+        const int n = c >> 2, quad = c & 3;
+        const float d = half_at(b + 80), dmin = half_at(b + 82);
+        for (int l = 0; l < 32; ++l) {
+            const int s = b[8 * n + 2 * quad + l / 16];
+            const int q = (b[16 + 32 * n + l] >> (2 * quad)) & 3;
+            out[l] = d * (s & 0xF) * q - dmin * (s >> 4);
+        }
+    } else if (T == LSG_GGUF_Q3_K) {
+        const int n = c >> 2, j = c & 3;
+        const float d = half_at(b + 108);
+        for (int l = 0; l < 32; ++l) {
+            const float dl = d * (q3k_scale6(8 * n + 2 * j + l / 16, b + 96) - 32);
+            const int q2 = (b[32 + 32 * n + l] >> (2 * j)) & 3;
+            const int hb = (b[l] >> (4 * n + j)) & 1;
+            out[l] = dl * (q2 - (hb ? 0 : 4));
+        }
+    } else {
+        dequant_block<T>(b, out);  // 32-value blocks: the chunk is the block
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Shared-memory loads by 32-bit shared address
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {

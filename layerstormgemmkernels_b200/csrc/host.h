@@ -28,4 +28,8 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
                 const int32_t* expert_offsets, void* D, int out_f32, const int* tile_expert,
                 const int* tile_mstart, int t_max, void* scratch, size_t scratch_bytes, cudaStream_t s);
 
+int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_rows, int K, int N,
+                void* C, int out_dtype, const float* alphas, int M, const int* tile_expert,
+                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s);
+
 }  // namespace lsg

@@ -1,0 +1,254 @@
+// MoE routing for the grouped GEMMs: router softmax + top-k + renormalisation, the stable
+// permutation that groups (token, slot) pairs by expert, row gather ("permute") and the
+// weighted combine ("unpermute").  The reference has none of this - its grouped operators
+// take rows that are already permuted plus expert_offsets (gguf_grouped_gemm.h:20-24,
+// grouped_gemm.h:24-25) - so the definition these kernels follow is the usual one:
+//   p = softmax(logits, -1);  (w, idx) = topk(p, k);  w /= sum(w)
+//   pairs (token, slot) in token-major order, stably sorted by idx -> permutation
+//   expert_offsets = [0, cumsum(bincount(idx))]
+// Everything stays on the device (no host synchronisation).
+#include "common.cuh"
+#include "host.h"
+
+namespace lsg {
+
+namespace {
+
+constexpr int kMaxTopK = 16;
+
+// One warp per token.  E <= 1024.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int32_t* __restrict__ topk_idx,
+                 float* __restrict__ topk_w) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* row = logits + static_cast<size_t>(t) * E;
+    constexpr int PER = 32;  // up to 1024 experts
+    float v[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = e < E ? row[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = e < E ? expf(v[i] - mx) : -1.0f;  // -1 marks "not a candidate"
+        if (e < E) sum += v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    // k rounds of arg-max over the remaining candidates; ties go to the lower expert id
+    float wsel[kMaxTopK];
+    int isel[kMaxTopK];
+    float wsum = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float best = -2.0f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int e = i * 32 + lane;
+            if (v[i] > best) { best = v[i]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i)
+            if (i * 32 + lane == bi) v[i] = -1.0f;
+        wsel[r] = best * inv;
+        isel[r] = bi;
+        wsum += wsel[r];
+    }
+    if (lane == 0) {
+        for (int r = 0; r < k; ++r) {
+            topk_idx[static_cast<size_t>(t) * k + r] = isel[r];
+            topk_w[static_cast<size_t>(t) * k + r] = wsel[r] / wsum;
+        }
+    }
+}
+
+// counts[e] = number of pairs routed to e.  One CTA per expert.
+__global__ void __launch_bounds__(256)
+moe_count_kernel(const int32_t* __restrict__ idx, int P, int32_t* __restrict__ counts) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int e = blockIdx.x;
+    int c = 0;
+    for (int i = threadIdx.x; i < P; i += blockDim.x) c += (idx[i] == e);
+    __shared__ int red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) s += red[w];
+        counts[e] = s;
+    }
+}
+
+// expert_offsets[0..E] = exclusive scan of counts.  One warp.
+__global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int E, int32_t* __restrict__ offsets) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < E; base += 32) {
+        const int e = base + lane;
+        const int c = e < E ? counts[e] : 0;
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (e < E) offsets[e] = carry + incl - c;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) offsets[E] = carry;
+}
+
+// Stable placement: CTA e walks the pairs in order and gives the j-th pair routed to e
+// the row offsets[e] + j.  perm[row] = pair, inv[pair] = row.
+__global__ void __launch_bounds__(256)
+moe_place_kernel(const int32_t* __restrict__ idx, int P, const int32_t* __restrict__ offsets,
+                 int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __shared__ int wcount[8];
+    __shared__ int base_sh;
+    if (threadIdx.x == 0) base_sh = offsets[e];
+    __syncthreads();
+    for (int start = 0; start < P; start += blockDim.x) {
+        const int i = start + threadIdx.x;
+        const bool hit = i < P && idx[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) wcount[warp] = __popc(m);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += wcount[w];
+        if (hit) {
+            const int row = base_sh + before + __popc(m & ((1u << lane) - 1u));
+            perm[row] = i;
+            inv[i] = row;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int s = 0;
+            for (int w = 0; w < nw; ++w) s += wcount[w];
+            base_sh += s;
+        }
+        __syncthreads();
+    }
+}
+
+// out[row, :] = hidden[perm[row] / k, :]   (bf16 rows, 16-byte vectors)
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int rows,
+                  int vec_per_row, uint4* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(rows) * vec_per_row) return;
+    const int row = static_cast<int>(i / vec_per_row), c = static_cast<int>(i - static_cast<long long>(row) * vec_per_row);
+    out[i] = __ldg(hidden + static_cast<size_t>(perm[row] / k) * vec_per_row + c);
+}
+
+// out[t, :] = sum_s w[t, s] * y[inv[t * k + s], :], slots in order, fp32 accumulate.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ inv,
+                   const float* __restrict__ w, int T, int k, int H, __nv_bfloat16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int hv = H >> 1;
+    if (i >= static_cast<long long>(T) * hv) return;
+    const int t = static_cast<int>(i / hv), c = static_cast<int>(i - static_cast<long long>(t) * hv);
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int s = 0; s < k; ++s) {
+        const int row = inv[static_cast<size_t>(t) * k + s];
+        const float ws = w[static_cast<size_t>(t) * k + s];
+        const __nv_bfloat162 v = reinterpret_cast<const __nv_bfloat162*>(y + static_cast<size_t>(row) * H)[c];
+        a0 = fmaf(ws, __bfloat162float(v.x), a0);
+        a1 = fmaf(ws, __bfloat162float(v.y), a1);
+    }
+    reinterpret_cast<__nv_bfloat162*>(out + static_cast<size_t>(t) * H)[c] = __floats2bfloat162_rn(a0, a1);
+}
+
+}  // namespace
+
+}  // namespace lsg
+
+using namespace lsg;
+
+extern "C" int lsg_moe_route(const float* logits, int num_tokens, int num_experts, int top_k,
+                             int32_t* topk_idx, float* topk_weights, void* stream) {
+    if (num_tokens <= 0) return LSG_OK;
+    if (!logits || !topk_idx || !topk_weights) return fail(LSG_ERR_INVALID, "moe_route: null pointer");
+    if (num_experts < 1 || num_experts > 1024 || top_k < 1 || top_k > kMaxTopK || top_k > num_experts)
+        return fail(LSG_ERR_INVALID, "moe_route: need 1 <= top_k <= min(16, E) and E <= 1024 (E=%d, k=%d)",
+                    num_experts, top_k);
+    LSG_CUDA_TRY(launch_kernel(moe_route_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, logits, num_tokens, num_experts,
+                               top_k, topk_idx, topk_weights));
+    return LSG_OK;
+}
+
+extern "C" int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int top_k, int num_experts,
+                                   int32_t* expert_offsets, int32_t* perm, int32_t* inv_perm,
+                                   int32_t* counts_scratch, void* stream) {
+    if (num_experts < 1) return fail(LSG_ERR_INVALID, "moe_permutation: num_experts must be positive");
+    if (!expert_offsets || !counts_scratch) return fail(LSG_ERR_INVALID, "moe_permutation: null pointer");
+    const int P = num_tokens * top_k;
+    if (P > 0 && (!topk_idx || !perm || !inv_perm)) return fail(LSG_ERR_INVALID, "moe_permutation: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LSG_CUDA_TRY(launch_kernel(moe_count_kernel, dim3(num_experts), dim3(256), 0, s, true, topk_idx, P,
+                               counts_scratch));
+    LSG_CUDA_TRY(launch_kernel(moe_offsets_kernel, dim3(1), dim3(32), 0, s, true,
+                               static_cast<const int32_t*>(counts_scratch), num_experts, expert_offsets));
+    if (P > 0)
+        LSG_CUDA_TRY(launch_kernel(moe_place_kernel, dim3(num_experts), dim3(256), 0, s, true, topk_idx, P,
+                                   static_cast<const int32_t*>(expert_offsets), perm, inv_perm));
+    return LSG_OK;
+}
+
+extern "C" int lsg_moe_permute(const void* hidden_bf16, const int32_t* perm, int rows, int top_k, int H,
+                               void* out_bf16, void* stream) {
+    if (rows <= 0) return LSG_OK;
+    if (!hidden_bf16 || !perm || !out_bf16) return fail(LSG_ERR_INVALID, "moe_permute: null pointer");
+    if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(hidden_bf16) & 15) || (reinterpret_cast<uintptr_t>(out_bf16) & 15))
+        return fail(LSG_ERR_ALIGNMENT, "moe_permute: H must be a multiple of 8 and buffers 16-byte aligned");
+    const int vpr = H / 8;
+    const long long total = static_cast<long long>(rows) * vpr;
+    LSG_CUDA_TRY(launch_kernel(moe_gather_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(hidden_bf16),
+                               perm, top_k, rows, vpr, static_cast<uint4*>(out_bf16)));
+    return LSG_OK;
+}
+
+extern "C" int lsg_moe_unpermute(const void* y_bf16, const int32_t* inv_perm, const float* topk_weights,
+                                 int num_tokens, int top_k, int H, void* out_bf16, void* stream) {
+    if (num_tokens <= 0) return LSG_OK;
+    if (!y_bf16 || !inv_perm || !topk_weights || !out_bf16) return fail(LSG_ERR_INVALID, "moe_unpermute: null pointer");
+    if (H % 2 != 0) return fail(LSG_ERR_INVALID, "moe_unpermute: H must be even");
+    const long long total = static_cast<long long>(num_tokens) * (H / 2);
+    LSG_CUDA_TRY(launch_kernel(moe_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, static_cast<const __nv_bfloat16*>(y_bf16),
+                               inv_perm, topk_weights, num_tokens, top_k, H, static_cast<__nv_bfloat16*>(out_bf16)));
+    return LSG_OK;
+}

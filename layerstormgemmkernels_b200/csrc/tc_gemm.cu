@@ -50,7 +50,8 @@ constexpr int kTcSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /
 struct TcArgs {
     void* C;                  // [rows, ldc] bf16 or f32
     int ldc;
-    int out_f32;
+    int out_f32;              // lsg_dtype of C: 0 bf16, 1 f32, 2 f16
+    const float* alphas;      // optional per-expert output scale (grouped) or single value (dense)
     int K;
     int N;                    // columns of one problem (per expert)
     int n_tiles;              // ceil(N / BN)
@@ -274,14 +275,20 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int row = mstart + warp * 32 + lane;
             const bool row_ok = row < mend;
             const int n0 = j * BN;
+            float alpha = 1.0f;
+            if (a.alphas) alpha = a.tile_expert ? a.alphas[a.tile_expert[t]] : a.alphas[0];
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * BN + c, r);
                 if (row_ok && n0 + c < a.N) {
+                    if (a.alphas) {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
+                    }
                     const size_t o = static_cast<size_t>(row) * a.ldc + n0 + c;
                     const int ncols = min(32, a.N - (n0 + c));
-                    if (a.out_f32) {
+                    if (a.out_f32 == LSG_DTYPE_F32) {
                         float* dst = static_cast<float*>(a.C) + o;
                         if (ncols == 32 && (a.ldc & 3) == 0) {
 #pragma unroll
@@ -292,21 +299,32 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                             for (int q = 0; q < ncols; ++q) dst[q] = __uint_as_float(r[q]);
                         }
                     } else {
-                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.C) + o;
+                        const bool f16 = a.out_f32 == LSG_DTYPE_F16;
+                        uint16_t* dst = static_cast<uint16_t*>(a.C) + o;
                         if (ncols == 32 && (a.ldc & 7) == 0) {
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t p[4];
 #pragma unroll
                                 for (int h = 0; h < 4; ++h) {
-                                    const __nv_bfloat162 v = __floats2bfloat162_rn(
-                                        __uint_as_float(r[8 * q + 2 * h]), __uint_as_float(r[8 * q + 2 * h + 1]));
-                                    p[h] = *reinterpret_cast<const uint32_t*>(&v);
+                                    const float v0 = __uint_as_float(r[8 * q + 2 * h]);
+                                    const float v1 = __uint_as_float(r[8 * q + 2 * h + 1]);
+                                    if (f16) {
+                                        const __half2 v = __floats2half2_rn(v0, v1);
+                                        p[h] = *reinterpret_cast<const uint32_t*>(&v);
+                                    } else {
+                                        const __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
+                                        p[h] = *reinterpret_cast<const uint32_t*>(&v);
+                                    }
                                 }
                                 reinterpret_cast<uint4*>(dst)[q] = make_uint4(p[0], p[1], p[2], p[3]);
                             }
                         } else {
-                            for (int q = 0; q < ncols; ++q) dst[q] = __float2bfloat16_rn(__uint_as_float(r[q]));
+                            for (int q = 0; q < ncols; ++q) {
+                                const float v = __uint_as_float(r[q]);
+                                dst[q] = f16 ? __half_as_ushort(__float2half_rn(v))
+                                             : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+                            }
                         }
                     }
                 }
@@ -329,8 +347,8 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 // ---------------------------------------------------------------------------
 // Operand preparation
 // ---------------------------------------------------------------------------
-// Packed GGUF rows -> fp16 [rows, K].  One thread per block; `row_owner`, when given,
-// skips experts without rows (grouped case).
+// Packed GGUF rows -> fp16 [rows, K].  One thread per 32 values.  With B_ptrs (grouped
+// case) blockIdx.y is the expert and experts without rows are skipped.
 template <int T>
 __global__ void weights_to_f16_kernel(const uint8_t* __restrict__ W, const void* const* __restrict__ B_ptrs,
                                       const int32_t* __restrict__ expert_offsets, __half* __restrict__ out,
@@ -345,13 +363,17 @@ __global__ void weights_to_f16_kernel(const uint8_t* __restrict__ W, const void*
         base = static_cast<const uint8_t*>(B_ptrs[e]);
         if (!base) return;
     }
-    const long long b = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (b >= n_blocks_per_matrix) return;
-    float v[F::VALS];
-    dequant_block<T>(base + b * F::BYTES, v);
-    __half* dst = out + (static_cast<long long>(e) * N * K) + b * F::VALS;
+    // one thread per 32 values: 64 contiguous bytes out per thread, 2 KB per warp
+    constexpr int CPB = F::VALS / 32;
+    const long long ch = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (ch >= n_blocks_per_matrix * CPB) return;
+    const long long b = ch / CPB;
+    const int c = static_cast<int>(ch - b * CPB);
+    float v[32];
+    dequant_chunk32<T>(base + b * F::BYTES, c, v);
+    __half* dst = out + (static_cast<long long>(e) * N * K) + ch * 32;
 #pragma unroll
-    for (int i = 0; i < F::VALS; i += 8) {
+    for (int i = 0; i < 32; i += 8) {
         uint32_t p[4];
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
@@ -435,8 +457,9 @@ template <int T>
 int launch_w16(const void* W, const void* const* B_ptrs, const int32_t* offs, __half* out, int E, int N,
                int K, cudaStream_t s) {
     const long long nb = static_cast<long long>(N) * (K / Fmt<T>::VALS);
-    dim3 grid(static_cast<unsigned>((nb + 63) / 64), E);
-    LSG_CUDA_TRY(launch_kernel(weights_to_f16_kernel<T>, grid, dim3(64), 0, s, true,
+    const long long chunks = nb * (Fmt<T>::VALS / 32);
+    dim3 grid(static_cast<unsigned>((chunks + 255) / 256), E);
+    LSG_CUDA_TRY(launch_kernel(weights_to_f16_kernel<T>, grid, dim3(256), 0, s, true,
                                static_cast<const uint8_t*>(W), B_ptrs, offs, out, N, K, nb));
     return LSG_OK;
 }
@@ -495,7 +518,7 @@ int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void*
     rc = make_map(&tmB, w16, N, K, BN);
     if (rc != LSG_OK) return rc;
     TcArgs a = {};
-    a.C = C; a.ldc = N; a.out_f32 = out_f32; a.K = K; a.N = N;
+    a.C = C; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = (M + BM - 1) / BM;
     a.M = M;
@@ -524,7 +547,7 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
     rc = make_map(&tmB, w16, static_cast<long long>(E) * N, K, BN);
     if (rc != LSG_OK) return rc;
     TcArgs a = {};
-    a.C = D; a.ldc = N; a.out_f32 = out_f32; a.K = K; a.N = N;
+    a.C = D; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = t_max;
     a.M = T;
@@ -532,6 +555,30 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
     a.tile_mstart = tile_mstart;
     a.expert_offsets = expert_offsets;
     a.status = device_status_word();
+    return launch_tc(tmA, tmB, a, a.m_tiles * a.n_tiles, s);
+}
+
+// C = alpha * A16 . B16^T on prepared fp16 operands.  Dense when tile_expert is null
+// (M rows), otherwise grouped through the device-built tile map; B16 then holds E
+// matrices of N rows each.
+int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_rows, int K, int N,
+                void* C, int out_dtype, const float* alphas, int M, const int* tile_expert,
+                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s) {
+    CUtensorMap tmA, tmB;
+    int rc = make_map(&tmA, A16, a_rows, K, BM);
+    if (rc != LSG_OK) return rc;
+    rc = make_map(&tmB, B16, b_rows, K, BN);
+    if (rc != LSG_OK) return rc;
+    TcArgs a = {};
+    a.C = C; a.ldc = N; a.out_f32 = out_dtype; a.alphas = alphas; a.K = K; a.N = N;
+    a.n_tiles = (N + BN - 1) / BN;
+    a.m_tiles = tile_expert ? t_max : (M + BM - 1) / BM;
+    a.M = M;
+    a.tile_expert = tile_expert;
+    a.tile_mstart = tile_mstart;
+    a.expert_offsets = expert_offsets;
+    a.status = device_status_word();
+    if (a.m_tiles <= 0) return LSG_OK;
     return launch_tc(tmA, tmB, a, a.m_tiles * a.n_tiles, s);
 }
 

@@ -1,0 +1,116 @@
+"""The two places where the path shards across the GPUs of one node (one process per GPU,
+torch.distributed over NCCL / NVLink; gloo on CPU for the tests of the host logic).
+
+* Expert-parallel MoE: rank r owns experts [r*E/G, (r+1)*E/G); every rank routes its own
+  tokens, sends each (token, slot) row to the rank that owns its expert (all-to-all with
+  a preceding all-to-all of the per-expert counts), runs the grouped GEMMs on what it
+  received, and the results travel back the same way.
+* Column-split prefill: rank r owns output columns [r*N/G, (r+1)*N/G) of a weight (a
+  contiguous slab of packed rows); activations are replicated; one all-gather assembles
+  the output.
+
+The reference has no multi-GPU code; these functions define that layer.  Nothing here
+touches a peer's memory directly: rows land in local memory through the collective before
+any kernel reads them.  Decode mat-vec and the quantizers do not shard ("replicas only").
+"""
+import torch
+import torch.distributed as dist
+
+
+def expert_range(rank, world, num_experts):
+    """Experts owned by `rank`: a contiguous block, E divisible by world."""
+    if num_experts % world != 0:
+        raise ValueError(f"num_experts={num_experts} must be divisible by world size {world}")
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+class EpPlan:
+    """Everything both directions of the exchange need, derived from the per-expert row
+    counts of every rank (one small all-to-all + one device-to-host copy)."""
+
+    def __init__(self, send_counts, recv_counts, experts_per_rank):
+        # send_counts [world, per]: rows this rank sends, by destination rank and local expert
+        # recv_counts [world, per]: rows this rank receives, by source rank and local expert
+        self.per = experts_per_rank
+        self.send_counts = send_counts
+        self.recv_counts = recv_counts
+        self.send_splits = send_counts.sum(1).tolist()
+        self.recv_splits = recv_counts.sum(1).tolist()
+        self.recv_rows = int(sum(self.recv_splits))
+        # received order is (source, expert, row); the grouped GEMM wants (expert, source, row)
+        world = recv_counts.shape[0]
+        blocks = recv_counts.reshape(-1)                       # [(s, e)] sizes
+        starts = torch.cumsum(blocks, 0) - blocks              # start of block (s, e) in recv order
+        order = torch.arange(world * self.per).reshape(world, self.per).t().reshape(-1)  # (e, s)
+        sizes = blocks[order]
+        src = torch.repeat_interleave(starts[order], sizes)
+        within = torch.arange(int(sizes.sum())) - torch.repeat_interleave(torch.cumsum(sizes, 0) - sizes, sizes)
+        self.to_expert_order = (src + within).to(torch.int64)  # gather index: expert-order row -> recv row
+        self.local_offsets = torch.zeros(self.per + 1, dtype=torch.int32)
+        self.local_offsets[1:] = torch.cumsum(recv_counts.sum(0), 0).to(torch.int32)
+
+
+def make_ep_plan(expert_offsets, num_experts, group=None):
+    """expert_offsets: int32 [E+1] of THIS rank's permuted rows (device or CPU tensor)."""
+    world = dist.get_world_size(group)
+    per = num_experts // world
+    offs = expert_offsets.to(torch.int64)
+    counts = (offs[1:] - offs[:-1]).reshape(world, per).contiguous()
+    recv = torch.empty_like(counts)
+    dist.all_to_all_single(recv, counts, group=group)
+    return EpPlan(counts.cpu(), recv.cpu(), per)
+
+
+def ep_dispatch(rows, plan, group=None):
+    """rows [P, H] permuted by global expert id -> rows of this rank's experts, grouped by
+    local expert: ([R, H], local expert_offsets int32 [per+1] on rows.device)."""
+    out = rows.new_empty((plan.recv_rows, rows.shape[1]))
+    dist.all_to_all_single(out, rows.contiguous(), plan.recv_splits, plan.send_splits, group=group)
+    idx = plan.to_expert_order.to(rows.device)
+    return out.index_select(0, idx), plan.local_offsets.to(rows.device)
+
+
+def ep_combine(expert_rows, plan, group=None):
+    """Inverse of ep_dispatch for the experts' outputs: [R, H'] -> [P, H'] in the sender's order."""
+    idx = plan.to_expert_order.to(expert_rows.device)
+    recv_order = torch.empty_like(expert_rows)
+    recv_order.index_copy_(0, idx, expert_rows)
+    out = expert_rows.new_empty((int(sum(plan.send_splits)), expert_rows.shape[1]))
+    dist.all_to_all_single(out, recv_order, plan.send_splits, plan.recv_splits, group=group)
+    return out
+
+
+def ep_moe_layer(hidden, logits, top_k, num_experts, expert_ffn, route, permutation, permute, unpermute,
+                 group=None):
+    """One expert-parallel MoE layer on this rank's tokens.
+
+    expert_ffn(rows [R,H], local_offsets int32 [per+1]) -> [R,H] applies this rank's experts
+    (gate / up grouped GEMMs, SwiGLU, down grouped GEMM).  route / permutation / permute /
+    unpermute are the routing operators (the CUDA ones on a GPU; torch stand-ins in CPU
+    tests of this host logic)."""
+    idx, w = route(logits, top_k)
+    offs, perm, inv = permutation(idx, num_experts)
+    plan = make_ep_plan(offs, num_experts, group)
+    x = permute(hidden, perm, top_k)
+    rows, local_offs = ep_dispatch(x, plan, group)
+    y = expert_ffn(rows, local_offs)
+    back = ep_combine(y, plan, group)
+    return unpermute(back, inv, w)
+
+
+def column_slab(rank, world, N, align=128):
+    """Output columns [n0, n1) owned by `rank`: contiguous, multiples of `align`."""
+    if N % (world * align) != 0:
+        raise ValueError(f"N={N} must be divisible by world*{align}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def column_split_gather(local_out, group=None):
+    """local_out [M, N/G] of every rank -> [M, N] on every rank (one all-gather)."""
+    world = dist.get_world_size(group)
+    M, n = local_out.shape
+    buf = local_out.new_empty((world * M, n))
+    dist.all_gather_into_tensor(buf, local_out.contiguous(), group=group)
+    return buf.view(world, M, n).permute(1, 0, 2).reshape(M, world * n)

@@ -263,3 +263,104 @@ def gguf_mmq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
                      capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
     capi.check(_lib.lsg_gguf_mmq(ctypes.byref(p), _ptr(ws), ws_bytes, _stream()))
     return C
+
+
+# ---------------------------------------------------------------------------
+# NVFP4 grouped GEMM
+# ---------------------------------------------------------------------------
+def _parse_output_dtype(s):
+    if s in ("bf16", "bfloat16"):
+        return capi.DTYPE_BF16, torch.bfloat16
+    if s in ("fp16", "float16"):
+        return capi.DTYPE_F16, torch.float16
+    raise RuntimeError(f"Unknown output dtype: {s}. Expected 'bf16' or 'fp16'.")
+
+
+def nvfp4_gemm_preprocess(weight_scales, N, K):
+    """fp32 (or fp8) weight scales [N, K/16] -> ue4m3 bytes in the interleaved layout.
+
+    Mirrors nvfp4_gemm_preprocess (csrc/bindings_python.cu:115-145)."""
+    _require(weight_scales.is_cuda, "weight_scales must be on CUDA")
+    _require(weight_scales.dim() == 2 and weight_scales.is_contiguous(),
+             "weight_scales must be contiguous [N, K/16]")
+    _require(weight_scales.size(0) == N and weight_scales.size(1) == K // 16,
+             "weight_scales shape mismatch")
+    src = weight_scales.to(torch.float32).contiguous()
+    out = torch.zeros((_lib.lsg_nvfp4_sf_buffer_bytes(int(N), int(K)),), dtype=torch.uint8,
+                      device=weight_scales.device)
+    capi.check(_lib.lsg_nvfp4_reformat_scales(_ptr(src), _ptr(out), int(N), int(K), _stream()))
+    return out
+
+
+def query_sf_buffer_size_b(M, N, K):
+    return _lib.lsg_nvfp4_sf_buffer_bytes(int(N), int(K))
+
+
+def query_sf_buffer_size_a(M, N, K):
+    return _lib.lsg_nvfp4_sf_buffer_bytes(int(M), int(K))
+
+
+def nvfp4_grouped_gemm(A_base, B_base, D_base, scale_A_base, scale_B_base, alphas, expert_offsets,
+                       sf_offsets, problem_sizes, N, K, output_dtype):
+    """NVFP4 grouped GEMM, in place into D_base; returns D_base.
+
+    Mirrors nvfp4_grouped_gemm (csrc/bindings_python.cu:248-283)."""
+    _require(A_base.is_cuda, "nvfp4_grouped_gemm: A_base must be on CUDA")
+    code, tdtype = _parse_output_dtype(output_dtype)
+    _require(D_base.dtype == tdtype, "nvfp4_grouped_gemm: D_base dtype must match output_dtype")
+    E = expert_offsets.size(0) - 1
+    T = A_base.size(0)
+    ws_bytes = _lib.lsg_nvfp4_grouped_gemm_workspace_bytes(T, E, int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
+    p = capi.Nvfp4GroupedGemmParams(
+        num_experts=E, N=int(N), K=int(K), A_base=A_base.data_ptr(), B_base=B_base.data_ptr(),
+        D_base=D_base.data_ptr(), scale_A_base=scale_A_base.data_ptr(),
+        scale_B_base=scale_B_base.data_ptr(), alphas=alphas.data_ptr(),
+        expert_offsets=expert_offsets.data_ptr(), sf_offsets=sf_offsets.data_ptr(),
+        problem_sizes=problem_sizes.data_ptr() if problem_sizes is not None else None,
+        output_dtype=code, B_ptrs=None, scale_B_ptrs=None)
+    capi.check(_lib.lsg_nvfp4_grouped_gemm(ctypes.byref(p), T, _ptr(ws), ws_bytes, _stream()))
+    return D_base
+
+
+# ---------------------------------------------------------------------------
+# MoE routing (additions; the reference takes pre-permuted rows)
+# ---------------------------------------------------------------------------
+def moe_route(logits, top_k):
+    """fp32 logits [T,E] -> (topk_idx int32 [T,k], topk_weights fp32 [T,k])."""
+    _require(logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous(),
+             "moe_route: logits must be contiguous fp32 on CUDA")
+    T, E = logits.shape
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    capi.check(_lib.lsg_moe_route(_ptr(logits), T, E, int(top_k), _ptr(idx), _ptr(w), _stream()))
+    return idx, w
+
+
+def moe_permutation(topk_idx, num_experts):
+    """-> (expert_offsets int32 [E+1], perm int32 [T*k], inv_perm int32 [T*k])."""
+    T, k = topk_idx.shape
+    dev = topk_idx.device
+    offs = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
+    perm = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
+    scratch = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+    capi.check(_lib.lsg_moe_permutation(_ptr(topk_idx), T, k, int(num_experts), _ptr(offs), _ptr(perm),
+                                        _ptr(inv), _ptr(scratch), _stream()))
+    return offs, perm, inv
+
+
+def moe_permute(hidden, perm, top_k):
+    rows, H = perm.numel(), hidden.size(1)
+    out = torch.empty((rows, H), dtype=torch.bfloat16, device=hidden.device)
+    capi.check(_lib.lsg_moe_permute(_ptr(hidden), _ptr(perm), rows, int(top_k), H, _ptr(out), _stream()))
+    return out
+
+
+def moe_unpermute(y, inv_perm, topk_weights):
+    T, k = topk_weights.shape
+    H = y.size(1)
+    out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
+    capi.check(_lib.lsg_moe_unpermute(_ptr(y), _ptr(inv_perm), _ptr(topk_weights), T, k, H, _ptr(out),
+                                      _stream()))
+    return out

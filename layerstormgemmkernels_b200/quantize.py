@@ -175,3 +175,39 @@ def random_gguf_weight(name, N, K, seed):
     if name == "MXFP4":
         w[:, :, 0] = 121
     return w.reshape(N, nb * bb)
+
+
+E2M1_TABLE = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
+                       -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=np.float32)
+
+
+def _to_e4m3_f32(x):
+    """float32 array -> nearest e4m3 value as float32 (torch's float8_e4m3fn rounding)."""
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).to(torch.float8_e4m3fn).float().numpy()
+
+
+def quantize_nvfp4(w):
+    """float [N,K] -> (uint8 [N,K/2] codes, float32 [N,K/16] e4m3-valued group scales,
+    float32 global scale).  Restates the reference's quantize_to_nvfp4
+    (tests/test_reference.py:162-199): global scale amax/6, group scale
+    amax_g/(6*global) rounded to e4m3, nearest table entry (first on ties)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    N, K = w.shape
+    assert K % 16 == 0
+    scale2 = np.float32(max(np.abs(w).max() / np.float32(6.0), np.float32(1e-12)))
+    g = w.reshape(N, K // 16, 16)
+    raw = np.abs(g).max(-1) / (scale2 * np.float32(6.0))
+    raw = np.clip(raw, np.float32(1e-12), np.float32(448.0)).astype(np.float32)
+    sc = np.maximum(_to_e4m3_f32(raw), np.float32(1e-12)).astype(np.float32)
+    local = w / (np.repeat(sc, 16, axis=1) * scale2)
+    idx = np.abs(local[..., None] - E2M1_TABLE).argmin(-1).astype(np.uint8)
+    pairs = idx.reshape(N, K // 2, 2)
+    return (pairs[:, :, 0] | (pairs[:, :, 1] << 4)).astype(np.uint8), sc, scale2
+
+
+def dequantize_nvfp4(codes_u8, scales, scale2=1.0):
+    """Inverse of quantize_nvfp4 (reference: ref_nvfp4_dequant, tests/test_reference.py:107-128)."""
+    N, half = codes_u8.shape
+    idx = np.stack([codes_u8 & 0xF, codes_u8 >> 4], -1).reshape(N, half * 2)
+    return E2M1_TABLE[idx] * np.repeat(np.asarray(scales, np.float32), 16, axis=1) * np.float32(scale2)

@@ -1,0 +1,93 @@
+"""GPU tests of the NVFP4 grouped GEMM.  The reference's arithmetic for this operator lives
+in NVIDIA CUTLASS (v4.4.2, sm_120 only; not vendored in the reference), so parity is
+anchored on the reference's own tests for the operator (tests/test_kernels.py:273-317,
+543-652) and on its Python definition ref_nvfp4_dequant + matmul."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from layerstormgemmkernels_b200 import quantize as Q
+from test_oracle_quant import _decode_grouped
+
+pytestmark = pytest.mark.gpu
+UE4M3_ONE = 0x38
+TOL = 2e-2        # north-star bound for NVFP4 GEMM outputs
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from layerstormgemmkernels_b200 import ops as _ops, capi
+    yield _ops
+    assert capi.device_status() == 0
+
+
+def bits_of(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_known_answer_all_half(ops):
+    """tests/test_kernels.py:273-317: every value 0.5, scales 1 -> K * 0.25."""
+    E, M_per, N, K = 4, 128, 128, 128
+    T = E * M_per
+    A = torch.full((T, K // 2), 0x11, dtype=torch.uint8, device="cuda")
+    B = torch.full((E * N, K // 2), 0x11, dtype=torch.uint8, device="cuda")
+    sA = torch.full((T * 8,), UE4M3_ONE, dtype=torch.uint8, device="cuda")
+    sB = torch.full((E * N * 8,), UE4M3_ONE, dtype=torch.uint8, device="cuda")
+    offs = torch.tensor([i * M_per for i in range(E + 1)], dtype=torch.int32, device="cuda")
+    ps = torch.tensor([[M_per, N, K]] * E, dtype=torch.int32, device="cuda")
+    alphas = torch.ones(E, dtype=torch.float32, device="cuda")
+    for dt, td in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+        D = torch.zeros(T, N, dtype=td, device="cuda")
+        out = ops.nvfp4_grouped_gemm(A, B, D, sA, sB, alphas, offs, offs, ps, N, K, dt)
+        assert out.data_ptr() == D.data_ptr()
+        assert torch.equal(D.float(), torch.full((T, N), K * 0.25, device="cuda"))
+
+
+@pytest.mark.parametrize("N,K,offs,with_is", [
+    (128, 256, [0, 5, 5, 133, 163], False),       # reference pairing test: ragged, one empty
+    (128, 256, [0, 64, 128], True),               # per-expert input_scales (TRT-LLM scheme)
+    (256, 1024, [0, 300, 301, 700], False),
+    (384, 512, [0, 0, 17], False),
+])
+def test_quantizer_to_gemm_pairing(ops, N, K, offs, with_is):
+    E, T = len(offs) - 1, offs[-1]
+    g = torch.Generator().manual_seed(42 + N)
+    scale = 1e-3 if with_is else 1.0
+    x = (torch.randn(T, K, generator=g) * scale).to(torch.bfloat16).cuda()
+    offs_t = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    codes, sbufs, wdeq, alphas = [], [], [], []
+    isc = None
+    if with_is:
+        xf = x.float().cpu().numpy()
+        isc = torch.tensor([np.abs(xf[offs[e]:offs[e + 1]]).max() / (448.0 * 6.0) for e in range(E)],
+                           dtype=torch.float32, device="cuda")
+    for e in range(E):
+        w = (torch.randn(N, K, generator=g) * (0.05 if e % 2 else 1.0)).numpy()
+        c, sc, s2 = Q.quantize_nvfp4(w)
+        codes.append(torch.from_numpy(c).cuda())
+        sbufs.append(ops.nvfp4_gemm_preprocess(torch.from_numpy(sc).cuda(), N, K))
+        wdeq.append(Q.dequantize_nvfp4(c, sc, 1.0).astype(np.float64))
+        alphas.append(float(s2) * (float(isc[e]) if with_is else 1.0))
+    A_packed, A_scales, sf = ops.bf16_to_nvfp4_grouped(x, offs_t, isc)
+    B = torch.cat(codes, 0)
+    sB = torch.cat(sbufs, 0)
+    al = torch.tensor(alphas, dtype=torch.float32, device="cuda")
+    ps = torch.tensor([[offs[e + 1] - offs[e], N, K] for e in range(E)], dtype=torch.int32, device="cuda")
+    D = torch.zeros(T, N, dtype=torch.bfloat16, device="cuda")
+    ops.nvfp4_grouped_gemm(A_packed, B, D, A_scales, sB, al, offs_t, sf, ps, N, K, "bf16")
+    # oracle: dequantized (bit-exact) activation codes x dequantized weights, float64
+    xa = _decode_grouped(A_packed.cpu().numpy(), A_scales.cpu().numpy(), sf.cpu().numpy(), offs, K).astype(np.float64)
+    got = D.float().cpu().numpy()
+    xf = x.float().cpu().numpy()
+    for e in range(E):
+        s, t = offs[e], offs[e + 1]
+        if s == t:
+            continue
+        ref = (xa[s:t] @ wdeq[e].T) * np.float64(np.float32(alphas[e]))
+        assert np.abs(got[s:t] - ref).max() <= (2.0 ** -8 + 1e-5) * np.abs(ref).max()   # bf16 rounding only
+        assert np.abs(got[s:t] - ref).max() <= TOL * np.abs(ref).max()
+        # and the reference test's own criterion: cosine > 0.99 vs bf16 activations x dequantized weights
+        full = xf[s:t] @ (wdeq[e].T * (alphas[e] / (float(isc[e]) if with_is else 1.0)))
+        cos = (full * got[s:t]).sum() / np.sqrt((full * full).sum() * (got[s:t] ** 2).sum())
+        assert cos > 0.99

@@ -129,3 +129,16 @@ def test_nvfp4_tiny_values_hit_the_scale_floor_and_input_scales_lift_it():
 
     isc = np.array([np.abs(xb[offs[e]:offs[e + 1]]).max() / (448.0 * 6.0) for e in range(2)], np.float32)
     assert cos(isc) > 0.99 and cos(isc) > cos(None)
+
+
+def test_host_nvfp4_weight_quantizer_matches_reference(golden_dir):
+    from layerstormgemmkernels_b200 import quantize as Q
+    z = np.load(os.path.join(golden_dir, "nvfp4_reference.npz"))
+    codes, sc, s2 = Q.quantize_nvfp4(z["w"])
+    np.testing.assert_array_equal(codes, z["w_u8"])
+    np.testing.assert_array_equal(sc, z["w_scale"])
+    assert s2 == z["w_scale2"]
+    deq = Q.dequantize_nvfp4(codes, sc, s2)
+    np.testing.assert_allclose(deq, z["dequant"], rtol=1e-6, atol=0)
+    np.testing.assert_allclose(z["x"].astype(np.float64) @ deq.astype(np.float64).T, z["gemm"], rtol=0,
+                               atol=1e-5 * np.abs(z["gemm"]).max())
