@@ -201,12 +201,27 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--type", default="Q4_K", choices=["Q4_K", "Q6_K", "Q8_0", "Q4_0"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="mmvq", choices=["mmvq", "moe", "prefill"],
+                    help="mmvq: the headline decode layer (default); moe: expert-parallel grouped "
+                         "GEMM layer (128 experts, top-8, H=2048, I=768, Q4_K); prefill: Q4_K "
+                         "14336x4096 GEMM, column-split across ranks")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens (moe) or rows M (prefill)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.workload != "mmvq":
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the CPU reference arm is implemented for the headline mmvq workload only"}))
+            return
+        from layerstormgemmkernels_b200 import bench_extra
+        bench_extra.run(args, rank, local_rank, world)
+        return
 
     if args.impl == "reference":
         if args.steps > 5:

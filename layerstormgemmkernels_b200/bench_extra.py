@@ -1,0 +1,168 @@
+"""Secondary benchmark workloads behind `bench.py --workload moe|prefill` (same JSON line as
+the headline workload): the expert-parallel MoE layer and the column-split prefill GEMM.
+"""
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import capi, ops, quantize as Q, distributed as D
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+    return 1400.0, "fallback"
+
+
+def _time_steps(step, steps, warmup, world, dev):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def run(args, rank, local_rank, world):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    steps = min(args.steps, 200)
+    warmup = max(3, min(args.warmup, 10))
+    if args.workload == "moe":
+        line = _moe(args, rank, world, dev, steps, warmup)
+    else:
+        line = _prefill(args, rank, world, dev, steps, warmup)
+    status = capi.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel reported a timed-out device-side wait (code {status})")
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _moe(args, rank, world, dev, steps, warmup):
+    E, k, H, I = 128, 8, 2048, 768
+    T_total = args.tokens
+    if T_total % world != 0:
+        raise SystemExit("--tokens must be divisible by the number of GPUs")
+    T = T_total // world                       # strong scaling: the batch is split
+    t = capi.Q4_K
+    e0, e1 = D.expert_range(rank, world, E)
+    # eight distinct experts quantized from N(0, 0.02) seed 3, tiled over the rank's experts
+    g = torch.Generator().manual_seed(3)
+    base = []
+    for _ in range(8):
+        base.append((Q.quantize_q4_k((torch.randn(I, H, generator=g) * 0.02).numpy()),
+                     Q.quantize_q4_k((torch.randn(I, H, generator=g) * 0.02).numpy()),
+                     Q.quantize_q4_k((torch.randn(H, I, generator=g) * 0.02).numpy())))
+    gate_w = [torch.from_numpy(base[e % 8][0]).to(dev) for e in range(e0, e1)]
+    up_w = [torch.from_numpy(base[e % 8][1]).to(dev) for e in range(e0, e1)]
+    down_w = [torch.from_numpy(base[e % 8][2]).to(dev) for e in range(e0, e1)]
+    ptr = lambda ws: torch.tensor([w.data_ptr() for w in ws], dtype=torch.int64, device=dev)
+    gate_p, up_p, down_p = ptr(gate_w), ptr(up_w), ptr(down_w)
+    gg = torch.Generator().manual_seed(1000 + rank)
+    hidden = torch.randn(T, H, generator=gg).to(torch.bfloat16).to(dev)
+    logits = torch.randn(T, E, generator=gg).to(dev)
+    hidden_host = hidden.cpu().pin_memory()
+    logits_host = logits.cpu().pin_memory()
+
+    def ffn(rows, offs):
+        gt = ops.gguf_grouped_gemm(rows, offs, gate_p, t, 1, I, H, 0)
+        u = ops.gguf_grouped_gemm(rows, offs, up_p, t, 1, I, H, 0)
+        act = torch.nn.functional.silu(gt.float()).mul_(u.float()).to(torch.bfloat16)
+        return ops.gguf_grouped_gemm(act, offs, down_p, t, 1, H, I, 0)
+
+    def layer(h, lg):
+        if world == 1:
+            idx, w = ops.moe_route(lg, k)
+            offs, perm, inv = ops.moe_permutation(idx, E)
+            return ops.moe_unpermute(ffn(ops.moe_permute(h, perm, k), offs), inv, w)
+        return D.ep_moe_layer(h, lg, k, E, ffn, ops.moe_route, ops.moe_permutation, ops.moe_permute,
+                              ops.moe_unpermute)
+
+    ms = _time_steps(lambda: layer(hidden, logits), steps, warmup, world, dev)
+
+    def e2e_step():
+        h = hidden_host.to(dev, non_blocking=True)
+        lg = logits_host.to(dev, non_blocking=True)
+        return layer(h, lg).cpu()
+    e2e_ms = _time_steps(e2e_step, min(steps, 20), 3, world, dev)
+
+    flops = 6.0 * T_total * k * H * I
+    peak, kind = _peak_tflops()
+    value = flops / (ms * 1e-3) / 1e12
+    return {
+        "metric": "moe_grouped_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 (tcgen05, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"MoE layer, 128 experts top-8, H=2048, I=768, Q4_K, {T_total} tokens: "
+                               "route, permute, gate/up/down grouped GEMMs, SwiGLU, combine",
+                   "tokens": T_total, "parallelism": f"ep{world}" if world > 1 else "single",
+                   "l2_defeat": "339 MB of expert weights per rank set exceed the 126 MB L2"},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                     "frac": value / world / peak, "peak_kind": kind, "traffic": None},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2},
+        "gpu_launches": None,
+    }
+
+
+def _prefill(args, rank, world, dev, steps, warmup):
+    N, K, M = 14336, 4096, args.tokens
+    t = capi.Q4_K
+    n0, n1 = D.column_slab(rank, world, N)
+    g = torch.Generator().manual_seed(2)
+    w = (torch.randn(N, K, generator=g) * 0.02).numpy()
+    slab = torch.from_numpy(Q.quantize_q4_k(w[n0:n1])).to(dev)
+    A = torch.randn(M, K, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(dev)
+    A_host = A.cpu().pin_memory()
+
+    def step(a=A):
+        out = ops.gguf_mmq(a, slab, t, n1 - n0, K)
+        return out if world == 1 else D.column_split_gather(out)
+
+    ms = _time_steps(step, steps, warmup, world, dev)
+    e2e_ms = _time_steps(lambda: step(A_host.to(dev, non_blocking=True)).cpu(), min(steps, 10), 3, world, dev)
+    flops = 2.0 * M * N * K
+    peak, kind = _peak_tflops()
+    value = flops / (ms * 1e-3) / 1e12
+    return {
+        "metric": "q4_k_mmq_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 (tcgen05, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"Q4_K 14336x4096 prefill GEMM, M={M}, Q8_1 activations",
+                   "parallelism": f"column-split x{world} + all-gather" if world > 1 else "single",
+                   "l2_defeat": "operands (fp16 weights 117 MB + outputs 117 MB at M=4096) exceed L2"},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
+                     "frac": value / world / peak, "peak_kind": kind, "traffic": None},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
+        "gpu_launches": None,
+    }

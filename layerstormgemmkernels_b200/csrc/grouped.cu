@@ -89,8 +89,7 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
         return fail(LSG_ERR_WORKSPACE, "GGUF grouped int: workspace too small (have %zu, need %zu)",
                     ws_bytes, w.total);
     uint8_t* base = static_cast<uint8_t*>(ws);
-    int rc = quantize_q8_1(p->A_base, base, T, p->K, s, true);
-    if (rc != LSG_OK) return rc;
+    int rc = LSG_OK;
 
     // As the reference (gguf_grouped_int.cu:947-950): tensor cores when there are more
     // than 8 rows per expert on average, unless forced either way.  The tensor-core path
@@ -113,6 +112,8 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
                            p->out_dtype == LSG_DTYPE_F32, tile_expert, tile_mstart, t_max,
                            base + w.total, ws_bytes - w.total, s);
     }
+    rc = quantize_q8_1(p->A_base, base, T, p->K, s, true);
+    if (rc != LSG_OK) return rc;
     int* active = reinterpret_cast<int*>(base + w.active_off);
     int* seg = reinterpret_cast<int*>(base + w.seg_off);
     rc = build_active_expert_list(static_cast<const int32_t*>(p->expert_offsets), p->num_experts, w.cap,

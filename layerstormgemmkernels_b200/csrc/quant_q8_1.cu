@@ -4,8 +4,8 @@
 // (csrc/sm120/gemm/gguf/gguf_mmvq.cu:42-63): d = amax / 127 as an IEEE fp32
 // divide, q = rn(x / d) with the un-rounded fp32 d, the stored d rounded to
 // fp16, and the block sum taken by the same 16-8-4-2-1 xor butterfly in fp32
-// before rounding to fp16.  One warp owns one block (lane = element), eight
-// blocks per CTA; the reference launches one 32-thread CTA per block.
+// before rounding to fp16.  Four lanes own one block (eight values = one 16-byte
+// load each); the reference launches one 32-thread CTA per block.
 #include "common.cuh"
 #include "formats.cuh"
 
@@ -13,32 +13,67 @@ namespace lsg {
 
 namespace {
 
-constexpr int kQuantWarps = 8;
+constexpr int kQuantThreads = 256;
 
-__global__ void __launch_bounds__(kQuantWarps * 32)
+// q = rn(fl(x / d)) without a division per element: x * fl(1/d) is within 2.3e-5 of
+// fl(x/d) for |x/d| <= 127, so rounding it gives the same integer unless it lies within
+// 1e-4 of a half-integer; only then is the true quotient formed.
+__device__ __forceinline__ int q8_round(float x, float d, float rcp) {
+    const float t = x * rcp;
+    int k = __float2int_rn(t);
+    if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x / d);
+    return k;
+}
+
+// Four lanes per 32-value block, eight consecutive values (one 16-byte load) per lane.
+// The block sum is formed in exactly the order of the reference's xor butterfly
+// (offsets 16, 8, 4, 2, 1 over lanes = elements): element pairs (i, i+16), then
+// (i, i+8), (i, i+4), (i, i+2), (i, i+1).  With eight values per lane the first two
+// levels are lane exchanges (lane+2, lane+1) and the last three are in-register.
+__global__ void __launch_bounds__(kQuantThreads)
 quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y,
                      long long n_blocks) {
     pdl_launch_dependents();
     pdl_wait_prior();  // x may be the output of the previous kernel in the stream
-    const int lane = threadIdx.x & 31;
-    const long long blk = static_cast<long long>(blockIdx.x) * kQuantWarps + (threadIdx.x >> 5);
-    if (blk >= n_blocks) return;
-
-    const float xi = __bfloat162float(x[blk * 32 + lane]);
-    float amax = fabsf(xi);
-    float sum = xi;
+    const long long task = static_cast<long long>(blockIdx.x) * kQuantThreads + threadIdx.x;
+    const bool live = task < n_blocks * 4;
+    const long long tk = live ? task : 0;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
+    float v[8];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
-    const float d = amax / 127.0f;
-    const int q = (amax == 0.0f) ? 0 : __float2int_rn(xi / d);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // butterfly-ordered sum
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = v[i] + __shfl_xor_sync(0xffffffffu, v[i], 2);   // (i, i+16)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = s[i] + __shfl_xor_sync(0xffffffffu, s[i], 1);   // (i, i+8)
+    const float c0 = s[0] + s[4], c1 = s[1] + s[5], c2 = s[2] + s[6], c3 = s[3] + s[7];  // (i, i+4)
+    const float sum = (c0 + c2) + (c1 + c3);                                             // (i, i+2), (i, i+1)
+    if (!live) return;
 
-    uint8_t* out = y + blk * kQ8_1Bytes;
-    reinterpret_cast<int8_t*>(out + 4)[lane] = static_cast<int8_t>(q);
-    if (lane == 0) {
-        *reinterpret_cast<__half2*>(out) = __halves2half2(__float2half(d), __float2half(sum));
+    const float d = amax / 127.0f;
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    uint32_t q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = static_cast<uint32_t>(q8_round(v[i], d, rcp)) & 0xFFu;
+    const long long blk = tk >> 2;
+    const int part = static_cast<int>(tk & 3);
+    uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
+    out[1 + 2 * part] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+    out[2 + 2 * part] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+    if (part == 0) {
+        const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
+        out[0] = *reinterpret_cast<const uint32_t*>(&ds);
     }
 }
 
@@ -51,10 +86,12 @@ int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t
     const long long n_blocks = static_cast<long long>(M) * (K / 32);
     if (n_blocks == 0) return LSG_OK;
     if (!x_bf16 || !q8_1_out) return fail(LSG_ERR_INVALID, "quantize_q8_1: null pointer");
-    const long long grid = (n_blocks + kQuantWarps - 1) / kQuantWarps;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(q8_1_out) & 3))
+        return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1: input must be 16-byte and output 4-byte aligned");
+    const long long grid = (n_blocks * 4 + kQuantThreads - 1) / kQuantThreads;
     if (grid > 0x7fffffffLL) return fail(LSG_ERR_INVALID, "quantize_q8_1: too many blocks");
     LSG_CUDA_TRY(launch_kernel(quantize_q8_1_kernel, dim3(static_cast<unsigned>(grid)),
-                               dim3(kQuantWarps * 32), 0, stream, pdl,
+                               dim3(kQuantThreads), 0, stream, pdl,
                                static_cast<const __nv_bfloat16*>(x_bf16),
                                static_cast<uint8_t*>(q8_1_out), n_blocks));
     return LSG_OK;

@@ -385,22 +385,48 @@ __global__ void weights_to_f16_kernel(const uint8_t* __restrict__ W, const void*
 }
 
 // bf16 x[M,K] -> fp16 of the Q8_1 round trip: d_h * rn(x / d) with d = amax/127 per 32
-// values and d_h its fp16 rounding (what the integer paths multiply by).
+// values and d_h its fp16 rounding (what the integer paths multiply by).  Four lanes per
+// block, eight values per lane.
 __global__ void __launch_bounds__(256)
 x_q8_1_roundtrip_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int lane = threadIdx.x & 31;
-    const long long blk = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (blk >= n_blocks) return;
-    const float xi = __bfloat162float(x[blk * 32 + lane]);
-    float amax = fabsf(xi);
+    const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const bool live = task < n_blocks * 4;
+    const long long tk = live ? task : 0;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
+    float v[8];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) return;
     const float d = amax / 127.0f;
-    const int q = (amax == 0.0f) ? 0 : __float2int_rn(xi / d);
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
     const float dh = __half2float(__float2half(d));
-    out[blk * 32 + lane] = __float2half(dh * static_cast<float>(q));
+    uint32_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float r[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float t = v[2 * i + h] * rcp;
+            int k = __float2int_rn(t);
+            // same integer as rn(fl(x / d)): see quantize_q8_1_kernel
+            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + h] / d);
+            r[h] = dh * static_cast<float>(k);
+        }
+        const __half2 hv = __floats2half2_rn(r[0], r[1]);
+        p[i] = *reinterpret_cast<const uint32_t*>(&hv);
+    }
+    reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
 }
 
 // ---------------------------------------------------------------------------
@@ -482,7 +508,7 @@ int weights_to_f16(int type, const void* W, const void* const* B_ptrs, const int
 int x_to_f16(const void* x_bf16, __half* out, long long rows, int K, cudaStream_t s) {
     const long long nb = rows * (K / 32);
     if (nb == 0) return LSG_OK;
-    LSG_CUDA_TRY(launch_kernel(x_q8_1_roundtrip_f16_kernel, dim3(static_cast<unsigned>((nb + 7) / 8)), dim3(256),
+    LSG_CUDA_TRY(launch_kernel(x_q8_1_roundtrip_f16_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256),
                                0, s, true, static_cast<const __nv_bfloat16*>(x_bf16), out, nb));
     return LSG_OK;
 }
