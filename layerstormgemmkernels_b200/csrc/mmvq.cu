@@ -15,7 +15,7 @@ namespace {
 // override them.
 MmvqTune& tuning() {
     static MmvqTune t = [] {
-        MmvqTune v{7, 1, 16, 2, 0};
+        MmvqTune v{15, 1, 24, 1, 0};
         if (const char* e = getenv("LSG_MMVQ_WARPS")) v.warps = atoi(e);
         if (const char* e = getenv("LSG_MMVQ_CTAS")) v.ctas = atoi(e);
         if (const char* e = getenv("LSG_MMVQ_STAGE_KB")) v.stage_kb = atoi(e);

@@ -90,6 +90,9 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pd
         // are enough to occupy every consumer warp.
         rw = (lanes == 32 && a.row_bytes * 2 * tn.warps > (smem_cap * 3) / 4) ? 1 : 2;
         int slab_rows = tn.stage_kb * 1024 / a.row_bytes;
+        // whole row groups per slab, so that no lane group idles on a ragged slab end
+        const int rpp = (32 / lanes) * rw;
+        if (slab_rows > rpp) slab_rows -= slab_rows % rpp;
         if (slab_rows < 1) slab_rows = 1;
         if (slab_rows > rows_per_cta) slab_rows = rows_per_cta;
         int stage_bytes = ((slab_rows * a.row_bytes + 47 + 127) / 128) * 128;

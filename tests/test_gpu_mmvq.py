@@ -208,7 +208,7 @@ def test_mmvq_results_do_not_depend_on_launch_geometry(ops, warps, ctas, stage_k
             A = torch.randn(M, K, generator=torch.Generator().manual_seed(N)).to(torch.bfloat16).cuda()
             W = Q.random_gguf_weight(name, N, K, seed=K + N)
             Wd = torch.from_numpy(W).cuda()
-            capi.check(capi.lib.lsg_mmvq_set_tuning(7, 1, 16, 2, 0))
+            capi.check(capi.lib.lsg_mmvq_set_tuning(15, 1, 24, 1, 0))
             base = ops.gguf_mmvq(A, Wd, t, N, K, out_dtype=torch.float32)
             capi.check(capi.lib.lsg_mmvq_set_tuning(warps, ctas, stage_kib, share, 0))
             for _ in range(3):
@@ -219,4 +219,4 @@ def test_mmvq_results_do_not_depend_on_launch_geometry(ops, warps, ctas, stage_k
                 assert rel_err(got.cpu().numpy(), ref) <= TOL_F32
         assert capi.device_status() == 0
     finally:
-        capi.check(capi.lib.lsg_mmvq_set_tuning(7, 1, 16, 2, 0))
+        capi.check(capi.lib.lsg_mmvq_set_tuning(15, 1, 24, 1, 0))
