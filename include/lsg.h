@@ -165,6 +165,17 @@ LSG_API size_t lsg_gguf_mmq_workspace_bytes(int M, int N, int K);
 LSG_API int lsg_gguf_mmq(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* How the tensor-core GEMMs (lsg_gguf_mmq and the grouped GEMM's tensor-core route) obtain
+ * their fp16 weights, process-wide:
+ *   0  a preparation kernel expands the packed matrix into workspace first;
+ *   1  (default) types with a register-staged decoder (Q4_K) are decoded inside the GEMM
+ *      kernel and never expanded; the others as in 0;
+ *   2  every type is decoded inside the GEMM kernel.
+ * A negative mode restores the default (or the LSG_TC_FUSED environment variable).  Results
+ * agree between the modes to the fp16 rounding of the weights.  No counterpart in the
+ * reference. */
+LSG_API int lsg_mmq_set_weight_path(int mode);
+
 /* ------------------------------------------------------------------------ */
 /* GGUF dequant GEMM (lossless-activation golden strategy)                  */
 /* ------------------------------------------------------------------------ */

@@ -96,6 +96,7 @@ def _load():
         "lsg_gguf_mmvq_q8_1": (ci, [ctypes.POINTER(GgufMmvqParams), vp, vp]),
         "lsg_gguf_mmvq_noalloc": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_mmvq_set_tuning": (ci, [ci, ci, ci, ci, ci]),
+        "lsg_mmq_set_weight_path": (ci, [ci]),
         "lsg_dynamic_fp8_quant": (ci, [ctypes.POINTER(DynamicFp8QuantParams), vp]),
         "lsg_bf16_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
         "lsg_silu_mul_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),

@@ -72,7 +72,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 2000u) {
     uint32_t ok;
     // The third operand is a suspend-time hint in nanoseconds: the thread sleeps in
     // hardware until the phase completes or the hint runs out, instead of polling
@@ -84,28 +84,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(2000u)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
 
-// Time limit of every device-side wait.  Nothing in these kernels legitimately
-// waits longer than a few microseconds; 0.2 s only ever elapses when a
-// copy or an MMA was mis-issued, and then the kernel reports and returns.
-constexpr uint64_t kWaitLimitNs = 200000000ull;
+// Time limit of every device-side wait, in SM clock cycles (about 0.2 s at 2 GHz).  Nothing
+// in these kernels legitimately waits longer than a few microseconds; the limit only ever
+// runs out when a copy or an MMA was mis-issued, and then the kernel reports and returns.
+// The SM-local cycle counter is used because it is read in a few cycles; the global
+// nanosecond timer is not, and a read of it would sit on the critical path of every wait
+// that does not succeed at once.
+constexpr long long kWaitLimitCycles = 400000000ll;
+
+__device__ __forceinline__ long long sm_clock() {
+    long long t;
+    asm volatile("mov.u64 %0, %clock64;" : "=l"(t));
+    return t;
+}
 
 // Waits for the phase with the given parity to complete.  Returns false (after
 // recording `code` in *status) when the time limit runs out.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  unsigned int* status, unsigned int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+                                                  unsigned int* status, unsigned int code,
+                                                  uint32_t hint_ns = 2000u) {
+    if (mbar_try_wait(bar, parity, hint_ns)) return true;
+    const long long t0 = sm_clock();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait(bar, parity, hint_ns)) return true;
         }
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (sm_clock() - t0 > kWaitLimitCycles) {
             if (status) atomicCAS(status, 0u, code);
             return false;
         }

@@ -98,11 +98,24 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
     bool use_mmq = (T / p->num_experts) > 8;
     if (force == LSG_GGUF_FORCE_MMVQ) use_mmq = false;
     if (force == LSG_GGUF_FORCE_MMQ) use_mmq = true;
+    int* tile_expert = reinterpret_cast<int*>(base + w.tile_off);
+    // Preferred: weights decoded inside the GEMM (needs only the fp16 activations as scratch).
+    if (use_mmq && tc_fused_available(p->type) &&
+        ws_bytes >= w.total + tc_fused_grouped_scratch_bytes(T, p->num_experts, p->N, p->K)) {
+        const int tile_m = tc_fused_grouped_tile_m(T, p->num_experts);   // 64, 128 or 256
+        const int t_max = (T + tile_m - 1) / tile_m + p->num_experts;
+        int* tile_mstart = tile_expert + t_max;  // t_max(tile_m >= 64) <= t_max(64): fits the reserved map
+        rc = build_mmq_tile_map(static_cast<const int32_t*>(p->expert_offsets), p->num_experts, tile_m,
+                                t_max, tile_expert, tile_mstart, s);
+        if (rc != LSG_OK) return rc;
+        return tc_fused_grouped(p->type, T, p->num_experts, p->N, p->K, p->A_base, p->B_ptrs,
+                                static_cast<const int32_t*>(p->expert_offsets), p->D_base, p->out_dtype,
+                                tile_expert, tile_mstart, t_max, tile_m, base + w.total, ws_bytes - w.total, s);
+    }
     const size_t mmq_need = mmq_scratch_bytes(T, p->K, p->num_experts, p->N);
     if (use_mmq && ws_bytes >= w.total + mmq_need && (p->K % 8) == 0) {
         const int tile_m = 128;
         const int t_max = (T + tile_m - 1) / tile_m + p->num_experts;
-        int* tile_expert = reinterpret_cast<int*>(base + w.tile_off);
         int* tile_mstart = tile_expert + t_max;  // t_max(128) <= t_max(64): fits the reserved map
         rc = build_mmq_tile_map(static_cast<const int32_t*>(p->expert_offsets), p->num_experts, tile_m,
                                 t_max, tile_expert, tile_mstart, s);

@@ -32,4 +32,17 @@ int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_
                 void* C, int out_dtype, const float* alphas, int M, const int* tile_expert,
                 const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s);
 
+// Tensor-core GEMM with in-kernel weight decoding (tc_fused.cu).
+bool tc_fused_available(int type);
+bool tc_fused_forced();   // weight path 2: every call takes the fused kernel
+size_t tc_fused_dense_scratch_bytes(int M, int N, int K);
+int tc_fused_grouped_tile_m(long long T, int E);
+size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K);
+int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
+                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s);
+int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, const void* const* B_ptrs,
+                     const int32_t* expert_offsets, void* D, int out_dtype, const int* tile_expert,
+                     const int* tile_mstart, int t_max, int tile_m, void* scratch, size_t scratch_bytes,
+                     cudaStream_t s);
+
 }  // namespace lsg

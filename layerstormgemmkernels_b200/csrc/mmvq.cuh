@@ -428,10 +428,10 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         // claim a group whose slab is more than a ring ahead of the slowest warp; so
         // first wait until the producer has started loading exactly this slab.
         if (slab_in_stage[s] != i) {
-            const uint64_t t0 = global_timer_ns();
+            const long long t0 = sm_clock();
             while (slab_in_stage[s] != i) {
                 __nanosleep(64);
-                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                if (sm_clock() - t0 > kWaitLimitCycles) {
                     if (a.status) atomicCAS(a.status, 0u, static_cast<unsigned int>(kDevWaitFull));
                     return;
                 }

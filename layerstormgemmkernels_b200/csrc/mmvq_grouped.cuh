@@ -185,10 +185,10 @@ __global__ void __launch_bounds__(512, 1) mmvq_grouped_kernel(const GroupedArgs 
             // barriers above need every warp) but no longer wait or compute.
             bool ok = *abort_flag == 0;
             if (ok && slab_in_stage[s] != i) {
-                const uint64_t t0 = global_timer_ns();
+                const long long t0 = sm_clock();
                 while (slab_in_stage[s] != i && *abort_flag == 0) {
                     __nanosleep(64);
-                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    if (sm_clock() - t0 > kWaitLimitCycles) {
                         if (a.status) atomicCAS(a.status, 0u, static_cast<unsigned int>(kDevWaitFull));
                         *abort_flag = 1;
                     }

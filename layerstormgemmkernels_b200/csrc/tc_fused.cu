@@ -1,0 +1,913 @@
+// Tensor-core GGUF GEMM with the weight dequantization fused into the operand pipeline.
+//
+// Same contract as the prepared-operand path (tc_gemm.cu): C[m, n] = sum_k x16[m,k] * w16[n,k]
+// with w16 the fp16 of the dequantized weight and x16 the fp16 of the activation's Q8_1
+// round trip, i.e. the reference's integer result (csrc/sm120/gemm/gguf/mmq_mma/
+// mmq_kernel_32aligned.cuh:34-169, gguf_mmvq.cu:66-187) up to one fp16 rounding per operand.
+// The difference is where w16 comes from: here the packed GGUF blocks are read straight from
+// global memory by eight decoder warps, which write fp16 tiles in the 128-byte-swizzled K-major
+// layout the tensor core reads.  No fp16 copy of the weights ever exists in HBM, so the
+// weights cost their packed 4.5-8.5 bits per value of traffic.
+//
+// The roles are swapped with respect to the usual GEMM: the WEIGHT rows are the M = 128 side
+// of tcgen05.mma and the token rows the N side (32..256).  A decode batch of a few tokens then
+// still fills the 128 tensor-memory lanes, and one kernel serves 2-token decode, expert-routed
+// MoE batches and 4096-token prefill.
+//
+//   warps 0-3   epilogue: tcgen05.ld (lane = weight row, column = token), stores transposed
+//               into C (32 lanes = 32 consecutive output columns of one token)
+//   warp 4      TMA producer: one (64 x NT) box of x16 per stage
+//   warp 5      MMA issuer: 4 x tcgen05.mma.cta_group::1.kind::f16 (M128, N = NT, K16) per stage
+//   warps 6-13  weight decoders: thread (row r, half h) turns 32 packed values of its row into
+//               four 16-byte chunks per 64-value K block; loads run two K blocks ahead
+// A stage is "full" after nine arrivals (eight decoder warps + the TMA transaction); it is
+// released by tcgen05.commit.  Two accumulators alternate so the epilogue overlaps the next
+// tile.  All waits are time-limited; a time-out ends every role and is reported in the status
+// word.
+//
+// Small token counts with few weight rows would leave most SMs idle, so the K range of an
+// output tile can be split over several CTAs.  Each split stores its fp32 partial tile; the
+// CTA that arrives last at the tile's counter adds the partials in split order (deterministic)
+// and writes C.  The counters are zeroed by the activation-preparation kernel of the same call.
+#include "common.cuh"
+#include "formats.cuh"
+#include "host.h"
+#include "tcgen05.cuh"
+
+namespace lsg {
+
+using namespace tc;
+
+namespace {
+
+constexpr int WM = 128;                  // weight rows per tile
+constexpr int kDecWarps = 8;
+constexpr int kFusedThreads = (6 + kDecWarps) * 32;
+constexpr int kWBytes = WM * BK * 2;     // 16 KB of fp16 weights per stage
+constexpr int kMaxStages = 8;
+constexpr int kRawSlotBytes = WM * 32;     // 32 packed bytes per weight row and K block (Q4_K)
+constexpr int kHdrRingBytes = 4 * WM * 16; // block headers of four consecutive 256-value blocks
+
+struct FusedArgs {
+    const uint8_t* W;             // dense: packed rows
+    const void* const* B_ptrs;    // grouped: per-expert packed matrices
+    long long row_bytes;
+    void* C;
+    int ldc;
+    int out_dtype;
+    int K, N, M;
+    int nt;                       // token rows per tile: 32, 64, 128 or 256
+    int n_wtiles;                 // ceil(N / 128)
+    int t_tiles;                  // dense: ceil(M / nt); grouped: capacity of the tile map
+    const int* tile_expert;
+    const int* tile_mstart;
+    const int32_t* expert_offsets;
+    int stages;
+    int raw_depth;                // K blocks of packed weights in flight per decoder (0: none)
+    int raw_bytes;                // shared memory of that ring
+    int ksplit;                   // CTAs per output tile along K
+    int kb_per_split;             // K blocks per split
+    float* partial;               // [items][ksplit][128][nt] fp32, only with ksplit > 1
+    unsigned int* counters;       // [tiles][4 epilogue warps], zero on entry
+    unsigned int* status;
+};
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// True in exactly one lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ---------------------------------------------------------------------------
+// Weight decoders.  load() fetches what thread (row, half h) needs for K block kb into
+// registers; emit() turns it into 32 fp16 values (four 16-byte chunks, K order).
+// ---------------------------------------------------------------------------
+template <int T>
+struct DecGeneric {
+    // Generic decoder: no register staging, the packed bytes are read while decoding.
+    static constexpr bool kFast = false;
+    struct Regs {
+        const uint8_t* blk;
+        int c;
+    };
+    __device__ static __forceinline__ Regs load(const uint8_t* row, int kb, int h, int K) {
+        using F = Fmt<T>;
+        Regs r;
+        const int k0 = kb * BK + 32 * h;
+        if (row == nullptr || k0 >= K) {
+            r.blk = nullptr;
+            r.c = 0;
+        } else if (F::VALS == 256) {
+            r.blk = row + static_cast<long long>(k0 >> 8) * F::BYTES;
+            r.c = (k0 >> 5) & 7;
+        } else {
+            r.blk = row + static_cast<long long>(k0 >> 5) * F::BYTES;
+            r.c = 0;
+        }
+        return r;
+    }
+    __device__ static __forceinline__ void emit(const Regs& r, int, uint4 (&out)[4]) {
+        if (r.blk == nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[j] = make_uint4(0, 0, 0, 0);
+            return;
+        }
+        float v[32];
+        dequant_chunk32<T>(r.blk, r.c, v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            out[j] = make_uint4(pack_h2(v[8 * j], v[8 * j + 1]), pack_h2(v[8 * j + 2], v[8 * j + 3]),
+                                pack_h2(v[8 * j + 4], v[8 * j + 5]), pack_h2(v[8 * j + 6], v[8 * j + 7]));
+    }
+};
+
+template <int T>
+struct Dec : DecGeneric<T> {};
+
+// Q4_K: 144-byte blocks {fp16 d, fp16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of
+// nibbles}; K block kb of a row is nibble pair p = kb % 4: low nibbles of qs[32p..32p+31]
+// are values 64p..64p+31 (half 0), high nibbles values 64p+32..64p+63 (half 1)
+// (csrc/formats/q4k_format.h:112-133).  Blocks are 16-byte aligned whenever the matrix is.
+template <>
+struct Dec<LSG_GGUF_Q4_K> {
+    static constexpr bool kFast = true;
+    struct Regs {
+        uint4 hdr, q0, q1;
+    };
+    __device__ static __forceinline__ Regs load(const uint8_t* row, int kb, int, int) {
+        Regs r;
+        const uint8_t* blk = row + static_cast<long long>(kb >> 2) * 144;
+        r.hdr = ldg128(blk);
+        r.q0 = ldg128(blk + 16 + (kb & 3) * 32);
+        r.q1 = ldg128(blk + 32 + (kb & 3) * 32);
+        return r;
+    }
+    __device__ static __forceinline__ uint32_t scale_byte(const uint4& hdr, int j) {
+        const uint32_t w = j < 4 ? hdr.y : (j < 8 ? hdr.z : hdr.w);
+        return (w >> (8 * (j & 3))) & 0xFFu;
+    }
+    __device__ static __forceinline__ void emit(const Regs& r, int c /* sub-block 0..7 */, uint4 (&out)[4]) {
+        // 6-bit scale and min of sub-block c (csrc/formats/kquant_common.h:36-46)
+        uint32_t sc, mn;
+        if (c < 4) {
+            sc = scale_byte(r.hdr, c) & 63u;
+            mn = scale_byte(r.hdr, c + 4) & 63u;
+        } else {
+            const uint32_t hi = scale_byte(r.hdr, c + 4);
+            sc = (hi & 0x0Fu) | ((scale_byte(r.hdr, c - 4) >> 6) << 4);
+            mn = (hi >> 4) | ((scale_byte(r.hdr, c) >> 6) << 4);
+        }
+        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(r.hdr.x & 0xFFFFu)));
+        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(r.hdr.x >> 16)));
+        const __half2 ds = __float2half2_rn(d * static_cast<float>(sc));
+        const __half2 nms = __float2half2_rn(-(dmin * static_cast<float>(mn)));
+        const __half2 k1024 = __float2half2_rn(1024.0f);
+        const uint32_t q[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t nib = ((c & 1) ? (q[i] >> 4) : q[i]) & 0x0F0F0F0Fu;
+            // bytes -> fp16 1024 + q by placing each under the exponent byte 0x64
+            uint32_t lo = __byte_perm(nib, 0x64646464u, 0x4140);
+            uint32_t hi = __byte_perm(nib, 0x64646464u, 0x4342);
+            __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), k1024);
+            __half2 b = __hsub2(*reinterpret_cast<__half2*>(&hi), k1024);
+            a = __hfma2(a, ds, nms);
+            b = __hfma2(b, ds, nms);
+            o[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+            o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+    }
+};
+
+// Work item -> tile coordinates.  Items are ordered weight tile fastest, then K split, then
+// token tile, so CTAs running together share a token tile (and, grouped, an expert).
+struct Item {
+    int tt, wt, ks;
+    int expert;       // -1 dense
+    int mstart, mend;
+    bool live;
+};
+
+__device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
+    Item it;
+    it.wt = w % a.n_wtiles;
+    const int rest = w / a.n_wtiles;
+    it.ks = rest % a.ksplit;
+    it.tt = rest / a.ksplit;
+    it.expert = -1;
+    it.mstart = it.tt * a.nt;
+    it.mend = a.M;
+    it.live = true;
+    if (a.tile_expert) {
+        const int e = a.tile_expert[it.tt];
+        it.expert = e;
+        it.live = e >= 0;
+        if (it.live) {
+            it.mstart = a.tile_mstart[it.tt];
+            it.mend = a.expert_offsets[e + 1];
+        }
+    }
+    return it;
+}
+
+// One item's K range for one decoder thread: row `row`, half `h` of every 64-value K block.
+// Three register sets rotate by name (the loop body is written out three times): copying a
+// set whose loads are still in flight would wait for them and collapse the lookahead.
+// Lookahead loads past the end re-read the last block instead of being skipped, so no load
+// is conditional.  Returns false after a wait timed out.
+template <class D>
+__device__ __forceinline__ bool decode_rows(const FusedArgs& a, const uint8_t* row, int kb0, int kb1, int h, int r,
+                                            uint32_t row_off, uint8_t* smem, int stage_bytes, int nstages,
+                                            uint64_t* full, uint64_t* empty, int& s, uint32_t& lap, uint32_t hint) {
+    const int lane = threadIdx.x & 31;
+    const int last = kb1 - 1;
+    typename D::Regs b0 = D::load(row, kb0, h, a.K);
+    typename D::Regs b1 = D::load(row, min(kb0 + 1, last), h, a.K);
+    typename D::Regs b2;
+    auto step = [&](const typename D::Regs& cur, int kb) -> bool {
+        if (lap > 0 &&
+            !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
+            return false;
+        uint4 out[4];
+        D::emit(cur, (kb & 3) * 2 + h, out);
+        const uint32_t dst = smem_u32(smem + s * stage_bytes) + row_off;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sts128(dst + (static_cast<uint32_t>((4 * h + j) ^ (r & 7)) << 4), out[j]);
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[s]);
+        if (++s == nstages) { s = 0; ++lap; }
+        return true;
+    };
+    for (int kb = kb0; kb < kb1; kb += 3) {
+        b2 = D::load(row, min(kb + 2, last), h, a.K);
+        if (!step(b0, kb)) return false;
+        if (kb + 1 >= kb1) break;
+        b0 = D::load(row, min(kb + 3, last), h, a.K);
+        if (!step(b1, kb + 1)) return false;
+        if (kb + 2 >= kb1) break;
+        b1 = D::load(row, min(kb + 4, last), h, a.K);
+        if (!step(b2, kb + 2)) return false;
+    }
+    return true;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Q4_K rows through a private shared-memory ring: every decoder thread copies its own 16
+// bytes of nibbles per K block (and, for half 0, the 16-byte block header once per four K
+// blocks) with cp.async, DEPTH K blocks ahead of where it decodes, so the lookahead costs no
+// registers.  The two halves of a row sit in the same warp; __syncwarp orders a lane's reads
+// of its partner's bytes against the copies that later reuse the slot.
+//
+// A 144-byte block is {fp16 d, fp16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of
+// nibbles} (csrc/formats/q4k_format.h:112-133); K block p of the block is nibble pair p: the
+// low nibbles of qs[32p..32p+31] are values 64p..64p+31 (half 0, sub-block 2p), the high
+// nibbles values 64p+32..64p+63 (half 1, sub-block 2p+1).  The value is d*sc*q - dmin*mn with
+// the 6-bit sc, mn of the sub-block (csrc/formats/kquant_common.h:36-46).  Here d*sc and
+// dmin*mn are formed as fp16 products (one rounding of an exact product, the same number
+// fp32 arithmetic followed by a conversion gives) and the value by one fp16 fma.
+//
+// Requires 16-byte aligned rows and a K range that starts and ends on a 256-value block.
+// Returns false after a wait timed out.
+template <int DEPTH>
+__device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_t* row, int kb0, int kb1, int h,
+                                                int r, uint32_t row_off, uint8_t* smem, uint8_t* raw,
+                                                int stage_bytes, int nstages, uint64_t* full, uint64_t* empty,
+                                                int& s, uint32_t& lap, uint32_t hint) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t q_ring = smem_u32(raw) + static_cast<uint32_t>(r * 32);           // + slot * kRawSlotBytes
+    const uint32_t h_ring = smem_u32(raw) + DEPTH * kRawSlotBytes + static_cast<uint32_t>(r * 16);  // + (blk & 3) * 2048
+    // destination of this thread's four 16-byte chunks inside a stage (128-byte swizzle)
+    uint32_t chunk_off[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) chunk_off[j] = row_off + (static_cast<uint32_t>((4 * h + j) ^ (r & 7)) << 4);
+
+    const uint8_t* src = row + static_cast<long long>(kb0 >> 2) * 144;  // block of the next copy
+    int issue_kb = kb0;
+    auto issue = [&](int slot) {
+        if (issue_kb < kb1) {
+            const int p = issue_kb & 3;
+            cp_async16(q_ring + slot * kRawSlotBytes + 16 * h, src + 16 + p * 32 + 16 * h);
+            if (h == 0 && p == 0) cp_async16(h_ring + ((issue_kb >> 2) & 3) * (WM * 16), src);
+            if (p == 3) src += 144;
+        }
+        ++issue_kb;
+        cp_async_commit();  // one group per K block, empty past the end, so the count below is fixed
+    };
+#pragma unroll
+    for (int i = 0; i < DEPTH; ++i) issue(i);
+
+    const __half2 k1024 = __float2half2_rn(1024.0f);
+    const uint32_t nib_shift = 4u * h;
+    int slot = 0;
+    for (int kb = kb0; kb < kb1; kb += 4) {
+        // ---- once per 256-value block: the four (scale, min) pairs of this thread's half ----
+        cp_async_wait<DEPTH - 1>();
+        __syncwarp();
+        const uint4 hdr = lds128(h_ring + ((kb >> 2) & 3) * (WM * 16));
+        // bytes of sc[0..3], sc[4..7], mn[0..3], mn[4..7]
+        const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu;
+        const uint32_t mn_lo = hdr.z & 0x3F3F3F3Fu;
+        const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+        const uint32_t mn_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+        // this half's sub-blocks are h, 2+h, 4+h, 6+h: bytes h and 2+h of the lo and hi words
+        const uint32_t sh = 8u * h;
+        const uint32_t scw[2] = {sc_lo >> sh, sc_hi >> sh};
+        const uint32_t mnw[2] = {mn_lo >> sh, mn_hi >> sh};
+        // (d, -dmin) as a half2
+        const uint32_t dd = hdr.x ^ 0x80000000u;
+        const __half2 d_ndmin = *reinterpret_cast<const __half2*>(&dd);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            if (p > 0) {
+                cp_async_wait<DEPTH - 1>();
+                __syncwarp();
+            }
+            if (lap > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
+                return false;
+            const uint4 q0 = lds128(q_ring + slot * kRawSlotBytes);
+            const uint4 q1 = lds128(q_ring + slot * kRawSlotBytes + 16);
+            // half2 (sc, mn) -> (d*sc, -dmin*mn), each broadcast to both halves
+            const uint32_t pair = __byte_perm(scw[p >> 1], mnw[p >> 1], (p & 1) ? 0x0062 : 0x0040);  // bytes sc, mn
+            uint32_t sm = __byte_perm(pair, 0x64646464u, 0x4140);
+            const __half2 scmn = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&sm), k1024), d_ndmin);
+            const __half2 ds = __low2half2(scmn), nms = __high2half2(scmn);
+            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t nib = (q[i] >> nib_shift) & 0x0F0F0F0Fu;
+                // bytes -> fp16 1024 + q by placing each under the exponent byte 0x64
+                uint32_t lo = __byte_perm(nib, 0x64646464u, 0x4140);
+                uint32_t hi = __byte_perm(nib, 0x64646464u, 0x4342);
+                const __half2 x = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&lo), k1024), ds, nms);
+                const __half2 y = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&hi), k1024), ds, nms);
+                o[2 * i] = *reinterpret_cast<const uint32_t*>(&x);
+                o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&y);
+            }
+            const uint32_t dst = smem_u32(smem + s * stage_bytes);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                sts128(dst + chunk_off[j], make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();              // both lanes are done with the slot before it is refilled
+            if (lane == 0) mbar_arrive(&full[s]);
+            issue(slot);
+            if (++slot == DEPTH) slot = 0;
+            if (++s == nstages) { s = 0; ++lap; }
+        }
+    }
+    cp_async_wait<0>();
+    return true;
+}
+
+template <int T>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int stage_bytes = kWBytes + a.nt * 128;
+    uint8_t* raw = smem + a.stages * stage_bytes;   // packed-weight ring of the staged decoders
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + a.raw_bytes);
+    uint64_t* empty = full + kMaxStages;
+    uint64_t* acc_full = empty + kMaxStages;  // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = 2u * a.nt;  // 64..512, a power of two
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(&full[s], kDecWarps + 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) tmem_alloc(tmem_slot, tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    pdl_wait_prior();  // x16, the tile map and the zeroed counters come from earlier kernels
+
+    const int kblocks_all = (a.K + BK - 1) / BK;
+    const int total = a.t_tiles * a.ksplit * a.n_wtiles;
+    const int nstages = a.stages;
+    const uint32_t hint = 2000u;  // suspend-time hint of the barrier waits, ns
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer (x16 tiles) ------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t lap = 0;  // ring position: stage and how often the ring has wrapped
+            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+                const Item im = decode_item(a, w);
+                if (!im.live) continue;
+                const int kb0 = im.ks * a.kb_per_split;
+                const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (lap > 0 &&
+                        !mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)) {
+                        *abort_flag = 1;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(a.nt) * 128u);
+                    tma_load_2d(smem + s * stage_bytes + kWBytes, &tmX, kb * BK, im.mstart, &full[s]);
+                    if (++s == nstages) { s = 0; ++lap; }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer --------------------------------
+        // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
+        // values; one elected lane issues the tensor-core instructions.
+        const uint32_t idesc = idesc_f16(WM, a.nt);
+        int s = 0, tile_i = 0;
+        uint32_t lap = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
+            const Item im = decode_item(a, w);
+            if (!im.live) continue;
+            const int kb0 = im.ks * a.kb_per_split;
+            const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
+            const int ab = tile_i & 1;
+            if (tile_i >= 2)
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status,
+                                                               kDevWaitTmem, hint));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + ab * a.nt;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[s], lap & 1, a.status, kDevWaitFull, hint));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sW = smem_u32(smem + s * stage_bytes);
+                const uint64_t wdesc = smem_desc_sw128(sW);
+                const uint64_t xdesc = smem_desc_sw128(sW + kWBytes);
+                if (elect_one()) {
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma_f16(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+                    tc_commit(&empty[s]);
+                }
+                __syncwarp();
+                if (++s == nstages) { s = 0; ++lap; }
+            }
+            if (!ok) break;
+            if (elect_one()) tc_commit(&acc_full[ab]);
+            __syncwarp();
+            ++tile_i;
+        }
+        if (!ok) *abort_flag = 1;
+    } else if (warp >= 6) {
+        // ------------------------------ weight decoders ---------------------------
+        const int dt = threadIdx.x - 6 * 32;
+        const int r = dt >> 1, h = dt & 1;
+        const uint32_t row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
+        int s = 0;
+        uint32_t lap = 0;
+        for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+            const Item im = decode_item(a, w);
+            if (!im.live) continue;
+            const int kb0 = im.ks * a.kb_per_split;
+            const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
+            const uint8_t* base = a.B_ptrs ? static_cast<const uint8_t*>(a.B_ptrs[im.expert]) : a.W;
+            const int n = min(im.wt * WM + r, a.N - 1);
+            const uint8_t* row = base ? base + static_cast<long long>(n) * a.row_bytes : nullptr;
+            // The register-staged decoder issues 16-byte vector loads; a matrix that is not
+            // 16-byte aligned goes through the byte-wise generic decoder instead.  The choice
+            // is uniform over the CTA and made per item, so neither loop carries a branch
+            // between a load and its use.
+            bool ok;
+            const bool aligned16 =
+                ((reinterpret_cast<uintptr_t>(base) | static_cast<uintptr_t>(a.row_bytes)) & 15) == 0;
+            if (T == LSG_GGUF_Q4_K && a.raw_depth > 0 && row != nullptr && aligned16) {
+                if (a.raw_depth == 8)
+                    ok = decode_rows_q4k<8>(a, row, kb0, kb1, h, r, row_off, smem, raw, stage_bytes, nstages, full,
+                                            empty, s, lap, hint);
+                else
+                    ok = decode_rows_q4k<4>(a, row, kb0, kb1, h, r, row_off, smem, raw, stage_bytes, nstages, full,
+                                            empty, s, lap, hint);
+            } else {
+                ok = decode_rows<DecGeneric<T>>(a, row, kb0, kb1, h, r, row_off, smem, stage_bytes, nstages, full,
+                                                empty, s, lap, hint);
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                break;
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (warps 0-3) ----------------------
+        int tile_i = 0;
+        for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+            const Item im = decode_item(a, w);
+            if (!im.live) continue;
+            const int ab = tile_i & 1;
+            const bool landed = __all_sync(
+                0xffffffffu, mbar_wait_bounded(&acc_full[ab], (tile_i >> 1) & 1, a.status, kDevWaitMma, hint));
+            if (!landed) {
+                *abort_flag = 1;
+                break;
+            }
+            tc_fence_after();
+            const int n = im.wt * WM + warp * 32 + lane;   // this thread's output column
+            const bool n_ok = n < a.N;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * a.nt;
+
+            if (a.ksplit == 1) {
+#pragma unroll 1
+                for (int c = 0; c < a.nt; c += 32) {
+                    if (im.mstart + c >= im.mend) break;  // warp-uniform: no token rows left in this tile
+                    uint32_t v[32];
+                    tmem_ld32(t_lane + c, v);
+                    if (n_ok) {
+                        const int rows = min(32, im.mend - (im.mstart + c));
+                        const size_t o = static_cast<size_t>(im.mstart + c) * a.ldc + n;
+                        if (a.out_dtype == LSG_DTYPE_F32) {
+                            float* dst = static_cast<float*>(a.C) + o;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < rows) dst[static_cast<size_t>(i) * a.ldc] = __uint_as_float(v[i]);
+                        } else {
+                            uint16_t* dst = static_cast<uint16_t*>(a.C) + o;
+                            const bool f16 = a.out_dtype == LSG_DTYPE_F16;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < rows) {
+                                    const float x = __uint_as_float(v[i]);
+                                    dst[static_cast<size_t>(i) * a.ldc] =
+                                        f16 ? __half_as_ushort(__float2half_rn(x))
+                                            : __bfloat16_as_ushort(__float2bfloat16_rn(x));
+                                }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            } else {
+                // Split K: park this split's fp32 tile [token][128 weight rows]; per 32-row
+                // slice of the tile, the warp that arrives last at the slice's counter adds
+                // the splits in order and writes C.  Each epilogue warp works alone, so no
+                // CTA-wide barrier sits inside a loop that a time-out may leave.
+                const int tile_id = im.tt * a.n_wtiles + im.wt;
+                const size_t tile_elems = static_cast<size_t>(WM) * a.nt;
+                float* mine = a.partial + (static_cast<size_t>(tile_id) * a.ksplit + im.ks) * tile_elems;
+                const int live_rows = min(a.nt, im.mend - im.mstart);
+#pragma unroll 1
+                for (int c = 0; c < live_rows; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(t_lane + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        mine[static_cast<size_t>(c + i) * WM + warp * 32 + lane] = __uint_as_float(v[i]);
+                }
+                tc_fence_before();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[ab]);
+                unsigned int prev = 0;
+                if (lane == 0) prev = atomicAdd(&a.counters[tile_id * 4 + warp], 1u);
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                if (prev == static_cast<unsigned int>(a.ksplit - 1)) {
+                    __threadfence();
+                    const float* tile0 = a.partial + static_cast<size_t>(tile_id) * a.ksplit * tile_elems;
+                    if (n_ok) {
+                        // 32 token rows at a time: the loads of one split are independent and all
+                        // in flight together; the splits are added in order.
+                        for (int i0 = 0; i0 < live_rows; i0 += 32) {
+                            float acc[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+                            const float* col = tile0 + static_cast<size_t>(i0) * WM + warp * 32 + lane;
+                            for (int sp = 0; sp < a.ksplit; ++sp) {
+                                float v[32];
+#pragma unroll
+                                for (int i = 0; i < 32; ++i)
+                                    v[i] = (i0 + i < live_rows) ? __ldcg(col + sp * tile_elems + static_cast<size_t>(i) * WM)
+                                                                : 0.0f;
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) acc[i] += v[i];
+                            }
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (i0 + i < live_rows) {
+                                    const size_t o = static_cast<size_t>(im.mstart + i0 + i) * a.ldc + n;
+                                    if (a.out_dtype == LSG_DTYPE_F32)
+                                        static_cast<float*>(a.C)[o] = acc[i];
+                                    else if (a.out_dtype == LSG_DTYPE_F16)
+                                        static_cast<uint16_t*>(a.C)[o] = __half_as_ushort(__float2half_rn(acc[i]));
+                                    else
+                                        static_cast<uint16_t*>(a.C)[o] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            ++tile_i;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Activation preparation: bf16 -> fp16 of the Q8_1 round trip (d_h * rn(x / d), the values
+// the integer kernels multiply by), plus zeroing of the split-K tile counters.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks,
+              unsigned int* __restrict__ counters, int n_counters) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (counters && task < n_counters) counters[task] = 0;
+    const bool live = task < n_blocks * 4;
+    const long long tk = live ? task : 0;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
+    float v[8];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) return;
+    const float d = amax / 127.0f;
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    const float dh = __half2float(__float2half(d));
+    uint32_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float r[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const float t = v[2 * i + hh] * rcp;
+            int k = __float2int_rn(t);
+            // same integer as rn(fl(x / d)): the product with the reciprocal only differs
+            // next to a half-integer, and there the true quotient decides
+            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + hh] / d);
+            r[hh] = dh * static_cast<float>(k);
+        }
+        p[i] = pack_h2(r[0], r[1]);
+    }
+    reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+bool staged_decoder(int type) { return type == LSG_GGUF_Q4_K; }
+
+struct Plan {
+    int nt, stages, raw_depth, raw_bytes, t_tiles, n_wtiles, ksplit, kb_per_split;
+    size_t x_bytes, partial_bytes, counter_bytes;
+    size_t total() const { return x_bytes + partial_bytes + counter_bytes; }
+};
+
+int pick_nt(long long rows_per_problem) {
+    if (rows_per_problem <= 32) return 32;
+    if (rows_per_problem <= 64) return 64;
+    if (rows_per_problem <= 128) return 128;
+    return 256;
+}
+
+// rows: token rows of the whole call; t_tiles: dense tile count or the tile map's capacity.
+Plan make_plan(long long rows, int nt, int t_tiles, int N, int K, bool allow_split, bool staged) {
+    Plan p = {};
+    p.nt = nt;
+    const int stage_bytes = kWBytes + nt * 128;
+    // packed-weight ring: 8 K blocks deep, 4 when 256-token tiles leave less room
+    p.raw_depth = staged ? (nt >= 256 ? 4 : 8) : 0;
+    p.raw_bytes = staged ? p.raw_depth * kRawSlotBytes + kHdrRingBytes : 0;
+    p.stages = (224 * 1024 - p.raw_bytes) / stage_bytes;
+    if (p.stages > kMaxStages) p.stages = kMaxStages;
+    p.t_tiles = t_tiles;
+    p.n_wtiles = (N + WM - 1) / WM;
+    const int kblocks = (K + BK - 1) / BK;
+    p.ksplit = 1;
+    if (allow_split) {
+        // split K until every SM has an item, keeping at least 8 K blocks per split
+        const int items = p.t_tiles * p.n_wtiles;
+        const int sms = sm_count();
+        int want = (sms + items - 1) / items;
+        const int cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+        if (want > cap) want = cap;
+        // the last arrival adds ksplit partial tiles; keep that short next to the main loop
+        const int most = nt <= 32 ? 16 : (nt <= 64 ? 4 : (nt <= 128 ? 2 : 1));
+        if (want > most) want = most;
+        if (want > 1) p.ksplit = want;
+    }
+    p.kb_per_split = (kblocks + p.ksplit - 1) / p.ksplit;
+    p.kb_per_split = (p.kb_per_split + 3) & ~3;  // splits cover whole 256-value blocks
+    p.ksplit = (kblocks + p.kb_per_split - 1) / p.kb_per_split;  // no empty splits
+    p.x_bytes = align256(static_cast<size_t>(rows) * K * 2);
+    if (p.ksplit > 1) {
+        p.partial_bytes = align256(static_cast<size_t>(p.t_tiles) * p.n_wtiles * p.ksplit * WM * nt * 4);
+        p.counter_bytes = align256(static_cast<size_t>(p.t_tiles) * p.n_wtiles * 4 * 4);
+    }
+    return p;
+}
+
+template <int T>
+int launch_fused_t(const CUtensorMap& tmX, const FusedArgs& a, cudaStream_t s) {
+    static bool configured[64] = {};
+    int dev = 0;
+    LSG_CUDA_TRY(cudaGetDevice(&dev));
+    const int smem = a.stages * (kWBytes + a.nt * 128) + a.raw_bytes + 1024 + 512;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        LSG_CUDA_TRY(cudaFuncSetAttribute(tc_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          227 * 1024));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const long long items = static_cast<long long>(a.t_tiles) * a.ksplit * a.n_wtiles;
+    int grid = sm_count();
+    if (grid > items) grid = static_cast<int>(items);
+    if (grid < 1) grid = 1;
+    LSG_CUDA_TRY(launch_kernel(tc_fused_kernel<T>, dim3(grid), dim3(kFusedThreads), smem, s, true, tmX, a));
+    return LSG_OK;
+}
+
+int launch_fused(int type, const CUtensorMap& tmX, const FusedArgs& a, cudaStream_t s) {
+    switch (type) {
+        case 0: return launch_fused_t<0>(tmX, a, s);
+        case 1: return launch_fused_t<1>(tmX, a, s);
+        case 2: return launch_fused_t<2>(tmX, a, s);
+        case 3: return launch_fused_t<3>(tmX, a, s);
+        case 4: return launch_fused_t<4>(tmX, a, s);
+        case 5: return launch_fused_t<5>(tmX, a, s);
+        case 6: return launch_fused_t<6>(tmX, a, s);
+        case 7: return launch_fused_t<7>(tmX, a, s);
+    }
+    return fail(LSG_ERR_UNSUPPORTED, "gguf fused mmq: unknown type %d", type);
+}
+
+int g_mode_override = -1;
+
+int env_mode() {
+    static int mode = [] {
+        const char* e = getenv("LSG_TC_FUSED");
+        return e ? atoi(e) : 1;
+    }();
+    return g_mode_override >= 0 ? g_mode_override : mode;
+}
+
+}  // namespace
+
+// 0: never; 1: types with a register-staged decoder; 2: every type (generic decoder).
+bool tc_fused_available(int type) {
+    const int mode = env_mode();
+    if (mode <= 0) return false;
+    if (type == LSG_GGUF_Q4_K) return true;
+    return mode >= 2;
+}
+
+bool tc_fused_forced() { return env_mode() >= 2; }
+
+size_t tc_fused_dense_scratch_bytes(int M, int N, int K) {
+    const int nt = pick_nt(M);
+    return make_plan(M, nt, (M + nt - 1) / nt, N, K, true, false).total();
+}
+
+int tc_fused_grouped_tile_m(long long T, int E) {
+    const int nt = pick_nt(E > 0 ? (T + E - 1) / E : T);
+    return nt < 64 ? 64 : nt;  // the workspace reserves a tile map for tiles of 64 rows or more
+}
+
+size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K) {
+    const int nt = tc_fused_grouped_tile_m(T, E);
+    return make_plan(T, nt, static_cast<int>((T + nt - 1) / nt) + E, N, K, false, false).total();
+}
+
+// Dense: C[M, N] (ldc) = x . W^T with W packed GGUF rows.
+int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
+                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (M == 0 || N == 0) return LSG_OK;
+    if (K % 32 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf fused mmq: K must be a multiple of 32");
+    const int nt = pick_nt(M);
+    const Plan p = make_plan(M, nt, (M + nt - 1) / nt, N, K, true, staged_decoder(type));
+    if (!ws || ws_bytes < p.total())
+        return fail(LSG_ERR_WORKSPACE, "gguf_mmq: workspace too small (have %zu, need %zu)",
+                    ws ? ws_bytes : size_t(0), p.total());
+    if (reinterpret_cast<uintptr_t>(ws) & 255)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_mmq: workspace must be 256-byte aligned");
+    uint8_t* wsb = static_cast<uint8_t*>(ws);
+    __half* x16 = reinterpret_cast<__half*>(wsb);
+    float* partial = reinterpret_cast<float*>(wsb + p.x_bytes);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(wsb + p.x_bytes + p.partial_bytes);
+    const int n_counters = p.ksplit > 1 ? p.t_tiles * p.n_wtiles * 4 : 0;
+    const long long nb = static_cast<long long>(M) * (K / 32);
+    long long tasks = nb * 4;
+    if (tasks < n_counters) tasks = n_counters;
+    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((tasks + 255) / 256)), dim3(256), 0, s, true,
+                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
+                               n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters));
+    CUtensorMap tmX;
+    int rc = make_map(&tmX, x16, M, K, nt);
+    if (rc != LSG_OK) return rc;
+    FusedArgs a = {};
+    a.W = static_cast<const uint8_t*>(W);
+    a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
+    a.C = C; a.ldc = ldc; a.out_dtype = out_dtype;
+    a.K = K; a.N = N; a.M = M;
+    a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
+    a.partial = partial; a.counters = counters;
+    a.status = device_status_word();
+    return launch_fused(type, tmX, a, s);
+}
+
+// Grouped: token rows of expert e are expert_offsets[e]..[e+1] of A; the tile map (tile_m =
+// tc_fused_grouped_tile_m) routes token tiles to experts on the device.
+int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, const void* const* B_ptrs,
+                     const int32_t* expert_offsets, void* D, int out_dtype, const int* tile_expert,
+                     const int* tile_mstart, int t_max, int tile_m, void* scratch, size_t scratch_bytes,
+                     cudaStream_t s) {
+    if (T == 0 || N == 0) return LSG_OK;
+    if (K % 32 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf fused grouped mmq: K must be a multiple of 32");
+    const Plan p = make_plan(T, tile_m, t_max, N, K, false, staged_decoder(type));
+    if (!scratch || scratch_bytes < p.total())
+        return fail(LSG_ERR_WORKSPACE, "gguf grouped mmq: scratch too small (have %zu, need %zu)",
+                    scratch ? scratch_bytes : size_t(0), p.total());
+    __half* x16 = static_cast<__half*>(scratch);
+    const long long nb = static_cast<long long>(T) * (K / 32);
+    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
+                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
+                               static_cast<unsigned int*>(nullptr), 0));
+    CUtensorMap tmX;
+    int rc = make_map(&tmX, x16, T, K, tile_m);
+    if (rc != LSG_OK) return rc;
+    FusedArgs a = {};
+    a.B_ptrs = B_ptrs;
+    a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
+    a.C = D; a.ldc = N; a.out_dtype = out_dtype;
+    a.K = K; a.N = N; a.M = T;
+    a.nt = tile_m; a.n_wtiles = p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.ksplit = 1; a.kb_per_split = p.kb_per_split;
+    a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
+    a.status = device_status_word();
+    return launch_fused(type, tmX, a, s);
+}
+
+}  // namespace lsg
+
+extern "C" int lsg_mmq_set_weight_path(int mode) {
+    if (mode > 2) return lsg::fail(LSG_ERR_INVALID, "mmq_set_weight_path: mode must be 0, 1, 2 or negative");
+    lsg::g_mode_override = mode < 0 ? -1 : mode;
+    return LSG_OK;
+}

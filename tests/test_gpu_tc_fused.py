@@ -1,0 +1,154 @@
+"""GPU tests of the tensor-core GEMM that decodes the packed weights inside the kernel
+(weight rows on the 128-lane side, tokens on the N side, optional split of K).  The
+checker is the CPU oracle of the reference's integer path (gguf_mmvq.cu:66-187 after
+quantize_bf16_to_q8_1); the bound is the GEMM tolerance max|y - ref| <= 1e-3 max|ref|."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from layerstormgemmkernels_b200 import quantize as Q
+from layerstormgemmkernels_b200.capi import GGUF_TYPES
+
+pytestmark = pytest.mark.gpu
+T = GGUF_TYPES
+ALL_TYPES = ["Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "Q8_0", "MXFP4", "Q4_0"]
+TOL_TC = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from layerstormgemmkernels_b200 import ops as _ops, capi
+    yield _ops
+    capi.check(capi.lib.lsg_mmq_set_weight_path(-1))
+    assert capi.device_status() == 0
+
+
+@pytest.fixture
+def weight_path():
+    from layerstormgemmkernels_b200 import capi
+
+    def set_mode(mode):
+        capi.check(capi.lib.lsg_mmq_set_weight_path(mode))
+    yield set_mode
+    capi.check(capi.lib.lsg_mmq_set_weight_path(-1))
+
+
+def bits_of(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def make_case(name, M, N, K, seed):
+    A = (torch.randn(M, K, generator=torch.Generator().manual_seed(seed)) * 0.4).to(torch.bfloat16).cuda()
+    W = Q.random_gguf_weight(name, N, K, seed=seed + 1)
+    return A, W, torch.from_numpy(W).cuda()
+
+
+@pytest.mark.parametrize("name", ALL_TYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (5, 200, 512), (33, 384, 256), (129, 130, 768), (300, 256, 1024)])
+def test_fused_dense_every_type_vs_oracle(ops, weight_path, name, M, N, K):
+    weight_path(2)
+    A, W, Wd = make_case(name, M, N, K, seed=M + N)
+    ref = oracle.mmvq(T[name], oracle.quantize_q8_1(bits_of(A)), W, K)
+    got = ops.gguf_mmq(A, Wd, T[name], N, K, out_dtype=torch.float32).cpu().numpy()
+    assert got.shape == (M, N)
+    assert np.abs(got - ref).max() <= TOL_TC * np.abs(ref).max()
+    g16 = ops.gguf_mmq(A, Wd, T[name], N, K).float().cpu().numpy()
+    assert np.abs(g16 - ref).max() <= (TOL_TC + 2.0 ** -8) * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "MXFP4"])
+def test_fused_k_not_a_multiple_of_64(ops, weight_path, name):
+    """32-value block types allow K = 32 (mod 64): the last K block is half empty."""
+    weight_path(2)
+    M, N, K = 20, 256, 96
+    A, W, Wd = make_case(name, M, N, K, seed=9)
+    ref = oracle.mmvq(T[name], oracle.quantize_q8_1(bits_of(A)), W, K)
+    got = ops.gguf_mmq(A, Wd, T[name], N, K, out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(got - ref).max() <= TOL_TC * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("M", [2, 4, 8, 16, 40])
+@pytest.mark.parametrize("N,K", [(1024, 4096), (4096, 4096), (512, 14336)])
+def test_fused_q4k_decode_batches_split_k(ops, weight_path, M, N, K):
+    """Few tokens and few weight tiles: K is split over CTAs and the partial tiles are added
+    in split order by the last arrival, so two runs agree bit for bit."""
+    weight_path(1)
+    A, W, Wd = make_case("Q4_K", M, N, K, seed=M)
+    got = ops.gguf_mmq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32)
+    again = ops.gguf_mmq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32)
+    assert torch.equal(got, again)
+    cols = np.r_[0:16, N // 2:N // 2 + 16, N - 16:N]
+    ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bits_of(A)), W[cols], K)
+    assert np.abs(got.cpu().numpy()[:, cols] - ref).max() <= TOL_TC * np.abs(ref).max()
+    # the mat-vec kernel computes the same numbers from the same Q8_1 activations
+    mv = ops.gguf_mmvq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32)
+    assert (got - mv).abs().max().item() <= TOL_TC * np.abs(ref).max()
+
+
+def test_fused_and_prepared_weight_paths_agree(ops, weight_path):
+    M, N, K = 260, 640, 2048
+    A, W, Wd = make_case("Q4_K", M, N, K, seed=4)
+    outs = []
+    for mode in (0, 1, 2):
+        weight_path(mode)
+        outs.append(ops.gguf_mmq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32))
+    scale = outs[0].abs().max().item()
+    assert (outs[0] - outs[1]).abs().max().item() <= TOL_TC * scale
+    assert (outs[0] - outs[2]).abs().max().item() <= TOL_TC * scale
+
+
+def test_fused_q4k_matrix_at_an_odd_address(ops, weight_path):
+    """The staged Q4_K decoder copies 16-byte pieces and needs 16-byte alignment; a matrix
+    that starts at another address goes through the byte-wise decoder (fp32 arithmetic,
+    one rounding to fp16) and agrees to the fp16 rounding of the weights."""
+    weight_path(1)
+    M, N, K = 24, 256, 512
+    A, W, Wd = make_case("Q4_K", M, N, K, seed=21)
+    aligned = ops.gguf_mmq(A, Wd, T["Q4_K"], N, K, out_dtype=torch.float32)
+    buf = torch.zeros(Wd.numel() + 64, dtype=torch.uint8, device="cuda")
+    shifted = buf[6:6 + Wd.numel()]
+    shifted.copy_(Wd.reshape(-1))
+    assert shifted.data_ptr() % 16 != 0
+    moved = ops.gguf_mmq(A, shifted.view(N, -1), T["Q4_K"], N, K, out_dtype=torch.float32)
+    scale = aligned.abs().max().item()
+    assert (aligned - moved).abs().max().item() <= TOL_TC * scale
+    ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bits_of(A)), W, K)
+    assert np.abs(moved.cpu().numpy() - ref).max() <= TOL_TC * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("name", ALL_TYPES)
+def test_fused_grouped_every_type(ops, weight_path, name):
+    """Expert-routed tiles through the fused kernel (reference: launch_gguf_grouped_gemm_int
+    with force = mmq, gguf_grouped_int.cu:930-1010)."""
+    weight_path(2)
+    E, K, N = 5, 512, 320
+    counts = [70, 0, 3, 130, 257]
+    offs = np.zeros(E + 1, dtype=np.int32)
+    offs[1:] = np.cumsum(counts)
+    A = (torch.randn(int(offs[-1]), K, generator=torch.Generator().manual_seed(5)) * 0.4).to(torch.bfloat16).cuda()
+    host_w = [Q.random_gguf_weight(name, N, K, 50 + e) for e in range(E)]
+    dev_w = [torch.from_numpy(w).cuda() for w in host_w]
+    ptrs = torch.tensor([w.data_ptr() for w in dev_w], dtype=torch.int64, device="cuda")
+    out = ops.gguf_grouped_gemm(A, torch.from_numpy(offs).cuda(), ptrs, T[name], 1, N, K, 2,
+                                out_dtype=torch.float32).cpu().numpy()
+    xq = bits_of(A)
+    for e in range(E):
+        s, en = int(offs[e]), int(offs[e + 1])
+        if s == en:
+            continue
+        ref = oracle.mmvq(T[name], oracle.quantize_q8_1(xq[s:en]), host_w[e], K)
+        assert np.abs(out[s:en] - ref).max() <= TOL_TC * np.abs(ref).max()
+
+
+def test_fused_prefill_config_shape_sampled(ops, weight_path):
+    """Prefill config: Q4_K 14336 x 4096, M = 512; sampled rows/columns against the oracle."""
+    weight_path(1)
+    N, K, M = 14336, 4096, 512
+    A = torch.randn(M, K, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).cuda()
+    W = Q.random_gguf_weight("Q4_K", N, K, seed=2)
+    got = ops.gguf_mmq(A, torch.from_numpy(W).cuda(), T["Q4_K"], N, K, out_dtype=torch.float32).cpu().numpy()
+    rows = np.r_[0:4, 250:254, 508:512]
+    cols = np.r_[0:8, 7000:7008, N - 8:N]
+    ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bits_of(A)[rows]), W[cols], K)
+    assert np.abs(got[np.ix_(rows, cols)] - ref).max() <= TOL_TC * np.abs(ref).max()
