@@ -47,7 +47,32 @@ struct MmvqArgs {
     int x_bytes;              // bytes of the activation image (multiple of 128)
     int debug_skip;           // tuning aid: 1 = consumers skip the math
     int cons_warps;           // consumer warps per CTA (block = 32 * (cons_warps + 1))
+    // Division-free index arithmetic (set by finish_args): CTA b owns rows
+    // [b*rows_q + min(b, rows_r), ...) and quotients by the two small divisors below
+    // are taken with a multiply-high.
+    int rows_q, rows_r;       // N / grid, N % grid
+    int gps;                  // row groups per slab
+    uint32_t gps_magic;       // ceil(2^32 / gps), 0 when gps == 1
+    uint32_t stages_magic;    // ceil(2^32 / stages), 0 when stages == 1
 };
+
+// n / d for 0 <= n < 65536 and 1 <= d < 65536 with magic = ceil(2^32 / d) (0 for d == 1):
+// exact because n * (magic * d - 2^32) < n * d < 2^32.
+inline uint32_t div_magic(int d) { return d <= 1 ? 0u : static_cast<uint32_t>((0x100000000ull + d - 1) / d); }
+#if defined(__CUDACC__)
+__device__ __forceinline__ int fast_div(int n, uint32_t magic) {
+    return magic == 0u ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), magic));
+}
+#endif
+
+// Fills the derived fields once grid, slab_rows and stages are known (rpp = rows per warp pass).
+inline void finish_args(MmvqArgs& a, int grid, int rpp) {
+    a.rows_q = a.N / grid;
+    a.rows_r = a.N % grid;
+    a.gps = (a.slab_rows + rpp - 1) / rpp;
+    a.gps_magic = div_magic(a.gps);
+    a.stages_magic = div_magic(a.stages);
+}
 
 // Launch geometry knobs (see lsg_mmvq_set_tuning in lsg.h).
 struct MmvqTune {
@@ -327,10 +352,12 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     const bool is_producer = (warp == n_cons_warps);
 
     // Contiguous row range of this CTA.
-    const int row_begin = static_cast<int>((static_cast<long long>(a.N) * blockIdx.x) / gridDim.x);
-    const int row_end = static_cast<int>((static_cast<long long>(a.N) * (blockIdx.x + 1)) / gridDim.x);
+    const int bx = static_cast<int>(blockIdx.x);
+    const int row_begin = bx * a.rows_q + min(bx, a.rows_r);
+    const int row_end = row_begin + a.rows_q + (bx < a.rows_r ? 1 : 0);
+    const int groups_per_slab = a.gps;
+
     const int n_slabs = (row_end - row_begin + a.slab_rows - 1) / a.slab_rows;
-    const int groups_per_slab = (a.slab_rows + RPP - 1) / RPP;
 
     if (tid == 0) {
         for (int s = 0; s < a.stages; ++s) {
@@ -354,12 +381,10 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
             const uint64_t policy = l2_policy_evict_first();
             const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.W);
             const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(a.N) * a.row_bytes) & ~uintptr_t(15);
-            for (int i = 0; i < n_slabs; ++i) {
-                const int s = i % a.stages;
-                if (i >= a.stages) {
-                    const uint32_t parity = ((i / a.stages) - 1) & 1;
-                    if (!mbar_wait_bounded(&empty[s], parity, a.status, kDevWaitEmpty)) break;
-                }
+            int s = 0;
+            uint32_t lap = 0;  // ring position of slab i: stage s, lap = i / stages
+            for (int i = 0; i < n_slabs; ++i, s = (s + 1 == a.stages) ? 0 : s + 1, lap += (s == 0)) {
+                if (lap > 0 && !mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty)) break;
                 const int r0 = row_begin + i * a.slab_rows;
                 const int r1 = min(r0 + a.slab_rows, row_end);
                 const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
@@ -417,9 +442,10 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         if (lane == 0) gidx = atomicAdd(next_group, 1);
         gidx = __shfl_sync(0xffffffffu, gidx, 0);
         if (gidx >= total_groups) break;
-        const int i = gidx / groups_per_slab;
+        const int i = fast_div(gidx, a.gps_magic);
         const int g = (gidx - i * groups_per_slab) * RPP;
-        const int s = i % a.stages;
+        const int lap = fast_div(i, a.stages_magic);
+        const int s = i - lap * a.stages;
         const int r0 = row_begin + i * a.slab_rows;
         const int nrows = min(a.slab_rows, row_end - r0);
         // Every claim waits for its slab, including the groups past the end of a short
@@ -437,7 +463,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                 }
             }
         }
-        if (!mbar_wait_bounded(&full[s], (i / a.stages) & 1, a.status, kDevWaitFull)) return;
+        if (!mbar_wait_bounded(&full[s], lap & 1, a.status, kDevWaitFull)) return;
         if (g < nrows) {
             const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
             const uint32_t slab = smem_u32(ring + static_cast<size_t>(s) * a.stage_bytes) +

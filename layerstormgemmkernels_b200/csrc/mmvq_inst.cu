@@ -118,6 +118,7 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pd
         break;
     }
 
+    finish_args(a, grid, (32 / lanes) * rw);
     if (a.M == 1) return launch_rows<1>(rw, lanes, a, grid, smem, stream, pdl);
     if (a.M == 2) return launch_rows<2>(rw, lanes, a, grid, smem, stream, pdl);
     if (a.M <= 4) return launch_rows<4>(rw, lanes, a, grid, smem, stream, pdl);

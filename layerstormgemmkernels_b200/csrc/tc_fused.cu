@@ -334,10 +334,15 @@ __device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_
     const __half2 k1024 = __float2half2_rn(1024.0f);
     const uint32_t nib_shift = 4u * h;
     int slot = 0;
+    // The nibbles of K block kb are read from the ring one iteration ahead of their use, so
+    // the shared-memory latency hides behind the arithmetic of block kb - 1; the wait for a
+    // free stage comes after the arithmetic, right before the stores.
+    cp_async_wait<DEPTH - 1>();
+    __syncwarp();
+    uint4 q0 = lds128(q_ring), q1 = lds128(q_ring + 16);
     for (int kb = kb0; kb < kb1; kb += 4) {
         // ---- once per 256-value block: the four (scale, min) pairs of this thread's half ----
-        cp_async_wait<DEPTH - 1>();
-        __syncwarp();
+        // (the header arrived with the group of the block's first K block, already waited for)
         const uint4 hdr = lds128(h_ring + ((kb >> 2) & 3) * (WM * 16));
         // bytes of sc[0..3], sc[4..7], mn[0..3], mn[4..7]
         const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu;
@@ -353,21 +358,19 @@ __device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_
         const __half2 d_ndmin = *reinterpret_cast<const __half2*>(&dd);
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            if (p > 0) {
-                cp_async_wait<DEPTH - 1>();
-                __syncwarp();
-            }
-            if (lap > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
-                return false;
-            const uint4 q0 = lds128(q_ring + slot * kRawSlotBytes);
-            const uint4 q1 = lds128(q_ring + slot * kRawSlotBytes + 16);
+            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            // the next K block's copies have landed (its group is the oldest but one): fetch
+            // its nibbles now; past the end this re-reads a finished slot and is not used
+            const int nslot = (slot + 1 == DEPTH) ? 0 : slot + 1;
+            cp_async_wait<DEPTH - 2>();
+            __syncwarp();
+            q0 = lds128(q_ring + nslot * kRawSlotBytes);
+            q1 = lds128(q_ring + nslot * kRawSlotBytes + 16);
             // half2 (sc, mn) -> (d*sc, -dmin*mn), each broadcast to both halves
             const uint32_t pair = __byte_perm(scw[p >> 1], mnw[p >> 1], (p & 1) ? 0x0062 : 0x0040);  // bytes sc, mn
             uint32_t sm = __byte_perm(pair, 0x64646464u, 0x4140);
             const __half2 scmn = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&sm), k1024), d_ndmin);
             const __half2 ds = __low2half2(scmn), nms = __high2half2(scmn);
-            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
             uint32_t o[16];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -380,6 +383,9 @@ __device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_
                 o[2 * i] = *reinterpret_cast<const uint32_t*>(&x);
                 o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&y);
             }
+            if (lap > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
+                return false;
             const uint32_t dst = smem_u32(smem + s * stage_bytes);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -388,7 +394,7 @@ __device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_
             __syncwarp();              // both lanes are done with the slot before it is refilled
             if (lane == 0) mbar_arrive(&full[s]);
             issue(slot);
-            if (++slot == DEPTH) slot = 0;
+            slot = nslot;
             if (++s == nstages) { s = 0; ++lap; }
         }
     }
