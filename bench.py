@@ -253,7 +253,9 @@ def main():
     outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _, N, _ in LAYER]
     ws = torch.empty((capi.lib.lsg_gguf_mmvq_workspace_bytes(M, 14336),), dtype=torch.uint8, device=dev)
     abytes = algorithmic_bytes(args.type, M)
-    launches_per_step = 2 * len(LAYER)
+    # one mat-vec launch per projection, plus a Q8_1 quantizer launch where the activation is
+    # too large to be quantized inside the mat-vec kernel (the library's rule: M * K > 16384)
+    launches_per_step = sum(1 if M * K <= 16384 else 2 for _, _, K in LAYER)
 
     def layer_step(weights):
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -354,13 +356,13 @@ def main():
         "gpu_launches": args.steps * launches_per_step,
         "clocks": clocks,
     }
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.txt")
     if os.path.exists(traffic_file):
         with open(traffic_file) as f:
-            tr = json.load(f)
-        key = f"{args.type}_M{M}"
-        if key in tr:
-            line["roofline"]["traffic"] = tr[key]
+            for ln in f:
+                parts = ln.split()
+                if len(parts) == 2 and parts[0] == f"{args.type}_M{M}":
+                    line["roofline"]["traffic"] = int(parts[1])
     if not args.no_cpu_baseline and world == 1:
         import oracle
         oracle.build()

@@ -1,11 +1,12 @@
 """Single-shape probe of the GGUF mat-vec, for profilers and quick timing.
 
-    python -m layerstormgemmkernels_b200.probe TYPE N K M COPIES CALLS [--time]
+    python -m layerstormgemmkernels_b200.probe TYPE N K M COPIES CALLS [--time] [--mmq]
 
 Makes COPIES device copies of one random-byte weight of the given type and shape (so that
 successive calls stream from DRAM, not from L2), quantizes an M x K activation once, and
 issues CALLS mat-vec calls through the C ABI, walking over the copies.  With --time it
-also reports CUDA-event time per call from a CUDA-graph replay.
+also reports CUDA-event time per call from a CUDA-graph replay.  With --mmq the calls go to
+the tensor-core GEMM (lsg_gguf_mmq) instead of the mat-vec.
 """
 import sys
 
@@ -21,14 +22,20 @@ def main(argv):
     weights = [base.clone() for _ in range(copies)]
     A = torch.randn(M, K, device="cuda").to(torch.bfloat16)
     xq = ops.quantize_q8_1(A)
+    if "--mmq" in argv:
+        def call(w):
+            return ops.gguf_mmq(A, w, t, N, K)
+    else:
+        def call(w):
+            return ops.gguf_mmvq_q8_1(xq, w, t, N, K)
     for i in range(calls):
-        ops.gguf_mmvq_q8_1(xq, weights[i % copies], t, N, K)
+        call(weights[i % copies])
     torch.cuda.synchronize()
     if "--time" in argv:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             for w in weights:
-                ops.gguf_mmvq_q8_1(xq, w, t, N, K)
+                call(w)
         g.replay()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -39,7 +46,8 @@ def main(argv):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (20 * copies)
         nbytes = N * (K // capi.BLOCK_VALUES[t]) * capi.BLOCK_BYTES[t] + M * K * 2 + M * N * 2
-        print(f"{name} N={N} K={K} M={M}: {us:.2f} us per call, {nbytes / us / 1e3:.0f} GB/s")
+        print(f"{name} N={N} K={K} M={M}: {us:.2f} us per call, {nbytes / us / 1e3:.0f} GB/s, "
+              f"{2.0 * M * N * K / us / 1e6:.1f} TFLOP/s")
     print("device status", capi.device_status())
 
 
