@@ -233,6 +233,32 @@ LSG_API size_t lsg_gguf_grouped_gemm_workspace_bytes_ex(int total_tokens, int K,
 LSG_API int lsg_gguf_grouped_gemm(const lsg_gguf_grouped_gemm_params* p, int total_tokens,
                                   void* workspace, size_t workspace_bytes, int force, void* stream);
 
+/* Expert feed-forward block of a SwiGLU MoE layer in one call, over rows grouped by expert:
+ *   D[T,H] = down( silu(gate(x)) * up(x) ),  silu(g) = g / (1 + exp(-g)),
+ * with gate/up packed [I, H] and down packed [H, I] per expert.  Numerically the three
+ * lsg_gguf_grouped_gemm calls (Int strategy, bf16 outputs) with the activation computed in
+ * fp32 and stored as bf16 in between, which is how a caller of the reference's
+ * gguf_grouped_gemm (csrc/bindings_python.cu:552-611) builds the block; the reference fuses
+ * activation and quantizer only on its NVFP4 path (launch_silu_mul_to_nvfp4_grouped).
+ * Never synchronizes with the host.  Rows of experts without rows are untouched; all three
+ * pointers of an expert that has rows must be valid. */
+typedef struct lsg_gguf_moe_ffn_params {
+    int type;                        /* lsg_gguf_type of all three matrices            */
+    int num_experts;
+    int H;                           /* model width: K of gate/up, N of down           */
+    int I;                           /* expert width: N of gate/up, K of down          */
+    const void* A_base;              /* [total_tokens, H] bf16, rows grouped by expert */
+    void* D_base;                    /* [total_tokens, H] out_dtype                    */
+    const int32_t* expert_offsets;   /* [E+1], device                                  */
+    const void* const* gate_ptrs;    /* [E] device array of device pointers            */
+    const void* const* up_ptrs;
+    const void* const* down_ptrs;
+    int out_dtype;
+} lsg_gguf_moe_ffn_params;
+LSG_API size_t lsg_gguf_moe_ffn_workspace_bytes(int total_tokens, int H, int I, int num_experts);
+LSG_API int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_tokens, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* Ascending list of the experts that have rows, padded with -1 to `cap` entries.
  * Replaces build_active_expert_list, gguf_grouped_int.cu:156-187. */
 LSG_API int lsg_build_active_expert_list(const int32_t* expert_offsets, int num_experts, int cap,
@@ -347,7 +373,10 @@ LSG_API int lsg_moe_route(const float* logits, int num_tokens, int num_experts, 
 
 /* Stable grouping of the T*k (token, slot) pairs by expert: expert_offsets int32 [E+1],
  * perm int32 [T*k] (row -> pair), inv_perm int32 [T*k] (pair -> row).
- * counts_scratch: int32 [E]. */
+ * E <= 1024.  Pairs with an expert id outside [0, E) get no row.
+ * counts_scratch: int32 [lsg_moe_permutation_scratch_ints(T, k, E)] (per-chunk histograms
+ * of a counting sort over chunks of 256 pairs). */
+LSG_API long long lsg_moe_permutation_scratch_ints(int num_tokens, int top_k, int num_experts);
 LSG_API int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int top_k, int num_experts,
                                 int32_t* expert_offsets, int32_t* perm, int32_t* inv_perm,
                                 int32_t* counts_scratch, void* stream);

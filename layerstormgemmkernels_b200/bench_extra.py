@@ -92,10 +92,7 @@ def _moe(args, rank, world, dev, steps, warmup):
     logits_host = logits.cpu().pin_memory()
 
     def ffn(rows, offs):
-        gt = ops.gguf_grouped_gemm(rows, offs, gate_p, t, 1, I, H, 0)
-        u = ops.gguf_grouped_gemm(rows, offs, up_p, t, 1, I, H, 0)
-        act = torch.nn.functional.silu(gt.float()).mul_(u.float()).to(torch.bfloat16)
-        return ops.gguf_grouped_gemm(act, offs, down_p, t, 1, H, I, 0)
+        return ops.gguf_moe_ffn(rows, offs, gate_p, up_p, down_p, t, H, I)
 
     def layer(h, lg):
         if world == 1:

@@ -67,6 +67,13 @@ class GgufGroupedGemmParams(ctypes.Structure):
                 ("B_ptrs", ctypes.c_void_p), ("out_dtype", ctypes.c_int)]
 
 
+class GgufMoeFfnParams(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("num_experts", ctypes.c_int), ("H", ctypes.c_int), ("I", ctypes.c_int),
+                ("A_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p),
+                ("gate_ptrs", ctypes.c_void_p), ("up_ptrs", ctypes.c_void_p), ("down_ptrs", ctypes.c_void_p),
+                ("out_dtype", ctypes.c_int)]
+
+
 class Nvfp4GroupedGemmParams(ctypes.Structure):
     _fields_ = [("num_experts", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
                 ("A_base", ctypes.c_void_p), ("B_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p),
@@ -103,6 +110,8 @@ def _load():
         "lsg_nvfp4_sf_offsets": (ci, [vp, vp, ci, vp]),
         "lsg_gguf_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_grouped_gemm": (ci, [ctypes.POINTER(GgufGroupedGemmParams), ci, vp, sz, ci, vp]),
+        "lsg_gguf_moe_ffn_workspace_bytes": (sz, [ci, ci, ci, ci]),
+        "lsg_gguf_moe_ffn": (ci, [ctypes.POINTER(GgufMoeFfnParams), ci, vp, sz, vp]),
         "lsg_build_active_expert_list": (ci, [vp, ci, ci, vp, vp]),
         "lsg_build_mmq_tile_map": (ci, [vp, ci, ci, ci, vp, vp, vp]),
         "lsg_gguf_grouped_gemm_workspace_bytes_ex": (sz, [ci, ci, ci, ci]),
@@ -113,6 +122,7 @@ def _load():
         "lsg_nvfp4_sf_buffer_bytes": (sz, [ci, ci]),
         "lsg_nvfp4_reformat_scales": (ci, [vp, vp, ci, ci, vp]),
         "lsg_moe_route": (ci, [vp, ci, ci, ci, vp, vp, vp]),
+        "lsg_moe_permutation_scratch_ints": (ctypes.c_longlong, [ci, ci, ci]),
         "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_moe_permute": (ci, [vp, vp, ci, ci, ci, vp, vp]),
         "lsg_moe_unpermute": (ci, [vp, vp, vp, ci, ci, ci, vp, vp]),

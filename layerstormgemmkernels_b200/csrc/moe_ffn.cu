@@ -1,0 +1,149 @@
+// Expert feed-forward block of a SwiGLU MoE layer over rows already grouped by expert:
+//   D = down( silu(gate(x)) * up(x) ),   silu(g) = g / (1 + exp(-g)),
+// i.e. the three grouped GEMMs a caller of the reference issues through
+// gguf_grouped_gemm (csrc/bindings_python.cu:552-611) with the activation in between,
+// as ONE call.  The reference fuses the activation with the quantizer only on its NVFP4
+// path (launch_silu_mul_to_nvfp4_grouped, csrc/smxx/quant/bf16_to_nvfp4_grouped.cu); this is
+// the same idea for GGUF weights.  Numerics: gate and up outputs rounded to bf16, the
+// activation computed in fp32 and rounded to bf16, then the usual Q8_1 activation
+// quantization of the down projection - what the three separate calls produce.
+//
+// Two routes:
+//   * tensor cores with the weights decoded inside the GEMM (tc_fused.cu): one activation
+//     preparation, gate and up in one launch, SwiGLU fused into the preparation of the down
+//     GEMM's operand, one tile map for both launches;
+//   * otherwise (types without an in-kernel decoder, or few rows per expert) the three
+//     grouped GEMMs of this library back to back with a SwiGLU kernel in between.
+#include "common.cuh"
+#include "formats.cuh"
+#include "host.h"
+
+namespace lsg {
+
+namespace {
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// act = bf16( silu(g) * u ), eight values per thread.
+__global__ void __launch_bounds__(256)
+silu_mul_bf16_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ out, long long n_vec) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= n_vec) return;
+    const uint4 gr = __ldg(g + i), ur = __ldg(u + i);
+    const uint32_t gw[4] = {gr.x, gr.y, gr.z, gr.w}, uw[4] = {ur.x, ur.y, ur.z, ur.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float a[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float gv = __uint_as_float(h ? (gw[j] & 0xFFFF0000u) : (gw[j] << 16));
+            const float uv = __uint_as_float(h ? (uw[j] & 0xFFFF0000u) : (uw[j] << 16));
+            a[h] = (gv / (1.0f + expf(-gv))) * uv;
+        }
+        const __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
+        o[j] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+struct FfnLayout {
+    size_t map_off, map_bytes;      // tile map of the tensor-core route
+    size_t fused_off, fused_bytes;  // scratch of the tensor-core route
+    size_t g_off, u_off, act_off;   // bf16 [T, I] buffers of the composed route
+    size_t grouped_off, grouped_bytes;
+    size_t total;
+};
+
+FfnLayout ffn_layout(int T, int H, int I, int E) {
+    FfnLayout l = {};
+    const size_t t_max64 = static_cast<size_t>((T + 63) / 64 + E);
+    l.map_off = 0;
+    l.map_bytes = align256(2 * t_max64 * sizeof(int));
+    l.fused_off = l.map_bytes;
+    l.fused_bytes = tc_fused_moe_ffn_scratch_bytes(T, H, I);
+    // composed route shares the space after the map
+    const size_t ti = align256(static_cast<size_t>(T) * I * 2);
+    l.g_off = l.map_bytes;
+    l.u_off = l.g_off + ti;
+    l.act_off = l.u_off + ti;
+    l.grouped_off = l.act_off + ti;
+    const size_t g1 = lsg_gguf_grouped_gemm_workspace_bytes_ex(T, H, E, I);
+    const size_t g2 = lsg_gguf_grouped_gemm_workspace_bytes_ex(T, I, E, H);
+    l.grouped_bytes = align256(g1 > g2 ? g1 : g2);
+    const size_t composed = l.grouped_off + l.grouped_bytes;
+    const size_t fused = l.fused_off + l.fused_bytes;
+    l.total = composed > fused ? composed : fused;
+    return l;
+}
+
+}  // namespace
+
+}  // namespace lsg
+
+using namespace lsg;
+
+extern "C" size_t lsg_gguf_moe_ffn_workspace_bytes(int total_tokens, int H, int I, int num_experts) {
+    if (total_tokens <= 0 || H <= 0 || I <= 0 || num_experts <= 0) return 0;
+    return ffn_layout(total_tokens, H, I, num_experts).total;
+}
+
+extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_tokens, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    if (!p) return fail(LSG_ERR_INVALID, "gguf_moe_ffn: null params");
+    const int qk = gguf_block_values(p->type);
+    if (qk == 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_moe_ffn: unknown GGUF type %d", p->type);
+    if (p->out_dtype != LSG_DTYPE_BF16 && p->out_dtype != LSG_DTYPE_F32)
+        return fail(LSG_ERR_UNSUPPORTED, "gguf_moe_ffn: out_dtype must be bf16 or f32");
+    if (total_tokens < 0 || p->num_experts < 0 || p->H <= 0 || p->I <= 0)
+        return fail(LSG_ERR_INVALID, "gguf_moe_ffn: negative or zero shape");
+    if (total_tokens == 0 || p->num_experts == 0) return LSG_OK;
+    if (p->H % qk != 0 || p->I % qk != 0 || p->H % 32 != 0 || p->I % 32 != 0)
+        return fail(LSG_ERR_INVALID, "gguf_moe_ffn: H=%d and I=%d must be divisible by the block size %d (and by 32)",
+                    p->H, p->I, qk);
+    if (!p->A_base || !p->D_base || !p->expert_offsets || !p->gate_ptrs || !p->up_ptrs || !p->down_ptrs)
+        return fail(LSG_ERR_INVALID, "gguf_moe_ffn: null A/D/expert_offsets/weight pointer arrays");
+    const int T = total_tokens, E = p->num_experts, H = p->H, I = p->I;
+    const FfnLayout l = ffn_layout(T, H, I, E);
+    if (!workspace || workspace_bytes < l.total)
+        return fail(LSG_ERR_WORKSPACE, "gguf_moe_ffn: workspace too small (have %zu, need %zu)",
+                    workspace ? workspace_bytes : size_t(0), l.total);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_moe_ffn: workspace must be 256-byte aligned");
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int32_t* offs = static_cast<const int32_t*>(p->expert_offsets);
+
+    // the reference's rule for leaving the mat-vec kernels: more than 8 rows per expert on average
+    if (tc_fused_available(p->type) && T / E > 8) {
+        const int tile_m = tc_fused_grouped_tile_m(T, E);
+        const int t_max = (T + tile_m - 1) / tile_m + E;
+        int* tile_expert = reinterpret_cast<int*>(base + l.map_off);
+        int* tile_mstart = tile_expert + t_max;
+        int rc = build_mmq_tile_map(offs, E, tile_m, t_max, tile_expert, tile_mstart, s);
+        if (rc != LSG_OK) return rc;
+        return tc_fused_moe_ffn(p->type, T, E, H, I, p->A_base, p->gate_ptrs, p->up_ptrs, p->down_ptrs, offs,
+                                p->D_base, p->out_dtype, tile_expert, tile_mstart, t_max, tile_m,
+                                base + l.fused_off, l.fused_bytes, s);
+    }
+
+    lsg_gguf_grouped_gemm_params g = {};
+    g.type = p->type; g.strategy = LSG_GGUF_STRATEGY_INT; g.num_experts = E;
+    g.N = I; g.K = H; g.A_base = p->A_base; g.expert_offsets = offs; g.out_dtype = LSG_DTYPE_BF16;
+    g.D_base = base + l.g_off; g.B_ptrs = p->gate_ptrs;
+    int rc = lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
+    if (rc != LSG_OK) return rc;
+    g.D_base = base + l.u_off; g.B_ptrs = p->up_ptrs;
+    rc = lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
+    if (rc != LSG_OK) return rc;
+    const long long n_vec = static_cast<long long>(T) * I / 8;
+    LSG_CUDA_TRY(launch_kernel(silu_mul_bf16_kernel, dim3(static_cast<unsigned>((n_vec + 255) / 256)), dim3(256), 0, s,
+                               true, reinterpret_cast<const uint4*>(base + l.g_off),
+                               reinterpret_cast<const uint4*>(base + l.u_off),
+                               reinterpret_cast<uint4*>(base + l.act_off), n_vec));
+    g.N = H; g.K = I; g.A_base = base + l.act_off; g.D_base = p->D_base; g.B_ptrs = p->down_ptrs;
+    g.out_dtype = p->out_dtype;
+    return lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
+}

@@ -80,80 +80,94 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int32_t*
     }
 }
 
-// counts[e] = number of pairs routed to e.  One CTA per expert.
-__global__ void __launch_bounds__(256)
-moe_count_kernel(const int32_t* __restrict__ idx, int P, int32_t* __restrict__ counts) {
+// Stable grouping of the pairs by expert as a counting sort over chunks of 256 pairs:
+//   1. per-chunk histogram over the experts,
+//   2. per expert, exclusive scan of the histograms over the chunks (in place) and the
+//      exclusive scan of the totals over the experts (= expert_offsets),
+//   3. per chunk, each pair's rank among the earlier pairs of the same expert:
+//      earlier chunks (step 2), earlier warps of the chunk, earlier lanes of the warp.
+// Pairs whose expert id lies outside [0, E) are ignored.
+constexpr int kChunk = 256;
+
+__global__ void __launch_bounds__(kChunk)
+moe_chunk_hist_kernel(const int32_t* __restrict__ idx, int P, int E, int32_t* __restrict__ hist) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int e = blockIdx.x;
-    int c = 0;
-    for (int i = threadIdx.x; i < P; i += blockDim.x) c += (idx[i] == e);
-    __shared__ int red[8];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+    __shared__ int h[1024];
+    for (int e = threadIdx.x; e < E; e += kChunk) h[e] = 0;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int s = 0;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) s += red[w];
-        counts[e] = s;
+    const int i = blockIdx.x * kChunk + threadIdx.x;
+    if (i < P) {
+        const int e = idx[i];
+        if (e >= 0 && e < E) atomicAdd(&h[e], 1);
     }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += kChunk) hist[static_cast<size_t>(blockIdx.x) * E + e] = h[e];
 }
 
-// expert_offsets[0..E] = exclusive scan of counts.  One warp.
-__global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int E, int32_t* __restrict__ offsets) {
+// One CTA of 1024 threads, thread e owns expert e (E <= 1024).
+__global__ void __launch_bounds__(1024)
+moe_chunk_scan_kernel(int32_t* __restrict__ hist, int n_chunks, int E, int32_t* __restrict__ offsets) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int lane = threadIdx.x & 31;
-    int carry = 0;
-    for (int base = 0; base < E; base += 32) {
-        const int e = base + lane;
-        const int c = e < E ? counts[e] : 0;
-        int incl = c;
+    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
+    int total = 0;
+    if (e < E) {
+        for (int c = 0; c < n_chunks; ++c) {
+            const size_t at = static_cast<size_t>(c) * E + e;
+            const int v = hist[at];
+            hist[at] = total;
+            total += v;
+        }
+    }
+    // exclusive scan of the totals over the experts
+    __shared__ int wsum[32];
+    int incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = wsum[lane];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
         }
-        if (e < E) offsets[e] = carry + incl - c;
-        carry += __shfl_sync(0xffffffffu, incl, 31);
+        wsum[lane] = w;  // inclusive over warps
     }
-    if (lane == 0) offsets[E] = carry;
+    __syncthreads();
+    const int before = warp > 0 ? wsum[warp - 1] : 0;
+    if (e < E) offsets[e] = before + incl - total;
+    if (e == E - 1) offsets[E] = before + incl;
 }
 
-// Stable placement: CTA e walks the pairs in order and gives the j-th pair routed to e
-// the row offsets[e] + j.  perm[row] = pair, inv[pair] = row.
-__global__ void __launch_bounds__(256)
-moe_place_kernel(const int32_t* __restrict__ idx, int P, const int32_t* __restrict__ offsets,
-                 int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+// perm[row] = pair, inv[pair] = row.
+__global__ void __launch_bounds__(kChunk)
+moe_place_kernel(const int32_t* __restrict__ idx, int P, int E, const int32_t* __restrict__ chunk_base,
+                 const int32_t* __restrict__ offsets, int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int e = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    __shared__ int wcount[8];
-    __shared__ int base_sh;
-    if (threadIdx.x == 0) base_sh = offsets[e];
+    extern __shared__ int whist[];  // [8 warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int j = threadIdx.x; j < (kChunk / 32) * E; j += kChunk) whist[j] = 0;
     __syncthreads();
-    for (int start = 0; start < P; start += blockDim.x) {
-        const int i = start + threadIdx.x;
-        const bool hit = i < P && idx[i] == e;
-        const unsigned m = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) wcount[warp] = __popc(m);
-        __syncthreads();
+    const int i = blockIdx.x * kChunk + threadIdx.x;
+    int e = i < P ? idx[i] : -1;
+    if (e >= E) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) whist[warp * E + e] = __popc(same);
+    __syncthreads();
+    if (e >= 0) {
         int before = 0;
-        for (int w = 0; w < warp; ++w) before += wcount[w];
-        if (hit) {
-            const int row = base_sh + before + __popc(m & ((1u << lane) - 1u));
-            perm[row] = i;
-            inv[i] = row;
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int s = 0;
-            for (int w = 0; w < nw; ++w) s += wcount[w];
-            base_sh += s;
-        }
-        __syncthreads();
+        for (int w = 0; w < warp; ++w) before += whist[w * E + e];
+        const int row = offsets[e] + chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + before + rank;
+        perm[row] = i;
+        inv[i] = row;
     }
 }
 
@@ -209,6 +223,13 @@ extern "C" int lsg_moe_route(const float* logits, int num_tokens, int num_expert
     return LSG_OK;
 }
 
+extern "C" long long lsg_moe_permutation_scratch_ints(int num_tokens, int top_k, int num_experts) {
+    if (num_tokens < 0 || top_k < 0 || num_experts < 1) return 0;
+    const long long P = static_cast<long long>(num_tokens) * top_k;
+    const long long n_chunks = P > 0 ? (P + kChunk - 1) / kChunk : 1;
+    return n_chunks * num_experts;
+}
+
 extern "C" int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int top_k, int num_experts,
                                    int32_t* expert_offsets, int32_t* perm, int32_t* inv_perm,
                                    int32_t* counts_scratch, void* stream) {
@@ -217,12 +238,16 @@ extern "C" int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int 
     const int P = num_tokens * top_k;
     if (P > 0 && (!topk_idx || !perm || !inv_perm)) return fail(LSG_ERR_INVALID, "moe_permutation: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    LSG_CUDA_TRY(launch_kernel(moe_count_kernel, dim3(num_experts), dim3(256), 0, s, true, topk_idx, P,
-                               counts_scratch));
-    LSG_CUDA_TRY(launch_kernel(moe_offsets_kernel, dim3(1), dim3(32), 0, s, true,
-                               static_cast<const int32_t*>(counts_scratch), num_experts, expert_offsets));
+    if (num_experts > 1024) return fail(LSG_ERR_INVALID, "moe_permutation: at most 1024 experts (E=%d)", num_experts);
+    const int n_chunks = P > 0 ? (P + kChunk - 1) / kChunk : 1;
+    LSG_CUDA_TRY(launch_kernel(moe_chunk_hist_kernel, dim3(n_chunks), dim3(kChunk), 0, s, true, topk_idx, P,
+                               num_experts, counts_scratch));
+    LSG_CUDA_TRY(launch_kernel(moe_chunk_scan_kernel, dim3(1), dim3(1024), 0, s, true, counts_scratch, n_chunks,
+                               num_experts, expert_offsets));
     if (P > 0)
-        LSG_CUDA_TRY(launch_kernel(moe_place_kernel, dim3(num_experts), dim3(256), 0, s, true, topk_idx, P,
+        LSG_CUDA_TRY(launch_kernel(moe_place_kernel, dim3(n_chunks), dim3(kChunk),
+                                   static_cast<size_t>(kChunk / 32) * num_experts * sizeof(int), s, true, topk_idx,
+                                   P, num_experts, static_cast<const int32_t*>(counts_scratch),
                                    static_cast<const int32_t*>(expert_offsets), perm, inv_perm));
     return LSG_OK;
 }

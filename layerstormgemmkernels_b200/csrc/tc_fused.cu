@@ -51,6 +51,9 @@ constexpr int kHdrRingBytes = 4 * WM * 16; // block headers of four consecutive 
 struct FusedArgs {
     const uint8_t* W;             // dense: packed rows
     const void* const* B_ptrs;    // grouped: per-expert packed matrices
+    const void* const* B_ptrs2;   // optional second set (same shape): weight tiles from split_wt on come
+    int split_wt;                 //   from it and their outputs land col2_off columns further right
+    int col2_off;
     long long row_bytes;
     void* C;
     int ldc;
@@ -521,8 +524,10 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             if (!im.live) continue;
             const int kb0 = im.ks * a.kb_per_split;
             const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
-            const uint8_t* base = a.B_ptrs ? static_cast<const uint8_t*>(a.B_ptrs[im.expert]) : a.W;
-            const int n = min(im.wt * WM + r, a.N - 1);
+            const bool second = a.B_ptrs2 != nullptr && im.wt >= a.split_wt;
+            const uint8_t* base = a.B_ptrs ? static_cast<const uint8_t*>((second ? a.B_ptrs2 : a.B_ptrs)[im.expert])
+                                           : a.W;
+            const int n = min((second ? im.wt - a.split_wt : im.wt) * WM + r, a.N - 1);
             const uint8_t* row = base ? base + static_cast<long long>(n) * a.row_bytes : nullptr;
             // The register-staged decoder issues 16-byte vector loads; a matrix that is not
             // 16-byte aligned goes through the byte-wise generic decoder instead.  The choice
@@ -561,8 +566,10 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 break;
             }
             tc_fence_after();
-            const int n = im.wt * WM + warp * 32 + lane;   // this thread's output column
-            const bool n_ok = n < a.N;
+            const bool second = a.B_ptrs2 != nullptr && im.wt >= a.split_wt;
+            const int n_local = (second ? im.wt - a.split_wt : im.wt) * WM + warp * 32 + lane;
+            const bool n_ok = n_local < a.N;
+            const int n = n_local + (second ? a.col2_off : 0);   // this thread's output column
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * a.nt;
 
             if (a.ksplit == 1) {
@@ -708,6 +715,60 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, lon
             int k = __float2int_rn(t);
             // same integer as rn(fl(x / d)): the product with the reciprocal only differs
             // next to a half-integer, and there the true quotient decides
+            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + hh] / d);
+            r[hh] = dh * static_cast<float>(k);
+        }
+        p[i] = pack_h2(r[0], r[1]);
+    }
+    reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
+}
+
+// SwiGLU between the two halves of an expert feed-forward block, fused with the preparation
+// of the second GEMM's activation: gu[T, 2I] bf16 holds gate | up; per element
+//   act = bf16( silu(g) * u )  with silu(g) = g / (1 + exp(-g)) in fp32
+// (what a caller computing the activation in fp32 and storing bf16 gets), then the Q8_1 round
+// trip of act over 32-value blocks along I, as fp16.  Four lanes per block, eight values each.
+__global__ void __launch_bounds__(256)
+swiglu_prep_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ out, long long n_blocks, int I) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const bool live = task < n_blocks * 4;
+    const long long tk = live ? task : 0;
+    const int per_row = I / 8;
+    const long long row = tk / per_row;
+    const int c8 = static_cast<int>(tk - row * per_row);
+    const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gu + row * 2 * I + c8 * 8));
+    const uint4 uraw = __ldg(reinterpret_cast<const uint4*>(gu + row * 2 * I + I + c8 * 8));
+    const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w}, uw[4] = {uraw.x, uraw.y, uraw.z, uraw.w};
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const float g = __uint_as_float(hh ? (gw[i] & 0xFFFF0000u) : (gw[i] << 16));
+            const float u = __uint_as_float(hh ? (uw[i] & 0xFFFF0000u) : (uw[i] << 16));
+            const float a = (g / (1.0f + expf(-g))) * u;
+            v[2 * i + hh] = __bfloat162float(__float2bfloat16_rn(a));
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) return;
+    const float d = amax / 127.0f;
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    const float dh = __half2float(__float2half(d));
+    uint32_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float r[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            const float t = v[2 * i + hh] * rcp;
+            int k = __float2int_rn(t);
             if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + hh] / d);
             r[hh] = dh * static_cast<float>(k);
         }
@@ -908,6 +969,75 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
     a.status = device_status_word();
     return launch_fused(type, tmX, a, s);
+}
+
+// Expert feed-forward block on rows grouped by expert: D = down( silu(gate(x)) * up(x) ).
+// One activation preparation, one launch for gate and up together (weight tiles of both
+// matrices side by side, outputs gate | up in a bf16 scratch), SwiGLU fused with the second
+// preparation, one launch for down.  The same numbers as three grouped GEMMs with the
+// activation computed in fp32 and stored as bf16 in between.
+size_t tc_fused_moe_ffn_scratch_bytes(long long T, int H, int I) {
+    return align256(static_cast<size_t>(T) * H * 2) + align256(static_cast<size_t>(T) * 2 * I * 2) +
+           align256(static_cast<size_t>(T) * I * 2);
+}
+
+int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, const void* const* gate_ptrs,
+                     const void* const* up_ptrs, const void* const* down_ptrs, const int32_t* expert_offsets,
+                     void* D, int out_dtype, const int* tile_expert, const int* tile_mstart, int t_max, int tile_m,
+                     void* scratch, size_t scratch_bytes, cudaStream_t s) {
+    if (T == 0) return LSG_OK;
+    const size_t need = tc_fused_moe_ffn_scratch_bytes(T, H, I);
+    if (!scratch || scratch_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "gguf_moe_ffn: scratch too small (have %zu, need %zu)",
+                    scratch ? scratch_bytes : size_t(0), need);
+    uint8_t* base = static_cast<uint8_t*>(scratch);
+    __half* x16 = reinterpret_cast<__half*>(base);
+    __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(base + align256(static_cast<size_t>(T) * H * 2));
+    __half* act16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(gu) + align256(static_cast<size_t>(T) * 2 * I * 2));
+    const bool staged = staged_decoder(type);
+    const int qk = gguf_block_values(type), qb = gguf_block_bytes(type);
+
+    // gate | up
+    long long nb = static_cast<long long>(T) * (H / 32);
+    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
+                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
+                               static_cast<unsigned int*>(nullptr), 0));
+    CUtensorMap tmX;
+    int rc = make_map(&tmX, x16, T, H, tile_m);
+    if (rc != LSG_OK) return rc;
+    Plan p = make_plan(T, tile_m, t_max, I, H, false, staged);
+    FusedArgs a = {};
+    a.B_ptrs = gate_ptrs; a.B_ptrs2 = up_ptrs; a.split_wt = p.n_wtiles; a.col2_off = I;
+    a.row_bytes = static_cast<long long>(H / qk) * qb;
+    a.C = gu; a.ldc = 2 * I; a.out_dtype = LSG_DTYPE_BF16;
+    a.K = H; a.N = I; a.M = T;
+    a.nt = tile_m; a.n_wtiles = 2 * p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages;
+    a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.ksplit = 1; a.kb_per_split = p.kb_per_split;
+    a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
+    a.status = device_status_word();
+    rc = launch_fused(type, tmX, a, s);
+    if (rc != LSG_OK) return rc;
+
+    // SwiGLU + preparation, then down
+    nb = static_cast<long long>(T) * (I / 32);
+    LSG_CUDA_TRY(launch_kernel(swiglu_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s,
+                               true, static_cast<const __nv_bfloat16*>(gu), act16, nb, I));
+    CUtensorMap tmA;
+    rc = make_map(&tmA, act16, T, I, tile_m);
+    if (rc != LSG_OK) return rc;
+    p = make_plan(T, tile_m, t_max, H, I, false, staged);
+    FusedArgs b = {};
+    b.B_ptrs = down_ptrs;
+    b.row_bytes = static_cast<long long>(I / qk) * qb;
+    b.C = D; b.ldc = H; b.out_dtype = out_dtype;
+    b.K = I; b.N = H; b.M = T;
+    b.nt = tile_m; b.n_wtiles = p.n_wtiles; b.t_tiles = t_max; b.stages = p.stages;
+    b.raw_depth = p.raw_depth; b.raw_bytes = p.raw_bytes;
+    b.ksplit = 1; b.kb_per_split = p.kb_per_split;
+    b.tile_expert = tile_expert; b.tile_mstart = tile_mstart; b.expert_offsets = expert_offsets;
+    b.status = device_status_word();
+    return launch_fused(type, tmA, b, s);
 }
 
 }  // namespace lsg

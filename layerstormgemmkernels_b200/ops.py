@@ -230,6 +230,35 @@ def gguf_grouped_gemm(A_base, expert_offsets, b_ptrs, type, strategy, N, K, forc
     return D
 
 
+def gguf_moe_ffn(A_base, expert_offsets, gate_ptrs, up_ptrs, down_ptrs, type, H, I, out_dtype=torch.bfloat16):
+    """Expert feed-forward block over rows grouped by expert, one call:
+    down( silu(gate(x)) * up(x) ) with gate/up packed [I, H] and down packed [H, I] per expert
+    (`*_ptrs`: CUDA int64 tensors of device pointers).  The same numbers as three
+    gguf_grouped_gemm calls (Int strategy) with the activation computed in fp32 and stored as
+    bf16 in between.  An addition to the reference's operator set."""
+    _require(A_base.is_cuda and A_base.dtype == torch.bfloat16 and A_base.dim() == 2 and A_base.is_contiguous(),
+             "gguf_moe_ffn: A_base must be contiguous BF16 [T, H] on CUDA")
+    _require(A_base.size(1) == H, "gguf_moe_ffn: A_base.size(1) != H")
+    _require(expert_offsets.is_cuda and expert_offsets.dtype == torch.int32,
+             "gguf_moe_ffn: expert_offsets must be int32 on CUDA")
+    E = gate_ptrs.numel()
+    for name, ptrs in (("gate_ptrs", gate_ptrs), ("up_ptrs", up_ptrs), ("down_ptrs", down_ptrs)):
+        _require(ptrs.is_cuda and ptrs.dtype == torch.int64 and ptrs.numel() == E,
+                 f"gguf_moe_ffn: {name} must be int64 (device pointers) on CUDA, one per expert")
+    _require(expert_offsets.numel() == E + 1, "gguf_moe_ffn: expert_offsets must be [num_experts+1]")
+    T = A_base.size(0)
+    D = torch.empty((T, H), dtype=out_dtype, device=A_base.device)
+    p = capi.GgufMoeFfnParams(
+        type=int(type), num_experts=E, H=int(H), I=int(I), A_base=A_base.data_ptr(), D_base=D.data_ptr(),
+        expert_offsets=expert_offsets.data_ptr(), gate_ptrs=gate_ptrs.data_ptr(), up_ptrs=up_ptrs.data_ptr(),
+        down_ptrs=down_ptrs.data_ptr(),
+        out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+    ws_bytes = _lib.lsg_gguf_moe_ffn_workspace_bytes(T, int(H), int(I), E)
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
+    capi.check(_lib.lsg_gguf_moe_ffn(ctypes.byref(p), T, _ptr(ws), ws_bytes, _stream()))
+    return D
+
+
 def build_active_expert_list(expert_offsets, cap):
     """int32 [cap]: ascending experts with rows, -1 padded (device-side, no sync)."""
     E = expert_offsets.numel() - 1
@@ -344,7 +373,8 @@ def moe_permutation(topk_idx, num_experts):
     offs = torch.empty((num_experts + 1,), dtype=torch.int32, device=dev)
     perm = torch.empty((T * k,), dtype=torch.int32, device=dev)
     inv = torch.empty((T * k,), dtype=torch.int32, device=dev)
-    scratch = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+    n_scratch = _lib.lsg_moe_permutation_scratch_ints(T, k, int(num_experts))
+    scratch = torch.empty((max(int(n_scratch), 1),), dtype=torch.int32, device=dev)
     capi.check(_lib.lsg_moe_permutation(_ptr(topk_idx), T, k, int(num_experts), _ptr(offs), _ptr(perm),
                                         _ptr(inv), _ptr(scratch), _stream()))
     return offs, perm, inv

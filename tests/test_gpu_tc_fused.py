@@ -152,3 +152,63 @@ def test_fused_prefill_config_shape_sampled(ops, weight_path):
     cols = np.r_[0:8, 7000:7008, N - 8:N]
     ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bits_of(A)[rows]), W[cols], K)
     assert np.abs(got[np.ix_(rows, cols)] - ref).max() <= TOL_TC * np.abs(ref).max()
+
+
+def _ffn_case(name, counts, H, I, seed):
+    E = len(counts)
+    offs = np.zeros(E + 1, dtype=np.int32)
+    offs[1:] = np.cumsum(counts)
+    A = (torch.randn(int(offs[-1]), H, generator=torch.Generator().manual_seed(seed)) * 0.5).to(torch.bfloat16).cuda()
+    # real quantized weights of N(0, 0.05): with random block bytes the activations of the second
+    # GEMM leave the fp16 range of the tensor-core operands
+    quant = {"Q4_K": Q.quantize_q4_k, "Q6_K": Q.quantize_q6_k, "Q8_0": Q.quantize_q8_0, "Q4_0": Q.quantize_q4_0}[name]
+    rng = np.random.default_rng(seed)
+    ws = [[torch.from_numpy(quant((rng.standard_normal((n, k)) * 0.05).astype(np.float32))).cuda()
+           for (n, k) in ((I, H), (I, H), (H, I))] for e in range(E)]
+    ptr = lambda j: torch.tensor([w[j].data_ptr() for w in ws], dtype=torch.int64, device="cuda")
+    return A, torch.from_numpy(offs).cuda(), ws, ptr(0), ptr(1), ptr(2)
+
+
+@pytest.mark.parametrize("name,counts", [
+    ("Q4_K", [70, 0, 3, 130, 257]),      # tensor-core route, ragged tiles, an empty expert
+    ("Q4_K", [2, 1, 0, 3]),              # few rows per expert: composed from the grouped mat-vec
+    ("Q6_K", [40, 25, 0, 64]),           # no in-kernel decoder: composed route on tensor cores
+    ("Q8_0", [9, 30]),
+])
+def test_moe_ffn_equals_three_grouped_gemms(ops, name, counts):
+    """One-call expert block against the three grouped GEMMs with SwiGLU in between."""
+    H, I = 512, 256
+    A, offs, ws, gp, up, dp = _ffn_case(name, counts, H, I, seed=7)
+    t = T[name]
+    got = ops.gguf_moe_ffn(A, offs, gp, up, dp, t, H, I, out_dtype=torch.float32)
+    g = ops.gguf_grouped_gemm(A, offs, gp, t, 1, I, H, 0)
+    u = ops.gguf_grouped_gemm(A, offs, up, t, 1, I, H, 0)
+    act = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+    ref = ops.gguf_grouped_gemm(act, offs, dp, t, 1, H, I, 0, out_dtype=torch.float32)
+    live = torch.zeros(A.size(0), dtype=torch.bool, device="cuda")
+    o = offs.cpu().numpy()
+    for e in range(len(counts)):
+        live[o[e]:o[e + 1]] = True
+    scale = ref[live].abs().max().item()
+    # both sides round gate/up to bf16 before the activation; a last-bit difference there moves
+    # the activation by one bf16 ulp, hence the bf16-sized slack on top of the GEMM bound
+    assert (got[live] - ref[live]).abs().max().item() <= (TOL_TC + 2.0 ** -8) * scale
+
+
+def test_moe_ffn_vs_oracle_small(ops):
+    """End to end against the CPU oracle: Q8_1 mat-vec oracle for each projection, activation
+    in fp32 with bf16 rounding in between."""
+    name, H, I = "Q4_K", 256, 256
+    counts = [20, 33]
+    A, offs, ws, gp, up, dp = _ffn_case(name, counts, H, I, seed=11)
+    got = ops.gguf_moe_ffn(A, offs, gp, up, dp, T[name], H, I, out_dtype=torch.float32).cpu().numpy()
+    o = offs.cpu().numpy()
+    for e in range(len(counts)):
+        rows = slice(int(o[e]), int(o[e + 1]))
+        wg, wu, wd = (w.cpu().numpy() for w in ws[e])
+        xq = oracle.quantize_q8_1(bits_of(A)[rows])
+        g = torch.from_numpy(oracle.mmvq(T[name], xq, wg, H).astype(np.float32)).to(torch.bfloat16)
+        u = torch.from_numpy(oracle.mmvq(T[name], xq, wu, H).astype(np.float32)).to(torch.bfloat16)
+        act = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+        ref = oracle.mmvq(T[name], oracle.quantize_q8_1(act.view(torch.int16).numpy().view(np.uint16)), wd, I)
+        assert np.abs(got[rows] - ref).max() <= (TOL_TC + 2.0 ** -7) * np.abs(ref).max()
