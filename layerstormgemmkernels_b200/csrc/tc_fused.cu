@@ -5,9 +5,12 @@
 // round trip, i.e. the reference's integer result (csrc/sm120/gemm/gguf/mmq_mma/
 // mmq_kernel_32aligned.cuh:34-169, gguf_mmvq.cu:66-187) up to one fp16 rounding per operand.
 // The difference is where w16 comes from: here the packed GGUF blocks are read straight from
-// global memory by eight decoder warps, which write fp16 tiles in the 128-byte-swizzled K-major
-// layout the tensor core reads.  No fp16 copy of the weights ever exists in HBM, so the
-// weights cost their packed 4.5-8.5 bits per value of traffic.
+// global memory by eight decoder warps, dequantized in registers and stored into TENSOR
+// MEMORY (tcgen05.st), from where tcgen05.mma takes them as its A operand.  No fp16 copy of
+// the weights exists in HBM (they cost their packed 4.5-8.5 bits per value of traffic) nor in
+// shared memory: the shared-memory port, which limits a tcgen05 GEMM with both operands in
+// shared memory (128 x 256 x 64 tile: 48 KB read + 48 KB written per 512 tensor cycles at
+// 128 B/clk), only carries the token tile.
 //
 // The roles are swapped with respect to the usual GEMM: the WEIGHT rows are the M = 128 side
 // of tcgen05.mma and the token rows the N side (32..256).  A decode batch of a few tokens then
@@ -16,19 +19,23 @@
 //
 //   warps 0-3   epilogue: tcgen05.ld (lane = weight row, column = token), stores transposed
 //               into C (32 lanes = 32 consecutive output columns of one token)
-//   warp 4      TMA producer: one (64 x NT) box of x16 per stage
-//   warp 5      MMA issuer: 4 x tcgen05.mma.cta_group::1.kind::f16 (M128, N = NT, K16) per stage
-//   warps 6-13  weight decoders: thread (row r, half h) turns 32 packed values of its row into
-//               four 16-byte chunks per 64-value K block; loads run two K blocks ahead
-// A stage is "full" after nine arrivals (eight decoder warps + the TMA transaction); it is
-// released by tcgen05.commit.  Two accumulators alternate so the epilogue overlaps the next
-// tile.  All waits are time-limited; a time-out ends every role and is reported in the status
-// word.
+//   warp 4      TMA producer: one (64 x NT) box of x16 per stage into shared memory
+//   warp 5      MMA issuer: 4 x tcgen05.mma.cta_group::1.kind::f16 (M128, N = NT, K16) per
+//               stage, A from tensor memory, B through a shared-memory descriptor
+//   warps 6-13  weight decoders: warp w owns the 32 tensor-memory lanes (= weight rows) of its
+//               quadrant w % 4 and one half of every 64-value K block; per K block a thread
+//               writes its 32 fp16 values as 16 packed columns of its lane
+// Tensor memory (512 columns): the accumulators in columns 0..255 (two of NT <= 128 columns,
+// alternating so the epilogue overlaps the next tile, or one of 256), the weight ring in
+// columns 256..511 (8 stages x 32 columns).  A stage is "full" after nine arrivals (eight
+// decoder warps + the TMA transaction); tcgen05.commit releases it.  All waits are
+// time-limited; a time-out ends every role and is reported in the status word.
 //
 // Small token counts with few weight rows would leave most SMs idle, so the K range of an
-// output tile can be split over several CTAs.  Each split stores its fp32 partial tile; the
-// CTA that arrives last at the tile's counter adds the partials in split order (deterministic)
-// and writes C.  The counters are zeroed by the activation-preparation kernel of the same call.
+// output tile can be split over several CTAs.  Each split stores its fp32 partial tile; per
+// 32-row slice the warp that arrives last at the slice's counter adds the partials in split
+// order (deterministic) and writes C.  The counters are zeroed by the activation-preparation
+// kernel of the same call.
 #include "common.cuh"
 #include "formats.cuh"
 #include "host.h"
@@ -43,10 +50,13 @@ namespace {
 constexpr int WM = 128;                  // weight rows per tile
 constexpr int kDecWarps = 8;
 constexpr int kFusedThreads = (6 + kDecWarps) * 32;
-constexpr int kWBytes = WM * BK * 2;     // 16 KB of fp16 weights per stage
-constexpr int kMaxStages = 8;
-constexpr int kRawSlotBytes = WM * 32;     // 32 packed bytes per weight row and K block (Q4_K)
-constexpr int kHdrRingBytes = 4 * WM * 16; // block headers of four consecutive 256-value blocks
+constexpr int kMaxStages = 8;               // weight ring in tensor memory: 8 x 32 columns
+constexpr int kTmemCols = 512;
+constexpr int kAColBase = 256;              // first column of the weight ring
+constexpr int kAColsPerStage = BK / 2;      // 64 fp16 of a row = 32 packed columns
+constexpr int kDecThreads = kDecWarps * 32;
+constexpr int kRawSlotBytes = kDecThreads * 16;     // 16 packed bytes per decoder thread and K block (Q4_K)
+constexpr int kHdrRingBytes = 4 * kDecThreads * 16; // block headers of four consecutive 256-value blocks, per thread
 
 struct FusedArgs {
     const uint8_t* W;             // dense: packed rows
@@ -75,9 +85,6 @@ struct FusedArgs {
     unsigned int* status;
 };
 
-__device__ __forceinline__ void fence_proxy_async_smem() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 // True in exactly one lane of the (converged) warp.
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
@@ -90,14 +97,24 @@ __device__ __forceinline__ bool elect_one() {
         : "=r"(pred));
     return pred != 0;
 }
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+// Eight 32-bit columns of this thread's tensor-memory lane (the warp's lane quadrant).
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
 }
-__device__ __forceinline__ uint4 ldg128(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: A is M x 16 fp16, row m in lane m, two values per column.
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 v = __floats2half2_rn(a, b);
@@ -111,7 +128,6 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 template <int T>
 struct DecGeneric {
     // Generic decoder: no register staging, the packed bytes are read while decoding.
-    static constexpr bool kFast = false;
     struct Regs {
         const uint8_t* blk;
         int c;
@@ -147,67 +163,6 @@ struct DecGeneric {
     }
 };
 
-template <int T>
-struct Dec : DecGeneric<T> {};
-
-// Q4_K: 144-byte blocks {fp16 d, fp16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of
-// nibbles}; K block kb of a row is nibble pair p = kb % 4: low nibbles of qs[32p..32p+31]
-// are values 64p..64p+31 (half 0), high nibbles values 64p+32..64p+63 (half 1)
-// (csrc/formats/q4k_format.h:112-133).  Blocks are 16-byte aligned whenever the matrix is.
-template <>
-struct Dec<LSG_GGUF_Q4_K> {
-    static constexpr bool kFast = true;
-    struct Regs {
-        uint4 hdr, q0, q1;
-    };
-    __device__ static __forceinline__ Regs load(const uint8_t* row, int kb, int, int) {
-        Regs r;
-        const uint8_t* blk = row + static_cast<long long>(kb >> 2) * 144;
-        r.hdr = ldg128(blk);
-        r.q0 = ldg128(blk + 16 + (kb & 3) * 32);
-        r.q1 = ldg128(blk + 32 + (kb & 3) * 32);
-        return r;
-    }
-    __device__ static __forceinline__ uint32_t scale_byte(const uint4& hdr, int j) {
-        const uint32_t w = j < 4 ? hdr.y : (j < 8 ? hdr.z : hdr.w);
-        return (w >> (8 * (j & 3))) & 0xFFu;
-    }
-    __device__ static __forceinline__ void emit(const Regs& r, int c /* sub-block 0..7 */, uint4 (&out)[4]) {
-        // 6-bit scale and min of sub-block c (csrc/formats/kquant_common.h:36-46)
-        uint32_t sc, mn;
-        if (c < 4) {
-            sc = scale_byte(r.hdr, c) & 63u;
-            mn = scale_byte(r.hdr, c + 4) & 63u;
-        } else {
-            const uint32_t hi = scale_byte(r.hdr, c + 4);
-            sc = (hi & 0x0Fu) | ((scale_byte(r.hdr, c - 4) >> 6) << 4);
-            mn = (hi >> 4) | ((scale_byte(r.hdr, c) >> 6) << 4);
-        }
-        const float d = __half2float(__ushort_as_half(static_cast<unsigned short>(r.hdr.x & 0xFFFFu)));
-        const float dmin = __half2float(__ushort_as_half(static_cast<unsigned short>(r.hdr.x >> 16)));
-        const __half2 ds = __float2half2_rn(d * static_cast<float>(sc));
-        const __half2 nms = __float2half2_rn(-(dmin * static_cast<float>(mn)));
-        const __half2 k1024 = __float2half2_rn(1024.0f);
-        const uint32_t q[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
-        uint32_t o[16];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t nib = ((c & 1) ? (q[i] >> 4) : q[i]) & 0x0F0F0F0Fu;
-            // bytes -> fp16 1024 + q by placing each under the exponent byte 0x64
-            uint32_t lo = __byte_perm(nib, 0x64646464u, 0x4140);
-            uint32_t hi = __byte_perm(nib, 0x64646464u, 0x4342);
-            __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo), k1024);
-            __half2 b = __hsub2(*reinterpret_cast<__half2*>(&hi), k1024);
-            a = __hfma2(a, ds, nms);
-            b = __hfma2(b, ds, nms);
-            o[2 * i] = *reinterpret_cast<uint32_t*>(&a);
-            o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) out[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-    }
-};
-
 // Work item -> tile coordinates.  Items are ordered weight tile fastest, then K split, then
 // token tile, so CTAs running together share a token tile (and, grouped, an expert).
 struct Item {
@@ -239,43 +194,75 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
     return it;
 }
 
-// One item's K range for one decoder thread: row `row`, half `h` of every 64-value K block.
-// Three register sets rotate by name (the loop body is written out three times): copying a
-// set whose loads are still in flight would wait for them and collapse the lookahead.
-// Lookahead loads past the end re-read the last block instead of being skipped, so no load
-// is conditional.  Returns false after a wait timed out.
+// Ring position shared by the roles: stage index and how often the ring has wrapped.
+struct Ring {
+    int s;
+    uint32_t lap;
+    int n;
+    __device__ __forceinline__ void advance() {
+        if (++s == n) {
+            s = 0;
+            ++lap;
+        }
+    }
+};
+
+// What a decoder thread needs to publish a K block: barriers, its tensor-memory lane base
+// (lane quadrant of the warp) and the status word.
+struct DecCtx {
+    uint64_t* full;
+    uint64_t* empty;
+    uint32_t tmem_a;        // tensor-memory address of column kAColBase in this warp's lane quadrant
+    unsigned int* status;
+    uint32_t hint;
+};
+
+// Waits until the stage is free, stores 2 x 8 packed columns of this thread's lane (column
+// offsets c0 and c1 inside the stage), and arrives on the stage's "full" barrier.
+__device__ __forceinline__ bool publish_stage(const DecCtx& c, Ring& ring, const uint32_t* lo, uint32_t c0,
+                                              const uint32_t* hi, uint32_t c1) {
+    if (ring.lap > 0 &&
+        !__all_sync(0xffffffffu, mbar_wait_bounded(&c.empty[ring.s], (ring.lap - 1) & 1, c.status, kDevWaitEmpty, c.hint)))
+        return false;
+    tc_fence_after();  // the MMAs that last read this stage are ordered before the stores
+    const uint32_t col = c.tmem_a + static_cast<uint32_t>(ring.s * kAColsPerStage);
+    tmem_st8(col + c0, lo);
+    tmem_st8(col + c1, hi);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(&c.full[ring.s]);
+    ring.advance();
+    return true;
+}
+
+// One item's K range for one decoder thread: row `row`, half `h` (32 consecutive values) of
+// every 64-value K block, any type, any alignment.  Three register sets rotate by name (the
+// loop body is written out three times): copying a set whose loads are still in flight would
+// wait for them and collapse the lookahead.  Lookahead loads past the end re-read the last
+// block instead of being skipped, so no load is conditional.  Returns false after a time-out.
 template <class D>
-__device__ __forceinline__ bool decode_rows(const FusedArgs& a, const uint8_t* row, int kb0, int kb1, int h, int r,
-                                            uint32_t row_off, uint8_t* smem, int stage_bytes, int nstages,
-                                            uint64_t* full, uint64_t* empty, int& s, uint32_t& lap, uint32_t hint) {
-    const int lane = threadIdx.x & 31;
+__device__ __forceinline__ bool decode_rows(const DecCtx& c, Ring& ring, const uint8_t* row, int kb0, int kb1,
+                                            int h, int K) {
     const int last = kb1 - 1;
-    typename D::Regs b0 = D::load(row, kb0, h, a.K);
-    typename D::Regs b1 = D::load(row, min(kb0 + 1, last), h, a.K);
+    typename D::Regs b0 = D::load(row, kb0, h, K);
+    typename D::Regs b1 = D::load(row, min(kb0 + 1, last), h, K);
     typename D::Regs b2;
     auto step = [&](const typename D::Regs& cur, int kb) -> bool {
-        if (lap > 0 &&
-            !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
-            return false;
         uint4 out[4];
         D::emit(cur, (kb & 3) * 2 + h, out);
-        const uint32_t dst = smem_u32(smem + s * stage_bytes) + row_off;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) sts128(dst + (static_cast<uint32_t>((4 * h + j) ^ (r & 7)) << 4), out[j]);
-        fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
-        if (++s == nstages) { s = 0; ++lap; }
-        return true;
+        const uint32_t o[16] = {out[0].x, out[0].y, out[0].z, out[0].w, out[1].x, out[1].y, out[1].z, out[1].w,
+                                out[2].x, out[2].y, out[2].z, out[2].w, out[3].x, out[3].y, out[3].z, out[3].w};
+        return publish_stage(c, ring, o, 16u * h, o + 8, 16u * h + 8u);
     };
     for (int kb = kb0; kb < kb1; kb += 3) {
-        b2 = D::load(row, min(kb + 2, last), h, a.K);
+        b2 = D::load(row, min(kb + 2, last), h, K);
         if (!step(b0, kb)) return false;
         if (kb + 1 >= kb1) break;
-        b0 = D::load(row, min(kb + 3, last), h, a.K);
+        b0 = D::load(row, min(kb + 3, last), h, K);
         if (!step(b1, kb + 1)) return false;
         if (kb + 2 >= kb1) break;
-        b1 = D::load(row, min(kb + 4, last), h, a.K);
+        b1 = D::load(row, min(kb + 4, last), h, K);
         if (!step(b2, kb + 2)) return false;
     }
     return true;
@@ -290,42 +277,35 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Q4_K rows through a private shared-memory ring: every decoder thread copies its own 16
-// bytes of nibbles per K block (and, for half 0, the 16-byte block header once per four K
-// blocks) with cp.async, DEPTH K blocks ahead of where it decodes, so the lookahead costs no
-// registers.  The two halves of a row sit in the same warp; __syncwarp orders a lane's reads
-// of its partner's bytes against the copies that later reuse the slot.
+// Q4_K rows through a private shared-memory ring: every decoder thread copies the 16 bytes
+// of nibbles it decodes per K block (and the 16-byte block header once per four K blocks)
+// with cp.async, DEPTH K blocks ahead of where it decodes, so the lookahead costs no
+// registers and the ring needs no synchronisation between threads.
 //
 // A 144-byte block is {fp16 d, fp16 dmin, 12 bytes of 6-bit scales/mins, 128 bytes of
 // nibbles} (csrc/formats/q4k_format.h:112-133); K block p of the block is nibble pair p: the
-// low nibbles of qs[32p..32p+31] are values 64p..64p+31 (half 0, sub-block 2p), the high
-// nibbles values 64p+32..64p+63 (half 1, sub-block 2p+1).  The value is d*sc*q - dmin*mn with
-// the 6-bit sc, mn of the sub-block (csrc/formats/kquant_common.h:36-46).  Here d*sc and
-// dmin*mn are formed as fp16 products (one rounding of an exact product, the same number
-// fp32 arithmetic followed by a conversion gives) and the value by one fp16 fma.
+// low nibbles of qs[32p..32p+31] are values 64p..64p+31 (sub-block 2p), the high nibbles
+// values 64p+32..64p+63 (sub-block 2p+1).  Thread half hb owns bytes 16hb..16hb+15 of the
+// pair: values 64p+16hb+(0..15) from the low nibbles and 64p+32+16hb+(0..15) from the high
+// ones, i.e. packed columns 8hb..8hb+7 and 16+8hb..16+8hb+7 of the stage.  The value is
+// d*sc*q - dmin*mn with the 6-bit sc, mn of the sub-block (csrc/formats/kquant_common.h:36-46);
+// d*sc and dmin*mn are formed as fp16 products (one rounding of an exact product, the same
+// number fp32 arithmetic followed by a conversion gives) and the value by one fp16 fma.
 //
 // Requires 16-byte aligned rows and a K range that starts and ends on a 256-value block.
 // Returns false after a wait timed out.
 template <int DEPTH>
-__device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_t* row, int kb0, int kb1, int h,
-                                                int r, uint32_t row_off, uint8_t* smem, uint8_t* raw,
-                                                int stage_bytes, int nstages, uint64_t* full, uint64_t* empty,
-                                                int& s, uint32_t& lap, uint32_t hint) {
-    const int lane = threadIdx.x & 31;
-    const uint32_t q_ring = smem_u32(raw) + static_cast<uint32_t>(r * 32);           // + slot * kRawSlotBytes
-    const uint32_t h_ring = smem_u32(raw) + DEPTH * kRawSlotBytes + static_cast<uint32_t>(r * 16);  // + (blk & 3) * 2048
-    // destination of this thread's four 16-byte chunks inside a stage (128-byte swizzle)
-    uint32_t chunk_off[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) chunk_off[j] = row_off + (static_cast<uint32_t>((4 * h + j) ^ (r & 7)) << 4);
-
+__device__ __forceinline__ bool decode_rows_q4k(const DecCtx& c, Ring& ring, const uint8_t* row, int kb0, int kb1,
+                                                int hb, uint8_t* raw, int dec_tid) {
+    const uint32_t q_ring = smem_u32(raw) + static_cast<uint32_t>(dec_tid * 16);                          // + slot * kRawSlotBytes
+    const uint32_t h_ring = smem_u32(raw) + DEPTH * kRawSlotBytes + static_cast<uint32_t>(dec_tid * 16);  // + (blk & 3) * kRawSlotBytes
     const uint8_t* src = row + static_cast<long long>(kb0 >> 2) * 144;  // block of the next copy
     int issue_kb = kb0;
     auto issue = [&](int slot) {
         if (issue_kb < kb1) {
             const int p = issue_kb & 3;
-            cp_async16(q_ring + slot * kRawSlotBytes + 16 * h, src + 16 + p * 32 + 16 * h);
-            if (h == 0 && p == 0) cp_async16(h_ring + ((issue_kb >> 2) & 3) * (WM * 16), src);
+            cp_async16(q_ring + slot * kRawSlotBytes, src + 16 + p * 32 + 16 * hb);
+            if (p == 0) cp_async16(h_ring + ((issue_kb >> 2) & 3) * kRawSlotBytes, src);
             if (p == 3) src += 144;
         }
         ++issue_kb;
@@ -335,70 +315,57 @@ __device__ __forceinline__ bool decode_rows_q4k(const FusedArgs& a, const uint8_
     for (int i = 0; i < DEPTH; ++i) issue(i);
 
     const __half2 k1024 = __float2half2_rn(1024.0f);
-    const uint32_t nib_shift = 4u * h;
     int slot = 0;
     // The nibbles of K block kb are read from the ring one iteration ahead of their use, so
     // the shared-memory latency hides behind the arithmetic of block kb - 1; the wait for a
     // free stage comes after the arithmetic, right before the stores.
     cp_async_wait<DEPTH - 1>();
-    __syncwarp();
-    uint4 q0 = lds128(q_ring), q1 = lds128(q_ring + 16);
+    uint4 q = lds128(q_ring);
     for (int kb = kb0; kb < kb1; kb += 4) {
-        // ---- once per 256-value block: the four (scale, min) pairs of this thread's half ----
+        // ---- once per 256-value block: all eight (scale, min) pairs ----
         // (the header arrived with the group of the block's first K block, already waited for)
-        const uint4 hdr = lds128(h_ring + ((kb >> 2) & 3) * (WM * 16));
+        const uint4 hdr = lds128(h_ring + ((kb >> 2) & 3) * kRawSlotBytes);
         // bytes of sc[0..3], sc[4..7], mn[0..3], mn[4..7]
-        const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu;
-        const uint32_t mn_lo = hdr.z & 0x3F3F3F3Fu;
-        const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-        const uint32_t mn_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
-        // this half's sub-blocks are h, 2+h, 4+h, 6+h: bytes h and 2+h of the lo and hi words
-        const uint32_t sh = 8u * h;
-        const uint32_t scw[2] = {sc_lo >> sh, sc_hi >> sh};
-        const uint32_t mnw[2] = {mn_lo >> sh, mn_hi >> sh};
+        const uint32_t scw[2] = {hdr.y & 0x3F3F3F3Fu, (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u)};
+        const uint32_t mnw[2] = {hdr.z & 0x3F3F3F3Fu, ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)};
         // (d, -dmin) as a half2
         const uint32_t dd = hdr.x ^ 0x80000000u;
         const __half2 d_ndmin = *reinterpret_cast<const __half2*>(&dd);
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
             // the next K block's copies have landed (its group is the oldest but one): fetch
             // its nibbles now; past the end this re-reads a finished slot and is not used
             const int nslot = (slot + 1 == DEPTH) ? 0 : slot + 1;
             cp_async_wait<DEPTH - 2>();
-            __syncwarp();
-            q0 = lds128(q_ring + nslot * kRawSlotBytes);
-            q1 = lds128(q_ring + nslot * kRawSlotBytes + 16);
-            // half2 (sc, mn) -> (d*sc, -dmin*mn), each broadcast to both halves
-            const uint32_t pair = __byte_perm(scw[p >> 1], mnw[p >> 1], (p & 1) ? 0x0062 : 0x0040);  // bytes sc, mn
-            uint32_t sm = __byte_perm(pair, 0x64646464u, 0x4140);
-            const __half2 scmn = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&sm), k1024), d_ndmin);
-            const __half2 ds = __low2half2(scmn), nms = __high2half2(scmn);
-            uint32_t o[16];
+            q = lds128(q_ring + nslot * kRawSlotBytes);
+            // sub-blocks 2p (low nibbles) and 2p+1 (high): half2 (sc, mn) -> (d*sc, -dmin*mn)
+            const uint32_t pl = __byte_perm(scw[p >> 1], mnw[p >> 1], (p & 1) ? 0x0062 : 0x0040);
+            const uint32_t ph = __byte_perm(scw[p >> 1], mnw[p >> 1], (p & 1) ? 0x0073 : 0x0051);
+            uint32_t sl = __byte_perm(pl, 0x64646464u, 0x4140), sh = __byte_perm(ph, 0x64646464u, 0x4140);
+            const __half2 sml = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&sl), k1024), d_ndmin);
+            const __half2 smh = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&sh), k1024), d_ndmin);
+            const __half2 ds_l = __low2half2(sml), nms_l = __high2half2(sml);
+            const __half2 ds_h = __low2half2(smh), nms_h = __high2half2(smh);
+            uint32_t lo[8], hi[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t nib = (q[i] >> nib_shift) & 0x0F0F0F0Fu;
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t nl = w[i] & 0x0F0F0F0Fu, nh = (w[i] >> 4) & 0x0F0F0F0Fu;
                 // bytes -> fp16 1024 + q by placing each under the exponent byte 0x64
-                uint32_t lo = __byte_perm(nib, 0x64646464u, 0x4140);
-                uint32_t hi = __byte_perm(nib, 0x64646464u, 0x4342);
-                const __half2 x = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&lo), k1024), ds, nms);
-                const __half2 y = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&hi), k1024), ds, nms);
-                o[2 * i] = *reinterpret_cast<const uint32_t*>(&x);
-                o[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&y);
+                uint32_t a0 = __byte_perm(nl, 0x64646464u, 0x4140), a1 = __byte_perm(nl, 0x64646464u, 0x4342);
+                uint32_t b0 = __byte_perm(nh, 0x64646464u, 0x4140), b1 = __byte_perm(nh, 0x64646464u, 0x4342);
+                const __half2 x0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&a0), k1024), ds_l, nms_l);
+                const __half2 x1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&a1), k1024), ds_l, nms_l);
+                const __half2 y0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&b0), k1024), ds_h, nms_h);
+                const __half2 y1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&b1), k1024), ds_h, nms_h);
+                lo[2 * i] = *reinterpret_cast<const uint32_t*>(&x0);
+                lo[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&x1);
+                hi[2 * i] = *reinterpret_cast<const uint32_t*>(&y0);
+                hi[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&y1);
             }
-            if (lap > 0 &&
-                !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)))
-                return false;
-            const uint32_t dst = smem_u32(smem + s * stage_bytes);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                sts128(dst + chunk_off[j], make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
-            fence_proxy_async_smem();  // generic-proxy stores -> visible to the tensor core's reads
-            __syncwarp();              // both lanes are done with the slot before it is refilled
-            if (lane == 0) mbar_arrive(&full[s]);
+            if (!publish_stage(c, ring, lo, 8u * hb, hi, 16u + 8u * hb)) return false;
             issue(slot);
             slot = nslot;
-            if (++s == nstages) { s = 0; ++lap; }
         }
     }
     cp_async_wait<0>();
@@ -410,7 +377,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1)
 tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int stage_bytes = kWBytes + a.nt * 128;
+    const int stage_bytes = a.nt * 128;              // one (64 x NT) fp16 token tile
     uint8_t* raw = smem + a.stages * stage_bytes;   // packed-weight ring of the staged decoders
     uint64_t* full = reinterpret_cast<uint64_t*>(raw + a.raw_bytes);
     uint64_t* empty = full + kMaxStages;
@@ -420,7 +387,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = 2u * a.nt;  // 64..512, a power of two
+    const int nacc = a.nt > 128 ? 1 : 2;   // accumulators in columns 0..255
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -435,7 +402,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) tmem_alloc(tmem_slot, tmem_cols);
+    if (warp == 5) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -445,28 +412,26 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 
     const int kblocks_all = (a.K + BK - 1) / BK;
     const int total = a.t_tiles * a.ksplit * a.n_wtiles;
-    const int nstages = a.stages;
     const uint32_t hint = 2000u;  // suspend-time hint of the barrier waits, ns
 
     if (warp == 4) {
         // ------------------------------ TMA producer (x16 tiles) ------------------
         if (lane == 0) {
-            int s = 0;
-            uint32_t lap = 0;  // ring position: stage and how often the ring has wrapped
+            Ring ring = {0, 0u, a.stages};
             for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
                 const Item im = decode_item(a, w);
                 if (!im.live) continue;
                 const int kb0 = im.ks * a.kb_per_split;
                 const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (lap > 0 &&
-                        !mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, hint)) {
+                    if (ring.lap > 0 &&
+                        !mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint)) {
                         *abort_flag = 1;
                         break;
                     }
-                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(a.nt) * 128u);
-                    tma_load_2d(smem + s * stage_bytes + kWBytes, &tmX, kb * BK, im.mstart, &full[s]);
-                    if (++s == nstages) { s = 0; ++lap; }
+                    mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(stage_bytes));
+                    tma_load_2d(smem + ring.s * stage_bytes, &tmX, kb * BK, im.mstart, &full[ring.s]);
+                    ring.advance();
                 }
             }
         }
@@ -474,51 +439,65 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         // ------------------------------ MMA issuer --------------------------------
         // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
         // values; one elected lane issues the tensor-core instructions.
-        const uint32_t idesc = idesc_f16(WM, a.nt);
-        int s = 0, tile_i = 0;
-        uint32_t lap = 0;
+        Ring ring = {0, 0u, a.stages};
+        int tile_i = 0, ab = 0;
+        uint32_t acc_lap = 0;  // how often the accumulator set has been cycled through
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
             const Item im = decode_item(a, w);
             if (!im.live) continue;
             const int kb0 = im.ks * a.kb_per_split;
             const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
-            const int ab = tile_i & 1;
-            if (tile_i >= 2)
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status,
-                                                               kDevWaitTmem, hint));
+            if (acc_lap > 0)
+                ok = __all_sync(0xffffffffu,
+                                mbar_wait_bounded(&acc_empty[ab], (acc_lap - 1) & 1, a.status, kDevWaitTmem, hint));
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + ab * a.nt;
+            // N of the instruction follows the token rows that are really in the tile (a multiple
+            // of 16): the ragged last tile of an expert costs tensor time for its rows only
+            const int live = min(a.nt, im.mend - im.mstart);
+            const uint32_t idesc = idesc_f16(WM, max(16, (live + 15) & ~15));
             for (int kb = kb0; kb < kb1; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[s], lap & 1, a.status, kDevWaitFull, hint));
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sW = smem_u32(smem + s * stage_bytes);
-                const uint64_t wdesc = smem_desc_sw128(sW);
-                const uint64_t xdesc = smem_desc_sw128(sW + kWBytes);
+                const uint64_t xdesc = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes));
+                const uint32_t a_tmem = tmem_base + kAColBase + ring.s * kAColsPerStage;
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)
-                        tc_mma_f16(d_tmem, wdesc + 2 * k, xdesc + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
-                    tc_commit(&empty[s]);
+                        tc_mma_f16_ta(d_tmem, a_tmem + 8 * k, xdesc + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+                    tc_commit(&empty[ring.s]);
                 }
                 __syncwarp();
-                if (++s == nstages) { s = 0; ++lap; }
+                ring.advance();
             }
             if (!ok) break;
             if (elect_one()) tc_commit(&acc_full[ab]);
             __syncwarp();
             ++tile_i;
+            if (++ab == nacc) {
+                ab = 0;
+                ++acc_lap;
+            }
         }
         if (!ok) *abort_flag = 1;
     } else if (warp >= 6) {
         // ------------------------------ weight decoders ---------------------------
-        const int dt = threadIdx.x - 6 * 32;
-        const int r = dt >> 1, h = dt & 1;
-        const uint32_t row_off = static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128);
-        int s = 0;
-        uint32_t lap = 0;
+        // warp -> lane quadrant (a warp may only touch tensor-memory lanes 32 * (warp % 4) ..),
+        // and which half of each K block it decodes
+        const int quad = warp & 3;
+        const int half = (warp - 6) >> 2;
+        const int r = quad * 32 + lane;          // weight row inside the tile
+        const int dec_tid = threadIdx.x - 6 * 32;
+        DecCtx ctx;
+        ctx.full = full;
+        ctx.empty = empty;
+        ctx.tmem_a = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kAColBase;
+        ctx.status = a.status;
+        ctx.hint = hint;
+        Ring ring = {0, 0u, a.stages};
         for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
             const Item im = decode_item(a, w);
             if (!im.live) continue;
@@ -529,23 +508,18 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                                            : a.W;
             const int n = min((second ? im.wt - a.split_wt : im.wt) * WM + r, a.N - 1);
             const uint8_t* row = base ? base + static_cast<long long>(n) * a.row_bytes : nullptr;
-            // The register-staged decoder issues 16-byte vector loads; a matrix that is not
-            // 16-byte aligned goes through the byte-wise generic decoder instead.  The choice
-            // is uniform over the CTA and made per item, so neither loop carries a branch
-            // between a load and its use.
+            // The staged decoder copies 16-byte pieces; a matrix that is not 16-byte aligned goes
+            // through the byte-wise generic decoder instead.  The choice is uniform over the CTA.
             bool ok;
             const bool aligned16 =
                 ((reinterpret_cast<uintptr_t>(base) | static_cast<uintptr_t>(a.row_bytes)) & 15) == 0;
             if (T == LSG_GGUF_Q4_K && a.raw_depth > 0 && row != nullptr && aligned16) {
                 if (a.raw_depth == 8)
-                    ok = decode_rows_q4k<8>(a, row, kb0, kb1, h, r, row_off, smem, raw, stage_bytes, nstages, full,
-                                            empty, s, lap, hint);
+                    ok = decode_rows_q4k<8>(ctx, ring, row, kb0, kb1, half, raw, dec_tid);
                 else
-                    ok = decode_rows_q4k<4>(a, row, kb0, kb1, h, r, row_off, smem, raw, stage_bytes, nstages, full,
-                                            empty, s, lap, hint);
+                    ok = decode_rows_q4k<4>(ctx, ring, row, kb0, kb1, half, raw, dec_tid);
             } else {
-                ok = decode_rows<DecGeneric<T>>(a, row, kb0, kb1, h, r, row_off, smem, stage_bytes, nstages, full,
-                                                empty, s, lap, hint);
+                ok = decode_rows<DecGeneric<T>>(ctx, ring, row, kb0, kb1, half, a.K);
             }
             if (!ok) {
                 *abort_flag = 1;
@@ -554,13 +528,13 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         }
     } else {
         // ------------------------------ epilogue (warps 0-3) ----------------------
-        int tile_i = 0;
+        int tile_i = 0, ab = 0;
+        uint32_t acc_lap = 0;
         for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
             const Item im = decode_item(a, w);
             if (!im.live) continue;
-            const int ab = tile_i & 1;
             const bool landed = __all_sync(
-                0xffffffffu, mbar_wait_bounded(&acc_full[ab], (tile_i >> 1) & 1, a.status, kDevWaitMma, hint));
+                0xffffffffu, mbar_wait_bounded(&acc_full[ab], acc_lap & 1, a.status, kDevWaitMma, hint));
             if (!landed) {
                 *abort_flag = 1;
                 break;
@@ -664,6 +638,10 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 }
             }
             ++tile_i;
+            if (++ab == nacc) {
+                ab = 0;
+                ++acc_lap;
+            }
         }
     }
 
@@ -671,7 +649,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
     __syncthreads();
     if (warp == 5) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, tmem_cols);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -798,9 +776,9 @@ int pick_nt(long long rows_per_problem) {
 Plan make_plan(long long rows, int nt, int t_tiles, int N, int K, bool allow_split, bool staged) {
     Plan p = {};
     p.nt = nt;
-    const int stage_bytes = kWBytes + nt * 128;
-    // packed-weight ring: 8 K blocks deep, 4 when 256-token tiles leave less room
-    p.raw_depth = staged ? (nt >= 256 ? 4 : 8) : 0;
+    const int stage_bytes = nt * 128;
+    // packed-weight ring of the staged decoders, 8 K blocks deep
+    p.raw_depth = staged ? 8 : 0;
     p.raw_bytes = staged ? p.raw_depth * kRawSlotBytes + kHdrRingBytes : 0;
     p.stages = (224 * 1024 - p.raw_bytes) / stage_bytes;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
@@ -836,7 +814,7 @@ int launch_fused_t(const CUtensorMap& tmX, const FusedArgs& a, cudaStream_t s) {
     static bool configured[64] = {};
     int dev = 0;
     LSG_CUDA_TRY(cudaGetDevice(&dev));
-    const int smem = a.stages * (kWBytes + a.nt * 128) + a.raw_bytes + 1024 + 512;
+    const int smem = a.stages * a.nt * 128 + a.raw_bytes + 1024 + 512;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
         LSG_CUDA_TRY(cudaFuncSetAttribute(tc_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           227 * 1024));

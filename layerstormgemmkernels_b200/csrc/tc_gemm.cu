@@ -420,8 +420,8 @@ int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void*
     if (M == 0 || N == 0) return LSG_OK;
     // Decoding inside the GEMM repeats the decode once per 256-token tile; past a few tiles
     // one expansion pass plus the plain fp16 GEMM is cheaper (measured cross-over near
-    // M = 2048 for 14336 x 4096 Q4_K), unless every type is forced through the fused kernel.
-    if (tc_fused_available(type) && (M <= 1536 || tc_fused_forced()))
+    // M = 4096 for 14336 x 4096 Q4_K), unless every type is forced through the fused kernel.
+    if (tc_fused_available(type) && (M <= 2048 || tc_fused_forced()))
         return tc_fused_dense(type, M, N, K, A, W, C, N, out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16, ws, ws_bytes, s);
     if (K % 8 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_mmq: K must be a multiple of 8");
     const size_t need = mmq_scratch_bytes(M, K, 1, N);

@@ -27,27 +27,29 @@ def expert_range(rank, world, num_experts):
 
 class EpPlan:
     """Everything both directions of the exchange need, derived from the per-expert row
-    counts of every rank (one small all-to-all + one device-to-host copy)."""
+    counts of every rank.  The index arithmetic stays on the device of the counts; the host
+    only learns the split sizes of the all-to-all (one small device-to-host copy)."""
 
     def __init__(self, send_counts, recv_counts, experts_per_rank):
         # send_counts [world, per]: rows this rank sends, by destination rank and local expert
         # recv_counts [world, per]: rows this rank receives, by source rank and local expert
         self.per = experts_per_rank
-        self.send_counts = send_counts
-        self.recv_counts = recv_counts
-        self.send_splits = send_counts.sum(1).tolist()
-        self.recv_splits = recv_counts.sum(1).tolist()
-        self.recv_rows = int(sum(self.recv_splits))
-        # received order is (source, expert, row); the grouped GEMM wants (expert, source, row)
         world = recv_counts.shape[0]
+        both = torch.stack((send_counts.sum(1), recv_counts.sum(1))).cpu()   # the one host copy
+        self.send_splits = both[0].tolist()
+        self.recv_splits = both[1].tolist()
+        self.recv_rows = int(sum(self.recv_splits))
+        dev = recv_counts.device
+        # received order is (source, expert, row); the grouped GEMM wants (expert, source, row)
         blocks = recv_counts.reshape(-1)                       # [(s, e)] sizes
         starts = torch.cumsum(blocks, 0) - blocks              # start of block (s, e) in recv order
-        order = torch.arange(world * self.per).reshape(world, self.per).t().reshape(-1)  # (e, s)
+        order = torch.arange(world * self.per, device=dev).reshape(world, self.per).t().reshape(-1)  # (e, s)
         sizes = blocks[order]
-        src = torch.repeat_interleave(starts[order], sizes)
-        within = torch.arange(int(sizes.sum())) - torch.repeat_interleave(torch.cumsum(sizes, 0) - sizes, sizes)
+        src = torch.repeat_interleave(starts[order], sizes, output_size=self.recv_rows)
+        first = torch.repeat_interleave(torch.cumsum(sizes, 0) - sizes, sizes, output_size=self.recv_rows)
+        within = torch.arange(self.recv_rows, device=dev) - first
         self.to_expert_order = (src + within).to(torch.int64)  # gather index: expert-order row -> recv row
-        self.local_offsets = torch.zeros(self.per + 1, dtype=torch.int32)
+        self.local_offsets = torch.zeros(self.per + 1, dtype=torch.int32, device=dev)
         self.local_offsets[1:] = torch.cumsum(recv_counts.sum(0), 0).to(torch.int32)
 
 
@@ -59,7 +61,7 @@ def make_ep_plan(expert_offsets, num_experts, group=None):
     counts = (offs[1:] - offs[:-1]).reshape(world, per).contiguous()
     recv = torch.empty_like(counts)
     dist.all_to_all_single(recv, counts, group=group)
-    return EpPlan(counts.cpu(), recv.cpu(), per)
+    return EpPlan(counts, recv, per)
 
 
 def ep_dispatch(rows, plan, group=None):
