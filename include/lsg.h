@@ -165,6 +165,20 @@ LSG_API size_t lsg_gguf_mmq_workspace_bytes(int M, int N, int K);
 LSG_API int lsg_gguf_mmq(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* C[M,N] = A[M,K] (bf16, unquantized) . dequant(B)^T on the tensor cores: the packed weights
+ * are decoded to fp16 inside the kernel; each activation row is moved into fp16 range by a
+ * power of two of its own (exact for bf16 values) and the output row scaled back, so no
+ * activation precision is lost.  For Q4_K this replaces the legacy launch_q4k_dequant_gemm
+ * (csrc/sm120/gemm/q4k/q4k_dequant_gemm.cu:354-380) and launch_q4k_cutlass_gemm
+ * (csrc/sm120/gemm/q4k/q4k_cutlass_gemm.cu:305-343; the reference rounds the weights to bf16
+ * for its wmma tiles, fp16 keeps three more bits); for every type it is the fast sibling of
+ * lsg_gguf_dequant_gemm.  Workspace: lsg_gguf_gemm_bf16_workspace_bytes(M, N, K) bytes,
+ * 256-byte aligned (the reference's two launchers take none; its Python operators allocate
+ * their output the same way this library's bindings allocate the workspace). */
+LSG_API size_t lsg_gguf_gemm_bf16_workspace_bytes(int M, int N, int K);
+LSG_API int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
 /* How the tensor-core GEMMs (lsg_gguf_mmq and the grouped GEMM's tensor-core route) obtain
  * their fp16 weights, process-wide:
  *   0  a preparation kernel expands the packed matrix into workspace first;

@@ -104,6 +104,8 @@ def _load():
         "lsg_gguf_mmvq_noalloc": (ci, [ctypes.POINTER(GgufMmvqParams), vp]),
         "lsg_mmvq_set_tuning": (ci, [ci, ci, ci, ci, ci]),
         "lsg_mmq_set_weight_path": (ci, [ci]),
+        "lsg_gguf_gemm_bf16_workspace_bytes": (sz, [ci, ci, ci]),
+        "lsg_gguf_gemm_bf16": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_dynamic_fp8_quant": (ci, [ctypes.POINTER(DynamicFp8QuantParams), vp]),
         "lsg_bf16_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),
         "lsg_silu_mul_to_nvfp4_grouped": (ci, [ctypes.POINTER(Nvfp4GroupedQuantParams), vp]),

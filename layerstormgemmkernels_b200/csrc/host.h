@@ -45,6 +45,9 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
                      const int* tile_mstart, int t_max, int tile_m, void* scratch, size_t scratch_bytes,
                      cudaStream_t s);
 
+size_t tc_fused_bf16_scratch_bytes(int M, int N, int K);
+int tc_fused_dense_bf16(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
+                        int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s);
 size_t tc_fused_moe_ffn_scratch_bytes(long long T, int H, int I);
 int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, const void* const* gate_ptrs,
                      const void* const* up_ptrs, const void* const* down_ptrs, const int32_t* expert_offsets,

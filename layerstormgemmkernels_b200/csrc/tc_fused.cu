@@ -82,6 +82,7 @@ struct FusedArgs {
     int kb_per_split;             // K blocks per split
     float* partial;               // [items][ksplit][128][nt] fp32, only with ksplit > 1
     unsigned int* counters;       // [tiles][4 epilogue warps], zero on entry
+    const float* row_scale;       // optional per-token output scale (the unquantized-activation route)
     unsigned int* status;
 };
 
@@ -554,6 +555,12 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                     tmem_ld32(t_lane + c, v);
                     if (n_ok) {
                         const int rows = min(32, im.mend - (im.mstart + c));
+                        if (a.row_scale) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < rows)
+                                    v[i] = __float_as_uint(__uint_as_float(v[i]) * __ldg(a.row_scale + im.mstart + c + i));
+                        }
                         const size_t o = static_cast<size_t>(im.mstart + c) * a.ldc + n;
                         if (a.out_dtype == LSG_DTYPE_F32) {
                             float* dst = static_cast<float*>(a.C) + o;
@@ -624,6 +631,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 if (i0 + i < live_rows) {
+                                    if (a.row_scale) acc[i] *= __ldg(a.row_scale + im.mstart + i0 + i);
                                     const size_t o = static_cast<size_t>(im.mstart + i0 + i) * a.ldc + n;
                                     if (a.out_dtype == LSG_DTYPE_F32)
                                         static_cast<float*>(a.C)[o] = acc[i];
@@ -753,6 +761,51 @@ swiglu_prep_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ ou
         p[i] = pack_h2(r[0], r[1]);
     }
     reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
+}
+
+// bf16 activation rows -> fp16 scaled by a power of two per row: the row's largest magnitude
+// lands in [2^14, 2^15), out[m,k] = x[m,k] * 2^-e_m exactly, scale[m] = 2^e_m for the epilogue.
+// One warp per row.  Rows of zeros (or with no finite value) keep scale 1.
+__global__ void __launch_bounds__(256)
+x_rows_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, float* __restrict__ scale, int M,
+                     int K, unsigned int* __restrict__ counters, int n_counters) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < n_counters; i += gridDim.x * 256) counters[i] = 0;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= M) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K);
+    const int nvec = K / 8;
+    uint32_t amax_bits = 0;  // largest |x| as bf16 bits in the upper half (monotonic in magnitude)
+    for (int i = lane; i < nvec; i += 32) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            amax_bits = max(amax_bits, (w[j] << 16) & 0x7FFF0000u);
+            amax_bits = max(amax_bits, w[j] & 0x7FFF0000u);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
+    // exponent of the largest finite magnitude; shift it to 14
+    int ex = static_cast<int>(amax_bits >> 23);        // biased fp32 exponent, 0..255
+    int shift = (ex == 0 || ex == 255) ? 0 : (ex - 127) - 14;
+    // keep both factors normal fp32 numbers
+    shift = max(-100, min(100, shift));
+    const float down = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);  // 2^-shift
+    const float up = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);    // 2^shift
+    if (lane == 0) scale[row] = up;
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * K);
+    for (int i = lane; i < nvec; i += 32) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            o[j] = pack_h2(__uint_as_float(w[j] << 16) * down, __uint_as_float(w[j] & 0xFFFF0000u) * down);
+        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
 }
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -913,6 +966,57 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
+    a.status = device_status_word();
+    return launch_fused(type, tmX, a, s);
+}
+
+// Unquantized-activation variant: C[M, N] = A_bf16 . dequant(W)^T.  The tensor core multiplies
+// fp16 by fp16, so each activation row is brought into fp16 range by a power of two of its own
+// (exact: a bf16 value has 8 significant bits, fp16 holds 11) and the output row is scaled
+// back in the epilogue.  Only elements more than 2^28 below their row's largest magnitude lose
+// bits, which is below what fp32 accumulation resolves.
+size_t tc_fused_bf16_scratch_bytes(int M, int N, int K) {
+    const int nt = pick_nt(M);
+    return make_plan(M, nt, (M + nt - 1) / nt, N, K, true, false).total() + align256(static_cast<size_t>(M) * 4);
+}
+
+int tc_fused_dense_bf16(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
+                        int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
+    if (M == 0 || N == 0) return LSG_OK;
+    if (K % 32 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_gemm_bf16: K must be a multiple of 32");
+    if (reinterpret_cast<uintptr_t>(A_bf16) & 15)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_gemm_bf16: activations must be 16-byte aligned");
+    const int nt = pick_nt(M);
+    const Plan p = make_plan(M, nt, (M + nt - 1) / nt, N, K, true, staged_decoder(type));
+    const size_t need = p.total() + align256(static_cast<size_t>(M) * 4);
+    if (!ws || ws_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "gguf_gemm_bf16: workspace too small (have %zu, need %zu)",
+                    ws ? ws_bytes : size_t(0), need);
+    if (reinterpret_cast<uintptr_t>(ws) & 255)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_gemm_bf16: workspace must be 256-byte aligned");
+    uint8_t* wsb = static_cast<uint8_t*>(ws);
+    __half* x16 = reinterpret_cast<__half*>(wsb);
+    float* partial = reinterpret_cast<float*>(wsb + p.x_bytes);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(wsb + p.x_bytes + p.partial_bytes);
+    float* row_scale = reinterpret_cast<float*>(wsb + p.total());
+    const int n_counters = p.ksplit > 1 ? p.t_tiles * p.n_wtiles * 4 : 0;
+    // one warp per activation row; the first CTAs also zero the split-K counters
+    LSG_CUDA_TRY(launch_kernel(x_rows_to_f16_kernel, dim3(static_cast<unsigned>((M + 7) / 8)), dim3(256), 0, s, true,
+                               static_cast<const __nv_bfloat16*>(A_bf16), x16, row_scale, M, K,
+                               n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters));
+    CUtensorMap tmX;
+    int rc = make_map(&tmX, x16, M, K, nt);
+    if (rc != LSG_OK) return rc;
+    FusedArgs a = {};
+    a.W = static_cast<const uint8_t*>(W);
+    a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
+    a.C = C; a.ldc = ldc; a.out_dtype = out_dtype;
+    a.K = K; a.N = N; a.M = M;
+    a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages;
+    a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
+    a.partial = partial; a.counters = counters;
+    a.row_scale = row_scale;
     a.status = device_status_word();
     return launch_fused(type, tmX, a, s);
 }

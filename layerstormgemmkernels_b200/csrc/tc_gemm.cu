@@ -525,3 +525,18 @@ extern "C" int lsg_gguf_mmq(const lsg_gguf_mmvq_params* p, void* workspace, size
     return mmq_dense(p->type, p->M, p->N, p->K, p->A, p->B, p->C, p->out_dtype == LSG_DTYPE_F32, workspace,
                      workspace_bytes, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" size_t lsg_gguf_gemm_bf16_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return tc_fused_bf16_scratch_bytes(M, N, K);
+}
+
+extern "C" int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                                  void* stream) {
+    int rc = check_gemm_params("gguf_gemm_bf16", p);
+    if (rc != LSG_OK) return rc;
+    if (p->M == 0 || p->N == 0) return LSG_OK;
+    if (!p->A || !p->B || !p->C) return fail(LSG_ERR_INVALID, "gguf_gemm_bf16: null pointer");
+    return tc_fused_dense_bf16(p->type, p->M, p->N, p->K, p->A, p->B, p->C, p->N, p->out_dtype, workspace,
+                               workspace_bytes, static_cast<cudaStream_t>(stream));
+}

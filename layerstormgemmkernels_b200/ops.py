@@ -294,6 +294,50 @@ def gguf_mmq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     return C
 
 
+def gguf_gemm_bf16(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
+    """bf16 A[M,K] @ dequant(B)^T -> [M,N] on the tensor cores with unquantized activations
+    (the fast sibling of gguf_dequant_gemm)."""
+    _require(A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous(),
+             "gguf_gemm_bf16: A must be contiguous BF16 [M, K] on CUDA")
+    _require(A.size(1) == K, "gguf_gemm_bf16: A.size(1) != K")
+    M = A.size(0)
+    C = torch.empty((M, N), dtype=out_dtype, device=A.device)
+    ws_bytes = _lib.lsg_gguf_gemm_bf16_workspace_bytes(M, int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    p = _gemm_params(A, B_packed, C, type, N, K,
+                     capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+    capi.check(_lib.lsg_gguf_gemm_bf16(ctypes.byref(p), _ptr(ws), ws_bytes, _stream()))
+    return C
+
+
+def _q4k_legacy(name, x_bf16, weight_q4k_packed):
+    # checks of q4k_dequant_gemm / q4k_cutlass_gemm, csrc/bindings_python.cu:647-721
+    _require(x_bf16.is_cuda and x_bf16.dtype == torch.bfloat16, "x_bf16 must be BF16 on CUDA")
+    _require(x_bf16.dim() == 2 and x_bf16.is_contiguous(), "x_bf16 must be contiguous [M, K]")
+    _require(weight_q4k_packed.is_cuda and weight_q4k_packed.dtype == torch.uint8,
+             "weight_q4k_packed must be uint8 on CUDA")
+    _require(weight_q4k_packed.dim() == 2 and weight_q4k_packed.is_contiguous(),
+             "weight_q4k_packed must be contiguous [N, K*9/16]")
+    K = x_bf16.size(1)
+    N = weight_q4k_packed.size(0)
+    _require(K % 256 == 0, f"K must be divisible by 256, got K={K}")
+    expected = (K // 256) * 144
+    _require(weight_q4k_packed.size(1) == expected,
+             f"weight row bytes mismatch: expected {expected}, got {weight_q4k_packed.size(1)}")
+    return gguf_gemm_bf16(x_bf16, weight_q4k_packed, capi.Q4_K, N, K)
+
+
+def q4k_dequant_gemm(x_bf16, weight_q4k_packed):
+    """x_bf16 @ dequant(W_q4k).T -> BF16 (csrc/bindings_python.cu:647-682)."""
+    return _q4k_legacy("q4k_dequant_gemm", x_bf16, weight_q4k_packed)
+
+
+def q4k_cutlass_gemm(x_bf16, weight_q4k_packed):
+    """x_bf16 @ dequant(W_q4k).T -> BF16, the reference's tensor-core variant
+    (csrc/bindings_python.cu:686-721); same kernel as q4k_dequant_gemm here."""
+    return _q4k_legacy("q4k_cutlass_gemm", x_bf16, weight_q4k_packed)
+
+
 # ---------------------------------------------------------------------------
 # NVFP4 grouped GEMM
 # ---------------------------------------------------------------------------

@@ -198,6 +198,36 @@ torch::Tensor gguf_mmvq(torch::Tensor A, torch::Tensor B_packed, int64_t type_i,
     return C;
 }
 
+// Legacy Q4_K GEMMs (csrc/bindings_python.cu:647-721): x_bf16 @ dequant(W_q4k).T -> BF16.  Both
+// names run the tensor-core kernel with in-kernel decoding and unquantized activations.
+static torch::Tensor q4k_gemm(const char* op, torch::Tensor x_bf16, torch::Tensor weight_q4k_packed) {
+    TORCH_CHECK(x_bf16.is_cuda() && x_bf16.dtype() == torch::kBFloat16, "x_bf16 must be BF16 on CUDA");
+    TORCH_CHECK(x_bf16.dim() == 2 && x_bf16.is_contiguous(), "x_bf16 must be contiguous [M, K]");
+    TORCH_CHECK(weight_q4k_packed.is_cuda() && weight_q4k_packed.dtype() == torch::kUInt8,
+                "weight_q4k_packed must be uint8 on CUDA");
+    TORCH_CHECK(weight_q4k_packed.dim() == 2 && weight_q4k_packed.is_contiguous(),
+                "weight_q4k_packed must be contiguous [N, K*9/16]");
+    const int M = static_cast<int>(x_bf16.size(0));
+    const int K = static_cast<int>(x_bf16.size(1));
+    const int N = static_cast<int>(weight_q4k_packed.size(0));
+    TORCH_CHECK(K % 256 == 0, "K must be divisible by 256, got K=" + std::to_string(K));
+    const int expected_row_bytes = (K / 256) * 144;
+    TORCH_CHECK(weight_q4k_packed.size(1) == expected_row_bytes,
+                "weight row bytes mismatch: expected " + std::to_string(expected_row_bytes) + ", got " +
+                    std::to_string((int)weight_q4k_packed.size(1)));
+    auto output = torch::empty({M, N}, x_bf16.options());
+    lsg_gguf_mmvq_params p = {};
+    p.M = M; p.N = N; p.K = K; p.A = x_bf16.data_ptr(); p.B = weight_q4k_packed.data_ptr(); p.C = output.data_ptr();
+    p.type = LSG_GGUF_Q4_K; p.out_dtype = LSG_DTYPE_BF16;
+    const size_t ws_bytes = lsg_gguf_gemm_bf16_workspace_bytes(M, N, K);
+    auto ws = torch::empty({static_cast<int64_t>(ws_bytes > 0 ? ws_bytes : 1)}, x_bf16.options().dtype(at::kByte));
+    (void)op;
+    check(lsg_gguf_gemm_bf16(&p, ws.data_ptr(), ws_bytes, current_stream()));
+    return output;
+}
+torch::Tensor q4k_dequant_gemm(torch::Tensor x, torch::Tensor w) { return q4k_gemm("q4k_dequant_gemm", x, w); }
+torch::Tensor q4k_cutlass_gemm(torch::Tensor x, torch::Tensor w) { return q4k_gemm("q4k_cutlass_gemm", x, w); }
+
 int64_t query_sf_a(int64_t M, int64_t, int64_t K) { return (int64_t)lsg_nvfp4_sf_buffer_bytes((int)M, (int)K); }
 int64_t query_sf_b(int64_t, int64_t N, int64_t K) { return (int64_t)lsg_nvfp4_sf_buffer_bytes((int)N, (int)K); }
 int64_t query_nvfp4_grouped_gemm_ws(int64_t, int64_t, int64_t, const std::string&) {
@@ -214,8 +244,6 @@ torch::Tensor fp8_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tenso
                        const std::string&) { not_built("fp8_gemm"); }
 torch::Tensor fp8_grouped_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
                                torch::Tensor, torch::Tensor, int64_t, int64_t, const std::string&) { not_built("fp8_grouped_gemm"); }
-torch::Tensor q4k_dequant_gemm(torch::Tensor, torch::Tensor) { not_built("q4k_dequant_gemm"); }
-torch::Tensor q4k_cutlass_gemm(torch::Tensor, torch::Tensor) { not_built("q4k_cutlass_gemm"); }
 int64_t query_zero(int64_t, int64_t, int64_t, const std::string&) { return 0; }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -119,3 +119,22 @@ def test_errors_raise_like_the_reference(GK):
         GK.gguf_mmvq(A, W, 2, 8, 100)
     with pytest.raises(RuntimeError):        # TORCH_CHECK
         GK.gguf_mmvq(A.float(), W, 2, 8, 100)
+
+
+def test_legacy_q4k_gemm_operators(GK):
+    """q4k_dequant_gemm / q4k_cutlass_gemm (tests/test_kernels.py:736-820 of the reference):
+    x_bf16 @ dequant(W_q4k).T -> bf16, checked against the fp32 dequant-then-matmul oracle."""
+    import oracle
+    from layerstormgemmkernels_b200 import quantize as Q
+    from layerstormgemmkernels_b200.capi import GGUF_TYPES
+    M, N, K = 40, 384, 512
+    x = (torch.randn(M, K, generator=torch.Generator().manual_seed(5)) * 0.5).to(torch.bfloat16).cuda()
+    W = Q.quantize_q4_k((np.random.default_rng(5).standard_normal((N, K)) * 0.02).astype(np.float32))
+    Wd = torch.from_numpy(W).cuda()
+    ref = oracle.dequant_gemm(GGUF_TYPES["Q4_K"], x.view(torch.int16).cpu().numpy().view(np.uint16), W, K)
+    for fn in (GK.q4k_dequant_gemm, GK.q4k_cutlass_gemm):
+        out = fn(x, Wd)
+        assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= (1e-3 + 2.0 ** -8) * np.abs(ref).max()
+    with pytest.raises(RuntimeError):
+        GK.q4k_dequant_gemm(x[:, :500].contiguous(), Wd)

@@ -212,3 +212,40 @@ def test_moe_ffn_vs_oracle_small(ops):
         act = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
         ref = oracle.mmvq(T[name], oracle.quantize_q8_1(act.view(torch.int16).numpy().view(np.uint16)), wd, I)
         assert np.abs(got[rows] - ref).max() <= (TOL_TC + 2.0 ** -7) * np.abs(ref).max()
+
+
+# ---------------------------------------------------------------------------
+# Unquantized activations: bf16 x fp16 on the tensor core (legacy q4k_* operators)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name,M,N,K", [
+    ("Q4_K", 1, 256, 256), ("Q4_K", 7, 384, 1024), ("Q4_K", 64, 4096, 4096), ("Q4_K", 300, 200, 512),
+    ("Q6_K", 33, 256, 512), ("Q8_0", 20, 130, 96), ("Q2_K", 5, 128, 256),
+])
+def test_gemm_bf16_activations_vs_dequant_oracle(ops, name, M, N, K):
+    """C = A_bf16 . dequant(W)^T, checker = the fp32 dequant-then-matmul oracle
+    (the reference's CPU path, tests/test_reference.py:284-329)."""
+    A, W, Wd = make_case(name, M, N, K, seed=3 * M + N)
+    cols = np.r_[0:min(N, 24), max(0, N - 24):N]
+    ref = oracle.dequant_gemm(T[name], bits_of(A), W[cols], K)
+    got = ops.gguf_gemm_bf16(A, Wd, T[name], N, K, out_dtype=torch.float32).cpu().numpy()[:, cols]
+    assert np.abs(got - ref).max() <= TOL_TC * np.abs(ref).max()
+    again = ops.gguf_gemm_bf16(A, Wd, T[name], N, K, out_dtype=torch.float32).cpu().numpy()[:, cols]
+    assert np.array_equal(got, again)
+
+
+def test_q4k_legacy_operators(ops):
+    """q4k_dequant_gemm / q4k_cutlass_gemm of the reference (tests/test_kernels.py:736-820):
+    same signature, bf16 output, argument checks."""
+    M, N, K = 48, 512, 1024
+    A = (torch.randn(M, K, generator=torch.Generator().manual_seed(1)) * 0.5).to(torch.bfloat16).cuda()
+    W = Q.quantize_q4_k((np.random.default_rng(0).standard_normal((N, K)) * 0.02).astype(np.float32))
+    Wd = torch.from_numpy(W).cuda()
+    ref = oracle.dequant_gemm(T["Q4_K"], bits_of(A), W, K)
+    for fn in (ops.q4k_dequant_gemm, ops.q4k_cutlass_gemm):
+        out = fn(A, Wd)
+        assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N)
+        assert np.abs(out.float().cpu().numpy() - ref).max() <= (TOL_TC + 2.0 ** -8) * np.abs(ref).max()
+    with pytest.raises(RuntimeError):
+        ops.q4k_dequant_gemm(A[:, :1000].contiguous(), Wd)          # K not a multiple of 256
+    with pytest.raises(RuntimeError):
+        ops.q4k_cutlass_gemm(A, Wd[:, :100].contiguous())            # row bytes mismatch
