@@ -358,6 +358,27 @@ typedef struct lsg_nvfp4_grouped_gemm_params {
     const void* const* scale_B_ptrs; /* optional [E] per-expert scale pointers           */
 } lsg_nvfp4_grouped_gemm_params;
 
+/* Single-problem NVFP4 quantizer and GEMM.  Replace launch_bf16_to_nvfp4
+ * (csrc/smxx/quant/bf16_to_nvfp4.cu:76-140), query_nvfp4_gemm_workspace_size and
+ * launch_nvfp4_gemm (csrc/sm120/gemm/nvfp4/nvfp4_gemm.cu:189-200).  Scale buffers use the
+ * interleaved layout of lsg_nvfp4_sf_buffer_bytes(rows, K); the quantizer does not write the
+ * padding entries (callers zero the buffer first, as the reference's binding does). */
+LSG_API int lsg_bf16_to_nvfp4(const void* x_bf16, void* output_packed, void* output_scales, int M, int K,
+                              void* stream);
+typedef struct lsg_nvfp4_gemm_params {
+    int M, N, K;
+    const void* A;        /* [M, K/2] e2m1 codes, low nibble = even k   */
+    const void* B;        /* [N, K/2]                                   */
+    void* D;              /* [M, N] output_dtype                        */
+    const void* scale_A;  /* ue4m3, interleaved layout of (M, K/16)     */
+    const void* scale_B;  /* ue4m3, interleaved layout of (N, K/16)     */
+    float alpha;          /* output scale                               */
+    int output_dtype;     /* LSG_DTYPE_BF16, _F16 or _F32               */
+} lsg_nvfp4_gemm_params;
+LSG_API size_t lsg_nvfp4_gemm_workspace_bytes(int M, int N, int K);
+LSG_API int lsg_nvfp4_gemm(const lsg_nvfp4_gemm_params* p, void* workspace, size_t workspace_bytes,
+                           void* stream);
+
 /* Replaces query_nvfp4_grouped_gemm_workspace_size (nvfp4_grouped_gemm.cu:373-384); needs
  * the row count because this implementation expands the operands to fp16 in the workspace. */
 LSG_API size_t lsg_nvfp4_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K);

@@ -74,6 +74,12 @@ class GgufMoeFfnParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int)]
 
 
+class Nvfp4GemmParams(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("A", ctypes.c_void_p),
+                ("B", ctypes.c_void_p), ("D", ctypes.c_void_p), ("scale_A", ctypes.c_void_p),
+                ("scale_B", ctypes.c_void_p), ("alpha", ctypes.c_float), ("output_dtype", ctypes.c_int)]
+
+
 class Nvfp4GroupedGemmParams(ctypes.Structure):
     _fields_ = [("num_experts", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
                 ("A_base", ctypes.c_void_p), ("B_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p),
@@ -112,6 +118,9 @@ def _load():
         "lsg_nvfp4_sf_offsets": (ci, [vp, vp, ci, vp]),
         "lsg_gguf_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_grouped_gemm": (ci, [ctypes.POINTER(GgufGroupedGemmParams), ci, vp, sz, ci, vp]),
+        "lsg_bf16_to_nvfp4": (ci, [vp, vp, vp, ci, ci, vp]),
+        "lsg_nvfp4_gemm_workspace_bytes": (sz, [ci, ci, ci]),
+        "lsg_nvfp4_gemm": (ci, [ctypes.POINTER(Nvfp4GemmParams), vp, sz, vp]),
         "lsg_gguf_moe_ffn_workspace_bytes": (sz, [ci, ci, ci, ci]),
         "lsg_gguf_moe_ffn": (ci, [ctypes.POINTER(GgufMoeFfnParams), ci, vp, sz, vp]),
         "lsg_build_active_expert_list": (ci, [vp, ci, ci, vp, vp]),

@@ -30,7 +30,8 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
 
 int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_rows, int K, int N,
                 void* C, int out_dtype, const float* alphas, int M, const int* tile_expert,
-                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s);
+                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s,
+                float alpha_host = 1.0f);
 
 // Tensor-core GEMM with in-kernel weight decoding (tc_fused.cu).
 bool tc_fused_available(int type);

@@ -61,7 +61,12 @@ nvfp4_to_f16_kernel(const uint8_t* __restrict__ packed, const void* const* __res
     const uint8_t* src;
     const uint8_t* sc;
     int local;
-    if (is_b) {
+    if (expert_offsets == nullptr) {
+        // single problem: rows and scales as they are
+        local = static_cast<int>(row);
+        src = packed + static_cast<size_t>(row) * (K >> 1);
+        sc = scales;
+    } else if (is_b) {
         const int e = static_cast<int>(row / N);
         local = static_cast<int>(row - static_cast<long long>(e) * N);
         if (expert_offsets[e + 1] - expert_offsets[e] <= 0) return;  // expert without rows: never read
@@ -189,4 +194,57 @@ extern "C" int lsg_nvfp4_grouped_gemm(const lsg_nvfp4_grouped_gemm_params* p, in
     }
     return tc_gemm_f16(a16, T, b16, static_cast<long long>(E) * N, K, N, p->D_base, p->output_dtype,
                        p->alphas, T, tile_expert, tile_mstart, t_max, offs, s);
+}
+
+// ---------------------------------------------------------------------------
+// Single problem: D[M,N] = alpha * (A (x) SFA) . (B (x) SFB)^T.
+// Replaces launch_nvfp4_gemm / query_nvfp4_gemm_workspace_size
+// (csrc/sm120/gemm/nvfp4/nvfp4_gemm.cu:189-200, params gemm.h) on the same exact fp16
+// expansion as the grouped operator.
+// ---------------------------------------------------------------------------
+extern "C" size_t lsg_nvfp4_gemm_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return a256(static_cast<size_t>(M) * K * 2) + a256(static_cast<size_t>(N) * K * 2);
+}
+
+extern "C" int lsg_nvfp4_gemm(const lsg_nvfp4_gemm_params* p, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+    if (!p) return fail(LSG_ERR_INVALID, "nvfp4_gemm: null params");
+    if (p->M < 0 || p->N < 0 || p->K < 0) return fail(LSG_ERR_INVALID, "nvfp4_gemm: negative shape");
+    if (p->M == 0 || p->N == 0) return LSG_OK;
+    if (p->K % 32 != 0 || p->K == 0)
+        return fail(LSG_ERR_INVALID, "nvfp4_gemm: K must be a positive multiple of 32 (K=%d)", p->K);
+    if (p->output_dtype != LSG_DTYPE_BF16 && p->output_dtype != LSG_DTYPE_F16 && p->output_dtype != LSG_DTYPE_F32)
+        return fail(LSG_ERR_UNSUPPORTED, "nvfp4_gemm: output dtype must be bf16, fp16 or f32");
+    if (!p->A || !p->B || !p->D || !p->scale_A || !p->scale_B)
+        return fail(LSG_ERR_INVALID, "nvfp4_gemm: null pointer in params");
+    const size_t need = lsg_nvfp4_gemm_workspace_bytes(p->M, p->N, p->K);
+    if (!workspace || workspace_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "nvfp4_gemm: workspace too small (have %zu, need %zu)",
+                    workspace ? workspace_bytes : size_t(0), need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+        return fail(LSG_ERR_ALIGNMENT, "nvfp4_gemm: workspace must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int M = p->M, N = p->N, K = p->K, gpr = K / 16;
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    __half* a16 = reinterpret_cast<__half*>(base);
+    __half* b16 = reinterpret_cast<__half*>(base + a256(static_cast<size_t>(M) * K * 2));
+    const void* const* no_ptrs = nullptr;
+    const int32_t* no_offs = nullptr;
+    {
+        const long long total = static_cast<long long>(M) * gpr;
+        LSG_CUDA_TRY(launch_kernel(nvfp4_to_f16_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256),
+                                   0, s, true, static_cast<const uint8_t*>(p->A), no_ptrs,
+                                   static_cast<const uint8_t*>(p->scale_A), no_ptrs, no_offs, no_offs, a16,
+                                   static_cast<long long>(M), K, N, 1, 0));
+    }
+    {
+        const long long total = static_cast<long long>(N) * gpr;
+        LSG_CUDA_TRY(launch_kernel(nvfp4_to_f16_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256),
+                                   0, s, true, static_cast<const uint8_t*>(p->B), no_ptrs,
+                                   static_cast<const uint8_t*>(p->scale_B), no_ptrs, no_offs, no_offs, b16,
+                                   static_cast<long long>(N), K, N, 1, 1));
+    }
+    return tc_gemm_f16(a16, M, b16, N, K, N, p->D, p->output_dtype, nullptr, M, nullptr, nullptr, 0, nullptr, s,
+                       p->alpha);
 }

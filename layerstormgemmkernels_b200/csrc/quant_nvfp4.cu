@@ -66,10 +66,16 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
     const int row = blockIdx.y;
     const int gpr = K >> 4;
     if (threadIdx.x == 0) {
-        const int e = expert_of_row(expert_offsets, E, row);
-        s_info[0] = expert_offsets[e];
-        s_info[1] = sf_offsets[e];
-        s_info[2] = e;
+        if (expert_offsets == nullptr) {   // single problem
+            s_info[0] = 0;
+            s_info[1] = 0;
+            s_info[2] = 0;
+        } else {
+            const int e = expert_of_row(expert_offsets, E, row);
+            s_info[0] = expert_offsets[e];
+            s_info[1] = sf_offsets[e];
+            s_info[2] = e;
+        }
     }
     __syncthreads();
     const int g = blockIdx.x * blockDim.x + threadIdx.x;
@@ -197,5 +203,28 @@ extern "C" int lsg_nvfp4_sf_offsets(const int32_t* expert_offsets, int32_t* sf_o
     nvfp4_sf_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(expert_offsets,
                                                                              sf_offsets, num_experts);
     LSG_CUDA_TRY(cudaGetLastError());
+    return LSG_OK;
+}
+
+// Single-problem quantizer: x[M,K] bf16 -> e2m1 codes [M, K/2] + ue4m3 scales in the
+// interleaved layout of an (M, K/16) scale matrix.  Replaces launch_bf16_to_nvfp4,
+// csrc/smxx/quant/bf16_to_nvfp4.cu:76-140 (same arithmetic as the grouped kernel with one
+// expert and no global input scale).  Padding entries of the scale buffer are not written.
+extern "C" int lsg_bf16_to_nvfp4(const void* x_bf16, void* output_packed, void* output_scales, int M, int K,
+                                 void* stream) {
+    if (K % 16 != 0) return LSG_OK;   // as the reference: silently nothing (bf16_to_nvfp4.cu:137)
+    if (M <= 0 || K <= 0) return LSG_OK;
+    if (!x_bf16 || !output_packed || !output_scales) return fail(LSG_ERR_INVALID, "bf16_to_nvfp4: null pointer");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(output_packed) & 7))
+        return fail(LSG_ERR_ALIGNMENT, "bf16_to_nvfp4: input must be 16-byte and output 8-byte aligned");
+    if (M > 65535) return fail(LSG_ERR_UNSUPPORTED, "bf16_to_nvfp4: more than 65535 rows per call is not supported");
+    const int gpr = K / 16;
+    const int threads = gpr < 256 ? ((gpr + 31) / 32) * 32 : 256;
+    dim3 grid((gpr + threads - 1) / threads, M);
+    LSG_CUDA_TRY(launch_kernel(nvfp4_grouped_quant_kernel<false>, grid, dim3(threads), 0,
+                               static_cast<cudaStream_t>(stream), true, static_cast<const __nv_bfloat16*>(x_bf16),
+                               static_cast<const __nv_bfloat16*>(nullptr), static_cast<uint8_t*>(output_packed),
+                               static_cast<uint8_t*>(output_scales), static_cast<const int32_t*>(nullptr),
+                               static_cast<const int32_t*>(nullptr), static_cast<const float*>(nullptr), M, 1, K));
     return LSG_OK;
 }

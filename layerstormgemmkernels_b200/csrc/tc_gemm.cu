@@ -54,6 +54,7 @@ struct TcArgs {
     int ldc;
     int out_f32;              // lsg_dtype of C: 0 bf16, 1 f32, 2 f16
     const float* alphas;      // optional per-expert output scale (grouped) or single value (dense)
+    float alpha_host;         // output scale known on the host (used when alphas is null and it is not 1)
     int K;
     int N;                    // columns of one problem (per expert)
     int n_tiles;              // ceil(N / BN)
@@ -199,14 +200,15 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int row = mstart + warp * 32 + lane;
             const bool row_ok = row < mend;
             const int n0 = j * BN;
-            float alpha = 1.0f;
+            float alpha = a.alpha_host;
             if (a.alphas) alpha = a.tile_expert ? a.alphas[a.tile_expert[t]] : a.alphas[0];
+            const bool scaled = a.alphas != nullptr || alpha != 1.0f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * BN + c, r);
                 if (row_ok && n0 + c < a.N) {
-                    if (a.alphas) {
+                    if (scaled) {
 #pragma unroll
                         for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
                     }
@@ -441,6 +443,7 @@ int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void*
     rc = make_map(&tmB, w16, N, K, BN);
     if (rc != LSG_OK) return rc;
     TcArgs a = {};
+    a.alpha_host = 1.0f;
     a.C = C; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = (M + BM - 1) / BM;
@@ -470,6 +473,7 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
     rc = make_map(&tmB, w16, static_cast<long long>(E) * N, K, BN);
     if (rc != LSG_OK) return rc;
     TcArgs a = {};
+    a.alpha_host = 1.0f;
     a.C = D; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = t_max;
@@ -486,14 +490,15 @@ int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void*
 // matrices of N rows each.
 int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_rows, int K, int N,
                 void* C, int out_dtype, const float* alphas, int M, const int* tile_expert,
-                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s) {
+                const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s,
+                float alpha_host) {
     CUtensorMap tmA, tmB;
     int rc = make_map(&tmA, A16, a_rows, K, BM);
     if (rc != LSG_OK) return rc;
     rc = make_map(&tmB, B16, b_rows, K, BN);
     if (rc != LSG_OK) return rc;
     TcArgs a = {};
-    a.C = C; a.ldc = N; a.out_f32 = out_dtype; a.alphas = alphas; a.K = K; a.N = N;
+    a.C = C; a.ldc = N; a.out_f32 = out_dtype; a.alphas = alphas; a.alpha_host = alpha_host; a.K = K; a.N = N;
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = tile_expert ? t_max : (M + BM - 1) / BM;
     a.M = M;

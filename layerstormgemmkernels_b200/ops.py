@@ -365,6 +365,60 @@ def nvfp4_gemm_preprocess(weight_scales, N, K):
     return out
 
 
+def bf16_to_nvfp4(x):
+    """bf16 x[M,K] -> (codes uint8 [M, K/2], ue4m3 scales uint8 [sf_buffer_bytes(M, K)]), the
+    single-problem quantizer (launch_bf16_to_nvfp4, csrc/smxx/quant/bf16_to_nvfp4.cu:136-140)."""
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous(),
+             "bf16_to_nvfp4: x must be contiguous BF16 [M, K] on CUDA")
+    M, K = x.shape
+    _require(K % 16 == 0, "bf16_to_nvfp4: K must be divisible by 16")
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.zeros((_lib.lsg_nvfp4_sf_buffer_bytes(M, K),), dtype=torch.uint8, device=x.device)
+    capi.check(_lib.lsg_bf16_to_nvfp4(_ptr(x), _ptr(packed), _ptr(scales), M, K, _stream()))
+    return packed, scales
+
+
+def nvfp4_gemm(A, B, scale_A, scale_B, M, N, K, alpha, output_dtype):
+    """D[M,N] = alpha * (A x SFA) . (B x SFB)^T on pre-quantized operands.
+    Mirrors nvfp4_gemm (csrc/bindings_python.cu:64-110)."""
+    _require(A.is_cuda and B.is_cuda, "nvfp4_gemm: A and B must be on CUDA")
+    _require(scale_A.is_cuda and scale_B.is_cuda, "nvfp4_gemm: scales must be on CUDA")
+    _require(A.is_contiguous() and B.is_contiguous(), "nvfp4_gemm: A and B must be contiguous")
+    code, tdtype = _parse_output_dtype(output_dtype)
+    D = torch.empty((M, N), dtype=tdtype, device=A.device)
+    ws_bytes = _lib.lsg_nvfp4_gemm_workspace_bytes(int(M), int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    p = capi.Nvfp4GemmParams(M=int(M), N=int(N), K=int(K), A=A.data_ptr(), B=B.data_ptr(), D=D.data_ptr(),
+                             scale_A=scale_A.data_ptr(), scale_B=scale_B.data_ptr(), alpha=float(alpha),
+                             output_dtype=code)
+    capi.check(_lib.lsg_nvfp4_gemm(ctypes.byref(p), _ptr(ws), ws_bytes, _stream()))
+    return D
+
+
+def nvfp4_gemm_from_bf16(x_bf16, weight_packed_uint8, weight_scales, weight_scale_global):
+    """bf16 activations -> NVFP4 quantization -> GEMM against packed NVFP4 weights -> bf16.
+    Mirrors nvfp4_gemm_from_bf16 (csrc/bindings_python.cu:147-244): weight_scales either
+    [N, K/16] values or the preprocessed 1-D uint8 buffer of nvfp4_gemm_preprocess."""
+    _require(x_bf16.is_cuda and x_bf16.dtype == torch.bfloat16, "x_bf16 must be BF16 on CUDA")
+    _require(x_bf16.dim() == 2 and x_bf16.is_contiguous(), "x_bf16 must be contiguous [M, K]")
+    _require(weight_packed_uint8.is_cuda and weight_packed_uint8.dtype == torch.uint8,
+             "weight_packed_uint8 must be uint8 on CUDA")
+    _require(weight_packed_uint8.dim() == 2 and weight_packed_uint8.is_contiguous(),
+             "weight_packed_uint8 must be contiguous [N, K/2]")
+    _require(weight_scales.is_cuda, "weight_scales must be on CUDA")
+    M, K = x_bf16.shape
+    N = weight_packed_uint8.size(0)
+    _require(weight_packed_uint8.size(1) == K // 2, "weight shape mismatch: expected [N, K/2]")
+    _require(K % 32 == 0, f"K must be divisible by 32, got K={K}")
+    _require(N % 32 == 0, f"N must be divisible by 32, got N={N}")
+    if weight_scales.dtype == torch.uint8 and weight_scales.dim() == 1:
+        sfb = weight_scales
+    else:
+        sfb = nvfp4_gemm_preprocess(weight_scales, N, K)
+    codes, sfa = bf16_to_nvfp4(x_bf16)
+    return nvfp4_gemm(codes, weight_packed_uint8, sfa, sfb, M, N, K, float(weight_scale_global), "bf16")
+
+
 def query_sf_buffer_size_b(M, N, K):
     return _lib.lsg_nvfp4_sf_buffer_bytes(int(N), int(K))
 

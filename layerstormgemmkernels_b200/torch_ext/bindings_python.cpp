@@ -235,10 +235,51 @@ int64_t query_nvfp4_grouped_gemm_ws(int64_t, int64_t, int64_t, const std::string
     return 0;
 }
 
+// Single-problem NVFP4 (csrc/bindings_python.cu:64-110 and 147-244).
+torch::Tensor nvfp4_gemm(torch::Tensor A, torch::Tensor B, torch::Tensor scale_A, torch::Tensor scale_B, int64_t M,
+                         int64_t N, int64_t K, double alpha, const std::string& output_dtype) {
+    TORCH_CHECK(A.is_cuda() && B.is_cuda(), "nvfp4_gemm: A and B must be on CUDA");
+    TORCH_CHECK(scale_A.is_cuda() && scale_B.is_cuda(), "nvfp4_gemm: scales must be on CUDA");
+    TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "nvfp4_gemm: A and B must be contiguous");
+    at::ScalarType st;
+    const int code = parse_output_dtype(output_dtype, &st);
+    auto D = torch::empty({M, N}, A.options().dtype(st));
+    const size_t ws_bytes = lsg_nvfp4_gemm_workspace_bytes((int)M, (int)N, (int)K);
+    auto ws = torch::empty({static_cast<int64_t>(ws_bytes > 0 ? ws_bytes : 1)}, A.options().dtype(at::kByte));
+    lsg_nvfp4_gemm_params p = {};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = D.data_ptr();
+    p.scale_A = scale_A.data_ptr(); p.scale_B = scale_B.data_ptr();
+    p.alpha = static_cast<float>(alpha); p.output_dtype = code;
+    check(lsg_nvfp4_gemm(&p, ws.data_ptr(), ws_bytes, current_stream()));
+    return D;
+}
+
+torch::Tensor nvfp4_gemm_preprocess(torch::Tensor weight_scales, int64_t N, int64_t K);
+
+torch::Tensor nvfp4_gemm_from_bf16(torch::Tensor x_bf16, torch::Tensor weight_packed_uint8, torch::Tensor weight_scales,
+                                   double weight_scale_global) {
+    TORCH_CHECK(x_bf16.is_cuda() && x_bf16.dtype() == torch::kBFloat16, "x_bf16 must be BF16 on CUDA");
+    TORCH_CHECK(x_bf16.dim() == 2 && x_bf16.is_contiguous(), "x_bf16 must be contiguous [M, K]");
+    TORCH_CHECK(weight_packed_uint8.is_cuda() && weight_packed_uint8.dtype() == torch::kUInt8,
+                "weight_packed_uint8 must be uint8 on CUDA");
+    TORCH_CHECK(weight_packed_uint8.dim() == 2 && weight_packed_uint8.is_contiguous(),
+                "weight_packed_uint8 must be contiguous [N, K/2]");
+    TORCH_CHECK(weight_scales.is_cuda(), "weight_scales must be on CUDA");
+    const int M = (int)x_bf16.size(0), K = (int)x_bf16.size(1), N = (int)weight_packed_uint8.size(0);
+    TORCH_CHECK(weight_packed_uint8.size(1) == K / 2, "weight shape mismatch: expected [N, K/2]");
+    TORCH_CHECK(K % 32 == 0, "K must be divisible by 32, got K=" + std::to_string(K));
+    TORCH_CHECK(N % 32 == 0, "N must be divisible by 32, got N=" + std::to_string(N));
+    const bool pre = weight_scales.dtype() == torch::kUInt8 && weight_scales.dim() == 1;
+    torch::Tensor sfb = pre ? weight_scales : nvfp4_gemm_preprocess(weight_scales, N, K);
+    auto bytes = x_bf16.options().dtype(at::kByte);
+    auto codes = torch::empty({M, K / 2}, bytes);
+    auto sfa = torch::zeros({static_cast<int64_t>(lsg_nvfp4_sf_buffer_bytes(M, K))}, bytes);
+    check(lsg_bf16_to_nvfp4(x_bf16.data_ptr(), codes.data_ptr(), sfa.data_ptr(), M, K, current_stream()));
+    return nvfp4_gemm(codes, weight_packed_uint8, sfa, sfb, M, N, K, weight_scale_global, "bf16");
+}
+
 // Operators of the reference that this build does not carry yet.
-torch::Tensor nvfp4_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t, int64_t,
-                         double, const std::string&) { not_built("nvfp4_gemm"); }
-torch::Tensor nvfp4_gemm_from_bf16(torch::Tensor, torch::Tensor, torch::Tensor, double) { not_built("nvfp4_gemm_from_bf16"); }
 std::tuple<torch::Tensor, torch::Tensor> weight_fp8_quant(torch::Tensor) { not_built("weight_fp8_quant"); }
 torch::Tensor fp8_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t, int64_t,
                        const std::string&) { not_built("fp8_gemm"); }

@@ -91,3 +91,57 @@ def test_quantizer_to_gemm_pairing(ops, N, K, offs, with_is):
         full = xf[s:t] @ (wdeq[e].T * (alphas[e] / (float(isc[e]) if with_is else 1.0)))
         cos = (full * got[s:t]).sum() / np.sqrt((full * full).sum() * (got[s:t] ** 2).sum())
         assert cos > 0.99
+
+
+# ---------------------------------------------------------------------------
+# Single-problem operators (nvfp4_gemm, bf16_to_nvfp4, nvfp4_gemm_from_bf16)
+# ---------------------------------------------------------------------------
+def test_single_gemm_known_answer(ops):
+    """All values 0.5, scales 1, alpha 2 -> 2 * K * 0.25 (tests/test_kernels.py:244-268 style)."""
+    M, N, K = 96, 160, 256
+    A = torch.full((M, K // 2), 0x11, dtype=torch.uint8, device="cuda")
+    B = torch.full((N, K // 2), 0x11, dtype=torch.uint8, device="cuda")
+    sA = torch.full((ops.query_sf_buffer_size_a(M, N, K),), UE4M3_ONE, dtype=torch.uint8, device="cuda")
+    sB = torch.full((ops.query_sf_buffer_size_b(M, N, K),), UE4M3_ONE, dtype=torch.uint8, device="cuda")
+    for dt, td in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
+        D = ops.nvfp4_gemm(A, B, sA, sB, M, N, K, 2.0, dt)
+        assert D.dtype == td and tuple(D.shape) == (M, N)
+        assert torch.equal(D.float(), torch.full((M, N), 2.0 * K * 0.25, device="cuda"))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (37, 256, 512), (300, 96, 1024)])
+def test_single_quantizer_equals_grouped_with_one_expert(ops, M, N, K):
+    """bf16_to_nvfp4 is the grouped quantizer with one expert and no input scale: same bytes."""
+    x = (torch.randn(M, K, generator=torch.Generator().manual_seed(M)) * 0.7).to(torch.bfloat16).cuda()
+    codes, sfa = ops.bf16_to_nvfp4(x)
+    offs = torch.tensor([0, M], dtype=torch.int32, device="cuda")
+    gc, gs, _ = ops.bf16_to_nvfp4_grouped(x, offs, None)
+    assert torch.equal(codes, gc)
+    n = min(sfa.numel(), gs.numel())
+    assert torch.equal(sfa[:n], gs.reshape(-1)[:n])
+    # and against the CPU oracle of the grouped quantizer
+    oc, osc = oracle.bf16_to_nvfp4_grouped(bits_of(x), np.array([0, M], dtype=np.int32), None)[:2]
+    assert np.array_equal(codes.cpu().numpy(), oc)
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 128, 256), (130, 256, 512)])
+def test_single_gemm_from_bf16(ops, M, N, K):
+    """bf16 activations -> NVFP4 -> GEMM, against dequantized codes x dequantized weights."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(N, K, generator=g).numpy()
+    c, sc, s2 = Q.quantize_nvfp4(w)
+    wdeq = Q.dequantize_nvfp4(c, sc, 1.0).astype(np.float64)
+    wc = torch.from_numpy(c).cuda()
+    out = ops.nvfp4_gemm_from_bf16(x, wc, torch.from_numpy(sc).cuda(), float(s2))
+    pre = ops.nvfp4_gemm_preprocess(torch.from_numpy(sc).cuda(), N, K)
+    out2 = ops.nvfp4_gemm_from_bf16(x, wc, pre, float(s2))
+    assert torch.equal(out, out2)
+    codes, sfa = ops.bf16_to_nvfp4(x)
+    xa = _decode_grouped(codes.cpu().numpy(), sfa.cpu().numpy(), np.array([0, 0], dtype=np.int32), [0, M], K).astype(np.float64)
+    ref = (xa @ wdeq.T) * np.float64(np.float32(s2))
+    got = out.float().cpu().numpy()
+    assert np.abs(got - ref).max() <= (2.0 ** -8 + 1e-5) * np.abs(ref).max()
+    full = x.float().cpu().numpy() @ (wdeq.T * float(s2))
+    cos = (full * got).sum() / np.sqrt((full * full).sum() * (got ** 2).sum())
+    assert cos > 0.99
