@@ -289,6 +289,53 @@ LSG_API int lsg_build_mmq_tile_map(const int32_t* expert_offsets, int num_expert
 /* Activation quantizers for the FP8 / NVFP4 paths                          */
 /* ------------------------------------------------------------------------ */
 
+/* FP8 (e4m3) block-scaled GEMM family.  D = sum over 128-wide K blocks of
+ * scale_A[m,kb] * scale_B[n/128,kb] * (A8 . B8^T over the block).
+ *   scale_A: fp32 [M, ceil(K/128)] M-major (what lsg_dynamic_fp8_quant writes with
+ *            m_major_scales = 1); grouped: per expert, M-major inside the expert's rows,
+ *            starting at expert_offsets[e] * ceil(K/128) floats
+ *   scale_B: fp32 [ceil(K/128), ceil(N/128)] K-major (what lsg_weight_fp8_quant writes);
+ *            grouped: one such matrix per expert, contiguous or through scale_B_ptrs
+ * Replace launch_fp8_gemm / query_fp8_gemm_workspace_size (csrc/sm120/gemm/fp8/fp8_gemm.h:18-60,
+ * fp8_gemm.cu), launch_fp8_grouped_gemm (fp8_grouped_gemm.cu:52-151; no host synchronisation
+ * here) and launch_weight_fp8_quant (csrc/smxx/quant/weight_fp8_quant.cu:51-150, bit-exact).
+ * K must be a multiple of 16. */
+typedef struct lsg_fp8_gemm_params {
+    int M, N, K;
+    const void* A;         /* [M,K] e4m3 */
+    const void* B;         /* [N,K] e4m3 */
+    void* D;               /* [M,N] output_dtype */
+    const void* scale_A;
+    const void* scale_B;
+    int output_dtype;      /* LSG_DTYPE_BF16, _F16 or _F32 */
+} lsg_fp8_gemm_params;
+LSG_API size_t lsg_fp8_gemm_workspace_bytes(int M, int N, int K);
+LSG_API int lsg_fp8_gemm(const lsg_fp8_gemm_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Mirrors struct Fp8GroupedGemmParams, csrc/sm120/gemm/grouped_gemm.h:84-105 (problem_sizes is
+ * accepted and ignored: the row counts come from expert_offsets). */
+typedef struct lsg_fp8_grouped_gemm_params {
+    int num_experts, N, K;
+    const void* A_base;
+    const void* B_base;
+    void* D_base;
+    const void* scale_A_base;
+    const void* scale_B_base;
+    const int32_t* expert_offsets;
+    const int32_t* problem_sizes;
+    int output_dtype;
+    const void* const* B_ptrs;
+    const void* const* scale_B_ptrs;
+} lsg_fp8_grouped_gemm_params;
+LSG_API size_t lsg_fp8_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K);
+LSG_API int lsg_fp8_grouped_gemm(const lsg_fp8_grouped_gemm_params* p, int total_tokens, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+
+/* bf16 weight [N,K] -> e4m3 [N,K] + one fp32 scale per 128 x 128 tile, stored K-major
+ * (scales[kb + nb * ceil(K/128)]).  Not in-place safe. */
+LSG_API int lsg_weight_fp8_quant(const void* weight_bf16, void* output_e4m3, float* scales, int N, int K,
+                                 void* stream);
+
 /* Mirrors struct DynamicFp8QuantParams, csrc/smxx/quant/dynamic_fp8_quant.h:25-32. */
 typedef struct lsg_dynamic_fp8_quant_params {
     int num_tokens;     /* M */

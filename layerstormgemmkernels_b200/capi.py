@@ -74,6 +74,20 @@ class GgufMoeFfnParams(ctypes.Structure):
                 ("out_dtype", ctypes.c_int)]
 
 
+class Fp8GemmParams(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("A", ctypes.c_void_p),
+                ("B", ctypes.c_void_p), ("D", ctypes.c_void_p), ("scale_A", ctypes.c_void_p),
+                ("scale_B", ctypes.c_void_p), ("output_dtype", ctypes.c_int)]
+
+
+class Fp8GroupedGemmParams(ctypes.Structure):
+    _fields_ = [("num_experts", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("A_base", ctypes.c_void_p), ("B_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p),
+                ("scale_A_base", ctypes.c_void_p), ("scale_B_base", ctypes.c_void_p),
+                ("expert_offsets", ctypes.c_void_p), ("problem_sizes", ctypes.c_void_p),
+                ("output_dtype", ctypes.c_int), ("B_ptrs", ctypes.c_void_p), ("scale_B_ptrs", ctypes.c_void_p)]
+
+
 class Nvfp4GemmParams(ctypes.Structure):
     _fields_ = [("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("A", ctypes.c_void_p),
                 ("B", ctypes.c_void_p), ("D", ctypes.c_void_p), ("scale_A", ctypes.c_void_p),
@@ -118,6 +132,11 @@ def _load():
         "lsg_nvfp4_sf_offsets": (ci, [vp, vp, ci, vp]),
         "lsg_gguf_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_grouped_gemm": (ci, [ctypes.POINTER(GgufGroupedGemmParams), ci, vp, sz, ci, vp]),
+        "lsg_fp8_gemm_workspace_bytes": (sz, [ci, ci, ci]),
+        "lsg_fp8_gemm": (ci, [ctypes.POINTER(Fp8GemmParams), vp, sz, vp]),
+        "lsg_fp8_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci, ci]),
+        "lsg_fp8_grouped_gemm": (ci, [ctypes.POINTER(Fp8GroupedGemmParams), ci, vp, sz, vp]),
+        "lsg_weight_fp8_quant": (ci, [vp, vp, vp, ci, ci, vp]),
         "lsg_bf16_to_nvfp4": (ci, [vp, vp, vp, ci, ci, vp]),
         "lsg_nvfp4_gemm_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_nvfp4_gemm": (ci, [ctypes.POINTER(Nvfp4GemmParams), vp, sz, vp]),

@@ -133,6 +133,52 @@ def dynamic_fp8_quant(input, m_major_scales=False):
     return out, scales
 
 
+def weight_fp8_quant(weight):
+    """bf16 [N,K] -> (float8_e4m3fn [N,K], fp32 scales [ceil(N/128), ceil(K/128)]): one scale per
+    128 x 128 tile.  Mirrors weight_fp8_quant (csrc/bindings_python.cu:444-471)."""
+    _require(weight.is_cuda and weight.dtype == torch.bfloat16, "weight_fp8_quant: weight must be BF16 on CUDA")
+    _require(weight.dim() == 2 and weight.is_contiguous(), "weight_fp8_quant: weight must be contiguous [N, K]")
+    N, K = weight.shape
+    out = torch.empty((N, K), dtype=torch.float8_e4m3fn, device=weight.device)
+    scales = torch.empty(((N + 127) // 128, (K + 127) // 128), dtype=torch.float32, device=weight.device)
+    capi.check(_lib.lsg_weight_fp8_quant(_ptr(weight), _ptr(out), _ptr(scales), N, K, _stream()))
+    return out, scales
+
+
+def fp8_gemm(A, B, scale_A, scale_B, M, N, K, output_dtype):
+    """Block-scaled e4m3 GEMM -> [M,N].  Mirrors fp8_gemm (csrc/bindings_python.cu:475-510)."""
+    _require(A.is_cuda and B.is_cuda, "fp8_gemm: A and B must be on CUDA")
+    _require(A.is_contiguous() and B.is_contiguous(), "fp8_gemm: must be contiguous")
+    code, tdtype = _parse_output_dtype(output_dtype)
+    D = torch.empty((M, N), dtype=tdtype, device=A.device)
+    ws_bytes = _lib.lsg_fp8_gemm_workspace_bytes(int(M), int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    p = capi.Fp8GemmParams(M=int(M), N=int(N), K=int(K), A=A.data_ptr(), B=B.data_ptr(), D=D.data_ptr(),
+                           scale_A=scale_A.data_ptr(), scale_B=scale_B.data_ptr(), output_dtype=code)
+    capi.check(_lib.lsg_fp8_gemm(ctypes.byref(p), _ptr(ws), ws_bytes, _stream()))
+    return D
+
+
+def fp8_grouped_gemm(A_base, B_base, D_base, scale_A_base, scale_B_base, expert_offsets, problem_sizes, N, K,
+                     output_dtype):
+    """Grouped block-scaled e4m3 GEMM into D_base (returned).  Mirrors fp8_grouped_gemm
+    (csrc/bindings_python.cu:514-545); routed on the device, no host synchronisation."""
+    _require(A_base.is_cuda, "fp8_grouped_gemm: A_base must be on CUDA")
+    code, _ = _parse_output_dtype(output_dtype)
+    E = expert_offsets.size(0) - 1
+    T = A_base.size(0)
+    ws_bytes = _lib.lsg_fp8_grouped_gemm_workspace_bytes(T, E, int(N), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
+    p = capi.Fp8GroupedGemmParams(
+        num_experts=E, N=int(N), K=int(K), A_base=A_base.data_ptr(), B_base=B_base.data_ptr(),
+        D_base=D_base.data_ptr(), scale_A_base=scale_A_base.data_ptr(), scale_B_base=scale_B_base.data_ptr(),
+        expert_offsets=expert_offsets.data_ptr(),
+        problem_sizes=problem_sizes.data_ptr() if problem_sizes is not None else None,
+        output_dtype=code, B_ptrs=None, scale_B_ptrs=None)
+    capi.check(_lib.lsg_fp8_grouped_gemm(ctypes.byref(p), T, _ptr(ws), ws_bytes, _stream()))
+    return D_base
+
+
 def _nvfp4_grouped(op, fn, x, up, expert_offsets, input_scales):
     _require(x.is_cuda and x.dtype == torch.bfloat16, f"{op}: input must be BF16 on CUDA")
     _require(x.dim() == 2 and x.is_contiguous(), f"{op}: input must be contiguous [T, K]")

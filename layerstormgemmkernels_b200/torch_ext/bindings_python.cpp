@@ -279,12 +279,54 @@ torch::Tensor nvfp4_gemm_from_bf16(torch::Tensor x_bf16, torch::Tensor weight_pa
     return nvfp4_gemm(codes, weight_packed_uint8, sfa, sfb, M, N, K, weight_scale_global, "bf16");
 }
 
-// Operators of the reference that this build does not carry yet.
-std::tuple<torch::Tensor, torch::Tensor> weight_fp8_quant(torch::Tensor) { not_built("weight_fp8_quant"); }
-torch::Tensor fp8_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t, int64_t,
-                       const std::string&) { not_built("fp8_gemm"); }
-torch::Tensor fp8_grouped_gemm(torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor,
-                               torch::Tensor, torch::Tensor, int64_t, int64_t, const std::string&) { not_built("fp8_grouped_gemm"); }
+// FP8 family (csrc/bindings_python.cu:444-545).
+std::tuple<torch::Tensor, torch::Tensor> weight_fp8_quant(torch::Tensor weight) {
+    TORCH_CHECK(weight.is_cuda() && weight.dtype() == torch::kBFloat16, "weight_fp8_quant: weight must be BF16 on CUDA");
+    TORCH_CHECK(weight.dim() == 2 && weight.is_contiguous(), "weight_fp8_quant: weight must be contiguous [N, K]");
+    const int N = (int)weight.size(0), K = (int)weight.size(1);
+    auto output = torch::empty({N, K}, weight.options().dtype(at::kFloat8_e4m3fn));
+    auto scales = torch::empty({(N + 127) / 128, (K + 127) / 128}, weight.options().dtype(at::kFloat));
+    check(lsg_weight_fp8_quant(weight.data_ptr(), output.data_ptr(), scales.data_ptr<float>(), N, K, current_stream()));
+    return {output, scales};
+}
+
+torch::Tensor fp8_gemm(torch::Tensor A, torch::Tensor B, torch::Tensor scale_A, torch::Tensor scale_B, int64_t M,
+                       int64_t N, int64_t K, const std::string& output_dtype) {
+    TORCH_CHECK(A.is_cuda() && B.is_cuda(), "fp8_gemm: A and B must be on CUDA");
+    TORCH_CHECK(A.is_contiguous() && B.is_contiguous(), "fp8_gemm: must be contiguous");
+    at::ScalarType st;
+    const int code = parse_output_dtype(output_dtype, &st);
+    auto D = torch::empty({M, N}, A.options().dtype(st));
+    const size_t ws_bytes = lsg_fp8_gemm_workspace_bytes((int)M, (int)N, (int)K);
+    auto ws = torch::empty({static_cast<int64_t>(ws_bytes > 0 ? ws_bytes : 1)}, A.options().dtype(at::kByte));
+    lsg_fp8_gemm_params p = {};
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.A = A.data_ptr(); p.B = B.data_ptr(); p.D = D.data_ptr();
+    p.scale_A = scale_A.data_ptr(); p.scale_B = scale_B.data_ptr(); p.output_dtype = code;
+    check(lsg_fp8_gemm(&p, ws.data_ptr(), ws_bytes, current_stream()));
+    return D;
+}
+
+torch::Tensor fp8_grouped_gemm(torch::Tensor A_base, torch::Tensor B_base, torch::Tensor D_base,
+                               torch::Tensor scale_A_base, torch::Tensor scale_B_base, torch::Tensor expert_offsets,
+                               torch::Tensor problem_sizes, int64_t N, int64_t K, const std::string& output_dtype) {
+    TORCH_CHECK(A_base.is_cuda(), "fp8_grouped_gemm: A_base must be on CUDA");
+    at::ScalarType st;
+    const int code = parse_output_dtype(output_dtype, &st);
+    const int E = (int)expert_offsets.size(0) - 1;
+    const int T = (int)A_base.size(0);
+    const size_t ws_bytes = lsg_fp8_grouped_gemm_workspace_bytes(T, E, (int)N, (int)K);
+    auto ws = torch::empty({static_cast<int64_t>(ws_bytes > 0 ? ws_bytes : 1)}, A_base.options().dtype(at::kByte));
+    lsg_fp8_grouped_gemm_params p = {};
+    p.num_experts = E; p.N = (int)N; p.K = (int)K;
+    p.A_base = A_base.data_ptr(); p.B_base = B_base.data_ptr(); p.D_base = D_base.data_ptr();
+    p.scale_A_base = scale_A_base.data_ptr(); p.scale_B_base = scale_B_base.data_ptr();
+    p.expert_offsets = expert_offsets.data_ptr<int32_t>();
+    p.problem_sizes = problem_sizes.data_ptr<int32_t>();
+    p.output_dtype = code;
+    check(lsg_fp8_grouped_gemm(&p, T, ws.data_ptr(), ws_bytes, current_stream()));
+    return D_base;
+}
+
 int64_t query_zero(int64_t, int64_t, int64_t, const std::string&) { return 0; }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
