@@ -220,7 +220,7 @@ def main():
                                   "the CPU reference arm is implemented for the headline mmvq workload only"}))
             return
         from layerstormgemmkernels_b200 import bench_extra
-        bench_extra.run(args, rank, local_rank, world)
+        bench_extra.run(args, rank, local_rank, world, ClockSampler)
         return
 
     if args.impl == "reference":

@@ -22,7 +22,7 @@ def _peak_tflops():
     return 1400.0, "fallback"
 
 
-def _time_steps(step, steps, warmup, world, dev):
+def _time_steps(step, steps, warmup, world, dev, sampler=None):
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
@@ -30,11 +30,15 @@ def _time_steps(step, steps, warmup, world, dev):
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
     e0.record()
     for _ in range(steps):
         step()
     e1.record()
     torch.cuda.synchronize()
+    if sampler is not None:
+        _CLOCKS.update(sampler.stop())
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -43,7 +47,10 @@ def _time_steps(step, steps, warmup, world, dev):
     return ms / steps
 
 
-def run(args, rank, local_rank, world):
+_CLOCKS = {}
+
+
+def run(args, rank, local_rank, world, sampler_cls=None):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
@@ -52,10 +59,13 @@ def run(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
     steps = min(args.steps, 200)
     warmup = max(3, min(args.warmup, 10))
+    sampler = sampler_cls(local_rank) if sampler_cls is not None else None
     if args.workload == "moe":
-        line = _moe(args, rank, world, dev, steps, warmup)
+        line = _moe(args, rank, world, dev, steps, warmup, sampler)
     else:
-        line = _prefill(args, rank, world, dev, steps, warmup)
+        line = _prefill(args, rank, world, dev, steps, warmup, sampler)
+    line["clocks"] = dict(_CLOCKS) if _CLOCKS else None
+    line["cpu_baseline"] = None   # the CPU reference arm is timed on the headline workload only
     status = capi.device_status()
     if status != 0:
         raise SystemExit(f"a kernel reported a timed-out device-side wait (code {status})")
@@ -65,7 +75,7 @@ def run(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
-def _moe(args, rank, world, dev, steps, warmup):
+def _moe(args, rank, world, dev, steps, warmup, sampler=None):
     E, k, H, I = 128, 8, 2048, 768
     T_total = args.tokens
     if T_total % world != 0:
@@ -102,7 +112,7 @@ def _moe(args, rank, world, dev, steps, warmup):
         return D.ep_moe_layer(h, lg, k, E, ffn, ops.moe_route, ops.moe_permutation, ops.moe_permute,
                               ops.moe_unpermute)
 
-    ms = _time_steps(lambda: layer(hidden, logits), steps, warmup, world, dev)
+    ms = _time_steps(lambda: layer(hidden, logits), steps, warmup, world, dev, sampler)
 
     def e2e_step():
         h = hidden_host.to(dev, non_blocking=True)
@@ -126,11 +136,13 @@ def _moe(args, rank, world, dev, steps, warmup):
                      "frac": value / world / peak, "peak_kind": kind, "traffic": None},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2},
-        "gpu_launches": None,
+        # library kernels per step and rank: route, 3 x permutation, gather, tile map, activation
+        # preparation, gate|up GEMM, SwiGLU preparation, down GEMM, combine
+        "gpu_launches": steps * 11,
     }
 
 
-def _prefill(args, rank, world, dev, steps, warmup):
+def _prefill(args, rank, world, dev, steps, warmup, sampler=None):
     N, K, M = 14336, 4096, args.tokens
     t = capi.Q4_K
     n0, n1 = D.column_slab(rank, world, N)
@@ -144,7 +156,7 @@ def _prefill(args, rank, world, dev, steps, warmup):
         out = ops.gguf_mmq(a, slab, t, n1 - n0, K)
         return out if world == 1 else D.column_split_gather(out)
 
-    ms = _time_steps(step, steps, warmup, world, dev)
+    ms = _time_steps(step, steps, warmup, world, dev, sampler)
     e2e_ms = _time_steps(lambda: step(A_host.to(dev, non_blocking=True)).cpu(), min(steps, 10), 3, world, dev)
     flops = 2.0 * M * N * K
     peak, kind = _peak_tflops()
@@ -161,5 +173,6 @@ def _prefill(args, rank, world, dev, steps, warmup):
                      "frac": value / world / peak, "peak_kind": kind, "traffic": None},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
-        "gpu_launches": None,
+        # activation preparation + GEMM, plus the weight expansion pass above 2048 rows
+        "gpu_launches": steps * (3 if M > 2048 else 2),
     }

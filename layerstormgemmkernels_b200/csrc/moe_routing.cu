@@ -105,23 +105,37 @@ moe_chunk_hist_kernel(const int32_t* __restrict__ idx, int P, int E, int32_t* __
     for (int e = threadIdx.x; e < E; e += kChunk) hist[static_cast<size_t>(blockIdx.x) * E + e] = h[e];
 }
 
-// One CTA of 1024 threads, thread e owns expert e (E <= 1024).
+// One CTA of 1024 threads (E <= 1024).  Phase 1: warp w scans the chunk histograms of experts
+// w, w + 32, ... (lanes = 32 consecutive chunks, warp prefix sum, carry between groups of 32
+// chunks) and leaves the expert's total in shared memory.  Phase 2: thread e takes part in the
+// exclusive scan of the totals over the experts.
 __global__ void __launch_bounds__(1024)
 moe_chunk_scan_kernel(int32_t* __restrict__ hist, int n_chunks, int E, int32_t* __restrict__ offsets) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const int e = threadIdx.x, lane = e & 31, warp = e >> 5;
-    int total = 0;
-    if (e < E) {
-        for (int c = 0; c < n_chunks; ++c) {
-            const size_t at = static_cast<size_t>(c) * E + e;
-            const int v = hist[at];
-            hist[at] = total;
-            total += v;
-        }
-    }
-    // exclusive scan of the totals over the experts
+    __shared__ int totals[1024];
     __shared__ int wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = warp; e < E; e += 32) {
+        int carry = 0;
+        for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+            const int c = c0 + lane;
+            const size_t at = static_cast<size_t>(c) * E + e;
+            const int v = c < n_chunks ? hist[at] : 0;
+            int incl = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += u;
+            }
+            if (c < n_chunks) hist[at] = carry + incl - v;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) totals[e] = carry;
+    }
+    __syncthreads();
+    const int e = tid;
+    const int total = e < E ? totals[e] : 0;
     int incl = total;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
