@@ -98,6 +98,49 @@ def dequant_gemm(t, a_bf16_bits, W, K):
 
 
 # ---------------------------------------------------------------------------
+# FP8 (e4m3) block-scaled GEMM family, numpy restatements
+# ---------------------------------------------------------------------------
+def weight_fp8_quant(w_f32):
+    """bf16-valued weight [N,K] (as float32) -> (e4m3 bytes [N,K], fp32 scales [NB,KB]).
+
+    Restates weight_fp8_quant_kernel, csrc/smxx/quant/weight_fp8_quant.cu:51-138: one scale
+    per 128 x 128 tile = tile amax / 448 (1 for an all-zero tile), values
+    clamp(x * (1/scale), +-448) rounded to e4m3; scales[nb, kb] is the K-major buffer
+    scales[kb + nb*KB] the GEMM consumes."""
+    w = np.asarray(w_f32, dtype=np.float32)
+    N, K = w.shape
+    NB, KB = (N + 127) // 128, (K + 127) // 128
+    q = np.zeros((N, K), np.uint8)
+    s = np.zeros((NB, KB), np.float32)
+    for nb in range(NB):
+        for kb in range(KB):
+            tile = w[nb * 128:nb * 128 + 128, kb * 128:kb * 128 + 128]
+            amax = np.float32(np.abs(tile).max())
+            sc = np.float32(amax / np.float32(448.0)) if amax > 0 else np.float32(1.0)
+            inv = np.float32(1.0) / sc
+            s[nb, kb] = sc
+            scaled = np.clip((tile * inv).astype(np.float32), -448.0, 448.0)
+            q[nb * 128:nb * 128 + 128, kb * 128:kb * 128 + 128] = f32_to_e4m3(scaled).reshape(scaled.shape)
+    return q, s
+
+
+def fp8_gemm(a_e4m3, scale_a_mmajor, b_e4m3, scale_b, M, N, K):
+    """Block-scaled e4m3 GEMM in float64: the operand contract of launch_fp8_gemm,
+    csrc/sm120/gemm/fp8/fp8_gemm.h:18-44:
+      D[m,n] = sum_kb scale_A[m + kb*M] * scale_B[kb + (n/128)*KB] * sum_{k in kb} A[m,k]*B[n,k]."""
+    a = e4m3_to_f32(np.asarray(a_e4m3, dtype=np.uint8)).astype(np.float64).reshape(M, K)
+    b = e4m3_to_f32(np.asarray(b_e4m3, dtype=np.uint8)).astype(np.float64).reshape(N, K)
+    KB = (K + 127) // 128
+    sa = np.asarray(scale_a_mmajor, dtype=np.float64).reshape(KB, M)    # [kb, m]
+    sb = np.asarray(scale_b, dtype=np.float64).reshape(-1, KB)          # [nb, kb]
+    out = np.zeros((M, N))
+    for kb in range(KB):
+        ks = slice(kb * 128, min(K, kb * 128 + 128))
+        out += (a[:, ks] @ b[:, ks].T) * sa[kb][:, None] * np.repeat(sb[:, kb], 128)[:N][None, :]
+    return out
+
+
+# ---------------------------------------------------------------------------
 # The reference's own CUDA kernels, compiled for sm_100a from its sources where they
 # lie (oracle/Makefile target `ref`).  Optional second checker for the GPU tests.
 # ---------------------------------------------------------------------------

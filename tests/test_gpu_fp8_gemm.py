@@ -21,21 +21,8 @@ def ops():
     assert capi.device_status() == 0
 
 
-def e4m3_values(t):
-    return oracle.e4m3_to_f32(t.view(torch.uint8).cpu().numpy()).astype(np.float64).reshape(tuple(t.shape))
-
-
-def ref_gemm(a8, sa_mmajor, b8, sb, M, N, K):
-    """sum over K blocks of sA[m,kb] * sB[n/128,kb] * (A8 . B8^T), float64."""
-    KB = (K + 127) // 128
-    out = np.zeros((M, N))
-    sa = sa_mmajor.reshape(KB, M)          # [kb, m]
-    sbm = sb.reshape(-1, KB)               # [nb, kb]
-    for kb in range(KB):
-        ks = slice(kb * 128, min(K, kb * 128 + 128))
-        part = a8[:, ks] @ b8[:, ks].T
-        out += part * sa[kb][:, None] * np.repeat(sbm[:, kb], 128)[:N][None, :]
-    return out
+def raw(t):
+    return t.view(torch.uint8).cpu().numpy()
 
 
 @pytest.mark.parametrize("N,K", [(128, 128), (300, 384), (256, 1040), (1, 16)])
@@ -45,18 +32,7 @@ def test_weight_fp8_quant_bit_exact(ops, N, K):
         w[128:256, :min(K, 128)] = 0            # an all-zero tile: scale 1
     q, s = ops.weight_fp8_quant(w.cuda())
     assert q.dtype == torch.float8_e4m3fn and tuple(s.shape) == ((N + 127) // 128, (K + 127) // 128)
-    wf = w.float().numpy()
-    exp_q = np.zeros((N, K), np.uint8)
-    exp_s = np.zeros(s.shape, np.float32)
-    for nb in range(s.shape[0]):
-        for kb in range(s.shape[1]):
-            tile = wf[nb * 128:nb * 128 + 128, kb * 128:kb * 128 + 128]
-            amax = np.float32(np.abs(tile).max())
-            sc = np.float32(amax / np.float32(448.0)) if amax > 0 else np.float32(1.0)
-            inv = np.float32(1.0) / sc
-            exp_s[nb, kb] = sc
-            scaled = np.clip((tile * inv).astype(np.float32), -448.0, 448.0)
-            exp_q[nb * 128:nb * 128 + 128, kb * 128:kb * 128 + 128] = oracle.f32_to_e4m3(scaled).reshape(scaled.shape)
+    exp_q, exp_s = oracle.weight_fp8_quant(w.float().numpy())
     assert np.array_equal(s.cpu().numpy(), exp_s)
     assert np.array_equal(q.view(torch.uint8).cpu().numpy(), exp_q)
 
@@ -68,8 +44,7 @@ def test_fp8_gemm_quantizer_pairing(ops, M, N, K):
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
     a8, sa = ops.dynamic_fp8_quant(x, True)        # scales [KB, M] = M-major
     b8, sb = ops.weight_fp8_quant(w)               # scales [NB, KB] = K-major
-    ref = ref_gemm(e4m3_values(a8), sa.cpu().numpy().astype(np.float64), e4m3_values(b8),
-                   sb.cpu().numpy().astype(np.float64), M, N, K)
+    ref = oracle.fp8_gemm(raw(a8), sa.cpu().numpy(), raw(b8), sb.cpu().numpy(), M, N, K)
     for dt, td in (("bf16", torch.bfloat16), ("fp16", torch.float16)):
         out = ops.fp8_gemm(a8, b8, sa, sb, M, N, K, dt)
         assert out.dtype == td and tuple(out.shape) == (M, N)
@@ -105,8 +80,7 @@ def test_fp8_grouped_gemm_ragged_experts(ops):
         qa, sc = ops.dynamic_fp8_quant(x[s0:s1].contiguous(), True)     # M-major inside the expert
         a8[s0:s1] = qa
         sa[s0 * KB:s1 * KB] = sc.reshape(-1)
-        refs.append(ref_gemm(e4m3_values(qa), sc.cpu().numpy().astype(np.float64), e4m3_values(b8s[e]),
-                             sbs[e].cpu().numpy().astype(np.float64), s1 - s0, N, K))
+        refs.append(oracle.fp8_gemm(raw(qa), sc.cpu().numpy(), raw(b8s[e]), sbs[e].cpu().numpy(), s1 - s0, N, K))
     B = torch.cat([q.view(torch.uint8) for q in b8s], 0).view(torch.float8_e4m3fn)
     sB = torch.cat(sbs, 0)
     offs_t = torch.tensor(offs, dtype=torch.int32, device="cuda")

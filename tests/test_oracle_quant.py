@@ -142,3 +142,26 @@ def test_host_nvfp4_weight_quantizer_matches_reference(golden_dir):
     np.testing.assert_allclose(deq, z["dequant"], rtol=1e-6, atol=0)
     np.testing.assert_allclose(z["x"].astype(np.float64) @ deq.astype(np.float64).T, z["gemm"], rtol=0,
                                atol=1e-5 * np.abs(z["gemm"]).max())
+
+
+def test_fp8_weight_quant_and_gemm_oracle_consistency():
+    """The numpy restatements of weight_fp8_quant and of the block-scaled GEMM contract:
+    quantize -> GEMM reproduces the fp32 product to e4m3 precision, scales are tile amax / 448,
+    an all-zero tile gets scale 1 (csrc/smxx/quant/weight_fp8_quant.cu:102-105)."""
+    rng = np.random.default_rng(4)
+    N, K, M = 200, 384, 6
+    w = (rng.standard_normal((N, K)) * 0.1).astype(np.float32)
+    w[128:, 256:] = 0.0
+    q, s = oracle.weight_fp8_quant(w)
+    assert s.shape == (2, 3) and s[1, 2] == np.float32(1.0)
+    assert np.isclose(s[0, 0], np.abs(w[:128, :128]).max() / 448.0)
+    deq = (oracle.e4m3_to_f32(q).reshape(N, K).astype(np.float64) *
+           np.repeat(np.repeat(s.astype(np.float64), 128, 0)[:N], 128, 1)[:, :K])
+    assert np.abs(deq - w).max() <= np.abs(w).max() * 2.0 ** -4
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    # activations with unit scales and e4m3-representable values
+    xa = oracle.f32_to_e4m3(np.clip(x, -448, 448))
+    sa = np.ones((3, M), np.float32)
+    out = oracle.fp8_gemm(xa, sa, q, s, M, N, K)
+    ref = oracle.e4m3_to_f32(xa).reshape(M, K).astype(np.float64) @ deq.T
+    assert np.allclose(out, ref, rtol=1e-9, atol=1e-9)
