@@ -299,7 +299,8 @@ LSG_API int lsg_build_mmq_tile_map(const int32_t* expert_offsets, int num_expert
  * Replace launch_fp8_gemm / query_fp8_gemm_workspace_size (csrc/sm120/gemm/fp8/fp8_gemm.h:18-60,
  * fp8_gemm.cu), launch_fp8_grouped_gemm (fp8_grouped_gemm.cu:52-151; no host synchronisation
  * here) and launch_weight_fp8_quant (csrc/smxx/quant/weight_fp8_quant.cu:51-150, bit-exact).
- * K must be a multiple of 16. */
+ * K must be a multiple of 16.  M <= 4 with 16-byte aligned operands takes a mat-vec kernel
+ * that needs no workspace (the role of fp8_blockscaled_gemv.cu:54-145 for M = 1). */
 typedef struct lsg_fp8_gemm_params {
     int M, N, K;
     const void* A;         /* [M,K] e4m3 */
@@ -412,6 +413,11 @@ typedef struct lsg_nvfp4_grouped_gemm_params {
  * padding entries (callers zero the buffer first, as the reference's binding does). */
 LSG_API int lsg_bf16_to_nvfp4(const void* x_bf16, void* output_packed, void* output_scales, int M, int K,
                               void* stream);
+/* NVFP4 weight -> bf16: codes [N, K/2], RAW row-major ue4m3 group scales [N, K/16] (not the
+ * interleaved layout), global scalar; out[n,k] = (e2m1 * scale) * weight_scale_2 rounded to
+ * bf16.  Replaces launch_nvfp4_dequant_bf16, csrc/smxx/quant/nvfp4_dequant_bf16.cu:86-121. */
+LSG_API int lsg_nvfp4_dequant_bf16(const void* input_packed, const void* scales, float weight_scale_2,
+                                   void* output_bf16, int N, int K, void* stream);
 typedef struct lsg_nvfp4_gemm_params {
     int M, N, K;
     const void* A;        /* [M, K/2] e2m1 codes, low nibble = even k   */

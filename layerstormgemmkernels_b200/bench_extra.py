@@ -113,6 +113,14 @@ def _moe(args, rank, world, dev, steps, warmup, sampler=None):
                               ops.moe_unpermute)
 
     ms = _time_steps(lambda: layer(hidden, logits), steps, warmup, world, dev, sampler)
+    # the expert block alone (the grouped GEMMs with their operand preparation) on this rank's
+    # routed rows, single GPU only: what the tensor-pipe roofline is about
+    gemm_ms = None
+    if world == 1:
+        idx, _w = ops.moe_route(logits, k)
+        offs, perm, _inv = ops.moe_permutation(idx, E)
+        rows = ops.moe_permute(hidden, perm, k)
+        gemm_ms = _time_steps(lambda: ffn(rows, offs), steps, warmup, world, dev)
 
     def e2e_step():
         h = hidden_host.to(dev, non_blocking=True)
@@ -133,7 +141,12 @@ def _moe(args, rank, world, dev, steps, warmup, sampler=None):
                    "tokens": T_total, "parallelism": f"ep{world}" if world > 1 else "single",
                    "l2_defeat": "339 MB of expert weights per rank set exceed the 126 MB L2"},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
-                     "frac": value / world / peak, "peak_kind": kind, "traffic": None},
+                     "frac": value / world / peak, "peak_kind": kind, "traffic": None,
+                     "note": "whole layer (routing, permute, expert block, combine) over the GEMM flops"},
+        "expert_block": None if gemm_ms is None else {
+            "what": "lsg_gguf_moe_ffn alone on the routed rows: operand preparation, gate|up GEMM, SwiGLU, down GEMM",
+            "ms": gemm_ms, "tflops": flops / (gemm_ms * 1e-3) / 1e12,
+            "frac_of_peak": flops / (gemm_ms * 1e-3) / 1e12 / peak},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2},
         # library kernels per step and rank: route, 3 x permutation, gather, tile map, activation

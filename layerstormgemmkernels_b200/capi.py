@@ -138,6 +138,7 @@ def _load():
         "lsg_fp8_grouped_gemm": (ci, [ctypes.POINTER(Fp8GroupedGemmParams), ci, vp, sz, vp]),
         "lsg_weight_fp8_quant": (ci, [vp, vp, vp, ci, ci, vp]),
         "lsg_bf16_to_nvfp4": (ci, [vp, vp, vp, ci, ci, vp]),
+        "lsg_nvfp4_dequant_bf16": (ci, [vp, vp, ctypes.c_float, vp, ci, ci, vp]),
         "lsg_nvfp4_gemm_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_nvfp4_gemm": (ci, [ctypes.POINTER(Nvfp4GemmParams), vp, sz, vp]),
         "lsg_gguf_moe_ffn_workspace_bytes": (sz, [ci, ci, ci, ci]),

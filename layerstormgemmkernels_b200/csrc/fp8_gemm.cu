@@ -131,6 +131,84 @@ weight_fp8_quant_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restric
     }
 }
 
+// Small-batch path (M <= 4): one warp per output column n, lanes stride over 16-byte pieces
+// of the weight row, activations (M x K bytes) come from L1/L2, products and the per-128-K
+// scaling in fp32.  Exact up to fp32 summation order.  The role of the reference's
+// fp8_blockscaled_gemv_kernel (csrc/sm120/gemm/fp8/fp8_blockscaled_gemv.cu:54-145), which
+// covers M = 1.
+__device__ __forceinline__ void e4m3x4_to_float(uint32_t w, float (&f)[4]) {
+    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xFFFFu), __NV_E4M3);
+    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+
+template <int MR>
+__global__ void __launch_bounds__(256)
+fp8_gemv_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B, const float* __restrict__ sA,
+                const float* __restrict__ sB, void* __restrict__ D, int M, int N, int K, int out_dtype) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (n >= N) return;
+    const int KB = (K + 127) >> 7;
+    const uint8_t* brow = B + static_cast<size_t>(n) * K;
+    const float* sbrow = sB + static_cast<size_t>(n >> 7) * KB;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.0f;
+    const int pieces = K >> 4;
+    for (int c = lane; c < pieces; c += 32) {
+        const uint4 bw = __ldg(reinterpret_cast<const uint4*>(brow) + c);
+        const uint32_t b4[4] = {bw.x, bw.y, bw.z, bw.w};
+        float bf[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float t[4];
+            e4m3x4_to_float(b4[i], t);
+            bf[4 * i] = t[0]; bf[4 * i + 1] = t[1]; bf[4 * i + 2] = t[2]; bf[4 * i + 3] = t[3];
+        }
+        const int kb = c >> 3;
+        const float sb = sbrow[kb];
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            if (m < M) {
+                const uint4 aw = __ldg(reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * K) + c);
+                const uint32_t a4[4] = {aw.x, aw.y, aw.z, aw.w};
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float t[4];
+                    e4m3x4_to_float(a4[i], t);
+                    dot = fmaf(t[0], bf[4 * i], dot);
+                    dot = fmaf(t[1], bf[4 * i + 1], dot);
+                    dot = fmaf(t[2], bf[4 * i + 2], dot);
+                    dot = fmaf(t[3], bf[4 * i + 3], dot);
+                }
+                acc[m] = fmaf(dot, sA[m + static_cast<size_t>(kb) * M] * sb, acc[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[m] += __shfl_xor_sync(0xffffffffu, acc[m], o);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            if (m < M) {
+                const size_t o = static_cast<size_t>(m) * N + n;
+                if (out_dtype == LSG_DTYPE_F32) static_cast<float*>(D)[o] = acc[m];
+                else if (out_dtype == LSG_DTYPE_F16) static_cast<__half*>(D)[o] = __float2half_rn(acc[m]);
+                else static_cast<__nv_bfloat16*>(D)[o] = __float2bfloat16_rn(acc[m]);
+            }
+        }
+    }
+}
+
 int expand(const uint8_t* src, const void* const* ptrs, const float* scales, const void* const* scale_ptrs,
            const int32_t* offs, __half* out, long long rows, int K, int N, int E, int M_total, int mode,
            cudaStream_t s) {
@@ -183,6 +261,25 @@ extern "C" int lsg_fp8_gemm(const lsg_fp8_gemm_params* p, void* workspace, size_
     if (!p->A || !p->B || !p->D || !p->scale_A || !p->scale_B) return fail(LSG_ERR_INVALID, "fp8_gemm: null pointer");
     if ((reinterpret_cast<uintptr_t>(p->A) | reinterpret_cast<uintptr_t>(p->B)) & 7)
         return fail(LSG_ERR_ALIGNMENT, "fp8_gemm: operands must be 8-byte aligned");
+    if (p->M <= 4 && ((reinterpret_cast<uintptr_t>(p->A) | reinterpret_cast<uintptr_t>(p->B)) & 15) == 0) {
+        // decode-sized batch: stream the weights once, no operand expansion, no workspace
+        const dim3 grid((p->N + 7) / 8);
+        const uint8_t* A8 = static_cast<const uint8_t*>(p->A);
+        const uint8_t* B8 = static_cast<const uint8_t*>(p->B);
+        const float* sa = static_cast<const float*>(p->scale_A);
+        const float* sb = static_cast<const float*>(p->scale_B);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (p->M == 1)
+            LSG_CUDA_TRY(launch_kernel(fp8_gemv_kernel<1>, grid, dim3(256), 0, st, true, A8, B8, sa, sb, p->D, p->M,
+                                       p->N, p->K, p->output_dtype));
+        else if (p->M == 2)
+            LSG_CUDA_TRY(launch_kernel(fp8_gemv_kernel<2>, grid, dim3(256), 0, st, true, A8, B8, sa, sb, p->D, p->M,
+                                       p->N, p->K, p->output_dtype));
+        else
+            LSG_CUDA_TRY(launch_kernel(fp8_gemv_kernel<4>, grid, dim3(256), 0, st, true, A8, B8, sa, sb, p->D, p->M,
+                                       p->N, p->K, p->output_dtype));
+        return LSG_OK;
+    }
     const size_t need = lsg_fp8_gemm_workspace_bytes(p->M, p->N, p->K);
     if (!workspace || workspace_bytes < need)
         return fail(LSG_ERR_WORKSPACE, "fp8_gemm: workspace too small (have %zu, need %zu)",

@@ -89,6 +89,9 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pd
         // Long rows: one row per lane group, so that the rows resident in the ring
         // are enough to occupy every consumer warp.
         rw = (lanes == 32 && a.row_bytes * 2 * tn.warps > (smem_cap * 3) / 4) ? 1 : 2;
+        // Few rows per CTA (small matrices): one row per lane group doubles the number of row
+        // groups, so that they cover the consumer warps instead of leaving most of them idle.
+        if (rows_per_cta < (32 / lanes) * 2 * tn.warps) rw = 1;
         int slab_rows = tn.stage_kb * 1024 / a.row_bytes;
         // whole row groups per slab, so that no lane group idles on a ragged slab end
         const int rpp = (32 / lanes) * rw;

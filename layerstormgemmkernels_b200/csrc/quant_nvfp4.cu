@@ -228,3 +228,60 @@ extern "C" int lsg_bf16_to_nvfp4(const void* x_bf16, void* output_packed, void* 
                                static_cast<const int32_t*>(nullptr), static_cast<const float*>(nullptr), M, 1, K));
     return LSG_OK;
 }
+
+// NVFP4 weight [N, K/2] codes + raw row-major ue4m3 group scales [N, K/16] + global scalar
+// -> bf16 [N, K]: value = (e2m1(code) * e4m3(scale)) * weight_scale_2, rounded to bf16.
+// Replaces launch_nvfp4_dequant_bf16, csrc/smxx/quant/nvfp4_dequant_bf16.cu:41-121 (same
+// products in the same order, hence the same bf16 bits).  One thread per 16-value group.
+namespace lsg {
+namespace {
+__global__ void __launch_bounds__(256)
+nvfp4_dequant_bf16_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales, float ws2,
+                          __nv_bfloat16* __restrict__ out, long long groups) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long g = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (g >= groups) return;
+    __nv_fp8_e4m3 f8;
+    f8.__x = static_cast<__nv_fp8_storage_t>(scales[g]);
+    const float gs = static_cast<float>(f8);
+    const uint2 codes = *reinterpret_cast<const uint2*>(packed + g * 8);
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t byte = ((i < 4 ? codes.x : codes.y) >> (8 * (i & 3))) & 0xFFu;
+        float v[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t c = h ? (byte >> 4) : (byte & 0xFu);
+            const uint32_t m = c & 7u;
+            const float mag = (m < 4u) ? 0.5f * static_cast<float>(m)
+                                       : ((m == 4u) ? 2.0f : (m == 5u) ? 3.0f : (m == 6u) ? 4.0f : 6.0f);
+            v[h] = ((c & 8u) ? -mag : mag) * gs * ws2;
+        }
+        const __nv_bfloat162 r = __floats2bfloat162_rn(v[0], v[1]);
+        o[i] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + g * 16);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+}  // namespace
+}  // namespace lsg
+
+extern "C" int lsg_nvfp4_dequant_bf16(const void* input_packed, const void* scales, float weight_scale_2,
+                                      void* output_bf16, int N, int K, void* stream) {
+    if (N <= 0 || K <= 0) return LSG_OK;   // as the reference (nvfp4_dequant_bf16.cu:90)
+    if (!input_packed || !scales || !output_bf16)
+        return lsg::fail(LSG_ERR_INVALID, "launch_nvfp4_dequant_bf16: null pointer in params");
+    if (K % 16 != 0)
+        return lsg::fail(LSG_ERR_INVALID, "launch_nvfp4_dequant_bf16: K must be divisible by 16 (got %d)", K);
+    if ((reinterpret_cast<uintptr_t>(input_packed) & 7) || (reinterpret_cast<uintptr_t>(output_bf16) & 15))
+        return lsg::fail(LSG_ERR_ALIGNMENT, "nvfp4_dequant_bf16: input must be 8-byte and output 16-byte aligned");
+    const long long groups = static_cast<long long>(N) * (K / 16);
+    LSG_CUDA_TRY(lsg::launch_kernel(lsg::nvfp4_dequant_bf16_kernel, dim3(static_cast<unsigned>((groups + 255) / 256)),
+                                    dim3(256), 0, static_cast<cudaStream_t>(stream), true,
+                                    static_cast<const uint8_t*>(input_packed), static_cast<const uint8_t*>(scales),
+                                    weight_scale_2, static_cast<__nv_bfloat16*>(output_bf16), groups));
+    return LSG_OK;
+}

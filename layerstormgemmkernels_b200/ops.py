@@ -424,6 +424,22 @@ def bf16_to_nvfp4(x):
     return packed, scales
 
 
+def nvfp4_dequant_bf16(weight_packed, weight_scales_e4m3, weight_scale_2):
+    """NVFP4 weight [N, K/2] + raw ue4m3 scales [N, K/16] + global scalar -> bf16 [N, K]
+    (launch_nvfp4_dequant_bf16, csrc/smxx/quant/nvfp4_dequant_bf16.cu; C API only in the
+    reference)."""
+    _require(weight_packed.is_cuda and weight_packed.dtype == torch.uint8 and weight_packed.dim() == 2
+             and weight_packed.is_contiguous(), "nvfp4_dequant_bf16: weight must be contiguous uint8 [N, K/2] on CUDA")
+    N, K = weight_packed.size(0), weight_packed.size(1) * 2
+    sc = weight_scales_e4m3.view(torch.uint8)
+    _require(sc.is_cuda and sc.is_contiguous() and sc.numel() == N * (K // 16),
+             "nvfp4_dequant_bf16: scales must be contiguous [N, K/16] e4m3 bytes on CUDA")
+    out = torch.empty((N, K), dtype=torch.bfloat16, device=weight_packed.device)
+    capi.check(_lib.lsg_nvfp4_dequant_bf16(_ptr(weight_packed), _ptr(sc), float(weight_scale_2), _ptr(out), N, K,
+                                           _stream()))
+    return out
+
+
 def nvfp4_gemm(A, B, scale_A, scale_B, M, N, K, alpha, output_dtype):
     """D[M,N] = alpha * (A x SFA) . (B x SFB)^T on pre-quantized operands.
     Mirrors nvfp4_gemm (csrc/bindings_python.cu:64-110)."""

@@ -94,3 +94,18 @@ def test_fp8_grouped_gemm_ragged_experts(ops):
             continue
         s0, s1 = offs[e], offs[e + 1]
         assert np.abs(got[s0:s1] - refs[e]).max() <= (TOL + 2.0 ** -8) * np.abs(refs[e]).max()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(200, 384), (4096, 7168)])
+def test_fp8_small_batch_matvec(ops, M, N, K):
+    """M <= 4 takes the streaming mat-vec kernel (role of fp8_blockscaled_gemv.cu:54-145):
+    fp32 products and scaling, so it agrees with the float64 contract far inside the bound."""
+    g = torch.Generator().manual_seed(N + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    a8, sa = ops.dynamic_fp8_quant(x, True)
+    b8, sb = ops.weight_fp8_quant(w)
+    ref = oracle.fp8_gemm(raw(a8), sa.cpu().numpy(), raw(b8), sb.cpu().numpy(), M, N, K)
+    out = ops.fp8_gemm(a8, b8, sa, sb, M, N, K, "bf16").float().cpu().numpy()
+    assert np.abs(out - ref).max() <= (1e-5 + 2.0 ** -8) * np.abs(ref).max()

@@ -145,3 +145,19 @@ def test_single_gemm_from_bf16(ops, M, N, K):
     full = x.float().cpu().numpy() @ (wdeq.T * float(s2))
     cos = (full * got).sum() / np.sqrt((full * full).sum() * (got ** 2).sum())
     assert cos > 0.99
+
+
+@pytest.mark.parametrize("N,K,s2", [(64, 256, 1.0), (130, 512, 0.0371), (1, 16, 3.5)])
+def test_nvfp4_dequant_bf16_bit_exact(ops, N, K, s2):
+    """(e2m1 * e4m3 scale) * weight_scale_2 in fp32, rounded to bf16: same bits as the formula of
+    csrc/smxx/quant/nvfp4_dequant_bf16.h:20-24."""
+    rng = np.random.default_rng(N)
+    codes = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    sc = rng.integers(0x20, 0x50, size=(N, K // 16), dtype=np.uint8)     # positive, finite e4m3
+    out = ops.nvfp4_dequant_bf16(torch.from_numpy(codes).cuda(), torch.from_numpy(sc).cuda(), s2)
+    lut = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    nib = np.stack([codes & 0xF, codes >> 4], -1).reshape(N, K)
+    gs = np.repeat(oracle.e4m3_to_f32(sc).reshape(N, K // 16).astype(np.float32), 16, axis=1)
+    val = ((lut[nib] * gs).astype(np.float32) * np.float32(s2)).astype(np.float32)
+    exp = torch.from_numpy(val).to(torch.bfloat16)
+    assert torch.equal(out.cpu().view(torch.int16), exp.view(torch.int16))
