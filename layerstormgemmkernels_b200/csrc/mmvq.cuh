@@ -171,68 +171,60 @@ __device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bflo
     const int nb = K / 32;
     const int U = K / D::UV;
     const int rowb = x_row_bytes<T>(K);
-    const int total = M * nb * 4;  // tasks of 8 values
-    const int trips = (total + nthreads - 1) / nthreads;
-    constexpr int kBatch = 4;      // loads in flight per thread
-    for (int it0 = 0; it0 < trips; it0 += kBatch) {
-        uint4 raws[kBatch];
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-            const int idx = (it0 + k) * nthreads + tid;
-            raws[k] = __ldg(reinterpret_cast<const uint4*>(A) + (idx < total ? idx : 0));
-        }
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-            if (it0 + k >= trips) break;  // uniform across the CTA
-            const int idx = (it0 + k) * nthreads + tid;
-            const bool live = idx < total;
+    // Two lanes per 32-value block, sixteen values (two 16-byte loads) per lane: a 4096-wide
+    // row is one trip of 256 tasks for the consumer threads, and the only index arithmetic is
+    // shifts and divisions by compile-time constants.
+    const int tasks = nb * 2;
+    for (int m = 0; m < M; ++m) {
+        const uint4* src = reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * K);
+        uint8_t* row = img + static_cast<size_t>(m) * rowb;
+        uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
+        uint32_t* svec = dvec + nb;
+        for (int t0 = 0; t0 < tasks; t0 += nthreads) {
+            const int idx = t0 + tid;
+            const bool live = idx < tasks;
             const int task = live ? idx : 0;
-            const uint4 raw = raws[k];
-            float x[8];
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint4 r0 = __ldg(src + 2 * task), r1 = __ldg(src + 2 * task + 1);
+            const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            float x[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 x[2 * i] = __uint_as_float(w[i] << 16);
                 x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
             }
             float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             const float d = amax / 127.0f;
-            // q = rn(fl(x / d)) as the reference computes it, without eight IEEE divisions:
+            // q = rn(fl(x / d)) as the reference computes it, without sixteen IEEE divisions:
             // x * fl(1/d) is within 2.3e-5 of fl(x/d) for |x/d| <= 127, so rounding it gives
             // the same integer unless it lies within 1e-4 of a half-integer; only then
             // (about one value in 5000) is the true quotient formed.
             const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-            int q[8];
-            int sum8 = 0;
+            int q[16];
+            int sum16 = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 16; ++i) {
                 const float t = x[i] * rcp;
                 int k = __float2int_rn(t);
                 if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x[i] / d);
                 q[i] = k;
-                sum8 += k;
+                sum16 += k;
             }
-            const int sum16 = sum8 + __shfl_xor_sync(0xffffffffu, sum8, 1);
-            const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+            const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 1);
             if (!live) continue;
-            uint2 packed;
+            uint4 packed;
             packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
             packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+            packed.z = (q[8] & 0xFF) | ((q[9] & 0xFF) << 8) | ((q[10] & 0xFF) << 16) | ((q[11] & 0xFF) << 24);
+            packed.w = (q[12] & 0xFF) | ((q[13] & 0xFF) << 8) | ((q[14] & 0xFF) << 16) | ((q[15] & 0xFF) << 24);
             const float dh = __half2float(__float2half(d));  // the mat-vec sees the fp16-rounded scale
-            const int part = task & 3;
-            const int blk = task >> 2;
-            const int m = blk / nb, b = blk - m * nb;
-            uint8_t* row = img + static_cast<size_t>(m) * rowb;
-            uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
-            uint32_t* svec = dvec + nb;
+            const int half = task & 1;
+            const int b = task >> 1;
             const int u = b / UVB, jb = b % UVB;
-            uint2* piece = reinterpret_cast<uint2*>(row + (static_cast<size_t>(2 * jb + (part >> 1)) * U + u) * 16);
-            piece[part & 1] = packed;
-            if (part == 0) {
+            *reinterpret_cast<uint4*>(row + (static_cast<size_t>(2 * jb + half) * U + u) * 16) = packed;
+            if (half == 0) {
                 if (UVB >= 4) dvec[((jb >> 2) * U + u) * 4 + (jb & 3)] = __float_as_uint(dh);
                 else dvec[u] = __float_as_uint(dh);
                 if (D::SUM == kSumF32Per32) {
@@ -241,8 +233,8 @@ __device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bflo
                     else svec[u] = v;
                 }
             }
-            if ((part & 1) == 0 && (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16)) {
-                const int e = 2 * jb + (part >> 1);
+            if (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16) {
+                const int e = 2 * jb + half;
                 const uint32_t v = (D::SUM == kSumI32Per16) ? static_cast<uint32_t>(sum16)
                                                             : __float_as_uint(dh * static_cast<float>(sum16));
                 svec[((e >> 2) * U + u) * 4 + (e & 3)] = v;
