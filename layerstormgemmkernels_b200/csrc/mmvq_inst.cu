@@ -60,9 +60,25 @@ int MMVQ_FN(max_rows)(int K) {
     return rows < 1 ? 0 : rows;
 }
 
-int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn, cudaStream_t stream, bool pdl) {
+int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool pdl) {
     using F = Fmt<T>;
     a.row_bytes = (a.K / F::VALS) * F::BYTES;
+    // Small matrices (a CTA's share of the weights fits half an SM's shared memory): eleven
+    // consumer warps and half the shared memory, so that two consecutive launches of a
+    // stream are resident together and the second one's prologue and weight prefetch overlap
+    // the first one's tail.
+    MmvqTune tn = tn_in;
+    {
+        static const int small_kb = [] {
+            const char* e = getenv("LSG_MMVQ_SMALL_KB");
+            return e ? atoi(e) : 0;
+        }();
+        const long long per_cta = static_cast<long long>(a.N) * a.row_bytes / (sm_count() > 0 ? sm_count() : 1);
+        if (small_kb > 0 && per_cta <= static_cast<long long>(small_kb) * 1024 && tn.share == 1 && tn.ctas == 1) {
+            tn.warps = tn.warps > 11 ? 11 : tn.warps;
+            tn.share = 2;
+        }
+    }
     const int U = a.K / Mmvq<T>::UV;
     a.cons_warps = tn.warps;
     a.debug_skip = tn.skip_math;
