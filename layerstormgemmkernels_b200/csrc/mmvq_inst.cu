@@ -71,7 +71,7 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
     {
         static const int small_kb = [] {
             const char* e = getenv("LSG_MMVQ_SMALL_KB");
-            return e ? atoi(e) : 0;
+            return e ? atoi(e) : 70;   // 0 switches this off
         }();
         const long long per_cta = static_cast<long long>(a.N) * a.row_bytes / (sm_count() > 0 ? sm_count() : 1);
         if (small_kb > 0 && per_cta <= static_cast<long long>(small_kb) * 1024 && tn.share == 1 && tn.ctas == 1) {
