@@ -469,6 +469,18 @@ LSG_API int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int top
                                 int32_t* expert_offsets, int32_t* perm, int32_t* inv_perm,
                                 int32_t* counts_scratch, void* stream);
 
+/* Expert-parallel receive side.  After the all-to-all a rank holds `rows` rows grouped by
+ * (source rank, local expert); recv_counts int32 [world * experts_per_rank] gives the block
+ * sizes in that order.  Writes local_offsets int32 [experts_per_rank + 1] (rows per local
+ * expert, cumulative), order int32 [rows] (destination row -> received row, destination =
+ * grouped by (local expert, source rank)) and its inverse.  scratch: int32
+ * [2 * world * experts_per_rank].  world * experts_per_rank <= 1024.  Rows whose blocks have
+ * size zero do not exist; an empty-before-i search keeps the order stable.  No counterpart in
+ * the reference (it has no multi-GPU code). */
+LSG_API int lsg_ep_expert_order(const int32_t* recv_counts, int world, int experts_per_rank, int rows,
+                                int32_t* local_offsets, int32_t* order, int32_t* inv_order,
+                                int32_t* scratch, void* stream);
+
 /* out[row,:] = hidden[perm[row] / top_k, :]   (bf16, H multiple of 8). */
 LSG_API int lsg_moe_permute(const void* hidden_bf16, const int32_t* perm, int rows, int top_k, int H,
                             void* out_bf16, void* stream);

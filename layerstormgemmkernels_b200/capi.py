@@ -153,6 +153,7 @@ def _load():
         "lsg_nvfp4_sf_buffer_bytes": (sz, [ci, ci]),
         "lsg_nvfp4_reformat_scales": (ci, [vp, vp, ci, ci, vp]),
         "lsg_moe_route": (ci, [vp, ci, ci, ci, vp, vp, vp]),
+        "lsg_ep_expert_order": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_moe_permutation_scratch_ints": (ctypes.c_longlong, [ci, ci, ci]),
         "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_moe_permute": (ci, [vp, vp, ci, ci, ci, vp, vp]),

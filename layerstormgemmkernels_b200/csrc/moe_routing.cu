@@ -218,6 +218,77 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restric
     reinterpret_cast<__nv_bfloat162*>(out + static_cast<size_t>(t) * H)[c] = __floats2bfloat162_rn(a0, a1);
 }
 
+// Expert-parallel receive side: rows arrive grouped by (source rank, local expert); the
+// grouped GEMM wants them grouped by (local expert, source rank).  counts[s * per + e] = rows
+// from source s for local expert e.  One CTA: exclusive scans of the block sizes in both
+// orders.  starts_recv[s * per + e], starts_dst[e * world + s], local_offsets[per + 1].
+__global__ void __launch_bounds__(1024)
+ep_block_starts_kernel(const int32_t* __restrict__ counts, int world, int per, int32_t* __restrict__ starts_recv,
+                       int32_t* __restrict__ starts_dst, int32_t* __restrict__ local_offsets) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    __shared__ int wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int B = world * per;
+    for (int pass = 0; pass < 2; ++pass) {
+        // pass 0: receive order (s, e); pass 1: destination order (e, s)
+        int v = 0;
+        if (tid < B) v = pass == 0 ? counts[tid] : counts[(tid % world) * per + tid / world];
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += u;
+        }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = wsum[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, w, o);
+                if (lane >= o) w += u;
+            }
+            wsum[lane] = w;
+        }
+        __syncthreads();
+        const int excl = (warp > 0 ? wsum[warp - 1] : 0) + incl - v;
+        if (tid < B) {
+            if (pass == 0) starts_recv[tid] = excl;
+            else {
+                starts_dst[tid] = excl;
+                if (tid % world == 0) local_offsets[tid / world] = excl;
+                if (tid == B - 1) local_offsets[per] = excl + v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// order[i] = receive-order row of destination row i; inv_order[that row] = i.
+__global__ void __launch_bounds__(256)
+ep_order_kernel(const int32_t* __restrict__ counts, const int32_t* __restrict__ starts_recv,
+                const int32_t* __restrict__ starts_dst, int world, int per, int rows, int32_t* __restrict__ order,
+                int32_t* __restrict__ inv_order) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= rows) return;
+    const int B = world * per;
+    // last destination block whose start is <= i and that is not empty before i
+    int lo = 0, hi = B - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (starts_dst[mid] <= i) lo = mid;
+        else hi = mid - 1;
+    }
+    const int e = lo / world, s_rank = lo % world;
+    const int b = s_rank * per + e;
+    const int src = starts_recv[b] + (i - starts_dst[lo]);
+    order[i] = src;
+    inv_order[src] = i;
+}
+
 }  // namespace
 
 }  // namespace lsg
@@ -289,5 +360,26 @@ extern "C" int lsg_moe_unpermute(const void* y_bf16, const int32_t* inv_perm, co
     LSG_CUDA_TRY(launch_kernel(moe_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const __nv_bfloat16*>(y_bf16),
                                inv_perm, topk_weights, num_tokens, top_k, H, static_cast<__nv_bfloat16*>(out_bf16)));
+    return LSG_OK;
+}
+
+extern "C" int lsg_ep_expert_order(const int32_t* recv_counts, int world, int experts_per_rank, int rows,
+                                   int32_t* local_offsets, int32_t* order, int32_t* inv_order,
+                                   int32_t* scratch, void* stream) {
+    const long long B = static_cast<long long>(world) * experts_per_rank;
+    if (world < 1 || experts_per_rank < 1 || B > 1024)
+        return fail(LSG_ERR_INVALID, "ep_expert_order: need 1 <= world * experts_per_rank <= 1024");
+    if (rows < 0) return fail(LSG_ERR_INVALID, "ep_expert_order: negative row count");
+    if (!recv_counts || !local_offsets || !scratch || (rows > 0 && (!order || !inv_order)))
+        return fail(LSG_ERR_INVALID, "ep_expert_order: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int32_t* starts_recv = scratch;
+    int32_t* starts_dst = scratch + B;
+    LSG_CUDA_TRY(launch_kernel(ep_block_starts_kernel, dim3(1), dim3(1024), 0, s, true, recv_counts, world,
+                               experts_per_rank, starts_recv, starts_dst, local_offsets));
+    if (rows > 0)
+        LSG_CUDA_TRY(launch_kernel(ep_order_kernel, dim3((rows + 255) / 256), dim3(256), 0, s, true, recv_counts,
+                                   static_cast<const int32_t*>(starts_recv), static_cast<const int32_t*>(starts_dst),
+                                   world, experts_per_rank, rows, order, inv_order));
     return LSG_OK;
 }

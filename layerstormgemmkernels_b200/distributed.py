@@ -40,6 +40,15 @@ class EpPlan:
         self.recv_splits = both[1].tolist()
         self.recv_rows = int(sum(self.recv_splits))
         dev = recv_counts.device
+        self.inv_order = None
+        if recv_counts.is_cuda:
+            # device kernels: block starts in both orders, then one thread per row
+            from . import ops
+            self.local_offsets, order, inv = ops.ep_expert_order(recv_counts, world, self.per, self.recv_rows)
+            self.to_expert_order = order
+            self.inv_order = inv
+            return
+        # CPU (tests of the host logic): the same arrays with torch operations.
         # received order is (source, expert, row); the grouped GEMM wants (expert, source, row)
         blocks = recv_counts.reshape(-1)                       # [(s, e)] sizes
         starts = torch.cumsum(blocks, 0) - blocks              # start of block (s, e) in recv order
@@ -69,15 +78,22 @@ def ep_dispatch(rows, plan, group=None):
     local expert: ([R, H], local expert_offsets int32 [per+1] on rows.device)."""
     out = rows.new_empty((plan.recv_rows, rows.shape[1]))
     dist.all_to_all_single(out, rows.contiguous(), plan.recv_splits, plan.send_splits, group=group)
-    idx = plan.to_expert_order.to(rows.device)
+    if plan.inv_order is not None and rows.dtype == torch.bfloat16 and rows.shape[1] % 8 == 0:
+        from . import ops
+        return ops.moe_permute(out, plan.to_expert_order, 1), plan.local_offsets
+    idx = plan.to_expert_order.to(rows.device).to(torch.int64)
     return out.index_select(0, idx), plan.local_offsets.to(rows.device)
 
 
 def ep_combine(expert_rows, plan, group=None):
     """Inverse of ep_dispatch for the experts' outputs: [R, H'] -> [P, H'] in the sender's order."""
-    idx = plan.to_expert_order.to(expert_rows.device)
-    recv_order = torch.empty_like(expert_rows)
-    recv_order.index_copy_(0, idx, expert_rows)
+    if plan.inv_order is not None and expert_rows.dtype == torch.bfloat16 and expert_rows.shape[1] % 8 == 0:
+        from . import ops
+        recv_order = ops.moe_permute(expert_rows.contiguous(), plan.inv_order, 1)
+    else:
+        idx = plan.to_expert_order.to(expert_rows.device).to(torch.int64)
+        recv_order = torch.empty_like(expert_rows)
+        recv_order.index_copy_(0, idx, expert_rows)
     out = expert_rows.new_empty((int(sum(plan.send_splits)), expert_rows.shape[1]))
     dist.all_to_all_single(out, recv_order, plan.send_splits, plan.recv_splits, group=group)
     return out

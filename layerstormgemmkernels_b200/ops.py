@@ -540,6 +540,20 @@ def moe_permutation(topk_idx, num_experts):
     return offs, perm, inv
 
 
+def ep_expert_order(recv_counts, world, experts_per_rank, rows):
+    """recv_counts int32 [world, per] on CUDA -> (local_offsets int32 [per+1], order int32 [rows],
+    inv_order int32 [rows]): regrouping of rows received by (source, expert) into (expert, source)."""
+    dev = recv_counts.device
+    c = recv_counts.to(torch.int32).contiguous()
+    offs = torch.empty((experts_per_rank + 1,), dtype=torch.int32, device=dev)
+    order = torch.empty((max(rows, 1),), dtype=torch.int32, device=dev)
+    inv = torch.empty((max(rows, 1),), dtype=torch.int32, device=dev)
+    scratch = torch.empty((2 * world * experts_per_rank,), dtype=torch.int32, device=dev)
+    capi.check(_lib.lsg_ep_expert_order(_ptr(c), int(world), int(experts_per_rank), int(rows), _ptr(offs),
+                                        _ptr(order), _ptr(inv), _ptr(scratch), _stream()))
+    return offs, order[:rows], inv[:rows]
+
+
 def moe_permute(hidden, perm, top_k):
     rows, H = perm.numel(), hidden.size(1)
     out = torch.empty((rows, H), dtype=torch.bfloat16, device=hidden.device)

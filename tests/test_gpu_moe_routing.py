@@ -62,3 +62,27 @@ def test_permutation_with_skewed_routing(ops):
     offs, perm, inv = ops.moe_permutation(idx.cuda(), E)
     roffs, rperm, rinv = oracle_permutation(idx, E)
     assert torch.equal(offs.cpu(), roffs) and torch.equal(perm.cpu(), rperm) and torch.equal(inv.cpu(), rinv)
+
+
+@pytest.mark.parametrize("world,per,seed", [(2, 64, 0), (4, 3, 1), (8, 16, 2), (1, 5, 3)])
+def test_ep_expert_order_matches_definition(ops, world, per, seed):
+    """Regrouping of rows received by (source, expert) into (expert, source): against the
+    definition written with numpy; empty blocks included."""
+    rng = np.random.default_rng(seed)
+    counts = rng.integers(0, 40, size=(world, per)).astype(np.int32)
+    counts[rng.random((world, per)) < 0.3] = 0
+    rows = int(counts.sum())
+    offs, order, inv = ops.ep_expert_order(torch.from_numpy(counts).cuda(), world, per, rows)
+    starts = np.zeros(world * per + 1, np.int64)
+    starts[1:] = np.cumsum(counts.reshape(-1))
+    exp = []
+    for e in range(per):
+        for s in range(world):
+            b = s * per + e
+            exp.extend(range(starts[b], starts[b] + counts[s, e]))
+    exp = np.array(exp, dtype=np.int32)
+    assert np.array_equal(order.cpu().numpy(), exp)
+    assert np.array_equal(inv.cpu().numpy()[exp], np.arange(rows, dtype=np.int32))
+    exp_offs = np.zeros(per + 1, np.int32)
+    exp_offs[1:] = np.cumsum(counts.sum(0))
+    assert np.array_equal(offs.cpu().numpy(), exp_offs)
