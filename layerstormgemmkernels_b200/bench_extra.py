@@ -77,10 +77,11 @@ def run(args, rank, local_rank, world, sampler_cls=None):
 
 def _moe(args, rank, world, dev, steps, warmup, sampler=None):
     E, k, H, I = 128, 8, 2048, 768
-    T_total = args.tokens
+    weak = bool(getattr(args, "weak", False))
+    T_total = args.tokens * world if weak else args.tokens
     if T_total % world != 0:
         raise SystemExit("--tokens must be divisible by the number of GPUs")
-    T = T_total // world                       # strong scaling: the batch is split
+    T = T_total // world                       # strong scaling splits the batch, weak keeps it per GPU
     t = capi.Q4_K
     e0, e1 = D.expert_range(rank, world, E)
     # eight distinct experts quantized from N(0, 0.02) seed 3, tiled over the rank's experts
@@ -134,7 +135,7 @@ def _moe(args, rank, world, dev, steps, warmup, sampler=None):
     return {
         "metric": "moe_grouped_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16 (tcgen05, fp32 accumulate)",
+        "scaling": "weak" if weak else "strong", "vs_baseline": None, "dtype": "f16 (tcgen05, fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"MoE layer, 128 experts top-8, H=2048, I=768, Q4_K, {T_total} tokens: "
                                "route, permute, gate/up/down grouped GEMMs, SwiGLU, combine",
