@@ -206,6 +206,8 @@ def main():
                          "GEMM layer (128 experts, top-8, H=2048, I=768, Q4_K); prefill: Q4_K "
                          "14336x4096 GEMM, column-split across ranks")
     ap.add_argument("--tokens", type=int, default=4096, help="tokens (moe) or rows M (prefill)")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="moe on several GPUs: exchange rows by peer-memory stores or by NCCL all-to-all")
     ap.add_argument("--weak", action="store_true",
                     help="moe: --tokens is per GPU (weak scaling) instead of the whole batch")
     args = ap.parse_args()

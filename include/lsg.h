@@ -481,6 +481,32 @@ LSG_API int lsg_ep_expert_order(const int32_t* recv_counts, int world, int exper
                                 int32_t* local_offsets, int32_t* order, int32_t* inv_order,
                                 int32_t* scratch, void* stream);
 
+/* Expert-parallel exchange over peer memory (one node, one process per GPU, NVLink): the
+ * routed rows are stored straight into the destination GPU's receive buffer and the expert
+ * outputs straight back into the sender's return buffer, by plain kernels; no all-to-all
+ * collective, no host round trip.  Rank r owns experts [r*E/world, (r+1)*E/world).
+ * The `*_ptrs` arguments are DEVICE arrays of `world` device pointers, entry p = rank p's
+ * buffer (entry `rank` = the local one); the buffers must be peer-accessible (symmetric
+ * allocations).  The caller separates the steps with a barrier over all ranks on the stream:
+ *   publish_counts | barrier | plan, send_rows | barrier | (expert block) | return_rows | barrier
+ * counts table: int32 [world][E]; receive buffer: bf16 [capacity][H], rows grouped by
+ * (local expert, source rank), described by local_offsets int32 [E/world + 1]; return buffer:
+ * bf16 [num_pairs][H] in the sender's sorted-by-expert order.  send_base int32 [E], dst_start
+ * and ret_base int32 [E] (world * E/world), info int32 [2] = {rows received, overflow flag};
+ * rows that would land beyond `capacity` are dropped and flagged.  E <= 1024, H % 8 == 0.
+ * No counterpart in the reference (it has no multi-GPU code). */
+LSG_API int lsg_ep_publish_counts(const int32_t* expert_offsets, int num_experts, int rank, int world,
+                                  void* const* counts_table_ptrs, void* stream);
+LSG_API int lsg_ep_plan(const int32_t* counts_table, int rank, int world, int num_experts, int capacity,
+                        int32_t* send_base, int32_t* local_offsets, int32_t* dst_start, int32_t* ret_base,
+                        int32_t* info, void* stream);
+LSG_API int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
+                             const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
+                             void* const* recv_buf_ptrs, int capacity, void* stream);
+LSG_API int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
+                               const int32_t* info, int world, int experts_per_rank, int H, int capacity,
+                               void* const* back_buf_ptrs, void* stream);
+
 /* out[row,:] = hidden[perm[row] / top_k, :]   (bf16, H multiple of 8). */
 LSG_API int lsg_moe_permute(const void* hidden_bf16, const int32_t* perm, int rows, int top_k, int H,
                             void* out_bf16, void* stream);

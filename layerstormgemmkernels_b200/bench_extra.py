@@ -2,6 +2,7 @@
 the headline workload): the expert-parallel MoE layer and the column-split prefill GEMM.
 """
 import json
+import sys
 import os
 import time
 
@@ -105,15 +106,34 @@ def _moe(args, rank, world, dev, steps, warmup, sampler=None):
     def ffn(rows, offs):
         return ops.gguf_moe_ffn(rows, offs, gate_p, up_p, down_p, t, H, I)
 
+    # Exchange between the ranks: stores into the peers' buffers (default), or the NCCL
+    # all-to-all pair when symmetric memory cannot be set up (or with --ep nccl).
+    exchange = None
+    ep_mode = "single"
+    if world > 1:
+        ep_mode = getattr(args, "ep", "peer")
+        if ep_mode == "peer":
+            try:
+                exchange = D.EpPeerExchange.make(E, k, H, T)
+            except Exception as exc:   # noqa: BLE001 - any failure of the optional path falls back
+                if rank == 0:
+                    print(f"peer-memory exchange unavailable ({type(exc).__name__}: {exc}); using NCCL all-to-all",
+                          file=sys.stderr)
+                ep_mode = "nccl"
+
     def layer(h, lg):
         if world == 1:
             idx, w = ops.moe_route(lg, k)
             offs, perm, inv = ops.moe_permutation(idx, E)
             return ops.moe_unpermute(ffn(ops.moe_permute(h, perm, k), offs), inv, w)
+        if exchange is not None:
+            return exchange.layer(h, lg, ffn, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
         return D.ep_moe_layer(h, lg, k, E, ffn, ops.moe_route, ops.moe_permutation, ops.moe_permute,
                               ops.moe_unpermute)
 
     ms = _time_steps(lambda: layer(hidden, logits), steps, warmup, world, dev, sampler)
+    if exchange is not None and exchange.overflowed():
+        raise SystemExit("expert-parallel receive buffer overflowed (raise the capacity factor)")
     # the expert block alone (the grouped GEMMs with their operand preparation) on this rank's
     # routed rows, single GPU only: what the tensor-pipe roofline is about
     gemm_ms = None
@@ -139,7 +159,9 @@ def _moe(args, rank, world, dev, steps, warmup, sampler=None):
         "data": "synthetic",
         "config": {"workload": f"MoE layer, 128 experts top-8, H=2048, I=768, Q4_K, {T_total} tokens: "
                                "route, permute, gate/up/down grouped GEMMs, SwiGLU, combine",
-                   "tokens": T_total, "parallelism": f"ep{world}" if world > 1 else "single",
+                   "tokens": T_total,
+                   "parallelism": (f"ep{world}, rows exchanged by peer-memory stores" if ep_mode == "peer"
+                                   else f"ep{world}, NCCL all-to-all" if world > 1 else "single"),
                    "l2_defeat": "339 MB of expert weights per rank set exceed the 126 MB L2"},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                      "frac": value / world / peak, "peak_kind": kind, "traffic": None,

@@ -154,6 +154,10 @@ def _load():
         "lsg_nvfp4_reformat_scales": (ci, [vp, vp, ci, ci, vp]),
         "lsg_moe_route": (ci, [vp, ci, ci, ci, vp, vp, vp]),
         "lsg_ep_expert_order": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
+        "lsg_ep_publish_counts": (ci, [vp, ci, ci, ci, vp, vp]),
+        "lsg_ep_plan": (ci, [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
+        "lsg_ep_send_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
+        "lsg_ep_return_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]),
         "lsg_moe_permutation_scratch_ints": (ctypes.c_longlong, [ci, ci, ci]),
         "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_moe_permute": (ci, [vp, vp, ci, ci, ci, vp, vp]),

@@ -1,0 +1,243 @@
+// Expert-parallel MoE exchange over peer memory (NVLink / NVSwitch): the dispatch and the
+// return of the routed rows are plain kernels that store straight into the destination
+// GPU's buffer, instead of two all-to-all collectives with a host round trip for their split
+// sizes and a regrouping pass on each side.  The reference has no multi-GPU code; this defines
+// that layer for one node, one process per GPU.
+//
+// Every rank r owns experts [r*per, (r+1)*per).  Buffers the ranks share (symmetric
+// allocations; each rank holds the peers' addresses in a device array):
+//   counts table  int32 [world][E]   row s = rows rank s sends per global expert
+//   receive buffer bf16 [capacity][H] rows for this rank's experts, grouped by
+//                                    (local expert, source rank)
+//   return buffer  bf16 [P][H]       expert outputs back at the sender, in the sender's
+//                                    sorted-by-expert row order
+// Per layer: publish counts (stores into every peer's table) | barrier | plan (every rank
+// derives all offsets from the complete table, no communication) | send rows (gather from the
+// token matrix + peer stores) | barrier | expert block on the receive buffer | return rows
+// (peer stores) | barrier.  The barriers are the caller's (stream-ordered, between kernels);
+// no kernel here waits for another GPU, and all peer accesses are stores.
+#include "common.cuh"
+#include "host.h"
+
+namespace lsg {
+
+namespace {
+
+// counts of this rank -> row `rank` of every peer's table.
+__global__ void __launch_bounds__(256)
+ep_publish_counts_kernel(const int32_t* __restrict__ offs, int E, int rank, int world,
+                         int32_t* const* __restrict__ tabs) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= E * world) return;
+    const int peer = i / E, e = i - peer * E;
+    tabs[peer][static_cast<size_t>(rank) * E + e] = offs[e + 1] - offs[e];
+}
+
+// One CTA of 1024 threads; E <= 1024, world * per = E.
+//   send_base[e]            row in rank (e / per)'s receive buffer where this rank's block for
+//                           global expert e starts
+//   dst_start[el*world + s] start of block (local expert el, source s) in this rank's
+//                           receive buffer; local_offsets[el] = dst_start[el*world]
+//   ret_base[el*world + s]  row in source s's return buffer where that block goes back
+//                           (= exclusive scan of s's counts at global expert rank*per + el)
+//   info[0] = rows received, info[1] = 1 if some rank's receive buffer would overflow
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int capacity,
+               int32_t* __restrict__ send_base, int32_t* __restrict__ local_offsets, int32_t* __restrict__ dst_start,
+               int32_t* __restrict__ ret_base, int32_t* __restrict__ info) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    __shared__ int wsum[32];
+    __shared__ int colsum[1024];   // rows for global expert e over all sources
+    __shared__ int overflow;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = E / world;
+    if (tid == 0) overflow = 0;
+    // per-expert totals and, for this rank as a source, the rows of lower-ranked sources
+    int total_e = 0, before_me = 0;
+    if (tid < E) {
+        for (int s = 0; s < world; ++s) {
+            const int c = tab[static_cast<size_t>(s) * E + tid];
+            if (s < rank) before_me += c;
+            total_e += c;
+        }
+        colsum[tid] = total_e;
+    }
+    __syncthreads();
+    // exclusive scan of the totals inside each destination rank's expert range
+    if (tid < E) {
+        const int d = tid / per, el = tid - d * per;
+        int base = 0;
+        for (int j = 0; j < el; ++j) base += colsum[d * per + j];
+        send_base[tid] = base + before_me;
+        if (el == per - 1 && base + total_e > capacity) overflow = 1;
+    }
+    // this rank as a receiver: blocks (el, s) in destination order
+    const int B = per * world;
+    int v = 0;
+    if (tid < B) {
+        const int el = tid / world, s = tid - el * world;
+        v = tab[static_cast<size_t>(s) * E + rank * per + el];
+    }
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = wsum[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += u;
+        }
+        wsum[lane] = w;
+    }
+    __syncthreads();
+    const int excl = (warp > 0 ? wsum[warp - 1] : 0) + incl - v;
+    if (tid < B) {
+        const int el = tid / world, s = tid - el * world;
+        dst_start[tid] = excl;
+        if (s == 0) local_offsets[el] = excl;
+        if (tid == B - 1) {
+            local_offsets[per] = excl + v;
+            info[0] = excl + v;
+        }
+        // where the block goes back: source s's rows for experts below rank*per + el
+        int back = 0;
+        const int ge = rank * per + el;
+        for (int j = 0; j < ge; ++j) back += tab[static_cast<size_t>(s) * E + j];
+        ret_base[tid] = back;
+    }
+    __syncthreads();
+    if (tid == 0) info[1] = overflow;
+}
+
+// Sorted row i (expert e, j-th row of e) -> row send_base[e] + j of rank e / per.
+// One thread per 16-byte vector.
+__global__ void __launch_bounds__(256)
+ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm,
+                    const int32_t* __restrict__ offs, const int32_t* __restrict__ send_base, int P, int top_k,
+                    int vpr, int E, int per, uint4* const* __restrict__ recv, int capacity) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= static_cast<long long>(P) * vpr) return;
+    const int i = static_cast<int>(idx / vpr), v = static_cast<int>(idx - static_cast<long long>(i) * vpr);
+    int lo = 0, hi = E - 1;   // last expert whose first row is <= i and that owns row i
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (offs[mid] <= i) lo = mid;
+        else hi = mid - 1;
+    }
+    const int e = lo;
+    const int row = send_base[e] + (i - offs[e]);
+    if (row >= capacity) return;
+    const int token = perm[i] / top_k;
+    recv[e / per][static_cast<size_t>(row) * vpr + v] = __ldg(hidden + static_cast<size_t>(token) * vpr + v);
+}
+
+// Received row r of block (el, s) -> row ret_base[block] + j of source s's return buffer.
+__global__ void __launch_bounds__(256)
+ep_return_rows_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ dst_start,
+                      const int32_t* __restrict__ ret_base, const int32_t* __restrict__ info, int world, int B,
+                      int vpr, int capacity, uint4* const* __restrict__ back) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    const int rows = min(info[0], capacity);
+    if (idx >= static_cast<long long>(rows) * vpr) return;
+    const int r = static_cast<int>(idx / vpr), v = static_cast<int>(idx - static_cast<long long>(r) * vpr);
+    int lo = 0, hi = B - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (dst_start[mid] <= r) lo = mid;
+        else hi = mid - 1;
+    }
+    const int s = lo % world;
+    const int row = ret_base[lo] + (r - dst_start[lo]);
+    back[s][static_cast<size_t>(row) * vpr + v] = __ldg(y + static_cast<size_t>(r) * vpr + v);
+}
+
+int check_world(const char* op, int E, int world) {
+    if (world < 1 || E < 1 || E > 1024 || E % world != 0)
+        return fail(LSG_ERR_INVALID, "%s: need 1 <= num_experts <= 1024 divisible by the world size (E=%d, world=%d)", op, E,
+                    world);
+    return LSG_OK;
+}
+
+}  // namespace
+
+}  // namespace lsg
+
+using namespace lsg;
+
+extern "C" int lsg_ep_publish_counts(const int32_t* expert_offsets, int num_experts, int rank, int world,
+                                     void* const* counts_table_ptrs, void* stream) {
+    int rc = check_world("ep_publish_counts", num_experts, world);
+    if (rc != LSG_OK) return rc;
+    if (rank < 0 || rank >= world || !expert_offsets || !counts_table_ptrs)
+        return fail(LSG_ERR_INVALID, "ep_publish_counts: bad rank or null pointer");
+    const int n = num_experts * world;
+    LSG_CUDA_TRY(launch_kernel(ep_publish_counts_kernel, dim3((n + 255) / 256), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, expert_offsets, num_experts, rank, world,
+                               reinterpret_cast<int32_t* const*>(counts_table_ptrs)));
+    return LSG_OK;
+}
+
+extern "C" int lsg_ep_plan(const int32_t* counts_table, int rank, int world, int num_experts, int capacity,
+                           int32_t* send_base, int32_t* local_offsets, int32_t* dst_start, int32_t* ret_base,
+                           int32_t* info, void* stream) {
+    int rc = check_world("ep_plan", num_experts, world);
+    if (rc != LSG_OK) return rc;
+    if (rank < 0 || rank >= world || capacity < 0 || !counts_table || !send_base || !local_offsets || !dst_start ||
+        !ret_base || !info)
+        return fail(LSG_ERR_INVALID, "ep_plan: bad rank, negative capacity or null pointer");
+    LSG_CUDA_TRY(launch_kernel(ep_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), true,
+                               counts_table, rank, world, num_experts, capacity, send_base, local_offsets, dst_start,
+                               ret_base, info));
+    return LSG_OK;
+}
+
+extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
+                                const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
+                                void* const* recv_buf_ptrs, int capacity, void* stream) {
+    int rc = check_world("ep_send_rows", num_experts, world);
+    if (rc != LSG_OK) return rc;
+    if (num_pairs <= 0) return LSG_OK;
+    if (!hidden_bf16 || !perm || !expert_offsets || !send_base || !recv_buf_ptrs || top_k < 1)
+        return fail(LSG_ERR_INVALID, "ep_send_rows: null pointer or bad top_k");
+    if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(hidden_bf16) & 15))
+        return fail(LSG_ERR_ALIGNMENT, "ep_send_rows: H must be a multiple of 8 and buffers 16-byte aligned");
+    const int vpr = H / 8;
+    const long long total = static_cast<long long>(num_pairs) * vpr;
+    LSG_CUDA_TRY(launch_kernel(ep_send_rows_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(hidden_bf16), perm,
+                               expert_offsets, send_base, num_pairs, top_k, vpr, num_experts, num_experts / world,
+                               reinterpret_cast<uint4* const*>(recv_buf_ptrs), capacity));
+    return LSG_OK;
+}
+
+extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
+                                  const int32_t* info, int world, int experts_per_rank, int H, int capacity,
+                                  void* const* back_buf_ptrs, void* stream) {
+    if (world < 1 || experts_per_rank < 1 || world * experts_per_rank > 1024)
+        return fail(LSG_ERR_INVALID, "ep_return_rows: need 1 <= world * experts_per_rank <= 1024");
+    if (capacity <= 0) return LSG_OK;
+    if (!y_bf16 || !dst_start || !ret_base || !info || !back_buf_ptrs)
+        return fail(LSG_ERR_INVALID, "ep_return_rows: null pointer");
+    if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15))
+        return fail(LSG_ERR_ALIGNMENT, "ep_return_rows: H must be a multiple of 8 and buffers 16-byte aligned");
+    const int vpr = H / 8;
+    const long long total = static_cast<long long>(capacity) * vpr;
+    LSG_CUDA_TRY(launch_kernel(ep_return_rows_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+                               static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(y_bf16), dst_start,
+                               ret_base, info, world, world * experts_per_rank, vpr, capacity,
+                               reinterpret_cast<uint4* const*>(back_buf_ptrs)));
+    return LSG_OK;
+}

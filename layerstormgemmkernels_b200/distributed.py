@@ -117,6 +117,78 @@ def ep_moe_layer(hidden, logits, top_k, num_experts, expert_ffn, route, permutat
     return unpermute(back, inv, w)
 
 
+class EpPeerExchange:
+    """Expert-parallel MoE layer with the row exchange over peer memory: the routed rows are
+    stored straight into the destination GPU's receive buffer, the expert outputs straight
+    back (lsg_ep_* kernels), with stream-ordered barriers in between.  No all-to-all, no
+    device-to-host copy, no regrouping pass: rows arrive already grouped by (local expert,
+    source rank).
+
+    buffers: dict with, per name in ("counts", "recv", "back"), the LOCAL tensor and a CUDA
+    int64 tensor of the `world` peer addresses (entry = rank p's tensor).  `barrier()` must
+    order all ranks on the current stream (a symmetric-memory barrier, or a tiny all-reduce).
+    `make()` builds everything from torch symmetric memory."""
+
+    def __init__(self, rank, world, num_experts, top_k, H, num_pairs, capacity, buffers, barrier):
+        self.rank, self.world, self.E, self.k, self.H = rank, world, num_experts, top_k, H
+        self.per = num_experts // world
+        self.P, self.cap = num_pairs, capacity
+        self.b = buffers
+        self.barrier = barrier
+        dev = buffers["recv"][0].device
+        self.send_base = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+        self.local_offsets = torch.empty((self.per + 1,), dtype=torch.int32, device=dev)
+        self.dst_start = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+        self.ret_base = torch.empty((num_experts,), dtype=torch.int32, device=dev)
+        self.info = torch.zeros((2,), dtype=torch.int32, device=dev)
+
+    @staticmethod
+    def make(num_experts, top_k, H, tokens_per_rank, capacity_factor=1.5, group=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        P = tokens_per_rank * top_k
+        cap = int(P * capacity_factor + 255) // 256 * 256
+        local = {"counts": symm.empty((world, num_experts), dtype=torch.int32, device=dev),
+                 "recv": symm.empty((cap, H), dtype=torch.bfloat16, device=dev),
+                 "back": symm.empty((P, H), dtype=torch.bfloat16, device=dev)}
+        handles = {n: symm.rendezvous(t, group) for n, t in local.items()}
+        bufs = {n: (local[n], torch.tensor([int(p) for p in handles[n].buffer_ptrs], dtype=torch.int64, device=dev))
+                for n in local}
+        h = handles["recv"]
+        ex = EpPeerExchange(rank, world, num_experts, top_k, H, P, cap, bufs, lambda: h.barrier(0))
+        ex._handles = handles   # keep the mappings alive
+        return ex
+
+    def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
+        from . import capi
+        lib = capi.lib
+        st = torch.cuda.current_stream().cuda_stream
+        p = lambda t: t.data_ptr()
+        idx, w = route(logits, self.k)
+        offs, perm, inv = permutation(idx, self.E)
+        counts, counts_ptrs = self.b["counts"]
+        recv, recv_ptrs = self.b["recv"]
+        back, back_ptrs = self.b["back"]
+        capi.check(lib.lsg_ep_publish_counts(p(offs), self.E, self.rank, self.world, p(counts_ptrs), st))
+        self.barrier()
+        capi.check(lib.lsg_ep_plan(p(counts), self.rank, self.world, self.E, self.cap, p(self.send_base),
+                                   p(self.local_offsets), p(self.dst_start), p(self.ret_base), p(self.info), st))
+        capi.check(lib.lsg_ep_send_rows(p(hidden), p(perm), p(offs), p(self.send_base), self.P, self.k, self.H,
+                                        self.E, self.world, p(recv_ptrs), self.cap, st))
+        self.barrier()
+        y = expert_ffn(recv, self.local_offsets)
+        capi.check(lib.lsg_ep_return_rows(p(y), p(self.dst_start), p(self.ret_base), p(self.info), self.world,
+                                          self.per, y.shape[1], self.cap, p(back_ptrs), st))
+        self.barrier()
+        return unpermute(back, inv, w)
+
+    def overflowed(self):
+        """True if some rank's receive buffer was too small in the last layer (synchronizes)."""
+        return bool(self.info[1].item())
+
+
 def column_slab(rank, world, N, align=128):
     """Output columns [n0, n1) owned by `rank`: contiguous, multiples of `align`."""
     if N % (world * align) != 0:

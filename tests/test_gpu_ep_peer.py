@@ -1,0 +1,28 @@
+"""Expert-parallel MoE layer with the row exchange over peer memory, on two GPUs: identical
+output to the NCCL all-to-all exchange.  Skipped on a box with one GPU (the index arithmetic of
+the exchange kernels is covered there by test_gpu_moe_routing.py with emulated ranks)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.timeout(300)
+def test_peer_exchange_equals_nccl_exchange_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"   # plain peer stores and ring/tree collectives only
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29537", os.path.join(HERE, "ep_peer_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=280)
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("EP_PEER")]
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert len(lines) == 2
+    for ln in lines:
+        assert "equal=True" in ln and "overflow=False" in ln and "status=0" in ln, ln

@@ -86,3 +86,64 @@ def test_ep_expert_order_matches_definition(ops, world, per, seed):
     exp_offs = np.zeros(per + 1, np.int32)
     exp_offs[1:] = np.cumsum(counts.sum(0))
     assert np.array_equal(offs.cpu().numpy(), exp_offs)
+
+
+@pytest.mark.parametrize("world,E,T,k", [(2, 8, 40, 2), (4, 16, 64, 4), (1, 4, 10, 2), (2, 128, 512, 8)])
+def test_ep_peer_exchange_kernels_emulated_ranks(ops, world, E, T, k):
+    """The peer-memory exchange kernels (publish counts, plan, send rows, return rows) with the
+    ranks emulated one after the other on this GPU: every 'peer' buffer is a local tensor, so
+    the index arithmetic of a whole layer is checked without a second GPU.  The expert block
+    is replaced by y = x * (global expert id + 1)."""
+    from layerstormgemmkernels_b200 import capi
+    lib = capi.lib
+    H, P, per = 64, T * k, E // world
+    cap = P * world            # worst case: everything lands on one rank
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(world * 100 + E)
+    dev = "cuda"
+    hidden = [torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev) for _ in range(world)]
+    logits = [torch.randn(T, E, generator=g).to(dev) for _ in range(world)]
+    counts = [torch.zeros(world, E, dtype=torch.int32, device=dev) for _ in range(world)]
+    recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    back = [torch.zeros(P, H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    cp, rp, bp = ptrs(counts), ptrs(recv), ptrs(back)
+    routed = []
+    for r in range(world):
+        idx, w = ops.moe_route(logits[r], k)
+        offs, perm, inv = ops.moe_permutation(idx, E)
+        routed.append((idx, w, offs, perm, inv))
+        capi.check(lib.lsg_ep_publish_counts(offs.data_ptr(), E, r, world, cp.data_ptr(), st))
+    plans = []
+    for r in range(world):
+        sb = torch.empty(E, dtype=torch.int32, device=dev)
+        lo = torch.empty(per + 1, dtype=torch.int32, device=dev)
+        ds = torch.empty(E, dtype=torch.int32, device=dev)
+        rb = torch.empty(E, dtype=torch.int32, device=dev)
+        info = torch.zeros(2, dtype=torch.int32, device=dev)
+        capi.check(lib.lsg_ep_plan(counts[r].data_ptr(), r, world, E, cap, sb.data_ptr(), lo.data_ptr(),
+                                   ds.data_ptr(), rb.data_ptr(), info.data_ptr(), st))
+        plans.append((sb, lo, ds, rb, info))
+        idx, w, offs, perm, inv = routed[r]
+        capi.check(lib.lsg_ep_send_rows(hidden[r].data_ptr(), perm.data_ptr(), offs.data_ptr(), sb.data_ptr(), P, k,
+                                        H, E, world, rp.data_ptr(), cap, st))
+    for r in range(world):
+        sb, lo, ds, rb, info = plans[r]
+        assert info.tolist()[1] == 0
+        lo_h = lo.cpu().numpy()
+        # rows this rank received = all pairs routed to its experts
+        expected_rows = sum(int((routed[s][0] // per == r).sum().item()) for s in range(world))
+        assert int(lo_h[-1]) == expected_rows == info.tolist()[0]
+        y = recv[r].clone()
+        for el in range(per):
+            y[lo_h[el]:lo_h[el + 1]] = (y[lo_h[el]:lo_h[el + 1]].float() * (r * per + el + 1)).to(torch.bfloat16)
+        capi.check(lib.lsg_ep_return_rows(y.data_ptr(), ds.data_ptr(), rb.data_ptr(), info.data_ptr(), world, per, H,
+                                          cap, bp.data_ptr(), st))
+    torch.cuda.synchronize()
+    for r in range(world):
+        idx, w, offs, perm, inv = routed[r]
+        pair = perm.cpu().numpy()                      # sorted row -> pair index
+        e_of_row = idx.reshape(-1).cpu().numpy()[pair]
+        tok = pair // k
+        exp = (hidden[r].float().cpu()[tok] * torch.from_numpy((e_of_row + 1).astype(np.float32))[:, None]).to(torch.bfloat16)
+        assert torch.equal(back[r].cpu(), exp)
