@@ -667,11 +667,15 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks,
-              unsigned int* __restrict__ counters, int n_counters) {
+              unsigned int* __restrict__ counters, int n_counters, const int32_t* __restrict__ live_rows,
+              int blocks_per_row) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
     if (counters && task < n_counters) counters[task] = 0;
+    // grouped callers may hold fewer rows than the buffer they pass: the row count then lives
+    // on the device (the last entry of the expert offsets) and the rest is skipped
+    if (live_rows) n_blocks = min(n_blocks, static_cast<long long>(*live_rows) * blocks_per_row);
     const bool live = task < n_blocks * 4;
     const long long tk = live ? task : 0;
     const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
@@ -715,10 +719,12 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, lon
 // (what a caller computing the activation in fp32 and storing bf16 gets), then the Q8_1 round
 // trip of act over 32-value blocks along I, as fp16.  Four lanes per block, eight values each.
 __global__ void __launch_bounds__(256)
-swiglu_prep_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ out, long long n_blocks, int I) {
+swiglu_prep_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ out, long long n_blocks, int I,
+                   const int32_t* __restrict__ live_rows) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (live_rows) n_blocks = min(n_blocks, static_cast<long long>(*live_rows) * (I / 32));
     const bool live = task < n_blocks * 4;
     const long long tk = live ? task : 0;
     const int per_row = I / 8;
@@ -954,7 +960,8 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     if (tasks < n_counters) tasks = n_counters;
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((tasks + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters));
+                               n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters,
+                               static_cast<const int32_t*>(nullptr), 0));
     CUtensorMap tmX;
     int rc = make_map(&tmX, x16, M, K, nt);
     if (rc != LSG_OK) return rc;
@@ -1037,7 +1044,7 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
     const long long nb = static_cast<long long>(T) * (K / 32);
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0));
+                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, K / 32));
     CUtensorMap tmX;
     int rc = make_map(&tmX, x16, T, K, tile_m);
     if (rc != LSG_OK) return rc;
@@ -1083,7 +1090,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     long long nb = static_cast<long long>(T) * (H / 32);
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0));
+                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, H / 32));
     CUtensorMap tmX;
     int rc = make_map(&tmX, x16, T, H, tile_m);
     if (rc != LSG_OK) return rc;
@@ -1104,7 +1111,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     // SwiGLU + preparation, then down
     nb = static_cast<long long>(T) * (I / 32);
     LSG_CUDA_TRY(launch_kernel(swiglu_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s,
-                               true, static_cast<const __nv_bfloat16*>(gu), act16, nb, I));
+                               true, static_cast<const __nv_bfloat16*>(gu), act16, nb, I, expert_offsets + E));
     CUtensorMap tmA;
     rc = make_map(&tmA, act16, T, I, tile_m);
     if (rc != LSG_OK) return rc;
