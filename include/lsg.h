@@ -179,6 +179,16 @@ LSG_API size_t lsg_gguf_gemm_bf16_workspace_bytes(int M, int N, int K);
 LSG_API int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
                                void* stream);
 
+/* lsg_gguf_mmq fused with the all-gather of a column-split weight: this rank holds N of the
+ * ldc output columns (a slab of packed weight rows) and stores every output tile into each
+ * of the n_out matrices C_ptrs[i] (a DEVICE array of device pointers: this GPU's [M, ldc]
+ * output and its peers', peer-mapped) at column offset col_offset.  After a barrier over the
+ * ranks every rank holds the whole [M, ldc] product; no collective moves the data, the
+ * stores travel over NVLink while the tensor cores work on the next tiles.  p->C is ignored.
+ * No counterpart in the reference (it has no multi-GPU code). */
+LSG_API int lsg_gguf_mmq_gather(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
+                                int col_offset, void* workspace, size_t workspace_bytes, void* stream);
+
 /* How the tensor-core GEMMs (lsg_gguf_mmq and the grouped GEMM's tensor-core route) obtain
  * their fp16 weights, process-wide:
  *   0  a preparation kernel expands the packed matrix into workspace first;

@@ -188,7 +188,20 @@ def _prefill(args, rank, world, dev, steps, warmup, sampler=None):
     A = torch.randn(M, K, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(dev)
     A_host = A.cpu().pin_memory()
 
+    # Several GPUs: the all-gather is fused into the GEMM's epilogue (peer-memory stores), or,
+    # with --ep nccl or when symmetric memory cannot be set up, a separate NCCL all-gather.
+    fused_gather = None
+    if world > 1 and getattr(args, "ep", "peer") == "peer":
+        try:
+            fused_gather = D.ColumnSplitPeer(M, N)
+        except Exception as exc:   # noqa: BLE001 - the optional path falls back
+            if rank == 0:
+                print(f"peer-memory gather unavailable ({type(exc).__name__}: {exc}); using NCCL all-gather",
+                      file=sys.stderr)
+
     def step(a=A):
+        if fused_gather is not None:
+            return fused_gather.gemm(a, slab, t, K)
         out = ops.gguf_mmq(a, slab, t, n1 - n0, K)
         return out if world == 1 else D.column_split_gather(out)
 
@@ -203,7 +216,9 @@ def _prefill(args, rank, world, dev, steps, warmup, sampler=None):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 (tcgen05, fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"Q4_K 14336x4096 prefill GEMM, M={M}, Q8_1 activations",
-                   "parallelism": f"column-split x{world} + all-gather" if world > 1 else "single",
+                   "parallelism": ("single" if world == 1 else
+                                   f"column-split x{world}, all-gather fused into the GEMM epilogue (peer stores)"
+                                   if fused_gather is not None else f"column-split x{world} + NCCL all-gather"),
                    "l2_defeat": "operands (fp16 weights 117 MB + outputs 117 MB at M=4096) exceed L2"},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak, "unit": "TFLOP/s",
                      "frac": value / world / peak, "peak_kind": kind, "traffic": None},

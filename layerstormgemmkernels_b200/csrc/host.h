@@ -22,8 +22,17 @@ int build_segment_list(const int32_t* offs, const void* const* B_ptrs, int E, in
                        int max_segments, int* seg, cudaStream_t s);
 
 size_t mmq_scratch_bytes(long long rows, int K, int E, int N);
+// Several output matrices for one GEMM (this GPU's and its peers'): every tile is stored
+// into each at column offset col_off, row stride ldc (GEMM fused with the all-gather of a
+// column-split weight).
+struct MmqOutputs {
+    void* const* C_ptrs;   // device array of n_out device pointers
+    int n_out;
+    int ldc;
+    int col_off;
+};
 int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
-              size_t ws_bytes, cudaStream_t s);
+              size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs = nullptr);
 int mmq_grouped(int type, int T, int E, int N, int K, const void* A, const void* const* B_ptrs,
                 const int32_t* expert_offsets, void* D, int out_f32, const int* tile_expert,
                 const int* tile_mstart, int t_max, void* scratch, size_t scratch_bytes, cudaStream_t s);
@@ -40,7 +49,7 @@ size_t tc_fused_dense_scratch_bytes(int M, int N, int K);
 int tc_fused_grouped_tile_m(long long T, int E);
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K);
 int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
-                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s);
+                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs = nullptr);
 int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, const void* const* B_ptrs,
                      const int32_t* expert_offsets, void* D, int out_dtype, const int* tile_expert,
                      const int* tile_mstart, int t_max, int tile_m, void* scratch, size_t scratch_bytes,

@@ -83,6 +83,9 @@ struct FusedArgs {
     float* partial;               // [items][ksplit][128][nt] fp32, only with ksplit > 1
     unsigned int* counters;       // [tiles][4 epilogue warps], zero on entry
     const float* row_scale;       // optional per-token output scale (the unquantized-activation route)
+    void* const* C_ptrs;          // optional: n_out output matrices (this GPU's and its peers'); every
+    int n_out;                    //   element is stored into each of them (GEMM + all-gather)
+    int col_off;                  // column offset of this call's N columns inside the output rows
     unsigned int* status;
 };
 
@@ -544,7 +547,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             const bool second = a.B_ptrs2 != nullptr && im.wt >= a.split_wt;
             const int n_local = (second ? im.wt - a.split_wt : im.wt) * WM + warp * 32 + lane;
             const bool n_ok = n_local < a.N;
-            const int n = n_local + (second ? a.col2_off : 0);   // this thread's output column
+            const int n = n_local + (second ? a.col2_off : 0) + a.col_off;   // this thread's output column
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * a.nt;
 
             if (a.ksplit == 1) {
@@ -562,22 +565,26 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                                     v[i] = __float_as_uint(__uint_as_float(v[i]) * __ldg(a.row_scale + im.mstart + c + i));
                         }
                         const size_t o = static_cast<size_t>(im.mstart + c) * a.ldc + n;
-                        if (a.out_dtype == LSG_DTYPE_F32) {
-                            float* dst = static_cast<float*>(a.C) + o;
+                        const int n_out = a.n_out > 0 ? a.n_out : 1;
+                        for (int po = 0; po < n_out; ++po) {
+                            void* Cb = a.n_out > 0 ? a.C_ptrs[po] : a.C;
+                            if (a.out_dtype == LSG_DTYPE_F32) {
+                                float* dst = static_cast<float*>(Cb) + o;
 #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < rows) dst[static_cast<size_t>(i) * a.ldc] = __uint_as_float(v[i]);
-                        } else {
-                            uint16_t* dst = static_cast<uint16_t*>(a.C) + o;
-                            const bool f16 = a.out_dtype == LSG_DTYPE_F16;
+                                for (int i = 0; i < 32; ++i)
+                                    if (i < rows) dst[static_cast<size_t>(i) * a.ldc] = __uint_as_float(v[i]);
+                            } else {
+                                uint16_t* dst = static_cast<uint16_t*>(Cb) + o;
+                                const bool f16 = a.out_dtype == LSG_DTYPE_F16;
 #pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (i < rows) {
-                                    const float x = __uint_as_float(v[i]);
-                                    dst[static_cast<size_t>(i) * a.ldc] =
-                                        f16 ? __half_as_ushort(__float2half_rn(x))
-                                            : __bfloat16_as_ushort(__float2bfloat16_rn(x));
-                                }
+                                for (int i = 0; i < 32; ++i)
+                                    if (i < rows) {
+                                        const float x = __uint_as_float(v[i]);
+                                        dst[static_cast<size_t>(i) * a.ldc] =
+                                            f16 ? __half_as_ushort(__float2half_rn(x))
+                                                : __bfloat16_as_ushort(__float2bfloat16_rn(x));
+                                    }
+                            }
                         }
                     }
                 }
@@ -633,12 +640,16 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                                 if (i0 + i < live_rows) {
                                     if (a.row_scale) acc[i] *= __ldg(a.row_scale + im.mstart + i0 + i);
                                     const size_t o = static_cast<size_t>(im.mstart + i0 + i) * a.ldc + n;
-                                    if (a.out_dtype == LSG_DTYPE_F32)
-                                        static_cast<float*>(a.C)[o] = acc[i];
-                                    else if (a.out_dtype == LSG_DTYPE_F16)
-                                        static_cast<uint16_t*>(a.C)[o] = __half_as_ushort(__float2half_rn(acc[i]));
-                                    else
-                                        static_cast<uint16_t*>(a.C)[o] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]));
+                                    const int n_out = a.n_out > 0 ? a.n_out : 1;
+                                    for (int po = 0; po < n_out; ++po) {
+                                        void* Cb = a.n_out > 0 ? a.C_ptrs[po] : a.C;
+                                        if (a.out_dtype == LSG_DTYPE_F32)
+                                            static_cast<float*>(Cb)[o] = acc[i];
+                                        else if (a.out_dtype == LSG_DTYPE_F16)
+                                            static_cast<uint16_t*>(Cb)[o] = __half_as_ushort(__float2half_rn(acc[i]));
+                                        else
+                                            static_cast<uint16_t*>(Cb)[o] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]));
+                                    }
                                 }
                             }
                         }
@@ -940,7 +951,7 @@ size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K) {
 
 // Dense: C[M, N] (ldc) = x . W^T with W packed GGUF rows.
 int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,
-                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
+                   int out_dtype, void* ws, size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs) {
     if (M == 0 || N == 0) return LSG_OK;
     if (K % 32 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf fused mmq: K must be a multiple of 32");
     const int nt = pick_nt(M);
@@ -969,6 +980,9 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     a.W = static_cast<const uint8_t*>(W);
     a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
     a.C = C; a.ldc = ldc; a.out_dtype = out_dtype;
+    if (outs) {
+        a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off;
+    }
     a.K = K; a.N = N; a.M = M;
     a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;

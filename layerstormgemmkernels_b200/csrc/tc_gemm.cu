@@ -47,7 +47,8 @@ constexpr int kBBytes = BN * BK * 2;   // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTcThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kTcSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kOutStageBytes = 4 * 32 * 128;   // 4 epilogue warps x 32 rows x 64 bf16: coalescing buffer of the gather route
+constexpr int kTcSmem = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kOutStageBytes;
 
 struct TcArgs {
     void* C;                  // [rows, ldc] bf16 or f32
@@ -55,6 +56,9 @@ struct TcArgs {
     int out_f32;              // lsg_dtype of C: 0 bf16, 1 f32, 2 f16
     const float* alphas;      // optional per-expert output scale (grouped) or single value (dense)
     float alpha_host;         // output scale known on the host (used when alphas is null and it is not 1)
+    void* const* C_ptrs;      // optional: n_out output matrices (this GPU's and its peers'), every tile is
+    int n_out;                //   stored into each of them at column offset col_off (GEMM + all-gather)
+    int col_off;
     int K;
     int N;                    // columns of one problem (per expert)
     int n_tiles;              // ceil(N / BN)
@@ -82,6 +86,7 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint64_t* acc_empty = acc_full + 2;     // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint8_t* out_stage = smem + kStages * kStageBytes + 256;   // 16-byte aligned, behind the barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -203,6 +208,58 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             float alpha = a.alpha_host;
             if (a.alphas) alpha = a.tile_expert ? a.alphas[a.tile_expert[t]] : a.alphas[0];
             const bool scaled = a.alphas != nullptr || alpha != 1.0f;
+            // Gather route with 16-bit outputs: 64 columns at a time go through a swizzled
+            // shared-memory buffer so that every store instruction writes four 128-byte row
+            // segments (peer stores over NVLink travel as whole 128-byte packets instead of
+            // 16-byte pieces).  Needs the whole tile inside the matrix and aligned rows.
+            const bool staged_out = a.n_out > 0 && a.out_f32 != LSG_DTYPE_F32 && n0 + BN <= a.N &&
+                                    ((a.ldc | a.col_off) & 7) == 0;
+            if (staged_out) {
+                const bool f16 = a.out_f32 == LSG_DTYPE_F16;
+                const uint32_t buf = smem_u32(out_stage) + static_cast<uint32_t>(warp * 4096);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int hc = 0; hc < 2; ++hc) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + ab * BN + c + 32 * hc, r);
+#pragma unroll
+                        for (int h = 0; h < 16; ++h) {
+                            const float v0 = __uint_as_float(r[2 * h]) * (scaled ? alpha : 1.0f);
+                            const float v1 = __uint_as_float(r[2 * h + 1]) * (scaled ? alpha : 1.0f);
+                            if (f16) {
+                                const __half2 v = __floats2half2_rn(v0, v1);
+                                pk[16 * hc + h] = *reinterpret_cast<const uint32_t*>(&v);
+                            } else {
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
+                                pk[16 * hc + h] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                        }
+                    }
+                    __syncwarp();   // the previous 64 columns have been read out of the buffer
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(buf + lane * 128 + ((q ^ (lane & 7)) << 4)),
+                                     "r"(pk[4 * q]), "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                                     : "memory");
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3), q = lane & 7;
+                        uint4 v;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                     : "r"(buf + rr * 128 + ((q ^ (rr & 7)) << 4)));
+                        const int grow = mstart + warp * 32 + rr;
+                        if (grow < mend) {
+                            const size_t o = static_cast<size_t>(grow) * a.ldc + a.col_off + n0 + c + q * 8;
+                            for (int po = 0; po < a.n_out; ++po)
+                                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.C_ptrs[po]) + o) = v;
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t r[32];
@@ -212,44 +269,46 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
                         for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * alpha);
                     }
-                    const size_t o = static_cast<size_t>(row) * a.ldc + n0 + c;
+                    const size_t o = static_cast<size_t>(row) * a.ldc + a.col_off + n0 + c;
                     const int ncols = min(32, a.N - (n0 + c));
+                    const int n_out = a.n_out > 0 ? a.n_out : 1;
                     if (a.out_f32 == LSG_DTYPE_F32) {
-                        float* dst = static_cast<float*>(a.C) + o;
-                        if (ncols == 32 && (a.ldc & 3) == 0) {
+                        for (int po = 0; po < n_out; ++po) {
+                            float* dst = static_cast<float*>(a.n_out > 0 ? a.C_ptrs[po] : a.C) + o;
+                            if (ncols == 32 && ((a.ldc | a.col_off) & 3) == 0) {
 #pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                reinterpret_cast<uint4*>(dst)[q] =
-                                    make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
-                        } else {
-                            for (int q = 0; q < ncols; ++q) dst[q] = __uint_as_float(r[q]);
+                                for (int q = 0; q < 8; ++q)
+                                    reinterpret_cast<uint4*>(dst)[q] =
+                                        make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                            } else {
+                                for (int q = 0; q < ncols; ++q) dst[q] = __uint_as_float(r[q]);
+                            }
                         }
                     } else {
                         const bool f16 = a.out_f32 == LSG_DTYPE_F16;
-                        uint16_t* dst = static_cast<uint16_t*>(a.C) + o;
-                        if (ncols == 32 && (a.ldc & 7) == 0) {
+                        uint32_t pk[16];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                uint32_t p[4];
-#pragma unroll
-                                for (int h = 0; h < 4; ++h) {
-                                    const float v0 = __uint_as_float(r[8 * q + 2 * h]);
-                                    const float v1 = __uint_as_float(r[8 * q + 2 * h + 1]);
-                                    if (f16) {
-                                        const __half2 v = __floats2half2_rn(v0, v1);
-                                        p[h] = *reinterpret_cast<const uint32_t*>(&v);
-                                    } else {
-                                        const __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
-                                        p[h] = *reinterpret_cast<const uint32_t*>(&v);
-                                    }
-                                }
-                                reinterpret_cast<uint4*>(dst)[q] = make_uint4(p[0], p[1], p[2], p[3]);
+                        for (int h = 0; h < 16; ++h) {
+                            const float v0 = __uint_as_float(r[2 * h]);
+                            const float v1 = __uint_as_float(r[2 * h + 1]);
+                            if (f16) {
+                                const __half2 v = __floats2half2_rn(v0, v1);
+                                pk[h] = *reinterpret_cast<const uint32_t*>(&v);
+                            } else {
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(v0, v1);
+                                pk[h] = *reinterpret_cast<const uint32_t*>(&v);
                             }
-                        } else {
-                            for (int q = 0; q < ncols; ++q) {
-                                const float v = __uint_as_float(r[q]);
-                                dst[q] = f16 ? __half_as_ushort(__float2half_rn(v))
-                                             : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+                        }
+                        for (int po = 0; po < n_out; ++po) {
+                            uint16_t* dst = static_cast<uint16_t*>(a.n_out > 0 ? a.C_ptrs[po] : a.C) + o;
+                            if (ncols == 32 && ((a.ldc | a.col_off) & 7) == 0) {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    reinterpret_cast<uint4*>(dst)[q] =
+                                        make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                            } else {
+                                for (int q = 0; q < ncols; ++q)
+                                    dst[q] = static_cast<uint16_t>((q & 1) ? (pk[q >> 1] >> 16) : (pk[q >> 1] & 0xFFFFu));
                             }
                         }
                     }
@@ -418,13 +477,14 @@ size_t mmq_scratch_bytes(long long rows, int K, int E, int N) {
 
 // Dense: C[M,N] = x16 . w16^T.
 int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
-              size_t ws_bytes, cudaStream_t s) {
+              size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs) {
     if (M == 0 || N == 0) return LSG_OK;
     // Decoding inside the GEMM repeats the decode once per 256-token tile; past a few tiles
     // one expansion pass plus the plain fp16 GEMM is cheaper (measured cross-over near
     // M = 4096 for 14336 x 4096 Q4_K), unless every type is forced through the fused kernel.
     if (tc_fused_available(type) && (M <= 2048 || tc_fused_forced()))
-        return tc_fused_dense(type, M, N, K, A, W, C, N, out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16, ws, ws_bytes, s);
+        return tc_fused_dense(type, M, N, K, A, W, C, outs ? outs->ldc : N, out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16,
+                              ws, ws_bytes, s, outs);
     if (K % 8 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_mmq: K must be a multiple of 8");
     const size_t need = mmq_scratch_bytes(M, K, 1, N);
     if (!ws || ws_bytes < need)
@@ -445,6 +505,9 @@ int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void*
     TcArgs a = {};
     a.alpha_host = 1.0f;
     a.C = C; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
+    if (outs) {
+        a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off; a.ldc = outs->ldc;
+    }
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = (M + BM - 1) / BM;
     a.M = M;
@@ -544,4 +607,17 @@ extern "C" int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace
     if (!p->A || !p->B || !p->C) return fail(LSG_ERR_INVALID, "gguf_gemm_bf16: null pointer");
     return tc_fused_dense_bf16(p->type, p->M, p->N, p->K, p->A, p->B, p->C, p->N, p->out_dtype, workspace,
                                workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lsg_gguf_mmq_gather(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
+                                   int col_offset, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_gemm_params("gguf_mmq_gather", p);
+    if (rc != LSG_OK) return rc;
+    if (p->M == 0 || p->N == 0) return LSG_OK;
+    if (!p->A || !p->B || !C_ptrs) return fail(LSG_ERR_INVALID, "gguf_mmq_gather: null pointer");
+    if (n_out < 1 || n_out > 64 || col_offset < 0 || ldc < col_offset + p->N)
+        return fail(LSG_ERR_INVALID, "gguf_mmq_gather: need 1 <= n_out <= 64 and col_offset + N <= ldc");
+    MmqOutputs outs = {C_ptrs, n_out, ldc, col_offset};
+    return mmq_dense(p->type, p->M, p->N, p->K, p->A, p->B, nullptr, p->out_dtype == LSG_DTYPE_F32, workspace,
+                     workspace_bytes, static_cast<cudaStream_t>(stream), &outs);
 }

@@ -197,6 +197,34 @@ def column_slab(rank, world, N, align=128):
     return rank * per, (rank + 1) * per
 
 
+class ColumnSplitPeer:
+    """Column-split prefill GEMM with the all-gather fused into the GEMM's epilogue: every rank
+    computes its slab of output columns and stores each tile into the full [M, N] output of
+    every rank (peer-memory stores over NVLink, overlapped with the tensor-core work on the
+    following tiles); one barrier afterwards and every rank holds the whole product.  The
+    outputs are torch symmetric-memory allocations."""
+
+    def __init__(self, M, N, dtype=torch.bfloat16, group=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.M, self.N = M, N
+        self.out = symm.empty((M, N), dtype=dtype, device=dev)
+        self._h = symm.rendezvous(self.out, group)
+        self.ptrs = torch.tensor([int(p) for p in self._h.buffer_ptrs], dtype=torch.int64, device=dev)
+
+    def gemm(self, A, slab, type, K):
+        """A [M, K] bf16 (replicated), slab = this rank's packed rows [N / world, ...] -> the
+        full [M, N] product on every rank (the returned tensor is reused by the next call)."""
+        from . import ops
+        n0, n1 = column_slab(self.rank, self.world, self.N)
+        self._h.barrier(0)   # every rank is done reading the previous product
+        ops.gguf_mmq_gather(A, slab, type, n1 - n0, K, self.ptrs, self.N, n0, out_dtype=self.out.dtype)
+        self._h.barrier(0)   # every slab has landed everywhere
+        return self.out
+
+
 def column_split_gather(local_out, group=None):
     """local_out [M, N/G] of every rank -> [M, N] on every rank (one all-gather)."""
     world = dist.get_world_size(group)

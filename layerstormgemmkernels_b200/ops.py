@@ -340,6 +340,23 @@ def gguf_mmq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     return C
 
 
+def gguf_mmq_gather(A, B_slab, type, n_local, K, out_ptrs, ldc, col_offset, out_dtype=torch.bfloat16):
+    """gguf_mmq on a column slab of the weight, every output tile stored into each matrix of
+    `out_ptrs` (CUDA int64 tensor of device pointers to [M, ldc] matrices of `out_dtype`, this
+    GPU's and its peers') at column offset `col_offset`."""
+    _require(A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous(),
+             "gguf_mmq_gather: A must be contiguous BF16 [M, K] on CUDA")
+    _require(out_ptrs.is_cuda and out_ptrs.dtype == torch.int64, "gguf_mmq_gather: out_ptrs must be int64 on CUDA")
+    M = A.size(0)
+    ws_bytes = _lib.lsg_gguf_mmq_workspace_bytes(M, int(n_local), int(K))
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    p = capi.GgufMmvqParams(M=M, N=int(n_local), K=int(K), A=A.data_ptr(), B=B_slab.data_ptr(), C=None,
+                            type=int(type),
+                            out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+    capi.check(_lib.lsg_gguf_mmq_gather(ctypes.byref(p), _ptr(out_ptrs), out_ptrs.numel(), int(ldc), int(col_offset),
+                                        _ptr(ws), ws_bytes, _stream()))
+
+
 def gguf_gemm_bf16(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     """bf16 A[M,K] @ dequant(B)^T -> [M,N] on the tensor cores with unquantized activations
     (the fast sibling of gguf_dequant_gemm)."""

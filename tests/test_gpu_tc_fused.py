@@ -249,3 +249,20 @@ def test_q4k_legacy_operators(ops):
         ops.q4k_dequant_gemm(A[:, :1000].contiguous(), Wd)          # K not a multiple of 256
     with pytest.raises(RuntimeError):
         ops.q4k_cutlass_gemm(A, Wd[:, :100].contiguous())            # row bytes mismatch
+
+
+@pytest.mark.parametrize("M", [5, 300, 2100])      # split-K, fused, and prepared-operand routes
+def test_mmq_gather_stores_every_tile_into_every_output(ops, M):
+    """GEMM fused with the all-gather of a column-split weight: the slab's columns land at
+    their offset in each output matrix (peers emulated by local buffers), nothing else is
+    touched, and the values are those of gguf_mmq."""
+    N_total, n_local, K, col0 = 640, 256, 512, 128
+    A, W, Wd = make_case("Q4_K", M, n_local, K, seed=M)
+    ref = ops.gguf_mmq(A, Wd, T["Q4_K"], n_local, K)
+    outs = [torch.full((M, N_total), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    ptrs = torch.tensor([o.data_ptr() for o in outs], dtype=torch.int64, device="cuda")
+    ops.gguf_mmq_gather(A, Wd, T["Q4_K"], n_local, K, ptrs, N_total, col0)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o[:, col0:col0 + n_local], ref)
+        assert bool((o[:, :col0] == 7.0).all()) and bool((o[:, col0 + n_local:] == 7.0).all())
