@@ -26,3 +26,20 @@ def test_peer_exchange_equals_nccl_exchange_on_two_gpus():
     assert len(lines) == 2
     for ln in lines:
         assert "equal=True" in ln and "overflow=False" in ln and "status=0" in ln, ln
+
+
+@pytest.mark.timeout(300)
+def test_column_split_gemm_with_fused_gather_on_two_gpus():
+    """GEMM + all-gather in one kernel: the whole GEMM computed on one GPU, up to summation order."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29538", os.path.join(HERE, "colsplit_peer_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=280)
+    lines = [ln for ln in r.stdout.splitlines() if ln.startswith("COLSPLIT")]
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert len(lines) == 2
+    for ln in lines:
+        assert "equal=True" in ln and "status=0" in ln, ln
