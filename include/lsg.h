@@ -141,6 +141,29 @@ LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, vo
 #define LSG_NOALLOC_MAX_Q8_1_BYTES 147456
 LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
 
+/* Same operation with the activations and the result in HOST memory: p->A and p->C
+ * are host pointers (p->B stays on the device).  The call copies A into `workspace`,
+ * runs the mat-vec there and copies C back, all enqueued on `stream`; it does not wait
+ * for the stream.  Page-locked, 16-byte aligned host buffers are read and written by the
+ * kernels themselves through their device alias (no DMA copy, nothing blocks the calling
+ * thread); pageable ones go through cudaMemcpyAsync and follow its rules.  The
+ * caller must not touch A or C until the stream has passed this call.  Workspace:
+ * lsg_gguf_mmvq_host_workspace_bytes(M, N, K).  The reference has no host-memory
+ * variant; this is the entry a host-side integration binds when its tensors live in
+ * host memory (one call instead of copy, launch, copy). */
+LSG_API size_t lsg_gguf_mmvq_host_workspace_bytes(int M, int N, int K);
+LSG_API int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* n projections in one call, executed in order, each as lsg_gguf_mmvq_host would.
+ * Entries naming the same A, M and K as an earlier entry reuse its Q8_1 image (the q, k
+ * and v projections of one hidden state quantize it once).  All activations must be in
+ * place when the call is made and no C may overlap an A of the batch.  n <= 64.
+ * Workspace: lsg_gguf_mmvq_host_batch_workspace_bytes(p, n), 256-byte aligned. */
+LSG_API size_t lsg_gguf_mmvq_host_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
+LSG_API int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* Launch geometry of the mmvq kernels, process-wide: consumer warps per CTA
  * (1..15), CTAs of one launch per SM, KiB per pipeline stage, and how many CTAs
  * (of this and of neighbouring launches in the stream) split an SM's shared

@@ -162,6 +162,172 @@ extern "C" int lsg_gguf_mmvq(const lsg_gguf_mmvq_params* p, void* workspace,
                      p->out_dtype == LSG_DTYPE_F32, s, true);
 }
 
+namespace lsg {
+namespace {
+
+inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Device-side alias of a page-locked host buffer, or null when the memory is pageable
+// (or not 16-byte aligned, which the vector accesses below need).
+void* mapped_alias(const void* host) {
+    static const bool off = [] {
+        const char* e = getenv("LSG_MMVQ_HOST_DIRECT");
+        return e && atoi(e) == 0;
+    }();
+    if (off || (reinterpret_cast<uintptr_t>(host) & 15)) return nullptr;
+    cudaPointerAttributes at = {};
+    if (cudaPointerGetAttributes(&at, host) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return at.type == cudaMemoryTypeHost ? at.devicePointer : nullptr;
+}
+
+// Result rows from device scratch to the mapped host buffer, 16 bytes per store so that
+// the writes cross the bus as full segments.
+__global__ void __launch_bounds__(256)
+store_to_host_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long bytes) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long n16 = bytes >> 4;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride)
+        reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    if (blockIdx.x == 0 && threadIdx.x < (bytes & 15))
+        dst[(n16 << 4) + threadIdx.x] = src[(n16 << 4) + threadIdx.x];
+}
+
+}  // namespace
+}  // namespace lsg
+
+namespace lsg {
+namespace {
+
+constexpr int kMaxHostBatch = 64;
+
+struct HostSlot {
+    int first;            // earliest entry of the batch with the same activations
+    size_t a_off, q_off;  // staged activations (pageable source) and their Q8_1 image
+    size_t c_off;         // result rows when they are not written to the host directly
+};
+
+// Workspace layout of a batch; entries with the same A, M and K share one Q8_1 image.
+size_t plan_host_batch(const lsg_gguf_mmvq_params* p, int n, HostSlot* slot) {
+    size_t off = 0;
+    for (int i = 0; i < n; ++i) {
+        HostSlot h = {};
+        h.first = i;
+        for (int j = 0; j < i; ++j)
+            if (p[j].A == p[i].A && p[j].M == p[i].M && p[j].K == p[i].K) {
+                h.first = slot ? slot[j].first : j;
+                break;
+            }
+        const size_t M = p[i].M > 0 ? p[i].M : 0, N = p[i].N > 0 ? p[i].N : 0, K = p[i].K > 0 ? p[i].K : 0;
+        if (h.first == i) {
+            h.a_off = off;
+            off += align256(M * K * 2);
+            h.q_off = off;
+            off += align256(M * (K / 32) * kQ8_1Bytes);
+        } else if (slot) {
+            h.a_off = slot[h.first].a_off;
+            h.q_off = slot[h.first].q_off;
+        }
+        h.c_off = off;
+        off += align256(M * N * 4);
+        if (slot) slot[i] = h;
+    }
+    return off;
+}
+
+}  // namespace
+}  // namespace lsg
+
+extern "C" size_t lsg_gguf_mmvq_host_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n) {
+    if (!p || n <= 0 || n > kMaxHostBatch) return 0;
+    return plan_host_batch(p, n, nullptr);
+}
+
+extern "C" size_t lsg_gguf_mmvq_host_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    lsg_gguf_mmvq_params p = {};
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    return plan_host_batch(&p, 1, nullptr);
+}
+
+// Page-locked buffers are reached from the kernels themselves: the quantizer reads the
+// activations through their device alias and the mat-vec (or, above four batch rows, a
+// small kernel with 16-byte stores) writes the result rows, so that a projection is two
+// dependent kernels on one engine.  Copies by the DMA engines (the route for pageable
+// memory) cost an engine switch before and after the mat-vec, several times the
+// mat-vec's own duration at batch 1.
+extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+    if (n == 0) return LSG_OK;
+    if (!p || n < 0) return fail(LSG_ERR_INVALID, "gguf_mmvq_host: null params");
+    if (n > kMaxHostBatch)
+        return fail(LSG_ERR_INVALID, "gguf_mmvq_host: at most %d projections per batch, got %d", kMaxHostBatch, n);
+    for (int i = 0; i < n; ++i) {
+        const int rc = check_gemm_params("gguf_mmvq_host", p + i);
+        if (rc != LSG_OK) return rc;
+        if (p[i].M > 0 && p[i].N > 0 && (!p[i].A || !p[i].C))
+            return fail(LSG_ERR_INVALID, "gguf_mmvq_host: null host pointer (entry %d)", i);
+        if (p[i].M > 0 && p[i].N > 0 && p[i].K == 0)
+            return fail(LSG_ERR_INVALID, "gguf_mmvq: K must be positive");
+    }
+    HostSlot slot[kMaxHostBatch];
+    const size_t need = plan_host_batch(p, n, slot);
+    if (need == 0) return LSG_OK;
+    if (!workspace || workspace_bytes < need)
+        return fail(LSG_ERR_WORKSPACE, "gguf_mmvq_host: workspace too small (have %zu, need %zu)",
+                    workspace ? workspace_bytes : size_t(0), need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq_host: workspace must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    for (int i = 0; i < n; ++i) {
+        const lsg_gguf_mmvq_params& e = p[i];
+        if (e.M == 0 || e.N == 0) continue;
+        const int out_f32 = e.out_dtype == LSG_DTYPE_F32;
+        const size_t a_bytes = static_cast<size_t>(e.M) * e.K * 2;
+        const size_t c_bytes = static_cast<size_t>(e.M) * e.N * (out_f32 ? 4 : 2);
+        uint8_t* q_dev = base + slot[i].q_off;
+        int rc;
+        if (slot[i].first == i) {
+            const void* a_src = mapped_alias(e.A);
+            if (!a_src) {
+                LSG_CUDA_TRY(cudaMemcpyAsync(base + slot[i].a_off, e.A, a_bytes, cudaMemcpyHostToDevice, s));
+                a_src = base + slot[i].a_off;
+            }
+            rc = quantize_q8_1(a_src, q_dev, e.M, e.K, s, true);
+            if (rc != LSG_OK) return rc;
+        }
+        void* c_map = mapped_alias(e.C);
+        const bool direct = c_map && e.M <= 4;
+        uint8_t* c_dev = base + slot[i].c_off;
+        rc = mmvq_q8_1(e.type, e.M, e.N, e.K, e.B, q_dev, direct ? c_map : c_dev, e.N, out_f32, s, true);
+        if (rc != LSG_OK) return rc;
+        if (direct) continue;
+        if (c_map) {
+            const long long n16 = static_cast<long long>(c_bytes >> 4);
+            const unsigned grid = static_cast<unsigned>(n16 < 256 ? 1 : (n16 / 256 > 296 ? 296 : n16 / 256));
+            LSG_CUDA_TRY(launch_kernel(store_to_host_kernel, dim3(grid), dim3(256), 0, s, true,
+                                       static_cast<const uint8_t*>(c_dev), static_cast<uint8_t*>(c_map),
+                                       static_cast<long long>(c_bytes)));
+        } else {
+            LSG_CUDA_TRY(cudaMemcpyAsync(e.C, c_dev, c_bytes, cudaMemcpyDeviceToHost, s));
+        }
+    }
+    return LSG_OK;
+}
+
+extern "C" int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+    if (!p) return fail(LSG_ERR_INVALID, "gguf_mmvq_host: null params");
+    return lsg_gguf_mmvq_host_batch(p, 1, workspace, workspace_bytes, stream);
+}
+
 extern "C" int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_kib,
                                    int smem_share, int skip_math) {
     MmvqTune& t = tuning();

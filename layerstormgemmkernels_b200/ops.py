@@ -70,6 +70,107 @@ def gguf_mmvq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     return C
 
 
+def gguf_mmvq_host(A_host, B_packed, type, N, K, out=None, workspace=None):
+    """The same mat-vec with the activations and the result in host memory.
+
+    A_host: contiguous bf16 [M, K] CPU tensor (page-locked for an asynchronous call);
+    B_packed: packed weight on the device; out: optional bf16 or f32 [M, N] CPU tensor
+    (page-locked) to receive the result; workspace: optional uint8 device tensor of at
+    least lsg_gguf_mmvq_host_workspace_bytes(M, N, K) bytes.  One C call enqueues the
+    copy in, the kernels and the copy out on the current stream and returns without
+    waiting: synchronize the stream before reading `out`.  No counterpart in the
+    reference, whose operators take device tensors only.
+    """
+    _require(not A_host.is_cuda and A_host.dtype == torch.bfloat16 and A_host.dim() == 2
+             and A_host.is_contiguous(), "gguf_mmvq_host: A must be a contiguous BF16 [M, K] CPU tensor")
+    _require(A_host.size(1) == K, "gguf_mmvq_host: A.size(1) != K")
+    _require(B_packed.is_cuda and B_packed.dtype == torch.uint8 and B_packed.is_contiguous(),
+             "gguf_mmvq_host: B_packed must be contiguous uint8 on CUDA")
+    M = A_host.size(0)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    _require(not out.is_cuda and out.is_contiguous() and tuple(out.shape) == (M, N)
+             and out.dtype in (torch.bfloat16, torch.float32),
+             "gguf_mmvq_host: out must be a contiguous bf16 or f32 [M, N] CPU tensor")
+    need = _lib.lsg_gguf_mmvq_host_workspace_bytes(M, int(N), int(K))
+    if workspace is None:
+        workspace = torch.empty((max(need, 1),), dtype=torch.uint8, device=B_packed.device)
+    _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.numel() >= need,
+             "gguf_mmvq_host: workspace too small")
+    p = capi.GgufMmvqParams(M=M, N=int(N), K=int(K), A=A_host.data_ptr(), B=B_packed.data_ptr(),
+                            C=out.data_ptr(), type=int(type),
+                            out_dtype=capi.DTYPE_F32 if out.dtype == torch.float32 else capi.DTYPE_BF16)
+    capi.check(_lib.lsg_gguf_mmvq_host(ctypes.byref(p), _ptr(workspace), workspace.numel(), _stream()))
+    return out
+
+
+class HostMmvqBatch:
+    """Several projections on host-memory activations and results, enqueued by one C call
+    (lsg_gguf_mmvq_host_batch).
+
+    items: sequence of (A_host, B_packed, type, N, K, out_host) with the argument meaning of
+    gguf_mmvq_host.  The argument block and the device workspace are built once, here; run()
+    enqueues the whole batch on the current stream and returns without waiting.  Items that
+    share one A tensor (q, k and v of a hidden state) quantize it once.  The tensors are
+    held by the object, and every run() reads the activations' current contents.
+    """
+
+    def __init__(self, items, workspace=None):
+        items = list(items)
+        _require(0 < len(items) <= 64, "HostMmvqBatch: 1..64 projections")
+        self._keep = items
+        self.outs = []
+        arr = (capi.GgufMmvqParams * len(items))()
+        dev = items[0][1].device
+        for i, (A, B, type, N, K, out) in enumerate(items):
+            _require(not A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous()
+                     and A.size(1) == K, "HostMmvqBatch: A must be a contiguous BF16 [M, K] CPU tensor")
+            _require(B.is_cuda and B.dtype == torch.uint8 and B.is_contiguous() and B.device == dev,
+                     "HostMmvqBatch: B_packed must be contiguous uint8 on one CUDA device")
+            M = A.size(0)
+            if out is None:
+                out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+            _require(not out.is_cuda and out.is_contiguous() and tuple(out.shape) == (M, N)
+                     and out.dtype in (torch.bfloat16, torch.float32),
+                     "HostMmvqBatch: out must be a contiguous bf16 or f32 [M, N] CPU tensor")
+            self.outs.append(out)
+            arr[i] = capi.GgufMmvqParams(
+                M=M, N=int(N), K=int(K), A=A.data_ptr(), B=B.data_ptr(), C=out.data_ptr(), type=int(type),
+                out_dtype=capi.DTYPE_F32 if out.dtype == torch.float32 else capi.DTYPE_BF16)
+        self._arr = arr
+        self._n = len(items)
+        need = _lib.lsg_gguf_mmvq_host_batch_workspace_bytes(arr, self._n)
+        if workspace is None:
+            workspace = torch.empty((max(need, 1),), dtype=torch.uint8, device=dev)
+        _require(workspace.is_cuda and workspace.dtype == torch.uint8 and workspace.numel() >= need,
+                 "HostMmvqBatch: workspace too small")
+        self.workspace = workspace
+        self._ws = ctypes.c_void_p(workspace.data_ptr())
+        self._ws_bytes = workspace.numel()
+
+    def _enqueue(self):
+        capi.check(_lib.lsg_gguf_mmvq_host_batch(self._arr, self._n, self._ws, self._ws_bytes, _stream()))
+
+    def capture(self):
+        """Record the batch into a CUDA graph; run() then replays it (one launch from the
+        host).  Needs page-locked activations and results: their kernels read and write host
+        memory directly, so a replay sees the activations' current contents."""
+        self._enqueue()                      # first use outside capture
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._enqueue()
+        self._graph = g
+        return self
+
+    def run(self):
+        if getattr(self, "_graph", None) is not None:
+            self._graph.replay()
+        else:
+            self._enqueue()
+        return self.outs
+
+
 def gguf_mmvq_q8_1(xq, B_packed, type, N, K, out_dtype=torch.bfloat16):
     """Same mat-vec on pre-quantized activations (uint8 [M, K/32, 36])."""
     _require(xq.is_cuda and xq.dtype == torch.uint8 and xq.is_contiguous(),

@@ -143,6 +143,53 @@ def test_mmvq_bit_deterministic(ops):
         assert torch.equal(ref, ops.gguf_mmvq(A, W, T["Q8_0"], N, K))
 
 
+@pytest.mark.parametrize("name,M,pinned", [("Q4_K", 1, True), ("Q6_K", 3, True), ("Q8_0", 2, False),
+                                            ("Q4_K", 12, True)])
+def test_mmvq_host_buffers_equal_device_call(ops, name, M, pinned):
+    """lsg_gguf_mmvq_host (activations and result in host memory) returns the bits of the
+    device-memory call, for page-locked and pageable buffers, bf16 and f32 results."""
+    N, K = 768, 2048
+    A = (torch.randn(M, K, generator=torch.Generator().manual_seed(5)) * 0.4).to(torch.bfloat16)
+    W = torch.from_numpy(Q.random_gguf_weight(name, N, K, seed=13)).cuda()
+    for dt in (torch.bfloat16, torch.float32):
+        ref = ops.gguf_mmvq(A.cuda(), W, T[name], N, K, out_dtype=dt).cpu()
+        a = A.pin_memory() if pinned else A
+        out = torch.zeros((M, N), dtype=dt)
+        if pinned:
+            out = out.pin_memory()
+        got = ops.gguf_mmvq_host(a, W, T[name], N, K, out=out)
+        torch.cuda.synchronize()
+        assert got is out and torch.equal(got, ref)
+    with pytest.raises(RuntimeError):
+        ops.gguf_mmvq_host(A, W, T[name], N, K, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+
+
+def test_mmvq_host_batch_shares_quantized_activations(ops):
+    """lsg_gguf_mmvq_host_batch: seven projections of a decoder layer's shapes (scaled down),
+    three distinct activations, equal to the per-projection device calls bit for bit; a second
+    run() picks up new activation contents."""
+    H, I, KV = 1024, 2560, 256
+    shapes = [(H, H), (KV, H), (KV, H), (H, H), (I, H), (I, H), (H, I)]
+    g = torch.Generator().manual_seed(21)
+    xs = [(torch.randn(2, K, generator=g) * 0.4).to(torch.bfloat16).pin_memory() for K in (H, H, I)]
+    which = [0, 0, 0, 1, 0, 0, 2]
+    Ws = [torch.from_numpy(Q.random_gguf_weight("Q4_K", N, K, seed=30 + i)).cuda()
+          for i, (N, K) in enumerate(shapes)]
+    items = [(xs[w], W, T["Q4_K"], N, K, None) for w, W, (N, K) in zip(which, Ws, shapes)]
+    batch = ops.HostMmvqBatch(items)
+    for rnd in range(4):
+        if rnd == 2:
+            batch.capture()     # the last two rounds replay a CUDA graph of the batch
+        outs = batch.run()
+        torch.cuda.synchronize()
+        for w, W, (N, K), out in zip(which, Ws, shapes, outs):
+            assert torch.equal(out, ops.gguf_mmvq(xs[w].cuda(), W, T["Q4_K"], N, K).cpu())
+        for x in xs:
+            x.mul_(-0.5)
+    with pytest.raises(RuntimeError):
+        ops.HostMmvqBatch(items, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+
+
 def test_mmvq_graph_capture(ops):
     """tests/test_gguf_mmvq.py:106-134: capture + replay equals eager."""
     N, K = 512, 1024
