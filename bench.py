@@ -188,7 +188,7 @@ def workload_config(args):
             "type": args.type, "batch": args.batch,
             "shapes": {n: [N, K] for n, N, K in LAYER},
             "l2_defeat": "steps rotate over layer copies totalling more than the 126 MB L2",
-            "launch": "one CUDA graph per layer copy (7 quantizer + 7 mat-vec kernels)",
+            "launch": "one CUDA graph per layer copy of one lsg_gguf_mmvq_batch call: (q,k,v), o, (gate,up), down as four mat-vec launches, activations quantized inside them or by a quantizer launch",
             "parallelism": "replicas only"}
 
 
@@ -252,32 +252,52 @@ def main():
     copies = max(2, int(2.5 * L2_BYTES // layer_bytes) + 1)
     layers = [[torch.from_numpy(w).to(dev) for w in host_w] for _ in range(copies)]
     g = torch.Generator().manual_seed(0)
-    x_host = {K: torch.randn(M, K, generator=g).to(torch.bfloat16).pin_memory() for K in (4096, 14336)}
-    x_dev = {K: v.to(dev) for K, v in x_host.items()}
+    # four distinct inputs, as in a decoder layer: the attention input (q, k, v), the
+    # attention output (o), the MLP input (gate, up) and the gated product (down)
+    group = {"q": 0, "k": 0, "v": 0, "o": 1, "gate": 2, "up": 2, "down": 3}
+    xin = {}
+    for name, _, K in LAYER:
+        if group[name] not in xin:
+            xin[group[name]] = torch.randn(M, K, generator=g).to(torch.bfloat16).pin_memory()
+    x_dev = {k: v.to(dev) for k, v in xin.items()}
     outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _, N, _ in LAYER]
-    ws = torch.empty((capi.lib.lsg_gguf_mmvq_workspace_bytes(M, 14336),), dtype=torch.uint8, device=dev)
     abytes = algorithmic_bytes(args.type, M)
-    # one mat-vec launch per projection, plus a Q8_1 quantizer launch where the activation is
-    # too large to be quantized inside the mat-vec kernel (the library's rule: M * K > 16384)
-    launches_per_step = sum(1 if M * K <= 16384 else 2 for _, _, K in LAYER)
 
-    def layer_step(weights):
+    def layer_params(weights):
+        arr = (capi.GgufMmvqParams * len(LAYER))()
+        for i, (W, out, (name, N, K)) in enumerate(zip(weights, outs, LAYER)):
+            arr[i] = capi.GgufMmvqParams(M=M, N=N, K=K, A=x_dev[group[name]].data_ptr(), B=W.data_ptr(),
+                                         C=out.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+        return arr
+
+    layer_args = [layer_params(w) for w in layers]
+    ws = torch.empty((max(capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(layer_args[0], len(LAYER)), 256),),
+                     dtype=torch.uint8, device=dev)
+    # lsg_gguf_mmvq_batch joins consecutive projections of one input into one launch:
+    # (q, k, v), o, (gate, up), down -> four mat-vec launches, plus a Q8_1 quantizer launch
+    # where the activation is too large to be quantized inside the mat-vec kernel
+    # (the library's rule: M * K > 16384)
+    joined = []
+    for name, _, K in LAYER:
+        if not joined or joined[-1][0] != group[name] or joined[-1][2] >= 4:
+            joined.append([group[name], K, 0])
+        joined[-1][2] += 1
+    launches_per_step = sum(1 if M * K <= 16384 else 2 for _, K, _ in joined)
+
+    def layer_step(arr):
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        for W, out, (_, N, K) in zip(weights, outs, LAYER):
-            p = capi.GgufMmvqParams(M=M, N=N, K=K, A=x_dev[K].data_ptr(), B=W.data_ptr(),
-                                    C=out.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-            capi.check(capi.lib.lsg_gguf_mmvq(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()),
-                                              ws.numel(), st))
+        capi.check(capi.lib.lsg_gguf_mmvq_batch(arr, len(LAYER), ctypes.c_void_p(ws.data_ptr()),
+                                                ws.numel(), st))
 
     # ---- device-resident throughput: one CUDA graph per layer copy ------------------
-    for w in layers:
-        layer_step(w)
+    for arr in layer_args:
+        layer_step(arr)
     torch.cuda.synchronize()
     graphs = []
-    for w in layers:
+    for arr in layer_args:
         gr = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gr):
-            layer_step(w)
+            layer_step(arr)
         graphs.append(gr)
     for i in range(args.warmup):
         graphs[i % copies].replay()
@@ -310,13 +330,6 @@ def main():
 
     # one prepared batch per layer copy: pointers only; every run() reads the activations
     # from page-locked host memory and writes the results there
-    # four distinct inputs, as in a decoder layer: the attention input (q, k, v), the
-    # attention output (o), the MLP input (gate, up) and the gated product (down)
-    group = {"q": 0, "k": 0, "v": 0, "o": 1, "gate": 2, "up": 2, "down": 3}
-    xin = {}
-    for name, _, K in LAYER:
-        if group[name] not in xin:
-            xin[group[name]] = torch.randn(M, K, generator=g).to(torch.bfloat16).pin_memory()
     batches = [ops.HostMmvqBatch([(xin[group[name]], W, t, N, K, res)
                                   for W, res, (name, N, K) in zip(weights, res_host, LAYER)])
                for weights in layers]
@@ -355,7 +368,7 @@ def main():
     peak, peak_kind = load_peaks()
     # dominant kernel = the mat-vec; per launch: algorithmic bytes of one projection on
     # average, over the average launch duration (the quantizer launches are inside it).
-    n_gemv = len(LAYER)
+    n_gemv = len(joined)
     achieved = (abytes / n_gemv) / (ms_per_step * 1e-3 / n_gemv) / 1e9
     line = {
         "metric": f"{args.type.lower()}_mmvq_gbps", "value": value, "unit": "GB/s",

@@ -141,6 +141,18 @@ LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, vo
 #define LSG_NOALLOC_MAX_Q8_1_BYTES 147456
 LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
 
+/* n projections in one call, executed in order, each as lsg_gguf_mmvq would.
+ * Consecutive entries with the same A, M, K, type and out_dtype (q, k and v of one
+ * hidden state; gate and up of one MLP input) run as ONE launch, up to four matrices
+ * per launch, their CTAs divided in proportion to the rows: one prologue, one
+ * activation image and one pipeline fill instead of several.  Results are the bits of
+ * the separate calls.  Workspace: lsg_gguf_mmvq_batch_workspace_bytes(p, n) (the
+ * largest Q8_1 image of the batch).  The reference launches one kernel per projection
+ * (launch_gguf_mmvq, csrc/sm120/gemm/gguf/gguf_mmvq.cu:130-152). */
+LSG_API size_t lsg_gguf_mmvq_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
+LSG_API int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
 /* Same operation with the activations and the result in HOST memory: p->A and p->C
  * are host pointers (p->B stays on the device).  The call copies A into `workspace`,
  * runs the mat-vec there and copies C back, all enqueued on `stream`; it does not wait
@@ -157,7 +169,8 @@ LSG_API int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace, s
 
 /* n projections in one call, executed in order, each as lsg_gguf_mmvq_host would.
  * Entries naming the same A, M and K as an earlier entry reuse its Q8_1 image (the q, k
- * and v projections of one hidden state quantize it once).  All activations must be in
+ * and v projections of one hidden state quantize it once), and consecutive ones share a
+ * launch as in lsg_gguf_mmvq_batch.  All activations must be in
  * place when the call is made and no C may overlap an A of the batch.  n <= 64.
  * Workspace: lsg_gguf_mmvq_host_batch_workspace_bytes(p, n), 256-byte aligned. */
 LSG_API size_t lsg_gguf_mmvq_host_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);

@@ -117,6 +117,54 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
     return LSG_OK;
 }
 
+// The same activations against n <= 4 weight matrices of one type and K, as one launch
+// per batch of rows.  Matrix j writes C[j], [M][N[j]] row-major.
+int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* const* C, const int* N,
+                     const void* xq, int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16) {
+    if (n < 1 || n > 1 + kMmvqMaxExtra) return fail(LSG_ERR_INVALID, "gguf_mmvq: 1..4 matrices per joined launch");
+    if (n == 1) return mmvq_q8_1(type, M, N[0], K, W[0], xq, C[0], N[0], out_f32, stream, pdl, A_bf16);
+    if (M == 0) return LSG_OK;
+    if (K == 0) return fail(LSG_ERR_INVALID, "gguf_mmvq: K must be positive");
+    if (!xq && !A_bf16) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
+    for (int j = 0; j < n; ++j) {
+        if (N[j] < 1) return fail(LSG_ERR_INVALID, "gguf_mmvq: joined matrices need N >= 1");
+        if (!W[j] || !C[j]) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
+        if (reinterpret_cast<uintptr_t>(W[j]) & 15)
+            return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq: packed weight must be 16-byte aligned");
+    }
+    if (!A_bf16 && (reinterpret_cast<uintptr_t>(xq) & 3))
+        return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq: Q8_1 buffer must be 4-byte aligned");
+    const int max_rows = dispatch_max_rows(type, K);
+    if (max_rows < 1)
+        return fail(LSG_ERR_UNSUPPORTED, "gguf_mmvq: K=%d too large for the shared-memory pipeline", K);
+    int batch = max_rows >= 8 ? (max_rows / 8) * 8 : max_rows;
+    if (batch > 32) batch = 32;
+    const size_t xq_row = static_cast<size_t>(K / 32) * kQ8_1Bytes;
+    const size_t c_elem = out_f32 ? 4 : 2;
+    for (int m0 = 0; m0 < M; m0 += batch) {
+        MmvqArgs a = {};
+        a.W = static_cast<const uint8_t*>(W[0]);
+        a.xq = xq ? static_cast<const uint8_t*>(xq) + static_cast<size_t>(m0) * xq_row : nullptr;
+        a.A = A_bf16 ? static_cast<const __nv_bfloat16*>(A_bf16) + static_cast<size_t>(m0) * K : nullptr;
+        a.C = static_cast<uint8_t*>(C[0]) + static_cast<size_t>(m0) * N[0] * c_elem;
+        a.status = device_status_word();
+        a.M = (M - m0) < batch ? (M - m0) : batch;
+        a.N = N[0];
+        a.K = K;
+        a.ldc = N[0];
+        a.out_f32 = out_f32;
+        a.n_extra = n - 1;
+        for (int j = 1; j < n; ++j) {
+            a.Wx[j - 1] = static_cast<const uint8_t*>(W[j]);
+            a.Cx[j - 1] = static_cast<uint8_t*>(C[j]) + static_cast<size_t>(m0) * N[j] * c_elem;
+            a.Nx[j - 1] = N[j];
+        }
+        const int rc = dispatch_launch(type, a, stream, pdl && m0 == 0);
+        if (rc != LSG_OK) return rc;
+    }
+    return LSG_OK;
+}
+
 bool fused_quant_ok(int M, int K, const void* A) {
     static const long long limit = [] {
         const char* e = getenv("LSG_MMVQ_FUSED_QUANT_MAX");
@@ -199,6 +247,79 @@ store_to_host_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
 
 }  // namespace
 }  // namespace lsg
+
+namespace lsg {
+namespace {
+
+// Entries [i, i + run) of a batch that can share one launch: same activations, type, K,
+// batch rows and output type, at most four, every N >= 1.
+int joinable_run(const lsg_gguf_mmvq_params* p, int i, int n) {
+    int run = 1;
+    if (p[i].M < 1 || p[i].N < 1) return 1;
+    while (i + run < n && run < 1 + kMmvqMaxExtra) {
+        const lsg_gguf_mmvq_params& a = p[i];
+        const lsg_gguf_mmvq_params& b = p[i + run];
+        if (b.A != a.A || b.M != a.M || b.K != a.K || b.type != a.type || b.out_dtype != a.out_dtype || b.N < 1)
+            break;
+        ++run;
+    }
+    return run;
+}
+
+}  // namespace
+}  // namespace lsg
+
+extern "C" size_t lsg_gguf_mmvq_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n) {
+    size_t need = 0;
+    for (int i = 0; p && i < n; ++i) {
+        const size_t w = lsg_gguf_mmvq_workspace_bytes(p[i].M, p[i].K);
+        need = w > need ? w : need;
+    }
+    return need;
+}
+
+extern "C" int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+    if (n == 0) return LSG_OK;
+    if (!p || n < 0) return fail(LSG_ERR_INVALID, "gguf_mmvq_batch: null params");
+    for (int i = 0; i < n; ++i) {
+        const int rc = check_gemm_params("gguf_mmvq_batch", p + i);
+        if (rc != LSG_OK) return rc;
+    }
+    const size_t need = lsg_gguf_mmvq_batch_workspace_bytes(p, n);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return fail(LSG_ERR_WORKSPACE, "gguf_mmvq_batch: workspace too small (have %zu, need %zu)",
+                    workspace ? workspace_bytes : size_t(0), need);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < n;) {
+        const int run = joinable_run(p, i, n);
+        const lsg_gguf_mmvq_params& e = p[i];
+        if (e.M == 0 || e.N == 0) {
+            i += run;
+            continue;
+        }
+        const void* W[1 + kMmvqMaxExtra];
+        void* C[1 + kMmvqMaxExtra];
+        int N[1 + kMmvqMaxExtra];
+        for (int j = 0; j < run; ++j) {
+            W[j] = p[i + j].B;
+            C[j] = p[i + j].C;
+            N[j] = p[i + j].N;
+        }
+        const int out_f32 = e.out_dtype == LSG_DTYPE_F32;
+        int rc;
+        if (fused_quant_ok(e.M, e.K, e.A)) {
+            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, nullptr, out_f32, s, true, e.A);
+        } else {
+            rc = quantize_q8_1(e.A, workspace, e.M, e.K, s, true);
+            if (rc != LSG_OK) return rc;
+            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, workspace, out_f32, s, true, nullptr);
+        }
+        if (rc != LSG_OK) return rc;
+        i += run;
+    }
+    return LSG_OK;
+}
 
 namespace lsg {
 namespace {
@@ -286,12 +407,15 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
         return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq_host: workspace must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* base = static_cast<uint8_t*>(workspace);
-    for (int i = 0; i < n; ++i) {
+    for (int i = 0; i < n;) {
         const lsg_gguf_mmvq_params& e = p[i];
-        if (e.M == 0 || e.N == 0) continue;
+        const int run = joinable_run(p, i, n);
+        if (e.M == 0 || e.N == 0) {
+            i += run;
+            continue;
+        }
         const int out_f32 = e.out_dtype == LSG_DTYPE_F32;
         const size_t a_bytes = static_cast<size_t>(e.M) * e.K * 2;
-        const size_t c_bytes = static_cast<size_t>(e.M) * e.N * (out_f32 ? 4 : 2);
         uint8_t* q_dev = base + slot[i].q_off;
         int rc;
         if (slot[i].first == i) {
@@ -303,21 +427,34 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
             rc = quantize_q8_1(a_src, q_dev, e.M, e.K, s, true);
             if (rc != LSG_OK) return rc;
         }
-        void* c_map = mapped_alias(e.C);
-        const bool direct = c_map && e.M <= 4;
-        uint8_t* c_dev = base + slot[i].c_off;
-        rc = mmvq_q8_1(e.type, e.M, e.N, e.K, e.B, q_dev, direct ? c_map : c_dev, e.N, out_f32, s, true);
-        if (rc != LSG_OK) return rc;
-        if (direct) continue;
-        if (c_map) {
-            const long long n16 = static_cast<long long>(c_bytes >> 4);
-            const unsigned grid = static_cast<unsigned>(n16 < 256 ? 1 : (n16 / 256 > 296 ? 296 : n16 / 256));
-            LSG_CUDA_TRY(launch_kernel(store_to_host_kernel, dim3(grid), dim3(256), 0, s, true,
-                                       static_cast<const uint8_t*>(c_dev), static_cast<uint8_t*>(c_map),
-                                       static_cast<long long>(c_bytes)));
-        } else {
-            LSG_CUDA_TRY(cudaMemcpyAsync(e.C, c_dev, c_bytes, cudaMemcpyDeviceToHost, s));
+        // The projections of this input that can share a launch; each writes either the
+        // host buffer's alias or its rows of the workspace.
+        const void* W[1 + kMmvqMaxExtra];
+        void* C[1 + kMmvqMaxExtra];
+        void* c_map[1 + kMmvqMaxExtra];
+        int N[1 + kMmvqMaxExtra];
+        for (int j = 0; j < run; ++j) {
+            c_map[j] = mapped_alias(p[i + j].C);
+            W[j] = p[i + j].B;
+            N[j] = p[i + j].N;
+            C[j] = (c_map[j] && e.M <= 4) ? c_map[j] : static_cast<void*>(base + slot[i + j].c_off);
         }
+        rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, q_dev, out_f32, s, true, nullptr);
+        if (rc != LSG_OK) return rc;
+        for (int j = 0; j < run; ++j) {
+            if (C[j] == c_map[j]) continue;
+            const size_t c_bytes = static_cast<size_t>(e.M) * N[j] * (out_f32 ? 4 : 2);
+            if (c_map[j]) {
+                const long long n16 = static_cast<long long>(c_bytes >> 4);
+                const unsigned grid = static_cast<unsigned>(n16 < 256 ? 1 : (n16 / 256 > 296 ? 296 : n16 / 256));
+                LSG_CUDA_TRY(launch_kernel(store_to_host_kernel, dim3(grid), dim3(256), 0, s, true,
+                                           static_cast<const uint8_t*>(C[j]), static_cast<uint8_t*>(c_map[j]),
+                                           static_cast<long long>(c_bytes)));
+            } else {
+                LSG_CUDA_TRY(cudaMemcpyAsync(p[i + j].C, C[j], c_bytes, cudaMemcpyDeviceToHost, s));
+            }
+        }
+        i += run;
     }
     return LSG_OK;
 }

@@ -30,6 +30,7 @@
 namespace lsg {
 
 constexpr int kMmvqMaxStages = 8;
+constexpr int kMmvqMaxExtra = 3;
 
 struct MmvqArgs {
     const uint8_t* W;         // packed weight, 16-byte aligned
@@ -54,6 +55,16 @@ struct MmvqArgs {
     int gps;                  // row groups per slab
     uint32_t gps_magic;       // ceil(2^32 / gps), 0 when gps == 1
     uint32_t stages_magic;    // ceil(2^32 / stages), 0 when stages == 1
+    // Joined launch: up to three further weight matrices with the same type, K and
+    // activations (the q, k, v or the gate, up projections of one input).  Matrix j owns
+    // the CTAs from cta0x[j] up to the next matrix's first CTA; its output is [M][Nx[j]].
+    // For joined launches rows_q / rows_r describe matrix 0 over its cta0x[0] CTAs.
+    int n_extra;
+    const uint8_t* Wx[kMmvqMaxExtra];
+    void* Cx[kMmvqMaxExtra];
+    int Nx[kMmvqMaxExtra];
+    int cta0x[kMmvqMaxExtra];
+    int rows_qx[kMmvqMaxExtra], rows_rx[kMmvqMaxExtra];
 };
 
 // n / d for 0 <= n < 65536 and 1 <= d < 65536 with magic = ceil(2^32 / d) (0 for d == 1):
@@ -67,8 +78,10 @@ __device__ __forceinline__ int fast_div(int n, uint32_t magic) {
 
 // Fills the derived fields once grid, slab_rows and stages are known (rpp = rows per warp pass).
 inline void finish_args(MmvqArgs& a, int grid, int rpp) {
-    a.rows_q = a.N / grid;
-    a.rows_r = a.N % grid;
+    if (a.n_extra == 0) {
+        a.rows_q = a.N / grid;
+        a.rows_r = a.N % grid;
+    }
     a.gps = (a.slab_rows + rpp - 1) / rpp;
     a.gps_magic = div_magic(a.gps);
     a.stages_magic = div_magic(a.stages);
@@ -343,10 +356,26 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     const int n_cons_warps = (blockDim.x >> 5) - 1;
     const bool is_producer = (warp == n_cons_warps);
 
-    // Contiguous row range of this CTA.
-    const int bx = static_cast<int>(blockIdx.x);
-    const int row_begin = bx * a.rows_q + min(bx, a.rows_r);
-    const int row_end = row_begin + a.rows_q + (bx < a.rows_r ? 1 : 0);
+    // The matrix this CTA works on (joined launches) and its contiguous row range there.
+    int bx = static_cast<int>(blockIdx.x);
+    const uint8_t* Wm = a.W;
+    void* Cm = a.C;
+    int Nm = a.N, ldcm = a.ldc, rows_q = a.rows_q, rows_r = a.rows_r;
+    if (a.n_extra > 0) {
+        const int b = static_cast<int>(blockIdx.x);
+#pragma unroll
+        for (int j = 0; j < kMmvqMaxExtra; ++j)
+            if (j < a.n_extra && b >= a.cta0x[j]) {
+                Wm = a.Wx[j];
+                Cm = a.Cx[j];
+                Nm = ldcm = a.Nx[j];
+                rows_q = a.rows_qx[j];
+                rows_r = a.rows_rx[j];
+                bx = b - a.cta0x[j];
+            }
+    }
+    const int row_begin = bx * rows_q + min(bx, rows_r);
+    const int row_end = row_begin + rows_q + (bx < rows_r ? 1 : 0);
     const int groups_per_slab = a.gps;
 
     const int n_slabs = (row_end - row_begin + a.slab_rows - 1) / a.slab_rows;
@@ -371,8 +400,8 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         // ------------------------------------------------------------------
         if (lane == 0) {
             const uint64_t policy = l2_policy_evict_first();
-            const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.W);
-            const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(a.N) * a.row_bytes) & ~uintptr_t(15);
+            const uintptr_t w_base = reinterpret_cast<uintptr_t>(Wm);
+            const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(Nm) * a.row_bytes) & ~uintptr_t(15);
             int s = 0;
             uint32_t lap = 0;  // ring position of slab i: stage s, lap = i / stages
             for (int i = 0; i < n_slabs; ++i, s = (s + 1 == a.stages) ? 0 : s + 1, lap += (s == 0)) {
@@ -427,7 +456,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     // warp therefore waits on a stage only when it holds work in it, a short slab
     // never leaves warps polling, and the tail of the range balances itself.  Which
     // warp computes a group does not change its result.
-    const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.W);
+    const uintptr_t w_base = reinterpret_cast<uintptr_t>(Wm);
     const int total_groups = n_slabs * groups_per_slab;
     for (;;) {
         int gidx = 0;
@@ -469,7 +498,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                 xv.base = x_base + m0 * xv.rowb;
                 xv.mlast = a.M - 1 - m0;
                 group_dot_store<T, MT, RW, L>(raddr, xv, lane, g + sub * RW, nrows, r0, m0,
-                                              a.M - m0, a.C, a.ldc, a.out_f32, a.debug_skip != 0);
+                                              a.M - m0, Cm, ldcm, a.out_f32, a.debug_skip != 0);
             }
         }
         // Every stage collects one arrival per group, real or past the end.

@@ -68,12 +68,21 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
     // stream are resident together and the second one's prologue and weight prefetch overlap
     // the first one's tail.
     MmvqTune tn = tn_in;
+    // Joined launches: geometry follows the rows of all matrices together.
+    const int n_prob = 1 + a.n_extra;
+    int n_rows[1 + kMmvqMaxExtra] = {a.N, 0, 0, 0};
+    int n_total = a.N;
+    for (int j = 0; j < a.n_extra; ++j) {
+        n_rows[1 + j] = a.Nx[j];
+        n_total += a.Nx[j];
+    }
+    int ctas_of[1 + kMmvqMaxExtra] = {0, 0, 0, 0};
     {
         static const int small_kb = [] {
             const char* e = getenv("LSG_MMVQ_SMALL_KB");
             return e ? atoi(e) : 70;   // 0 switches this off
         }();
-        const long long per_cta = static_cast<long long>(a.N) * a.row_bytes / (sm_count() > 0 ? sm_count() : 1);
+        const long long per_cta = static_cast<long long>(n_total) * a.row_bytes / (sm_count() > 0 ? sm_count() : 1);
         if (small_kb > 0 && per_cta <= static_cast<long long>(small_kb) * 1024 && tn.share == 1 && tn.ctas == 1) {
             tn.warps = tn.warps > 11 ? 11 : tn.warps;
             tn.share = 2;
@@ -100,8 +109,36 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
         const int ctas = tn.ctas < share ? tn.ctas : share;
         const int smem_cap = kSmemCap / share - (share > 1 ? 1024 : 0);  // 1 KB per-CTA reserve
         const int slots = sm_count() * ctas;
-        grid = a.N < slots ? a.N : slots;
-        const int rows_per_cta = (a.N + grid - 1) / grid;
+        grid = n_total < slots ? n_total : slots;
+        int rows_per_cta = (n_total + grid - 1) / grid;
+        if (n_prob > 1) {
+            // CTAs in proportion to the rows; what rounding leaves over goes, one at a
+            // time, to the matrix with the most rows per CTA.
+            int used = 0;
+            for (int j = 0; j < n_prob; ++j) {
+                int g = static_cast<int>(static_cast<long long>(grid) * n_rows[j] / n_total);
+                ctas_of[j] = g < 1 ? 1 : g;
+                used += ctas_of[j];
+            }
+            while (used != grid) {
+                int pick = 0;
+                double worst = used < grid ? -1.0 : 1e30;
+                for (int j = 0; j < n_prob; ++j) {
+                    const double load = static_cast<double>(n_rows[j]) / ctas_of[j];
+                    if (used < grid ? load > worst : (ctas_of[j] > 1 && load < worst)) {
+                        worst = load;
+                        pick = j;
+                    }
+                }
+                ctas_of[pick] += used < grid ? 1 : -1;
+                used += used < grid ? 1 : -1;
+            }
+            rows_per_cta = 0;
+            for (int j = 0; j < n_prob; ++j) {
+                const int r = (n_rows[j] + ctas_of[j] - 1) / ctas_of[j];
+                rows_per_cta = r > rows_per_cta ? r : rows_per_cta;
+            }
+        }
         // Long rows: one row per lane group, so that the rows resident in the ring
         // are enough to occupy every consumer warp.
         rw = (lanes == 32 && a.row_bytes * 2 * tn.warps > (smem_cap * 3) / 4) ? 1 : 2;
@@ -137,6 +174,17 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
         break;
     }
 
+    if (n_prob > 1) {
+        a.rows_q = n_rows[0] / ctas_of[0];
+        a.rows_r = n_rows[0] % ctas_of[0];
+        int first = ctas_of[0];
+        for (int j = 0; j < a.n_extra; ++j) {
+            a.cta0x[j] = first;
+            a.rows_qx[j] = n_rows[1 + j] / ctas_of[1 + j];
+            a.rows_rx[j] = n_rows[1 + j] % ctas_of[1 + j];
+            first += ctas_of[1 + j];
+        }
+    }
     finish_args(a, grid, (32 / lanes) * rw);
     if (a.M == 1) return launch_rows<1>(rw, lanes, a, grid, smem, stream, pdl);
     if (a.M == 2) return launch_rows<2>(rw, lanes, a, grid, smem, stream, pdl);

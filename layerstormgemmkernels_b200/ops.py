@@ -70,6 +70,33 @@ def gguf_mmvq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     return C
 
 
+def gguf_mmvq_batch(A, weights, type, out_dtype=torch.bfloat16):
+    """Several projections of the same activations: bf16 A[M,K] against each packed weight
+    in `weights` (a sequence of (B_packed, N) with one GGUF type and K), through
+    lsg_gguf_mmvq_batch, which runs up to four of them per launch.  Returns the list of
+    [M, N] results, equal bit for bit to separate gguf_mmvq calls."""
+    _require(A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous(),
+             "gguf_mmvq_batch: A must be contiguous BF16 [M, K] on CUDA")
+    _require(out_dtype in (torch.bfloat16, torch.float32), "gguf_mmvq_batch: out_dtype bf16 or f32")
+    M, K = A.size(0), A.size(1)
+    weights = list(weights)
+    arr = (capi.GgufMmvqParams * max(len(weights), 1))()
+    outs = []
+    od = capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16
+    for i, (B, N) in enumerate(weights):
+        _require(B.is_cuda and B.dtype == torch.uint8 and B.is_contiguous(),
+                 "gguf_mmvq_batch: B_packed must be contiguous uint8 on CUDA")
+        C = torch.empty((M, int(N)), dtype=out_dtype, device=A.device)
+        outs.append(C)
+        arr[i] = capi.GgufMmvqParams(M=M, N=int(N), K=int(K), A=A.data_ptr(), B=B.data_ptr(),
+                                     C=C.data_ptr(), type=int(type), out_dtype=od)
+    n = len(weights)
+    ws_bytes = _lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, n)
+    ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A.device)
+    capi.check(_lib.lsg_gguf_mmvq_batch(arr, n, _ptr(ws), ws_bytes, _stream()))
+    return outs
+
+
 def gguf_mmvq_host(A_host, B_packed, type, N, K, out=None, workspace=None):
     """The same mat-vec with the activations and the result in host memory.
 

@@ -190,6 +190,37 @@ def test_mmvq_host_batch_shares_quantized_activations(ops):
         ops.HostMmvqBatch(items, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
 
 
+@pytest.mark.parametrize("name,M,K,Ns", [
+    ("Q4_K", 1, 4096, (4096, 1024, 1024)),       # q, k, v
+    ("Q4_K", 1, 4096, (14336, 14336)),           # gate, up
+    ("Q6_K", 3, 1024, (96, 7, 640, 33)),         # four matrices, ragged and tiny ones
+    ("Q8_0", 9, 512, (1, 300)),                  # more rows than one register pass
+    ("Q4_K", 40, 1024, (200, 120)),              # more rows than one launch holds
+    ("Q4_0", 2, 2048, (513, 511, 2, 2, 700)),    # five entries: a launch of four, then one
+])
+def test_mmvq_batch_joined_launch_equals_separate_calls(ops, name, M, K, Ns):
+    """lsg_gguf_mmvq_batch runs projections of one input as one launch; which CTA computes a
+    row does not change its bits."""
+    A = (torch.randn(M, K, generator=torch.Generator().manual_seed(17)) * 0.4).to(torch.bfloat16).cuda()
+    Ws = [torch.from_numpy(Q.random_gguf_weight(name, N, K, seed=40 + i)).cuda() for i, N in enumerate(Ns)]
+    for dt in (torch.bfloat16, torch.float32):
+        outs = ops.gguf_mmvq_batch(A, [(W, N) for W, N in zip(Ws, Ns)], T[name], out_dtype=dt)
+        for W, N, out in zip(Ws, Ns, outs):
+            assert torch.equal(out, ops.gguf_mmvq(A, W, T[name], N, K, out_dtype=dt))
+
+
+def test_mmvq_batch_matches_oracle(ops):
+    name, M, K, Ns = "Q4_K", 2, 1024, (160, 96, 40)
+    rng = np.random.default_rng(3)
+    A = (torch.randn(M, K, generator=torch.Generator().manual_seed(19)) * 0.4).to(torch.bfloat16)
+    Wn = [Q.random_gguf_weight(name, N, K, seed=50 + i) for i, N in enumerate(Ns)]
+    outs = ops.gguf_mmvq_batch(A.cuda(), [(torch.from_numpy(W).cuda(), N) for W, N in zip(Wn, Ns)],
+                               T[name], out_dtype=torch.float32)
+    xq = oracle.quantize_q8_1(bf16_bits(A))
+    for W, out in zip(Wn, outs):
+        assert rel_err(out.cpu().numpy(), oracle.mmvq(T[name], xq, W, K)) <= TOL_F32
+
+
 def test_mmvq_graph_capture(ops):
     """tests/test_gguf_mmvq.py:106-134: capture + replay equals eager."""
     N, K = 512, 1024
