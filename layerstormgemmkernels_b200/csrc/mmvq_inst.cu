@@ -63,7 +63,8 @@ int MMVQ_FN(max_rows)(int K) {
 int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool pdl) {
     using F = Fmt<T>;
     a.row_bytes = (a.K / F::VALS) * F::BYTES;
-    // Small matrices (a CTA's share of the weights fits half an SM's shared memory): eleven
+    // Small matrices (a CTA's share of the weights is at most 40 KB, e.g. a 1024 x 4096 Q4_K
+    // k or v projection launched alone): eleven
     // consumer warps and half the shared memory, so that two consecutive launches of a
     // stream are resident together and the second one's prologue and weight prefetch overlap
     // the first one's tail.
@@ -80,7 +81,7 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
     {
         static const int small_kb = [] {
             const char* e = getenv("LSG_MMVQ_SMALL_KB");
-            return e ? atoi(e) : 70;   // 0 switches this off
+            return e ? atoi(e) : 40;   // 0 switches this off
         }();
         const long long per_cta = static_cast<long long>(n_total) * a.row_bytes / (sm_count() > 0 ? sm_count() : 1);
         if (small_kb > 0 && per_cta <= static_cast<long long>(small_kb) * 1024 && tn.share == 1 && tn.ctas == 1) {
