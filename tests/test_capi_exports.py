@@ -30,3 +30,41 @@ def test_argument_errors_need_no_gpu(built_lib):
     assert capi.lib.lsg_gguf_mmvq_workspace_bytes(3, 4096) == 3 * 128 * 36
     assert capi.lib.lsg_gguf_block_bytes(capi.Q6_K) == 210
     assert capi.lib.lsg_gguf_block_values(capi.Q4_0) == 32
+
+
+def test_batch_workspace_plans_need_no_gpu(built_lib):
+    """The workspace of the batched mat-vec entries is planned on the host: the device batch
+    needs the largest Q8_1 image, the host-memory batch one staged copy and one image per
+    distinct activation plus result rows per projection; argument errors come back before
+    any CUDA call."""
+    from layerstormgemmkernels_b200 import capi
+    import pytest
+
+    def a256(v):
+        return (v + 255) & ~255
+
+    P = capi.GgufMmvqParams
+    # pointers are only compared, never dereferenced, by the planning functions
+    shapes = [(4096, 4096, 0x1000), (1024, 4096, 0x1000), (1024, 4096, 0x1000),
+              (4096, 4096, 0x2000), (14336, 4096, 0x3000), (14336, 4096, 0x3000), (4096, 14336, 0x4000)]
+    arr = (P * len(shapes))()
+    for i, (N, K, A) in enumerate(shapes):
+        arr[i] = P(M=2, N=N, K=K, A=A, B=0x10, C=0x20 + i, type=capi.Q4_K, out_dtype=0)
+    assert capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, len(shapes)) == 2 * (14336 // 32) * 36
+    want = sum(a256(2 * N * 4) for N, _, _ in shapes)
+    for K in (4096, 4096, 4096, 14336):           # four distinct activations
+        want += a256(2 * K * 2) + a256(2 * (K // 32) * 36)
+    assert capi.lib.lsg_gguf_mmvq_host_batch_workspace_bytes(arr, len(shapes)) == want
+    assert capi.lib.lsg_gguf_mmvq_host_workspace_bytes(2, 4096, 4096) == \
+        a256(2 * 4096 * 2) + a256(2 * 128 * 36) + a256(2 * 4096 * 4)
+    assert capi.lib.lsg_gguf_mmvq_host_batch_workspace_bytes(arr, 65) == 0   # more than 64 entries
+
+    bad = (P * 2)()
+    bad[0] = arr[0]
+    bad[1] = P(M=1, N=8, K=100, A=0x1000, B=0x10, C=0x20, type=capi.Q4_K, out_dtype=0)
+    for fn in (capi.lib.lsg_gguf_mmvq_batch, capi.lib.lsg_gguf_mmvq_host_batch):
+        with pytest.raises(ValueError, match="divisible by 256"):
+            capi.check(fn(bad, 2, None, 0, None))
+        with pytest.raises(capi.LsgError):
+            capi.check(fn(arr, len(shapes), None, 0, None))     # no workspace
+        assert fn(arr, 0, None, 0, None) == 0                     # empty batch
