@@ -145,7 +145,10 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
         rw = (lanes == 32 && a.row_bytes * 2 * tn.warps > (smem_cap * 3) / 4) ? 1 : 2;
         // Few rows per CTA (small matrices): one row per lane group doubles the number of row
         // groups, so that they cover the consumer warps instead of leaving most of them idle.
-        if (rows_per_cta < (32 / lanes) * 2 * tn.warps) rw = 1;
+        // (One row per group is only built for whole-warp groups; for narrower groups the
+        // slab must be planned with the two rows per group the kernel really takes, or a
+        // third of its row groups come out empty.)
+        if (lanes == 32 && rows_per_cta < 2 * tn.warps) rw = 1;
         int slab_rows = tn.stage_kb * 1024 / a.row_bytes;
         // whole row groups per slab, so that no lane group idles on a ragged slab end
         const int rpp = (32 / lanes) * rw;
