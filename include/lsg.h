@@ -53,6 +53,20 @@ LSG_API const char* lsg_version(void);
  * synchronizes the device.  *code receives 0 when no kernel reported. */
 LSG_API int lsg_device_status(int* code);
 
+/* Limit of the device-side waits of the decode mat-vec kernels and of lsg_ep_barrier, in SM
+ * clock cycles, process-wide (default 4e8, about 0.2 s; 0 restores the default).  Codes a
+ * wait that ran out leaves in the status word: 1 data did not land, 2 a pipeline stage was
+ * not released, 3 tensor-core completion, 4 tensor memory, 5 slab table of the grouped
+ * mat-vec too small, 6 cross-GPU barrier, 7 expert-parallel receive buffer overflow.  No counterpart in the reference (its kernels do not wait). */
+LSG_API int lsg_set_wait_limit_cycles(long long cycles);
+
+/* Failure-path test hook: from now on the first CTA of every decode mat-vec launch leaves out
+ * pipeline slab `slab` (it is neither loaded nor published), so that the consumers of that
+ * slab run into the wait limit, record code 1 and return; slab < 0 switches the hook off.
+ * The output of such a launch is incomplete by construction.  No counterpart in the
+ * reference. */
+LSG_API int lsg_test_mmvq_drop_slab(int slab);
+
 /* ------------------------------------------------------------------------ */
 /* GGUF weight types                                                        */
 /* ids 0..6 replace: enum class GgufType,                                   */
@@ -180,10 +194,10 @@ LSG_API int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, void*
 /* Launch geometry of the mmvq kernels, process-wide: consumer warps per CTA
  * (1..15), CTAs of one launch per SM, KiB per pipeline stage, and how many CTAs
  * (of this and of neighbouring launches in the stream) split an SM's shared
- * memory.  An argument <= 0 keeps the current value; skip_math < 0 keeps it,
- * 1 makes kernels stream the weights without doing the arithmetic (bandwidth
- * measurements only - outputs are then zeros).  Results do not depend on the
- * geometry.  No counterpart in the reference (its grid is fixed: one CTA per
+ * memory.  An argument <= 0 keeps the current value.  skip_math must be <= 0 in
+ * the shipped library; a bench build (-DLSG_DEBUG_KNOBS) accepts 1, which makes
+ * kernels stream the weights without doing the arithmetic (outputs are then
+ * zeros).  Results do not depend on the geometry.  No counterpart in the reference (its grid is fixed: one CTA per
  * output channel, gguf_mmvq.cu:104-112). */
 LSG_API int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_kib,
                                 int smem_share, int skip_math);
@@ -539,7 +553,13 @@ LSG_API int lsg_ep_expert_order(const int32_t* recv_counts, int world, int exper
  * (local expert, source rank), described by local_offsets int32 [E/world + 1]; return buffer:
  * bf16 [num_pairs][H] in the sender's sorted-by-expert order.  send_base int32 [E], dst_start
  * and ret_base int32 [E] (world * E/world), info int32 [2] = {rows received, overflow flag};
- * rows that would land beyond `capacity` are dropped and flagged.  E <= 1024, H % 8 == 0.
+ * E <= 1024, H % 8 == 0.
+ * Overflow: when the ranks send a rank more rows than its `capacity`, lsg_ep_plan clamps every
+ * start and offset it writes (local_offsets, dst_start, info[0]) to `capacity`, sets info[1]
+ * on every rank and records code 7 in the device status word (lsg_device_status);
+ * lsg_ep_send_rows drops the rows that do not fit and clears their slots of `back_local`
+ * (this rank's own return buffer, may be NULL), so a dropped row contributes zeros to the
+ * combine instead of the previous layer's output.  Nothing is written past `capacity`.
  * No counterpart in the reference (it has no multi-GPU code). */
 LSG_API int lsg_ep_publish_counts(const int32_t* expert_offsets, int num_experts, int rank, int world,
                                   void* const* counts_table_ptrs, void* stream);
@@ -548,10 +568,20 @@ LSG_API int lsg_ep_plan(const int32_t* counts_table, int rank, int world, int nu
                         int32_t* info, void* stream);
 LSG_API int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
                              const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
-                             void* const* recv_buf_ptrs, int capacity, void* stream);
+                             void* const* recv_buf_ptrs, int capacity, void* back_local, void* stream);
 LSG_API int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
                                const int32_t* info, int world, int experts_per_rank, int H, int capacity,
                                void* const* back_buf_ptrs, void* stream);
+
+/* Barrier over the ranks of the exchange, on the stream, with a time limit.  flag_ptrs is a
+ * DEVICE array of `world` device pointers, entry p = rank p's flag array uint32 [world + 1]
+ * in peer-accessible memory, zeroed once before the first use (all ranks zero, then
+ * synchronize once on the host).  mode 3 = arrive and wait (the normal call); 1 = arrive only,
+ * 2 = wait only (tests that emulate several ranks on one GPU).  A rank whose peers do not
+ * arrive within the wait limit (lsg_set_wait_limit_cycles) records code 6 in the device status
+ * word and returns; nothing waits without a limit and no multicast is used.  world <= 64.
+ * No counterpart in the reference. */
+LSG_API int lsg_ep_barrier(void* const* flag_ptrs, int rank, int world, int mode, void* stream);
 
 /* out[row,:] = hidden[perm[row] / top_k, :]   (bf16, H multiple of 8). */
 LSG_API int lsg_moe_permute(const void* hidden_bf16, const int32_t* perm, int rows, int top_k, int H,

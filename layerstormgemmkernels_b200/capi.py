@@ -10,14 +10,8 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsg_b200.so")
 
-# lsg_gguf_type ids (ids 0..6 are the reference's GgufType values)
-Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_0, MXFP4, Q4_0 = range(8)
-GGUF_TYPES = {"Q2_K": Q2_K, "Q3_K": Q3_K, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K,
-              "Q8_0": Q8_0, "MXFP4": MXFP4, "Q4_0": Q4_0}
-BLOCK_BYTES = {Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210, Q8_0: 34, MXFP4: 17, Q4_0: 18}
-BLOCK_VALUES = {Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256, Q8_0: 32, MXFP4: 32, Q4_0: 32}
-
-DTYPE_BF16, DTYPE_F32, DTYPE_F16 = 0, 1, 2
+from .formats import (Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, Q8_0, MXFP4, Q4_0, GGUF_TYPES, BLOCK_BYTES,  # noqa: F401
+                      BLOCK_VALUES, DTYPE_BF16, DTYPE_F32, DTYPE_F16)
 
 LSG_OK = 0
 LSG_ERR_INVALID = -1
@@ -115,6 +109,9 @@ def _load():
         "lsg_last_error": (ctypes.c_char_p, []),
         "lsg_version": (ctypes.c_char_p, []),
         "lsg_device_status": (ci, [ctypes.POINTER(ci)]),
+        "lsg_set_wait_limit_cycles": (ci, [ll]),
+        "lsg_test_mmvq_drop_slab": (ci, [ci]),
+        "lsg_ep_barrier": (ci, [vp, ci, ci, ci, vp]),
         "lsg_gguf_block_values": (ci, [ci]),
         "lsg_gguf_block_bytes": (ci, [ci]),
         "lsg_quantize_q8_1": (ci, [vp, vp, ci, ci, vp]),
@@ -163,7 +160,7 @@ def _load():
         "lsg_ep_expert_order": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_ep_publish_counts": (ci, [vp, ci, ci, ci, vp, vp]),
         "lsg_ep_plan": (ci, [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
-        "lsg_ep_send_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
+        "lsg_ep_send_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp, vp]),
         "lsg_ep_return_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]),
         "lsg_moe_permutation_scratch_ints": (ctypes.c_longlong, [ci, ci, ci]),
         "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),

@@ -10,7 +10,10 @@ namespace lsg {
 namespace {
 thread_local char g_err[512] = "";
 __device__ unsigned int g_status_word = 0;
+long long g_wait_limit = kWaitLimitCycles;
 }  // namespace
+
+long long wait_limit_cycles() { return g_wait_limit; }
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -67,6 +70,12 @@ extern "C" int lsg_device_status(int* code) {
         LSG_CUDA_TRY(cudaMemcpyToSymbol(g_status_word, &zero, sizeof(zero)));
     }
     *code = static_cast<int>(v);
+    return LSG_OK;
+}
+
+extern "C" int lsg_set_wait_limit_cycles(long long cycles) {
+    if (cycles < 0) return fail(LSG_ERR_INVALID, "set_wait_limit_cycles: negative limit");
+    g_wait_limit = cycles == 0 ? kWaitLimitCycles : cycles;
     return LSG_OK;
 }
 

@@ -35,7 +35,13 @@ enum : unsigned int {
     kDevWaitEmpty = 2,  // producer gave up waiting for a stage to be released
     kDevWaitMma = 3,    // epilogue gave up waiting for tensor-core completion
     kDevWaitTmem = 4,
+    kDevSlabTable = 5,   // grouped mat-vec: a CTA's slab table was too small for its rows
+    kDevBarrier = 6,     // a cross-GPU flag barrier gave up waiting for a peer
+    kDevEpOverflow = 7,  // an expert-parallel receive buffer was too small: rows were dropped
 };
+
+// Current limit of the device-side waits in SM cycles (lsg_set_wait_limit_cycles; capi.cu).
+long long wait_limit_cycles();
 
 #if defined(__CUDACC__)
 
@@ -95,6 +101,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 // The SM-local cycle counter is used because it is read in a few cycles; the global
 // nanosecond timer is not, and a read of it would sit on the critical path of every wait
 // that does not succeed at once.
+// Kernels take the limit as a launch argument (wait_limit_cycles()); this is its default.
 constexpr long long kWaitLimitCycles = 400000000ll;
 
 __device__ __forceinline__ long long sm_clock() {
@@ -107,7 +114,8 @@ __device__ __forceinline__ long long sm_clock() {
 // recording `code` in *status) when the time limit runs out.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   unsigned int* status, unsigned int code,
-                                                  uint32_t hint_ns = 2000u) {
+                                                  uint32_t hint_ns = 2000u,
+                                                  long long limit = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity, hint_ns)) return true;
     const long long t0 = sm_clock();
     for (;;) {
@@ -115,7 +123,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         for (int i = 0; i < 16; ++i) {
             if (mbar_try_wait(bar, parity, hint_ns)) return true;
         }
-        if (sm_clock() - t0 > kWaitLimitCycles) {
+        if (sm_clock() - t0 > limit) {
             if (status) atomicCAS(status, 0u, code);
             return false;
         }

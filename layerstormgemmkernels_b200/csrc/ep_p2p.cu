@@ -42,11 +42,16 @@ ep_publish_counts_kernel(const int32_t* __restrict__ offs, int E, int rank, int 
 //                           receive buffer; local_offsets[el] = dst_start[el*world]
 //   ret_base[el*world + s]  row in source s's return buffer where that block goes back
 //                           (= exclusive scan of s's counts at global expert rank*per + el)
-//   info[0] = rows received, info[1] = 1 if some rank's receive buffer would overflow
+//   info[0] = rows received (never more than the capacity), info[1] = 1 if some rank's receive
+//   buffer is too small for what the ranks send it
+// Overflow: every start and offset written here is clamped to `capacity`, so whatever runs on
+// the receive buffer afterwards stays inside it; rows that do not fit are dropped at the
+// sender (ep_send_rows_kernel zeroes their slots of the return buffer, so a dropped row
+// contributes nothing to the combine) and the device status word reports kDevEpOverflow.
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int capacity,
                int32_t* __restrict__ send_base, int32_t* __restrict__ local_offsets, int32_t* __restrict__ dst_start,
-               int32_t* __restrict__ ret_base, int32_t* __restrict__ info) {
+               int32_t* __restrict__ ret_base, int32_t* __restrict__ info, unsigned int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait_prior();
     __shared__ int wsum[32];
@@ -102,11 +107,11 @@ ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int 
     const int excl = (warp > 0 ? wsum[warp - 1] : 0) + incl - v;
     if (tid < B) {
         const int el = tid / world, s = tid - el * world;
-        dst_start[tid] = excl;
-        if (s == 0) local_offsets[el] = excl;
+        dst_start[tid] = min(excl, capacity);
+        if (s == 0) local_offsets[el] = min(excl, capacity);
         if (tid == B - 1) {
-            local_offsets[per] = excl + v;
-            info[0] = excl + v;
+            local_offsets[per] = min(excl + v, capacity);
+            info[0] = min(excl + v, capacity);
         }
         // where the block goes back: source s's rows for experts below rank*per + el
         int back = 0;
@@ -115,7 +120,10 @@ ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int 
         ret_base[tid] = back;
     }
     __syncthreads();
-    if (tid == 0) info[1] = overflow;
+    if (tid == 0) {
+        info[1] = overflow;
+        if (overflow && status) atomicCAS(status, 0u, static_cast<unsigned int>(kDevEpOverflow));
+    }
 }
 
 // Sorted row i (expert e, j-th row of e) -> row send_base[e] + j of rank e / per.
@@ -123,7 +131,8 @@ ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int 
 __global__ void __launch_bounds__(256)
 ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm,
                     const int32_t* __restrict__ offs, const int32_t* __restrict__ send_base, int P, int top_k,
-                    int vpr, int E, int per, uint4* const* __restrict__ recv, int capacity) {
+                    int vpr, int E, int per, uint4* const* __restrict__ recv, int capacity,
+                    uint4* __restrict__ back_local) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
@@ -137,7 +146,12 @@ ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict_
     }
     const int e = lo;
     const int row = send_base[e] + (i - offs[e]);
-    if (row >= capacity) return;
+    if (row >= capacity) {
+        // no room at the destination: nothing comes back for this row, so its slot of this
+        // rank's return buffer is cleared instead of keeping the previous layer's contents
+        if (back_local) back_local[static_cast<size_t>(i) * vpr + v] = make_uint4(0, 0, 0, 0);
+        return;
+    }
     const int token = perm[i] / top_k;
     recv[e / per][static_cast<size_t>(row) * vpr + v] = __ldg(hidden + static_cast<size_t>(token) * vpr + v);
 }
@@ -162,6 +176,53 @@ ep_return_rows_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ d
     const int s = lo % world;
     const int row = ret_base[lo] + (r - dst_start[lo]);
     back[s][static_cast<size_t>(row) * vpr + v] = __ldg(y + static_cast<size_t>(r) * vpr + v);
+}
+
+// Cross-GPU barrier on the stream, owned by this library: every rank holds a flag array
+// uint32 [world + 1] in peer-accessible memory (entry p = the last barrier rank p has arrived
+// at, entry world = this rank's own count).  Arriving = storing the new count into entry
+// `rank` of every peer's array (release, system scope, after a system-wide fence so that the
+// peer stores of the kernels before it are visible first); waiting = polling the local array
+// until every entry has reached the count, for at most `limit` SM cycles, after which the
+// kernel records kDevBarrier in the status word and returns - a rank that never arrives costs
+// its peers the limit, not a hung GPU.  Counts only grow, so a rank that is one barrier ahead
+// cannot be mistaken for one that is behind.  mode: 1 arrive, 2 wait, 3 both.
+__global__ void __launch_bounds__(64)
+ep_barrier_kernel(uint32_t* const* __restrict__ flags, int rank, int world, int mode, long long limit,
+                  unsigned int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    uint32_t* mine = flags[rank];
+    __shared__ uint32_t count;
+    if (threadIdx.x == 0) {
+        uint32_t c = *reinterpret_cast<volatile uint32_t*>(mine + world);
+        if (mode & 1) {
+            ++c;
+            *reinterpret_cast<volatile uint32_t*>(mine + world) = c;
+        }
+        count = c;
+    }
+    __syncthreads();
+    const uint32_t c = count;
+    const int p = threadIdx.x;
+    if (p >= world) return;
+    if (mode & 1) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[p] + rank), "r"(c) : "memory");
+    }
+    if (mode & 2) {
+        const long long t0 = sm_clock();
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + p) : "memory");
+            if (static_cast<int32_t>(v - c) >= 0) break;
+            if (sm_clock() - t0 > limit) {
+                if (status) atomicCAS(status, 0u, static_cast<unsigned int>(kDevBarrier));
+                return;
+            }
+            __nanosleep(100);
+        }
+    }
 }
 
 int check_world(const char* op, int E, int world) {
@@ -200,13 +261,13 @@ extern "C" int lsg_ep_plan(const int32_t* counts_table, int rank, int world, int
         return fail(LSG_ERR_INVALID, "ep_plan: bad rank, negative capacity or null pointer");
     LSG_CUDA_TRY(launch_kernel(ep_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), true,
                                counts_table, rank, world, num_experts, capacity, send_base, local_offsets, dst_start,
-                               ret_base, info));
+                               ret_base, info, device_status_word()));
     return LSG_OK;
 }
 
 extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
                                 const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
-                                void* const* recv_buf_ptrs, int capacity, void* stream) {
+                                void* const* recv_buf_ptrs, int capacity, void* back_local, void* stream) {
     int rc = check_world("ep_send_rows", num_experts, world);
     if (rc != LSG_OK) return rc;
     if (num_pairs <= 0) return LSG_OK;
@@ -219,7 +280,8 @@ extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, co
     LSG_CUDA_TRY(launch_kernel(ep_send_rows_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(hidden_bf16), perm,
                                expert_offsets, send_base, num_pairs, top_k, vpr, num_experts, num_experts / world,
-                               reinterpret_cast<uint4* const*>(recv_buf_ptrs), capacity));
+                               reinterpret_cast<uint4* const*>(recv_buf_ptrs), capacity,
+                               static_cast<uint4*>(back_local)));
     return LSG_OK;
 }
 
@@ -239,5 +301,14 @@ extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, 
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(y_bf16), dst_start,
                                ret_base, info, world, world * experts_per_rank, vpr, capacity,
                                reinterpret_cast<uint4* const*>(back_buf_ptrs)));
+    return LSG_OK;
+}
+
+extern "C" int lsg_ep_barrier(void* const* flag_ptrs, int rank, int world, int mode, void* stream) {
+    if (world < 1 || world > 64 || rank < 0 || rank >= world || !flag_ptrs || mode < 1 || mode > 3)
+        return fail(LSG_ERR_INVALID, "ep_barrier: need 1 <= world <= 64, 0 <= rank < world, mode 1..3, flag pointers");
+    LSG_CUDA_TRY(launch_kernel(ep_barrier_kernel, dim3(1), dim3(64), 0, static_cast<cudaStream_t>(stream), true,
+                               reinterpret_cast<uint32_t* const*>(flag_ptrs), rank, world, mode, wait_limit_cycles(),
+                               device_status_word()));
     return LSG_OK;
 }

@@ -16,10 +16,13 @@ int dequant_gemm(int type, int M, int N, int K, const void* A, const void* W, vo
                  int out_f32, cudaStream_t stream);
 
 int build_active_expert_list(const int32_t* offs, int E, int cap, int* active, cudaStream_t s);
+// `rows` bounds every offset read from the device: offsets that run past the caller's row
+// count (an expert-parallel receive buffer that overflowed) can then never index past it.
+// The default leaves the offsets as they are, which is the reference's behaviour.
 int build_mmq_tile_map(const int32_t* offs, int E, int tile_m, int T_max, int* tile_expert,
-                       int* tile_mstart, cudaStream_t s);
+                       int* tile_mstart, cudaStream_t s, int rows = 0x7fffffff);
 int build_segment_list(const int32_t* offs, const void* const* B_ptrs, int E, int max_rows,
-                       int max_segments, int* seg, cudaStream_t s);
+                       int max_segments, int* seg, cudaStream_t s, int rows = 0x7fffffff);
 
 size_t mmq_scratch_bytes(long long rows, int K, int E, int N);
 // Several output matrices for one GEMM (this GPU's and its peers'): every tile is stored

@@ -20,7 +20,10 @@ MmvqTune& tuning() {
         if (const char* e = getenv("LSG_MMVQ_CTAS")) v.ctas = atoi(e);
         if (const char* e = getenv("LSG_MMVQ_STAGE_KB")) v.stage_kb = atoi(e);
         if (const char* e = getenv("LSG_MMVQ_SHARE")) v.share = atoi(e);
+#ifdef LSG_DEBUG_KNOBS
         if (getenv("LSG_MMVQ_SKIP")) v.skip_math = 1;
+        if (const char* e = getenv("LSG_MMVQ_DBG")) v.skip_math |= atoi(e);
+#endif
         return v;
     }();
     return t;
@@ -35,8 +38,20 @@ MmvqTune sane_tuning() {
     return v;
 }
 
-int dispatch_launch(int type, const MmvqArgs& a, cudaStream_t s, bool pdl) {
+int g_drop_slab = -1;   // failure-path test hook (lsg_test_mmvq_drop_slab)
+#ifdef LSG_MMVQ_TRACE
+unsigned long long* g_trace = nullptr;
+int g_trace_launch = 0, g_trace_slots = 0;
+#endif
+
+int dispatch_launch(int type, const MmvqArgs& a_in, cudaStream_t s, bool pdl) {
     const MmvqTune tn = sane_tuning();
+    MmvqArgs a = a_in;
+    a.wait_limit = wait_limit_cycles();
+    a.drop_slab = g_drop_slab;
+#ifdef LSG_MMVQ_TRACE
+    a.trace = g_trace && g_trace_slots > 0 ? g_trace + static_cast<size_t>(g_trace_launch++ % g_trace_slots) * 1024 * 16 : nullptr;
+#endif
     switch (type) {
         case 0: return mmvq_launch_t0(a, tn, s, pdl);
         case 1: return mmvq_launch_t1(a, tn, s, pdl);
@@ -465,6 +480,20 @@ extern "C" int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace
     return lsg_gguf_mmvq_host_batch(p, 1, workspace, workspace_bytes, stream);
 }
 
+extern "C" int lsg_test_mmvq_drop_slab(int slab) {
+    g_drop_slab = slab < 0 ? -1 : slab;
+    return LSG_OK;
+}
+
+#ifdef LSG_MMVQ_TRACE
+extern "C" __attribute__((visibility("default"))) int lsg_mmvq_set_trace(void* buf, int slots) {
+    g_trace = static_cast<unsigned long long*>(buf);
+    g_trace_slots = slots;
+    g_trace_launch = 0;
+    return LSG_OK;
+}
+#endif
+
 extern "C" int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stage_kib,
                                    int smem_share, int skip_math) {
     MmvqTune& t = tuning();
@@ -472,6 +501,11 @@ extern "C" int lsg_mmvq_set_tuning(int consumer_warps, int ctas_per_sm, int stag
     if (ctas_per_sm > 0) t.ctas = ctas_per_sm;
     if (stage_kib > 0) t.stage_kb = stage_kib;
     if (smem_share > 0) t.share = smem_share;
+#ifdef LSG_DEBUG_KNOBS
     if (skip_math >= 0) t.skip_math = skip_math ? 1 : 0;
+#else
+    if (skip_math > 0)
+        return fail(LSG_ERR_UNSUPPORTED, "mmvq_set_tuning: skip_math exists in bench builds (-DLSG_DEBUG_KNOBS) only");
+#endif
     return LSG_OK;
 }

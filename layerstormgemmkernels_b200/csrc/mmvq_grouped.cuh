@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_grouped_kernel(const GroupedArgs 
             slab_tab[3 * n + 2] = static_cast<int>(rows);
             cur += rows;
             ++n;
-            if (n == kGroupedMaxSlabs && cur < ve && a.status) atomicCAS(a.status, 0u, 5u);
+            if (n == kGroupedMaxSlabs && cur < ve && a.status) atomicCAS(a.status, 0u, static_cast<unsigned int>(kDevSlabTable));
         }
         *n_slabs_sh = n;
     }

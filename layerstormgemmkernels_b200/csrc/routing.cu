@@ -37,7 +37,9 @@ __global__ void active_expert_list_kernel(const int32_t* __restrict__ offs, int 
     for (int s = written + lane; s < cap; s += 32) active[s] = -1;
 }
 
-__global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int tile_m, int T_max,
+// `rows` bounds every offset (callers whose offsets come from another GPU's counts pass the
+// row capacity of their buffers; INT_MAX leaves the offsets as they are).
+__global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int tile_m, int T_max, int rows,
                                     int* __restrict__ tile_expert, int* __restrict__ tile_mstart) {
     pdl_launch_dependents();
     pdl_wait_prior();
@@ -47,8 +49,8 @@ __global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int
         const int e = base + lane;
         int off = 0, nt = 0;
         if (e < E) {
-            off = offs[e];
-            const int m = offs[e + 1] - off;
+            off = min(offs[e], rows);
+            const int m = min(offs[e + 1], rows) - off;
             nt = m > 0 ? (m + tile_m - 1) / tile_m : 0;
         }
         // exclusive prefix sum of nt over the warp
@@ -78,7 +80,7 @@ __global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int
 // null weight pointer are skipped, as the reference's host loop skips them
 // (gguf_grouped_gemm.cu:114-118 with B_e == nullptr guarded in the engine).
 __global__ void segment_list_kernel(const int32_t* __restrict__ offs, const void* const* __restrict__ B_ptrs,
-                                    int E, int max_rows, int max_segments, int* __restrict__ seg) {
+                                    int E, int max_rows, int max_segments, int rows, int* __restrict__ seg) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const int lane = threadIdx.x & 31;
@@ -87,8 +89,8 @@ __global__ void segment_list_kernel(const int32_t* __restrict__ offs, const void
         const int e = base + lane;
         int off = 0, m = 0, ns = 0;
         if (e < E) {
-            off = offs[e];
-            m = offs[e + 1] - off;
+            off = min(offs[e], rows);
+            m = min(offs[e + 1], rows) - off;
             if (m < 0 || B_ptrs[e] == nullptr) m = 0;
             ns = (m + max_rows - 1) / max_rows;
         }
@@ -122,17 +124,17 @@ int build_active_expert_list(const int32_t* offs, int E, int cap, int* active, c
 }
 
 int build_mmq_tile_map(const int32_t* offs, int E, int tile_m, int T_max, int* tile_expert,
-                       int* tile_mstart, cudaStream_t s) {
+                       int* tile_mstart, cudaStream_t s, int rows) {
     if (T_max <= 0) return LSG_OK;
     LSG_CUDA_TRY(launch_kernel(mmq_tile_map_kernel, dim3(1), dim3(32), 0, s, true, offs, E, tile_m,
-                               T_max, tile_expert, tile_mstart));
+                               T_max, rows, tile_expert, tile_mstart));
     return LSG_OK;
 }
 
 int build_segment_list(const int32_t* offs, const void* const* B_ptrs, int E, int max_rows,
-                       int max_segments, int* seg, cudaStream_t s) {
+                       int max_segments, int* seg, cudaStream_t s, int rows) {
     LSG_CUDA_TRY(launch_kernel(segment_list_kernel, dim3(1), dim3(32), 0, s, true, offs, B_ptrs, E,
-                               max_rows, max_segments, seg));
+                               max_rows, max_segments, rows, seg));
     return LSG_OK;
 }
 

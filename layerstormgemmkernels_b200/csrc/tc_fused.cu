@@ -191,8 +191,9 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
         it.expert = e;
         it.live = e >= 0;
         if (it.live) {
-            it.mstart = a.tile_mstart[it.tt];
-            it.mend = a.expert_offsets[e + 1];
+            // never past the rows the caller holds, whatever the offsets say
+            it.mstart = min(a.tile_mstart[it.tt], a.M);
+            it.mend = min(a.expert_offsets[e + 1], a.M);
         }
     }
     return it;

@@ -9,12 +9,38 @@ torch.distributed over NCCL / NVLink; gloo on CPU for the tests of the host logi
   contiguous slab of packed rows); activations are replicated; one all-gather assembles
   the output.
 
-The reference has no multi-GPU code; these functions define that layer.  Nothing here
-touches a peer's memory directly: rows land in local memory through the collective before
-any kernel reads them.  Decode mat-vec and the quantizers do not shard ("replicas only").
+The reference has no multi-GPU code; these functions define that layer.  Two forms of each:
+through torch.distributed collectives (rows land in local memory before any kernel reads
+them), and through peer memory (EpPeerExchange, ColumnSplitPeer: the kernels store straight
+into the other GPUs' buffers, separated by the library's own time-limited flag barrier).
+Decode mat-vec and the quantizers do not shard ("replicas only").
 """
 import torch
 import torch.distributed as dist
+
+
+class FlagBarrier:
+    """Stream-ordered barrier over the ranks of a group on peer memory (lsg_ep_barrier): each
+    rank stores a growing count into every peer's flag array and polls its own, for at most
+    the library's wait limit; a peer that never arrives costs the limit and leaves code 6 in
+    the device status word instead of a spinning kernel."""
+
+    def __init__(self, group=None):
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.flags = symm.empty((self.world + 1,), dtype=torch.int32, device=dev)
+        self._h = symm.rendezvous(self.flags, group)
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group)            # every array is zero before anybody arrives
+        self.ptrs = torch.tensor([int(p) for p in self._h.buffer_ptrs], dtype=torch.int64, device=dev)
+
+    def __call__(self):
+        from . import capi
+        capi.check(capi.lib.lsg_ep_barrier(self.ptrs.data_ptr(), self.rank, self.world, 3,
+                                           torch.cuda.current_stream().cuda_stream))
 
 
 def expert_range(rank, world, num_experts):
@@ -156,16 +182,28 @@ class EpPeerExchange:
         handles = {n: symm.rendezvous(t, group) for n, t in local.items()}
         bufs = {n: (local[n], torch.tensor([int(p) for p in handles[n].buffer_ptrs], dtype=torch.int64, device=dev))
                 for n in local}
-        h = handles["recv"]
-        ex = EpPeerExchange(rank, world, num_experts, top_k, H, P, cap, bufs, lambda: h.barrier(0))
+        ex = EpPeerExchange(rank, world, num_experts, top_k, H, P, cap, bufs, FlagBarrier(group))
         ex._handles = handles   # keep the mappings alive
         return ex
+
+    def check_inputs(self, hidden, logits):
+        """Everything rank-local that could fail is checked here, before the first barrier of
+        a layer: a rank that raised between two barriers would leave its peers waiting for
+        the limit of theirs."""
+        if not (hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.dim() == 2 and hidden.is_contiguous()
+                and hidden.shape[1] == self.H and hidden.data_ptr() % 16 == 0):
+            raise ValueError(f"EpPeerExchange: hidden must be a contiguous, 16-byte aligned bf16 [T, {self.H}] CUDA tensor")
+        if hidden.shape[0] * self.k != self.P:
+            raise ValueError(f"EpPeerExchange: built for {self.P // self.k} tokens per rank, got {hidden.shape[0]}")
+        if not (logits.is_cuda and logits.dim() == 2 and tuple(logits.shape) == (hidden.shape[0], self.E)):
+            raise ValueError(f"EpPeerExchange: logits must be a CUDA tensor [{hidden.shape[0]}, {self.E}]")
 
     def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
         from . import capi
         lib = capi.lib
         st = torch.cuda.current_stream().cuda_stream
         p = lambda t: t.data_ptr()
+        self.check_inputs(hidden, logits)
         idx, w = route(logits, self.k)
         offs, perm, inv = permutation(idx, self.E)
         counts, counts_ptrs = self.b["counts"]
@@ -176,7 +214,7 @@ class EpPeerExchange:
         capi.check(lib.lsg_ep_plan(p(counts), self.rank, self.world, self.E, self.cap, p(self.send_base),
                                    p(self.local_offsets), p(self.dst_start), p(self.ret_base), p(self.info), st))
         capi.check(lib.lsg_ep_send_rows(p(hidden), p(perm), p(offs), p(self.send_base), self.P, self.k, self.H,
-                                        self.E, self.world, p(recv_ptrs), self.cap, st))
+                                        self.E, self.world, p(recv_ptrs), self.cap, p(back), st))
         self.barrier()
         y = expert_ffn(recv, self.local_offsets)
         capi.check(lib.lsg_ep_return_rows(p(y), p(self.dst_start), p(self.ret_base), p(self.info), self.world,
@@ -185,7 +223,10 @@ class EpPeerExchange:
         return unpermute(back, inv, w)
 
     def overflowed(self):
-        """True if some rank's receive buffer was too small in the last layer (synchronizes)."""
+        """True if some rank's receive buffer was too small in the last layer (synchronizes).
+        The same condition leaves code 7 in the device status word (capi.device_status()), so
+        a caller that checks the status after a run needs no extra call; rows that did not fit
+        contributed zeros."""
         return bool(self.info[1].item())
 
 
@@ -213,15 +254,16 @@ class ColumnSplitPeer:
         self.out = symm.empty((M, N), dtype=dtype, device=dev)
         self._h = symm.rendezvous(self.out, group)
         self.ptrs = torch.tensor([int(p) for p in self._h.buffer_ptrs], dtype=torch.int64, device=dev)
+        self.barrier = FlagBarrier(group)
 
     def gemm(self, A, slab, type, K):
         """A [M, K] bf16 (replicated), slab = this rank's packed rows [N / world, ...] -> the
         full [M, N] product on every rank (the returned tensor is reused by the next call)."""
         from . import ops
         n0, n1 = column_slab(self.rank, self.world, self.N)
-        self._h.barrier(0)   # every rank is done reading the previous product
+        self.barrier()   # every rank is done reading the previous product
         ops.gguf_mmq_gather(A, slab, type, n1 - n0, K, self.ptrs, self.N, n0, out_dtype=self.out.dtype)
-        self._h.barrier(0)   # every slab has landed everywhere
+        self.barrier()   # every slab has landed everywhere
         return self.out
 
 

@@ -175,8 +175,12 @@ class HostMmvqBatch:
         self._ws = ctypes.c_void_p(workspace.data_ptr())
         self._ws_bytes = workspace.numel()
 
-    def _enqueue(self):
+    def enqueue(self):
+        """Enqueues the batch on the current stream (one C call) and returns without waiting;
+        usable inside a stream capture, e.g. to record several batches into one graph."""
         capi.check(_lib.lsg_gguf_mmvq_host_batch(self._arr, self._n, self._ws, self._ws_bytes, _stream()))
+
+    _enqueue = enqueue
 
     def capture(self):
         """Record the batch into a CUDA graph; run() then replays it (one launch from the
@@ -370,13 +374,14 @@ def silu_mul_to_nvfp4_grouped(gate, up, expert_offsets, input_scales=None):
 # Grouped (MoE) GEMM
 # ---------------------------------------------------------------------------
 def gguf_grouped_gemm(A_base, expert_offsets, b_ptrs, type, strategy, N, K, force=0,
-                      out_dtype=torch.bfloat16):
+                      out_dtype=torch.bfloat16, out=None):
     """One MoE projection over E experts: rows [offsets[e], offsets[e+1]) of A_base times
     decode(weight e)^T.  `b_ptrs` is a CUDA int64 tensor of device pointers.
     strategy: 0 = Dequant, 1 = Int; force: 0 auto, 1 mmvq, 2 mmq, 3 host loop.
 
     Mirrors gguf_grouped_gemm (csrc/bindings_python.cu:553-604): the output comes from
-    torch.empty, so rows of empty or skipped experts are uninitialised.
+    torch.empty, so rows of empty or skipped experts are uninitialised.  `out` (not in the
+    reference) names a caller-owned contiguous [T, N] tensor to write instead.
     """
     _require(A_base.is_cuda and A_base.dtype == torch.bfloat16,
              "gguf_grouped_gemm: A_base must be BF16 on CUDA")
@@ -390,7 +395,13 @@ def gguf_grouped_gemm(A_base, expert_offsets, b_ptrs, type, strategy, N, K, forc
     E = b_ptrs.numel()
     _require(expert_offsets.numel() == E + 1,
              "gguf_grouped_gemm: expert_offsets must be [num_experts+1]")
-    D = torch.empty((T, N), dtype=out_dtype, device=A_base.device)
+    if out is not None:
+        _require(out.is_cuda and out.is_contiguous() and tuple(out.shape) == (T, N)
+                 and out.dtype in (torch.bfloat16, torch.float32),
+                 "gguf_grouped_gemm: out must be a contiguous bf16 or f32 [T, N] CUDA tensor")
+        D, out_dtype = out, out.dtype
+    else:
+        D = torch.empty((T, N), dtype=out_dtype, device=A_base.device)
     p = capi.GgufGroupedGemmParams(
         type=int(type), strategy=int(strategy), num_experts=E, N=int(N), K=int(K),
         A_base=A_base.data_ptr(), D_base=D.data_ptr(), expert_offsets=expert_offsets.data_ptr(),

@@ -13,7 +13,7 @@ These run offline, once per weight; they are not on the hot path.
 """
 import numpy as np
 
-from .capi import BLOCK_BYTES, BLOCK_VALUES, GGUF_TYPES, Q4_K, Q6_K, Q8_0, Q4_0  # noqa: F401
+from .formats import BLOCK_BYTES, BLOCK_VALUES, GGUF_TYPES, Q4_K, Q6_K, Q8_0, Q4_0  # noqa: F401
 
 
 def _f16_bytes(x):

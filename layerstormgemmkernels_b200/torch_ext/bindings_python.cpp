@@ -32,12 +32,6 @@ int parse_output_dtype(const std::string& s, at::ScalarType* t) {
     return LSG_DTYPE_BF16;
 }
 
-[[noreturn]] void not_built(const char* name) {
-    throw std::runtime_error(std::string(name) +
-                             ": this operator is not part of the B200 build yet "
-                             "(FP8 GEMM family, single NVFP4 GEMM and the legacy Q4_K GEMMs)");
-}
-
 }  // namespace
 
 std::tuple<torch::Tensor, torch::Tensor> dynamic_fp8_quant(torch::Tensor input, bool m_major_scales) {

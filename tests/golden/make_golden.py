@@ -65,4 +65,7 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LSG_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py <reference checkout>   (or set LSG_REFERENCE_ROOT)")
+    main(root)

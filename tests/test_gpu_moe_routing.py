@@ -126,7 +126,7 @@ def test_ep_peer_exchange_kernels_emulated_ranks(ops, world, E, T, k):
         plans.append((sb, lo, ds, rb, info))
         idx, w, offs, perm, inv = routed[r]
         capi.check(lib.lsg_ep_send_rows(hidden[r].data_ptr(), perm.data_ptr(), offs.data_ptr(), sb.data_ptr(), P, k,
-                                        H, E, world, rp.data_ptr(), cap, st))
+                                        H, E, world, rp.data_ptr(), cap, back[r].data_ptr(), st))
     for r in range(world):
         sb, lo, ds, rb, info = plans[r]
         assert info.tolist()[1] == 0
@@ -147,3 +147,126 @@ def test_ep_peer_exchange_kernels_emulated_ranks(ops, world, E, T, k):
         tok = pair // k
         exp = (hidden[r].float().cpu()[tok] * torch.from_numpy((e_of_row + 1).astype(np.float32))[:, None]).to(torch.bfloat16)
         assert torch.equal(back[r].cpu(), exp)
+
+
+def test_ep_peer_exchange_overflow_is_clamped_and_reported(ops):
+    """Receive buffers smaller than what the ranks send: every offset the plan writes stays
+    within the capacity, rows that do not fit are dropped at the sender and their slots of the
+    return buffer cleared, nothing is written past the buffers (canary rows), and the device
+    status word reports code 7.  Ranks emulated one after the other on this GPU."""
+    from layerstormgemmkernels_b200 import capi
+    lib = capi.lib
+    world, E, T, k, H = 2, 8, 64, 2, 64
+    P, per = T * k, E // world
+    cap = 40                                     # far below the ~64 rows each rank receives
+    canary = 8
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(7)
+    dev = "cuda"
+    hidden = [torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev) for _ in range(world)]
+    logits = [torch.randn(T, E, generator=g).to(dev) for _ in range(world)]
+    counts = [torch.zeros(world, E, dtype=torch.int32, device=dev) for _ in range(world)]
+    recv = [torch.full((cap + canary, H), 7.0, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    back = [torch.full((P + canary, H), 9.0, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    ptrs = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    cp, rp, bp = ptrs(counts), ptrs(recv), ptrs(back)
+    assert capi.device_status() == 0
+    routed = []
+    for r in range(world):
+        idx, w = ops.moe_route(logits[r], k)
+        offs, perm, inv = ops.moe_permutation(idx, E)
+        routed.append((idx, w, offs, perm, inv))
+        capi.check(lib.lsg_ep_publish_counts(offs.data_ptr(), E, r, world, cp.data_ptr(), st))
+    plans = []
+    for r in range(world):
+        sb = torch.empty(E, dtype=torch.int32, device=dev)
+        lo = torch.empty(per + 1, dtype=torch.int32, device=dev)
+        ds = torch.empty(E, dtype=torch.int32, device=dev)
+        rb = torch.empty(E, dtype=torch.int32, device=dev)
+        info = torch.zeros(2, dtype=torch.int32, device=dev)
+        capi.check(lib.lsg_ep_plan(counts[r].data_ptr(), r, world, E, cap, sb.data_ptr(), lo.data_ptr(),
+                                   ds.data_ptr(), rb.data_ptr(), info.data_ptr(), st))
+        plans.append((sb, lo, ds, rb, info))
+        idx, w, offs, perm, inv = routed[r]
+        capi.check(lib.lsg_ep_send_rows(hidden[r].data_ptr(), perm.data_ptr(), offs.data_ptr(), sb.data_ptr(), P, k,
+                                        H, E, world, rp.data_ptr(), cap, back[r].data_ptr(), st))
+    dropped_total = 0
+    for r in range(world):
+        sb, lo, ds, rb, info = plans[r]
+        rows, flag = info.tolist()
+        assert flag == 1 and rows <= cap
+        lo_h = lo.cpu().numpy()
+        assert (np.diff(lo_h) >= 0).all() and lo_h[-1] == rows and lo_h.max() <= cap
+        assert int(ds.max().item()) <= cap
+        # the expert block on the clamped offsets: a grouped GEMM call must stay inside its rows
+        y = recv[r][:cap].clone()
+        capi.check(lib.lsg_ep_return_rows(y.data_ptr(), ds.data_ptr(), rb.data_ptr(), info.data_ptr(), world, per, H,
+                                          cap, bp.data_ptr(), st))
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.all(recv[r][cap:] == 7.0), "rows were written past the receive buffer"
+        assert torch.all(back[r][P:] == 9.0), "rows were written past the return buffer"
+        # every slot of the return buffer was either filled by a peer or cleared by the sender
+        idx, w, offs, perm, inv = routed[r]
+        tok = perm.cpu().numpy() // k
+        got = back[r][:P].cpu()
+        exp = hidden[r].cpu()[tok]
+        same = (got == exp).all(dim=1)
+        zero = (got == 0).all(dim=1)
+        assert bool((same | zero).all())
+        dropped_total += int((zero & ~same).sum())
+    assert dropped_total > 0
+    assert capi.device_status() == 7             # expert-parallel overflow, read and cleared
+    assert capi.device_status() == 0
+
+
+def test_grouped_gemm_ignores_offsets_past_its_rows(ops):
+    """Expert offsets that run past the rows of the call (what an overflowed exchange would
+    have produced without the clamp): the tensor-core grouped GEMM must not touch anything
+    beyond its total_tokens rows."""
+    from layerstormgemmkernels_b200 import capi, quantize as Q
+    E, N, K, T = 4, 256, 512, 300
+    rng = np.random.default_rng(3)
+    Ws = [torch.from_numpy(Q.quantize_q4_k((rng.standard_normal((N, K)) * 0.02).astype(np.float32))).cuda()
+          for _ in range(E)]
+    b_ptrs = torch.tensor([w.data_ptr() for w in Ws], dtype=torch.int64, device="cuda")
+    A = torch.randn(T, K, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    good = torch.tensor([0, 100, 100, 220, 300], dtype=torch.int32, device="cuda")
+    bad = torch.tensor([0, 100, 100, 220, 900], dtype=torch.int32, device="cuda")     # last expert claims 680 rows
+    ref = ops.gguf_grouped_gemm(A, good, b_ptrs, capi.Q4_K, 1, N, K, force=2)
+    out = torch.full((T + 64, N), 3.0, dtype=torch.bfloat16, device="cuda")
+    ops.gguf_grouped_gemm(A, bad, b_ptrs, capi.Q4_K, 1, N, K, force=2, out=out[:T])
+    torch.cuda.synchronize()
+    assert torch.all(out[T:] == 3.0), "the GEMM wrote past its rows"
+    assert torch.equal(out[:T], ref)
+    assert capi.device_status() == 0
+
+
+def test_flag_barrier_emulated_ranks_and_timeout(ops):
+    """lsg_ep_barrier with two ranks emulated on this GPU (flag arrays are local tensors).
+    A kernel never waits for a kernel launched after it here: rank 1 arrives without waiting,
+    then rank 0 arrives and waits (succeeds at once), then rank 1 waits.  After that rank 0
+    arrives at a second barrier that rank 1 never reaches: with a short limit the wait gives
+    up, the status word reports code 6, and the context stays usable."""
+    from layerstormgemmkernels_b200 import capi
+    lib = capi.lib
+    world = 2
+    flags = [torch.zeros(world + 1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert capi.device_status() == 0
+    capi.check(lib.lsg_ep_barrier(ptrs.data_ptr(), 1, world, 1, st))     # rank 1 arrives
+    capi.check(lib.lsg_ep_barrier(ptrs.data_ptr(), 0, world, 3, st))     # rank 0 arrives and waits
+    capi.check(lib.lsg_ep_barrier(ptrs.data_ptr(), 1, world, 2, st))     # rank 1 waits
+    assert capi.device_status() == 0
+    assert flags[0].tolist() == [1, 1, 1] and flags[1].tolist() == [1, 1, 1]
+    capi.check(lib.lsg_set_wait_limit_cycles(500000))                     # a quarter of a millisecond
+    try:
+        capi.check(lib.lsg_ep_barrier(ptrs.data_ptr(), 0, world, 3, st))  # rank 1 never comes
+        assert capi.device_status() == 6
+    finally:
+        capi.check(lib.lsg_set_wait_limit_cycles(0))
+    assert capi.device_status() == 0
+    assert float(torch.ones(4, device="cuda").sum().item()) == 4.0
+    with pytest.raises(ValueError):
+        capi.check(lib.lsg_ep_barrier(ptrs.data_ptr(), 2, world, 3, st))
