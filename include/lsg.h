@@ -150,8 +150,11 @@ LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, vo
  * LSG_NOALLOC_MAX_Q8_1_BYTES, otherwise LSG_ERR_WORKSPACE.  The first call on a device
  * resolves the array's address: make it before any stream capture.  All calls share the
  * array (nothing in it needs clearing; each call rewrites what it reads), so calls whose
- * kernels may overlap on the GPU must be ordered by the caller.  This entry point has no
- * counterpart in the reference, whose launchers always take a caller workspace. */
+ * kernels may overlap on the GPU must be ordered by the caller.  The resolved address is
+ * remembered per device ordinal and belongs to the device's primary context: call this only
+ * under the primary context (what the runtime API and PyTorch use), and not across a
+ * cudaDeviceReset.  This entry point has no counterpart in the reference, whose launchers
+ * always take a caller workspace. */
 #define LSG_NOALLOC_MAX_Q8_1_BYTES 147456
 LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
 
@@ -470,7 +473,9 @@ typedef struct lsg_nvfp4_grouped_gemm_params {
  * (csrc/smxx/quant/bf16_to_nvfp4.cu:76-140), query_nvfp4_gemm_workspace_size and
  * launch_nvfp4_gemm (csrc/sm120/gemm/nvfp4/nvfp4_gemm.cu:189-200).  Scale buffers use the
  * interleaved layout of lsg_nvfp4_sf_buffer_bytes(rows, K); the quantizer does not write the
- * padding entries (callers zero the buffer first, as the reference's binding does). */
+ * padding entries (callers zero the buffer first, as the reference's binding does).  The GEMM
+ * takes the block-scaled tensor-core instruction when K is a multiple of 64 and the four
+ * buffers are 16-byte aligned (no workspace is touched then), else the fp16 expansion. */
 LSG_API int lsg_bf16_to_nvfp4(const void* x_bf16, void* output_packed, void* output_scales, int M, int K,
                               void* stream);
 /* NVFP4 weight -> bf16: codes [N, K/2], RAW row-major ue4m3 group scales [N, K/16] (not the
@@ -492,9 +497,15 @@ LSG_API size_t lsg_nvfp4_gemm_workspace_bytes(int M, int N, int K);
 LSG_API int lsg_nvfp4_gemm(const lsg_nvfp4_gemm_params* p, void* workspace, size_t workspace_bytes,
                            void* stream);
 
-/* Replaces query_nvfp4_grouped_gemm_workspace_size (nvfp4_grouped_gemm.cu:373-384); needs
- * the row count because this implementation expands the operands to fp16 in the workspace. */
+/* Replaces query_nvfp4_grouped_gemm_workspace_size (nvfp4_grouped_gemm.cu:373-384).  The
+ * operator runs on tcgen05.mma.kind::mxf4nvf4.block_scale straight from the caller's packed
+ * buffers and then needs only the token-tile map (a few KB).  Calls that cannot take that
+ * route - weight pointer arrays (B_ptrs / scale_B_ptrs), K not a multiple of 64, operands or
+ * scale buffers that are not 16-byte aligned - expand both operands to fp16 in the workspace
+ * and need the `_ex(..., 1)` size (total_tokens*K*2 + num_experts*N*K*2 bytes more). */
 LSG_API size_t lsg_nvfp4_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K);
+LSG_API size_t lsg_nvfp4_grouped_gemm_workspace_bytes_ex(int total_tokens, int num_experts, int N, int K,
+                                                         int expanded);
 
 /* Replaces launch_nvfp4_grouped_gemm, nvfp4_grouped_gemm.cu:386-423.  Device-routed (no
  * host synchronization); rows of empty experts are left untouched. */

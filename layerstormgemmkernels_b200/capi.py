@@ -153,6 +153,7 @@ def _load():
         "lsg_gguf_mmq_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_mmq": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_nvfp4_grouped_gemm_workspace_bytes": (sz, [ci, ci, ci, ci]),
+        "lsg_nvfp4_grouped_gemm_workspace_bytes_ex": (sz, [ci, ci, ci, ci, ci]),
         "lsg_nvfp4_grouped_gemm": (ci, [ctypes.POINTER(Nvfp4GroupedGemmParams), ci, vp, sz, vp]),
         "lsg_nvfp4_sf_buffer_bytes": (sz, [ci, ci]),
         "lsg_nvfp4_reformat_scales": (ci, [vp, vp, ci, ci, vp]),

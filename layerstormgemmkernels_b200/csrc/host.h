@@ -45,6 +45,13 @@ int tc_gemm_f16(const void* A16, long long a_rows, const void* B16, long long b_
                 const int* tile_mstart, int t_max, const int32_t* expert_offsets, cudaStream_t s,
                 float alpha_host = 1.0f);
 
+// NVFP4 GEMM on tcgen05.mma.kind::mxf4nvf4.block_scale (nvfp4_mma.cu).
+bool nvfp4_mma_usable(const void* A, const void* B, const void* sfa, const void* sfb, int K);
+int nvfp4_mma(const void* A, long long a_rows, const void* B, long long b_rows, const void* sfa, const void* sfb,
+              long long sfb_expert_bytes, int K, int N, void* D, int out_dtype, const float* alphas, float alpha_host,
+              int M, const int* tile_expert, const int* tile_mstart, int t_max, const int32_t* expert_offsets,
+              const int32_t* sf_offsets, cudaStream_t s);
+
 // Tensor-core GEMM with in-kernel weight decoding (tc_fused.cu).
 bool tc_fused_available(int type);
 bool tc_fused_forced();   // weight path 2: every call takes the fused kernel

@@ -22,7 +22,6 @@ MmvqTune& tuning() {
         if (const char* e = getenv("LSG_MMVQ_SHARE")) v.share = atoi(e);
 #ifdef LSG_DEBUG_KNOBS
         if (getenv("LSG_MMVQ_SKIP")) v.skip_math = 1;
-        if (const char* e = getenv("LSG_MMVQ_DBG")) v.skip_math |= atoi(e);
 #endif
         return v;
     }();

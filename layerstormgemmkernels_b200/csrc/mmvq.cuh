@@ -29,7 +29,7 @@
 
 namespace lsg {
 
-constexpr int kMmvqMaxStages = 32;
+constexpr int kMmvqMaxStages = 8;
 constexpr int kMmvqMaxExtra = 3;
 
 struct MmvqArgs {
@@ -176,186 +176,89 @@ __device__ __forceinline__ void build_x_image(uint8_t* img, const uint8_t* __res
 
 // Same image straight from bf16 activations: the Q8_1 quantization of
 // quantize_q8_1_kernel (d = amax/127, q = rn(x/d), d then rounded to fp16) done per CTA,
-// without the round trip through global memory and without a launch of its own.  Values are
-// identical to the quantizer kernel's: max and the per-element division do not depend on the
-// lane layout, and the block sum of the original values (the only order-dependent field of a
-// Q8_1 block) is not used by the mat-vec.
-//
-// This runs on the critical path of every launch (the consumers cannot start before it) and
-// every CTA repeats it.  It runs once per launch, so its instructions are fetched cold: what
-// it costs is the number of DIFFERENT instructions on the path (measured: wider, unrolled
-// variants that did the same arithmetic in fewer passes were no faster, in step with their
-// code size), plus one global-load latency.  So:
-//   * a task is eight values (one 16-byte load per thread, LPB = 4 lanes to a 32-value
-//     block), and a thread walks its tasks tid, tid + nthreads, ... in a rolled loop whose
-//     body is fetched once (the wider LPB = 2 and 1 forms are kept for reference);
-//   * rn(x * (1/d)) comes from adding 1.5 * 2^23: the sum's low mantissa bits are the rounded
-//     integer (two's complement in the low byte), the difference to the magic constant is the
-//     same integer as a float, so neither a float-to-int nor an int-to-float conversion is
-//     issued; the bytes are gathered with byte permutes and summed with dp4a;
-//   * x * fl(1/d) is within 2.3e-5 of fl(x/d) for |x/d| <= 127, so rounding it gives the
-//     integer the reference's rn(x / d) gives unless it lies within 1e-4 of a half-integer;
-//     a thread that holds such a value (about one in 600 tasks of eight) redoes its values
-//     with true divisions in an out-of-line branch.
-// The rows of A are contiguous, so the blocks of all M rows are numbered straight through.
-static __device__ __noinline__ uint2 q8_exact_quotients(uint4 raw, float d) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    uint32_t q[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        q[2 * i] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(w[i] << 16) / d)) & 0xFFu;
-        q[2 * i + 1] = static_cast<uint32_t>(__float2int_rn(__uint_as_float(w[i] & 0xFFFF0000u) / d)) & 0xFFu;
-    }
-    return make_uint2(q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24), q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24));
-}
-
-// One task: part `task % LPB` of block `task / LPB`.  All lanes of a warp call this together
-// (the shuffles need them); `live` masks the stores of lanes past the end.
-template <int T, int LPB>
-__device__ __forceinline__ void x_image_task(uint8_t* img, const uint4* __restrict__ src, int task, bool live, int K,
-                                             int dbg = 0) {
-    using D = Mmvq<T>;
-    constexpr int UVB = D::UV / 32;
-    constexpr int NL = 4 / LPB;            // 16-byte loads (groups of eight values) per thread
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    const int nb = K / 32;
-    const int U = K / D::UV;
-    uint4 raw[NL];
-    // plain (coherent) loads: under programmatic dependent launch A may have been written
-    // while this kernel was already resident
-#pragma unroll
-    for (int j = 0; j < NL; ++j) {
-#ifdef LSG_DEBUG_KNOBS
-        if (dbg & 4) {
-            uint64_t pol;
-            asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-            asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
-                         : "=r"(raw[j].x), "=r"(raw[j].y), "=r"(raw[j].z), "=r"(raw[j].w)
-                         : "l"(src + static_cast<size_t>(task) * NL + j), "l"(pol));
-            continue;
-        }
-#endif
-        raw[j] = __ldcg(src + static_cast<size_t>(task) * NL + j);
-    }
-    float x[NL][8];
-    float amax = 0.0f;
-#pragma unroll
-    for (int j = 0; j < NL; ++j) {
-        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            x[j][2 * i] = __uint_as_float(w[i] << 16);
-            x[j][2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[j][i]));
-    }
-    if (LPB >= 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    if (LPB >= 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float d = amax / 127.0f;
-    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-    uint2 packed[NL];
-    int sum8[NL];
-#pragma unroll
-    for (int j = 0; j < NL; ++j) {
-        uint32_t bits[8];
-        float emax = 0.0f;  // largest distance of a quotient from its rounded integer (<= 0.5)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float tq = x[j][i] * rcp;
-            const float tm = tq + kMagic;  // low mantissa bits = rn(tq)
-            const float kf = tm - kMagic;  // the same integer, as a float (exact)
-            emax = fmaxf(emax, fabsf(tq - kf));
-            bits[i] = __float_as_uint(tm);
-        }
-        packed[j].x = __byte_perm(__byte_perm(bits[0], bits[1], 0x0040), __byte_perm(bits[2], bits[3], 0x0040), 0x5410);
-        packed[j].y = __byte_perm(__byte_perm(bits[4], bits[5], 0x0040), __byte_perm(bits[6], bits[7], 0x0040), 0x5410);
-        if (emax > 0.4999f) packed[j] = q8_exact_quotients(raw[j], d);
-        sum8[j] = __dp4a(static_cast<int>(packed[j].x), 0x01010101, __dp4a(static_cast<int>(packed[j].y), 0x01010101, 0));
-    }
-    // sums of the 16-value halves this thread can see, and of the whole block
-    int sum16_a, sum16_b = 0, sum32;
-    if (LPB == 1) {
-        sum16_a = sum8[0] + sum8[NL > 1 ? 1 : 0];
-        sum16_b = sum8[NL > 2 ? 2 : 0] + sum8[NL > 3 ? 3 : 0];
-        sum32 = sum16_a + sum16_b;
-    } else if (LPB == 2) {
-        sum16_a = sum8[0] + sum8[NL > 1 ? 1 : 0];
-        sum32 = sum16_a + __shfl_xor_sync(0xffffffffu, sum16_a, 1);
-    } else {
-        sum16_a = sum8[0] + __shfl_xor_sync(0xffffffffu, sum8[0], 1);
-        sum32 = sum16_a + __shfl_xor_sync(0xffffffffu, sum16_a, 2);
-    }
-    if (!live) return;
-    const float dh = __half2float(__float2half(d));  // the mat-vec sees the fp16-rounded scale
-    const int part = task % LPB;
-    int b = task / LPB, m = 0;
-    while (b >= nb) {  // M is at most a handful of rows here
-        b -= nb;
-        ++m;
-    }
-    uint8_t* row = img + static_cast<size_t>(m) * x_row_bytes<T>(K);
-    uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
-    uint32_t* svec = dvec + nb;
-    const int u = b / UVB, jb = b % UVB;
-    // 16-byte piece `2 * jb + half` of unit u holds the sixteen values of that half
-    auto piece = [&](int half) { return row + (static_cast<size_t>(2 * jb + half) * U + u) * 16; };
-    if (LPB == 1) {
-        *reinterpret_cast<uint4*>(piece(0)) = make_uint4(packed[0].x, packed[0].y, packed[NL > 1 ? 1 : 0].x, packed[NL > 1 ? 1 : 0].y);
-        *reinterpret_cast<uint4*>(piece(1)) = make_uint4(packed[NL > 2 ? 2 : 0].x, packed[NL > 2 ? 2 : 0].y,
-                                                         packed[NL > 3 ? 3 : 0].x, packed[NL > 3 ? 3 : 0].y);
-    } else if (LPB == 2) {
-        *reinterpret_cast<uint4*>(piece(part)) = make_uint4(packed[0].x, packed[0].y, packed[NL > 1 ? 1 : 0].x, packed[NL > 1 ? 1 : 0].y);
-    } else {
-        *reinterpret_cast<uint2*>(piece(part >> 1) + (part & 1) * 8) = packed[0];
-    }
-    if (part == 0) {
-        if (UVB >= 4) dvec[((jb >> 2) * U + u) * 4 + (jb & 3)] = __float_as_uint(dh);
-        else dvec[u] = __float_as_uint(dh);
-        if (D::SUM == kSumF32Per32) {
-            const uint32_t v = __float_as_uint(dh * static_cast<float>(sum32));
-            if (UVB >= 4) svec[((jb >> 2) * U + u) * 4 + (jb & 3)] = v;
-            else svec[u] = v;
-        }
-    }
-    if (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16) {
-        auto put16 = [&](int half, int s16) {
-            const int e = 2 * jb + half;
-            svec[((e >> 2) * U + u) * 4 + (e & 3)] = (D::SUM == kSumI32Per16)
-                                                         ? static_cast<uint32_t>(s16)
-                                                         : __float_as_uint(dh * static_cast<float>(s16));
-        };
-        if (LPB == 1) {
-            put16(0, sum16_a);
-            put16(1, sum16_b);
-        } else if (LPB == 2) {
-            put16(part, sum16_a);
-        } else if ((part & 1) == 0) {
-            put16(part >> 1, sum16_a);
-        }
-    }
-}
-
-template <int T, int LPB>
-__device__ __forceinline__ void x_image_pass(uint8_t* img, const uint4* __restrict__ src, int total_blocks, int K,
-                                             int tid, int nthreads, int dbg = 0) {
-    const int total = total_blocks * LPB;
-    const int warp_first = tid & ~31;
-#pragma unroll 1
-    for (int base = 0; base + warp_first < total; base += nthreads) {
-        const int task = base + tid;
-        x_image_task<T, LPB>(img, src, min(task, total - 1), task < total, K, dbg);
-    }
-}
-
+// without the round trip through global memory and without a launch of its own.  Four
+// lanes share a 32-value block, eight values each.  Values are identical to the
+// quantizer kernel's: max and the per-element division do not depend on the lane layout,
+// and the block sum of the original values (the only order-dependent field of a Q8_1
+// block) is not used by the mat-vec.
 template <int T>
 __device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bfloat16* __restrict__ A,
-                                                   int M, int K, int tid, int nthreads, int dbg = 0) {
-    const int blocks = M * (K / 32);
-    const uint4* src = reinterpret_cast<const uint4*>(A);
-    if (blocks * 4 <= nthreads) x_image_pass<T, 4>(img, src, blocks, K, tid, nthreads, dbg);
-    else if (blocks * 2 <= nthreads) x_image_pass<T, 2>(img, src, blocks, K, tid, nthreads, dbg);
-    else x_image_pass<T, 1>(img, src, blocks, K, tid, nthreads, dbg);
+                                                   int M, int K, int tid, int nthreads) {
+    using D = Mmvq<T>;
+    constexpr int UVB = D::UV / 32;
+    const int nb = K / 32;
+    const int U = K / D::UV;
+    const int rowb = x_row_bytes<T>(K);
+    // Two lanes per 32-value block, sixteen values (two 16-byte loads) per lane: a 4096-wide
+    // row is one trip of 256 tasks for the consumer threads, and the only index arithmetic is
+    // shifts and divisions by compile-time constants.
+    const int tasks = nb * 2;
+    for (int m = 0; m < M; ++m) {
+        const uint4* src = reinterpret_cast<const uint4*>(A + static_cast<size_t>(m) * K);
+        uint8_t* row = img + static_cast<size_t>(m) * rowb;
+        uint32_t* dvec = reinterpret_cast<uint32_t*>(row + K);
+        uint32_t* svec = dvec + nb;
+        for (int t0 = 0; t0 < tasks; t0 += nthreads) {
+            const int idx = t0 + tid;
+            const bool live = idx < tasks;
+            const int task = live ? idx : 0;
+            const uint4 r0 = __ldg(src + 2 * task), r1 = __ldg(src + 2 * task + 1);
+            const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                x[2 * i] = __uint_as_float(w[i] << 16);
+                x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            const float d = amax / 127.0f;
+            // q = rn(fl(x / d)) as the reference computes it, without sixteen IEEE divisions:
+            // x * fl(1/d) is within 2.3e-5 of fl(x/d) for |x/d| <= 127, so rounding it gives
+            // the same integer unless it lies within 1e-4 of a half-integer; only then
+            // (about one value in 5000) is the true quotient formed.
+            const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+            int q[16];
+            int sum16 = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float t = x[i] * rcp;
+                int k = __float2int_rn(t);
+                if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x[i] / d);
+                q[i] = k;
+                sum16 += k;
+            }
+            const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 1);
+            if (!live) continue;
+            uint4 packed;
+            packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
+            packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+            packed.z = (q[8] & 0xFF) | ((q[9] & 0xFF) << 8) | ((q[10] & 0xFF) << 16) | ((q[11] & 0xFF) << 24);
+            packed.w = (q[12] & 0xFF) | ((q[13] & 0xFF) << 8) | ((q[14] & 0xFF) << 16) | ((q[15] & 0xFF) << 24);
+            const float dh = __half2float(__float2half(d));  // the mat-vec sees the fp16-rounded scale
+            const int half = task & 1;
+            const int b = task >> 1;
+            const int u = b / UVB, jb = b % UVB;
+            *reinterpret_cast<uint4*>(row + (static_cast<size_t>(2 * jb + half) * U + u) * 16) = packed;
+            if (half == 0) {
+                if (UVB >= 4) dvec[((jb >> 2) * U + u) * 4 + (jb & 3)] = __float_as_uint(dh);
+                else dvec[u] = __float_as_uint(dh);
+                if (D::SUM == kSumF32Per32) {
+                    const uint32_t v = __float_as_uint(dh * static_cast<float>(sum32));
+                    if (UVB >= 4) svec[((jb >> 2) * U + u) * 4 + (jb & 3)] = v;
+                    else svec[u] = v;
+                }
+            }
+            if (D::SUM == kSumF32Per16 || D::SUM == kSumI32Per16) {
+                const int e = 2 * jb + half;
+                const uint32_t v = (D::SUM == kSumI32Per16) ? static_cast<uint32_t>(sum16)
+                                                            : __float_as_uint(dh * static_cast<float>(sum16));
+                svec[((e >> 2) * U + u) * 4 + (e & 3)] = v;
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -455,17 +358,13 @@ __device__ __forceinline__ void group_dot_store(const uint32_t (&raddr)[RW], con
 #endif
 
 #ifdef LSG_DEBUG_KNOBS
-#define LSG_SKIP_MATH(a) (((a).debug_skip & 1) != 0)
+#define LSG_SKIP_MATH(a) ((a).debug_skip != 0)
 #else
 #define LSG_SKIP_MATH(a) false
 #endif
 
-// Batch 1 is compiled for two CTAs per SM (64 registers; it needs no more): a launch whose
-// CTAs leave shared memory free then shares the SMs with the next launch of the stream, whose
-// prologue and first weights overlap this one's tail (programmatic dependent launch).  The
-// wider batch tiles keep all 128 registers.
 template <int T, int MT, int RW, int L>
-__global__ void __launch_bounds__(512, (MT == 1 ? 2 : 1)) mmvq_kernel(const MmvqArgs a) {
+__global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     using D = Mmvq<T>;
     constexpr int SUBS = 32 / L;    // lane groups per warp
     constexpr int RPP = SUBS * RW;  // rows per warp pass
@@ -516,9 +415,7 @@ __global__ void __launch_bounds__(512, (MT == 1 ? 2 : 1)) mmvq_kernel(const Mmvq
         }
         *next_group = 0;
         for (int s = 0; s < kMmvqMaxStages; ++s) slab_in_stage[s] = -1;
-#ifdef LSG_DEBUG_KNOBS
-        *(slab_in_stage + kMmvqMaxStages) = 0;
-#endif
+
         mbar_fence_init();
     }
     __syncthreads();
@@ -531,12 +428,6 @@ __global__ void __launch_bounds__(512, (MT == 1 ? 2 : 1)) mmvq_kernel(const Mmvq
         // previous kernel in the stream.
         // ------------------------------------------------------------------
         if (lane == 0) {
-#ifdef LSG_DEBUG_KNOBS
-            if (a.debug_skip & 2) {
-                volatile int* img_done = slab_in_stage + kMmvqMaxStages;
-                while (*img_done == 0) __nanosleep(50);
-            }
-#endif
             const uint64_t policy = l2_policy_evict_first();
             const uintptr_t w_base = reinterpret_cast<uintptr_t>(Wm);
             const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(Nm) * a.row_bytes) & ~uintptr_t(15);
@@ -581,35 +472,13 @@ __global__ void __launch_bounds__(512, (MT == 1 ? 2 : 1)) mmvq_kernel(const Mmvq
     // ----------------------------------------------------------------------
     // Consumers
     // ----------------------------------------------------------------------
-    // The activations themselves may only be read after the wait below, but their address
-    // translation and their place in L2 can be prepared now: an L2 prefetch allocates nothing
-    // in L1, and L2 is where the previous kernel's writes land, so a line fetched early is
-    // still the current one when it is read.  (Measured: the first touch of the activation
-    // buffer after a layer's worth of streamed weights cost over a microsecond, on the
-    // critical path of every launch.)
     const int n_cons = n_cons_warps * 32;
-    {
-        const char* xsrc = a.A ? reinterpret_cast<const char*>(a.A) : reinterpret_cast<const char*>(a.xq);
-        const int xbytes = a.A ? a.M * a.K * 2 : a.M * (a.K / 32) * kQ8_1Bytes;
-#ifdef LSG_DEBUG_KNOBS
-        if (!(a.debug_skip & 8))
-#endif
-        for (int off = tid * 128; off < xbytes; off += n_cons * 128)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(xsrc + off));
-    }
     pdl_wait_prior();  // activations (and the output buffer) belong to the stream order
     if (tid == 0) LSG_TRACE(3);
-#ifdef LSG_DEBUG_KNOBS
-    if (a.A) build_x_image_bf16<T>(x_img, a.A, a.M, a.K, tid, n_cons, a.debug_skip);
-#else
     if (a.A) build_x_image_bf16<T>(x_img, a.A, a.M, a.K, tid, n_cons);
-#endif
     else build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
     asm volatile("bar.sync 1, %0;" ::"r"(n_cons) : "memory");
     if (tid == 0) LSG_TRACE(4);
-#ifdef LSG_DEBUG_KNOBS
-    if (tid == 0) *(slab_in_stage + kMmvqMaxStages) = 1;
-#endif
 
     const int sub = lane / L;
     XView xv;

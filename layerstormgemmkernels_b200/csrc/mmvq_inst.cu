@@ -24,10 +24,6 @@ int launch_variant(const MmvqArgs& a, int grid, size_t smem, cudaStream_t stream
     if (dev < 0 || dev >= 64 || !configured[dev]) {
         LSG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           kSmemCap));
-        // all of the SM's configurable memory as shared memory, so that two CTAs of
-        // consecutive launches fit whenever their rings do
-        LSG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                          cudaSharedmemCarveoutMaxShared));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     LSG_CUDA_TRY(launch_kernel(kernel, dim3(grid), dim3((a.cons_warps + 1) * 32), smem, stream, pdl, a));
@@ -97,7 +93,7 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
     a.cons_warps = tn.warps;
     a.debug_skip = tn.skip_math;
     a.x_bytes = ((a.M * x_row_bytes<T>(a.K) + 127) / 128) * 128;
-    const int bar_bytes = 2 * kMmvqMaxStages * 8 + 16 + kMmvqMaxStages * 4 + 16;
+    const int bar_bytes = 2 * kMmvqMaxStages * 8 + 16 + kMmvqMaxStages * 4;
 
     // lanes per weight row: the smallest power of two covering the units of a row
     int lanes = 4;

@@ -137,11 +137,21 @@ extern "C" int lsg_nvfp4_reformat_scales(const float* src, void* dst, int rows, 
     return LSG_OK;
 }
 
-extern "C" size_t lsg_nvfp4_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K) {
+// expanded != 0: room for the fp16 expansion of both operands (the route taken for weight
+// pointer arrays, K not a multiple of 64, or operands that are not 16-byte aligned);
+// otherwise only the tile map of the block-scaled tensor-core route.
+extern "C" size_t lsg_nvfp4_grouped_gemm_workspace_bytes_ex(int total_tokens, int num_experts, int N, int K,
+                                                            int expanded) {
     if (total_tokens <= 0 || num_experts <= 0 || N <= 0 || K <= 0) return 0;
     const int t_max = (total_tokens + 127) / 128 + num_experts;
-    return a256(2ull * t_max * 4) + a256(static_cast<size_t>(total_tokens) * K * 2) +
+    const size_t map_bytes = a256(2ull * t_max * 4);
+    if (!expanded && K % 64 == 0) return map_bytes;
+    return map_bytes + a256(static_cast<size_t>(total_tokens) * K * 2) +
            a256(static_cast<size_t>(num_experts) * N * K * 2);
+}
+
+extern "C" size_t lsg_nvfp4_grouped_gemm_workspace_bytes(int total_tokens, int num_experts, int N, int K) {
+    return lsg_nvfp4_grouped_gemm_workspace_bytes_ex(total_tokens, num_experts, N, K, 0);
 }
 
 extern "C" int lsg_nvfp4_grouped_gemm(const lsg_nvfp4_grouped_gemm_params* p, int total_tokens,
@@ -157,10 +167,15 @@ extern "C" int lsg_nvfp4_grouped_gemm(const lsg_nvfp4_grouped_gemm_params* p, in
     if (!p->A_base || (!p->B_base && !p->B_ptrs) || !p->D_base || !p->scale_A_base ||
         (!p->scale_B_base && !p->scale_B_ptrs) || !p->alphas || !p->expert_offsets || !p->sf_offsets)
         return fail(LSG_ERR_INVALID, "nvfp4_grouped_gemm: null pointer in params");
-    const size_t need = lsg_nvfp4_grouped_gemm_workspace_bytes(total_tokens, p->num_experts, p->N, p->K);
+    // Block-scaled tensor-core route: packed operands straight from the caller's buffers.
+    const bool native = !p->B_ptrs && !p->scale_B_ptrs &&
+                        nvfp4_mma_usable(p->A_base, p->B_base, p->scale_A_base, p->scale_B_base, p->K);
+    const size_t need = lsg_nvfp4_grouped_gemm_workspace_bytes_ex(total_tokens, p->num_experts, p->N, p->K, native ? 0 : 1);
     if (!workspace || workspace_bytes < need)
-        return fail(LSG_ERR_WORKSPACE, "nvfp4_grouped_gemm: workspace too small (have %zu, need %zu)",
-                    workspace ? workspace_bytes : size_t(0), need);
+        return fail(LSG_ERR_WORKSPACE,
+                    "nvfp4_grouped_gemm: workspace too small (have %zu, need %zu%s)",
+                    workspace ? workspace_bytes : size_t(0), need,
+                    native ? "" : "; this call takes the expanded route: size it with lsg_nvfp4_grouped_gemm_workspace_bytes_ex(..., 1)");
     if (reinterpret_cast<uintptr_t>(workspace) & 255)
         return fail(LSG_ERR_ALIGNMENT, "nvfp4_grouped_gemm: workspace must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -169,6 +184,13 @@ extern "C" int lsg_nvfp4_grouped_gemm(const lsg_nvfp4_grouped_gemm_params* p, in
     uint8_t* base = static_cast<uint8_t*>(workspace);
     int* tile_expert = reinterpret_cast<int*>(base);
     int* tile_mstart = tile_expert + t_max;
+    if (native) {
+        int rc = build_mmq_tile_map(p->expert_offsets, E, 128, t_max, tile_expert, tile_mstart, s, T);
+        if (rc != LSG_OK) return rc;
+        return nvfp4_mma(p->A_base, T, p->B_base, static_cast<long long>(E) * N, p->scale_A_base, p->scale_B_base,
+                         static_cast<long long>(lsg_nvfp4_sf_buffer_bytes(N, K)), K, N, p->D_base, p->output_dtype,
+                         p->alphas, 1.0f, T, tile_expert, tile_mstart, t_max, p->expert_offsets, p->sf_offsets, s);
+    }
     __half* a16 = reinterpret_cast<__half*>(base + a256(2ull * t_max * 4));
     __half* b16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a16) + a256(static_cast<size_t>(T) * K * 2));
     const int32_t* offs = p->expert_offsets;
@@ -206,6 +228,9 @@ extern "C" size_t lsg_nvfp4_gemm_workspace_bytes(int M, int N, int K) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     return a256(static_cast<size_t>(M) * K * 2) + a256(static_cast<size_t>(N) * K * 2);
 }
+// (The single-problem query keeps the size of the expanded route: whether a call can take the
+// block-scaled route also depends on pointer alignment, which a size query does not see;
+// the block-scaled route itself needs no workspace.)
 
 extern "C" int lsg_nvfp4_gemm(const lsg_nvfp4_gemm_params* p, void* workspace, size_t workspace_bytes,
                               void* stream) {
@@ -218,6 +243,9 @@ extern "C" int lsg_nvfp4_gemm(const lsg_nvfp4_gemm_params* p, void* workspace, s
         return fail(LSG_ERR_UNSUPPORTED, "nvfp4_gemm: output dtype must be bf16, fp16 or f32");
     if (!p->A || !p->B || !p->D || !p->scale_A || !p->scale_B)
         return fail(LSG_ERR_INVALID, "nvfp4_gemm: null pointer in params");
+    if (nvfp4_mma_usable(p->A, p->B, p->scale_A, p->scale_B, p->K))
+        return nvfp4_mma(p->A, p->M, p->B, p->N, p->scale_A, p->scale_B, 0, p->K, p->N, p->D, p->output_dtype, nullptr,
+                         p->alpha, p->M, nullptr, nullptr, 0, nullptr, nullptr, static_cast<cudaStream_t>(stream));
     const size_t need = lsg_nvfp4_gemm_workspace_bytes(p->M, p->N, p->K);
     if (!workspace || workspace_bytes < need)
         return fail(LSG_ERR_WORKSPACE, "nvfp4_gemm: workspace too small (have %zu, need %zu)",

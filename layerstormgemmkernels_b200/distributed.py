@@ -88,15 +88,40 @@ class EpPlan:
         self.local_offsets[1:] = torch.cumsum(recv_counts.sum(0), 0).to(torch.int32)
 
 
-def make_ep_plan(expert_offsets, num_experts, group=None):
-    """expert_offsets: int32 [E+1] of THIS rank's permuted rows (device or CPU tensor)."""
+class EpExchangeError(RuntimeError):
+    """The expert-parallel exchange cannot proceed: a rank's routing metadata is inconsistent
+    (raised on EVERY rank, before any row moves), or a peer did not take part in a collective."""
+
+
+def make_ep_plan(expert_offsets, num_experts, group=None, rows=None):
+    """expert_offsets: int32 [E+1] of THIS rank's permuted rows (device or CPU tensor).
+
+    `rows` (this rank's number of permuted rows) lets the plan be checked: offsets that do not
+    start at 0, decrease, or do not end at `rows` would make the row exchange send the wrong
+    amounts.  The verdict travels with the counts (one extra column of the same all-to-all), so
+    every rank learns of a bad rank and all of them raise EpExchangeError together instead of
+    some waiting in a collective the others never enter."""
     world = dist.get_world_size(group)
     per = num_experts // world
     offs = expert_offsets.to(torch.int64)
-    counts = (offs[1:] - offs[:-1]).reshape(world, per).contiguous()
-    recv = torch.empty_like(counts)
-    dist.all_to_all_single(recv, counts, group=group)
-    return EpPlan(counts, recv, per)
+    diffs = offs[1:] - offs[:-1]
+    bad = (offs[0] != 0) | (diffs < 0).any()
+    if rows is not None:
+        bad = bad | (offs[-1] != rows)
+    send = torch.empty((world, per + 1), dtype=torch.int64, device=offs.device)
+    send[:, :per] = diffs.reshape(world, per)
+    send[:, per] = bad.to(torch.int64)
+    recv = torch.empty_like(send)
+    try:
+        dist.all_to_all_single(recv, send, group=group)
+    except RuntimeError as exc:   # a peer that left, a timed-out process group
+        raise EpExchangeError(f"expert-parallel count exchange failed: {exc}") from exc
+    flags = recv[:, per].cpu()
+    if bool(bad) or bool(flags.any()):
+        who = [r for r in range(world) if int(flags[r]) != 0]
+        raise EpExchangeError(f"inconsistent expert_offsets on rank(s) {who}: they must start at 0, not decrease, "
+                              "and end at the rank's row count")
+    return EpPlan(send[:, :per].contiguous(), recv[:, :per].contiguous(), per)
 
 
 def ep_dispatch(rows, plan, group=None):
@@ -135,11 +160,17 @@ def ep_moe_layer(hidden, logits, top_k, num_experts, expert_ffn, route, permutat
     tests of this host logic)."""
     idx, w = route(logits, top_k)
     offs, perm, inv = permutation(idx, num_experts)
-    plan = make_ep_plan(offs, num_experts, group)
+    plan = make_ep_plan(offs, num_experts, group, rows=hidden.shape[0] * top_k)
     x = permute(hidden, perm, top_k)
-    rows, local_offs = ep_dispatch(x, plan, group)
+    try:
+        rows, local_offs = ep_dispatch(x, plan, group)
+    except RuntimeError as exc:
+        raise EpExchangeError(f"expert-parallel row dispatch failed: {exc}") from exc
     y = expert_ffn(rows, local_offs)
-    back = ep_combine(y, plan, group)
+    try:
+        back = ep_combine(y, plan, group)
+    except RuntimeError as exc:
+        raise EpExchangeError(f"expert-parallel row return failed: {exc}") from exc
     return unpermute(back, inv, w)
 
 

@@ -655,7 +655,10 @@ def nvfp4_grouped_gemm(A_base, B_base, D_base, scale_A_base, scale_B_base, alpha
     _require(D_base.dtype == tdtype, "nvfp4_grouped_gemm: D_base dtype must match output_dtype")
     E = expert_offsets.size(0) - 1
     T = A_base.size(0)
-    ws_bytes = _lib.lsg_nvfp4_grouped_gemm_workspace_bytes(T, E, int(N), int(K))
+    # the block-scaled tensor-core route needs a tile map only; unaligned views or odd K take the
+    # expanded route and its larger workspace
+    aligned = all(t.data_ptr() % 16 == 0 for t in (A_base, B_base, scale_A_base, scale_B_base))
+    ws_bytes = _lib.lsg_nvfp4_grouped_gemm_workspace_bytes_ex(T, E, int(N), int(K), 0 if aligned else 1)
     ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
     p = capi.Nvfp4GroupedGemmParams(
         num_experts=E, N=int(N), K=int(K), A_base=A_base.data_ptr(), B_base=B_base.data_ptr(),

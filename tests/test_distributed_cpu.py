@@ -108,3 +108,86 @@ def test_expert_range_and_slabs():
         D.expert_range(0, 3, 128)
     with pytest.raises(ValueError):
         D.column_slab(0, 3, 14336)
+
+
+def _worker_bad_offsets(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from layerstormgemmkernels_b200 import distributed as D
+        E, rows = 4, 6
+        good = torch.tensor([0, 2, 3, 5, 6], dtype=torch.int32)
+        bad = torch.tensor([0, 2, 3, 5, 9], dtype=torch.int32)      # ends past the rank's 6 rows
+        offs = bad if rank == 1 else good
+        try:
+            D.make_ep_plan(offs, E, rows=rows)
+            results[rank] = "no error"
+        except D.EpExchangeError as exc:
+            results[rank] = str(exc)
+        # the group is still usable afterwards: the good offsets go through on both ranks
+        plan = D.make_ep_plan(good, E, rows=rows)
+        results[f"{rank}_after"] = plan.recv_rows
+    finally:
+        dist.destroy_process_group()
+
+
+def test_inconsistent_expert_offsets_raise_on_every_rank_before_any_row_moves():
+    """One rank's offsets do not end at its row count.  The verdict travels with the counts, so
+    BOTH ranks raise (naming rank 1) instead of one of them entering a row exchange alone, and
+    the next layer works."""
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_worker_bad_offsets, args=(r, world, port, results)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        for r in range(world):
+            assert "rank(s) [1]" in results[r], results[r]
+        # each rank keeps 3 rows for its own experts and receives the peer's 3 (rank 0: experts 0-1)
+        assert results["0_after"] == 6 and results["1_after"] == 6
+
+
+def _worker_peer_leaves(rank, world, port, results):
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from layerstormgemmkernels_b200 import distributed as D
+    E, rows = 4, 6
+    good = torch.tensor([0, 2, 3, 5, 6], dtype=torch.int32)
+    D.make_ep_plan(good, E, rows=rows)               # step 1: both ranks
+    if rank == 1:
+        results[rank] = "left"
+        return                                       # leaves between steps, nothing in flight
+    try:
+        D.make_ep_plan(good, E, rows=rows)           # step 2: the peer is gone
+        results[rank] = "no error"
+    except D.EpExchangeError as exc:
+        results[rank] = "EpExchangeError"
+    except Exception as exc:                         # noqa: BLE001
+        results[rank] = f"other: {type(exc).__name__}"
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_exchange_with_a_clean_error():
+    """The failure is made on the host: rank 1 returns after a completed step.  Rank 0's next
+    count exchange ends within the process group's short timeout (or at once, on a closed
+    connection) with EpExchangeError, not with a hang."""
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        procs = [ctx.Process(target=_worker_peer_leaves, args=(r, world, port, results)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(90)
+            assert not p.is_alive()
+        assert results[1] == "left"
+        assert results[0] == "EpExchangeError", results[0]

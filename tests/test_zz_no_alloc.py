@@ -10,15 +10,17 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from layerstormgemmkernels_b200 import quantize as Q
 from layerstormgemmkernels_b200.capi import GGUF_TYPES
 
 pytestmark = pytest.mark.gpu
 
 
-def _call_noalloc(capi, A, W, C, t, N, K):
-    p = capi.GgufMmvqParams(M=A.shape[0], N=N, K=K, A=A.data_ptr(), B=W.data_ptr(),
-                            C=C.data_ptr(), type=t, out_dtype=capi.DTYPE_F32)
+def _call_noalloc(capi, A, W, C, t, N, K, M=None):
+    p = capi.GgufMmvqParams(M=A.shape[0] if M is None else M, N=N, K=K, A=A.data_ptr(), B=W.data_ptr(),
+                            C=C.data_ptr(), type=t,
+                            out_dtype=capi.DTYPE_F32 if C.dtype == torch.float32 else capi.DTYPE_BF16)
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     return capi.lib.lsg_gguf_mmvq_noalloc(ctypes.byref(p), st)
 
@@ -40,6 +42,38 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
         scale = want.abs().max().item()
         assert (got - want).abs().max().item() <= 2e-5 * scale
         assert torch.equal(got, want)
+        # and directly against the CPU oracle of the reference's integer path
+        bits = A.view(torch.int16).cpu().numpy().view(np.uint16)
+        ref = oracle.mmvq(t, oracle.quantize_q8_1(bits), W.cpu().numpy(), K)
+        assert np.abs(got.cpu().numpy() - ref).max() <= 2e-5 * np.abs(ref).max()
+    assert capi.device_status() == 0
+
+
+def test_noalloc_bf16_output_other_type_and_empty_shapes():
+    """bf16 output (what the reference operator returns), a type with 32-value blocks, and the
+    early returns for empty problems (nothing is launched, the output is left alone)."""
+    from layerstormgemmkernels_b200 import capi, ops
+    for name, M, N, K in (("Q6_K", 2, 320, 1024), ("Q8_0", 5, 130, 512)):
+        t = GGUF_TYPES[name]
+        A = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).cuda()
+        W = torch.from_numpy(Q.random_gguf_weight(name, N, K, seed=3)).cuda()
+        want = ops.gguf_mmvq(A, W, t, N, K)                               # bf16, caller workspace
+        got = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+        capi.check(_call_noalloc(capi, A, W, got, t, N, K))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+        bits = A.view(torch.int16).cpu().numpy().view(np.uint16)
+        ref = oracle.mmvq(t, oracle.quantize_q8_1(bits), W.cpu().numpy(), K)
+        assert np.abs(got.float().cpu().numpy() - ref).max() <= (2e-5 + 2.0 ** -8) * np.abs(ref).max()
+    t = GGUF_TYPES["Q4_K"]
+    A = torch.zeros((4, 256), dtype=torch.bfloat16, device="cuda")
+    W = torch.zeros((8, 144), dtype=torch.uint8, device="cuda")
+    C = torch.full((4, 8), 5.0, dtype=torch.float32, device="cuda")
+    assert _call_noalloc(capi, A, W, C, t, 8, 256, M=0) == 0              # M == 0
+    assert _call_noalloc(capi, A, W, C, t, 0, 256) == 0                   # N == 0
+    torch.cuda.synchronize()
+    assert torch.all(C == 5.0)
+    assert _call_noalloc(capi, A, W, C, t, 8, 0) != 0                     # K == 0 with rows is an error
     assert capi.device_status() == 0
 
 
