@@ -114,7 +114,9 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
         if world == 1:
             idx, w = ops.moe_route(lg, k)
             offs, perm, inv = ops.moe_permutation(idx, E)
-            return ops.moe_unpermute(ffn(ops.moe_permute(h, perm, k), offs), inv, w)
+            # the permute (gather) is folded into the expert block's first operand preparation
+            y = ops.gguf_moe_ffn(h, offs, gate_p, up_p, down_p, t, H, I, perm=perm, top_k=k)
+            return ops.moe_unpermute(y, inv, w)
         if exchange is not None:
             return exchange.layer(h, lg, ffn, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
         return D.ep_moe_layer(h, lg, k, E, ffn, ops.moe_route, ops.moe_permutation, ops.moe_permute,
@@ -129,7 +131,24 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
         ok = torch.tensor([1 if torch.equal(a, b) else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         equal = bool(ok.item())
-    ms = time_steps(lambda: layer(hidden, logits), steps, warmup, ctx)
+    # The layer as a serving stack runs it: captured once into a CUDA graph and replayed (every
+    # kernel of it is stream-ordered, nothing reads back to the host, and the cross-GPU barrier
+    # keeps its count on the device).  The NCCL fallback exchange copies split sizes to the
+    # host and stays eager.
+    graphed = world == 1 or exchange is not None
+    if graphed:
+        for _ in range(2):
+            layer(hidden, logits)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = layer(hidden, logits)
+        ms = time_steps(graph.replay, steps, warmup, ctx)
+        del graph_out
+    else:
+        ms = time_steps(lambda: layer(hidden, logits), steps, warmup, ctx)
     overflow = bool(exchange is not None and exchange.overflowed())
     gemm_ms = None
     if world == 1:
@@ -159,6 +178,7 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
         "config": {"workload": f"MoE layer, 128 experts top-8, H=2048, I=768, Q4_K, {T_total} tokens: "
                                "route, permute, gate/up/down grouped GEMMs, SwiGLU, combine",
                    "tokens": T_total, "tokens_per_gpu": T,
+                   "launch": "one CUDA graph per layer" if graphed else "eager (the NCCL exchange reads split sizes on the host)",
                    "parallelism": (f"ep{world}, rows exchanged by peer-memory stores, library flag barrier"
                                    if ep_mode == "peer" and exchange is not None
                                    else f"ep{world}, NCCL all-to-all" if world > 1 else "single"),
@@ -177,7 +197,7 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
             "frac_of_peak": flops / (gemm_ms * 1e-3) / 1e12 / pk.tf},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": T * H * 2 + T * E * 4, "d2h_bytes_per_step": T * H * 2},
-        "gpu_launches": steps * 11,
+        "gpu_launches": steps * (10 if world == 1 else 11),
     }
     if equal is not None:
         line["equal_to_nccl_exchange"] = equal

@@ -318,7 +318,11 @@ LSG_API int lsg_gguf_grouped_gemm(const lsg_gguf_grouped_gemm_params* p, int tot
  * gguf_grouped_gemm (csrc/bindings_python.cu:552-611) builds the block; the reference fuses
  * activation and quantizer only on its NVFP4 path (launch_silu_mul_to_nvfp4_grouped).
  * Never synchronizes with the host.  Rows of experts without rows are untouched; all three
- * pointers of an expert that has rows must be valid. */
+ * pointers of an expert that has rows must be valid.
+ * With `perm` set the permute (gather) of the MoE layer is folded into the call: A_base is
+ * then the UNPERMUTED token matrix [num_tokens, H] and row i of the block is token
+ * perm[i] / top_k (perm as lsg_moe_permutation writes it); the routed rows are never written
+ * to memory as bf16, the first operand preparation reads the tokens directly. */
 typedef struct lsg_gguf_moe_ffn_params {
     int type;                        /* lsg_gguf_type of all three matrices            */
     int num_experts;
@@ -331,6 +335,8 @@ typedef struct lsg_gguf_moe_ffn_params {
     const void* const* up_ptrs;
     const void* const* down_ptrs;
     int out_dtype;
+    const int32_t* perm;             /* optional [total_tokens] sorted-row -> (token, slot) pair  */
+    int top_k;                       /* slots per token (with perm)                               */
 } lsg_gguf_moe_ffn_params;
 LSG_API size_t lsg_gguf_moe_ffn_workspace_bytes(int total_tokens, int H, int I, int num_experts);
 LSG_API int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_tokens, void* workspace,

@@ -65,7 +65,7 @@ class GgufMoeFfnParams(ctypes.Structure):
     _fields_ = [("type", ctypes.c_int), ("num_experts", ctypes.c_int), ("H", ctypes.c_int), ("I", ctypes.c_int),
                 ("A_base", ctypes.c_void_p), ("D_base", ctypes.c_void_p), ("expert_offsets", ctypes.c_void_p),
                 ("gate_ptrs", ctypes.c_void_p), ("up_ptrs", ctypes.c_void_p), ("down_ptrs", ctypes.c_void_p),
-                ("out_dtype", ctypes.c_int)]
+                ("out_dtype", ctypes.c_int), ("perm", ctypes.c_void_p), ("top_k", ctypes.c_int)]
 
 
 class Fp8GemmParams(ctypes.Structure):

@@ -72,6 +72,6 @@ size_t tc_fused_moe_ffn_scratch_bytes(long long T, int H, int I);
 int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, const void* const* gate_ptrs,
                      const void* const* up_ptrs, const void* const* down_ptrs, const int32_t* expert_offsets,
                      void* D, int out_dtype, const int* tile_expert, const int* tile_mstart, int t_max, int tile_m,
-                     void* scratch, size_t scratch_bytes, cudaStream_t s);
+                     void* scratch, size_t scratch_bytes, cudaStream_t s, const int32_t* perm = nullptr, int top_k = 1);
 
 }  // namespace lsg

@@ -50,6 +50,7 @@ silu_mul_bf16_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, u
 }
 
 struct FfnLayout {
+    size_t gather_off, gather_bytes;  // routed rows of the composed route when the call carries a permutation
     size_t map_off, map_bytes;      // tile map of the tensor-core route
     size_t fused_off, fused_bytes;  // scratch of the tensor-core route
     size_t g_off, u_off, act_off;   // bf16 [T, I] buffers of the composed route
@@ -73,7 +74,11 @@ FfnLayout ffn_layout(int T, int H, int I, int E) {
     const size_t g1 = lsg_gguf_grouped_gemm_workspace_bytes_ex(T, H, E, I);
     const size_t g2 = lsg_gguf_grouped_gemm_workspace_bytes_ex(T, I, E, H);
     l.grouped_bytes = align256(g1 > g2 ? g1 : g2);
-    const size_t composed = l.grouped_off + l.grouped_bytes;
+    // the composed route gathers the routed rows first (it serves decode-sized batches only,
+    // so this is small); the tensor-core route reads the tokens through the permutation
+    l.gather_off = l.grouped_off + l.grouped_bytes;
+    l.gather_bytes = (T / E > 8) ? 0 : align256(static_cast<size_t>(T) * H * 2);
+    const size_t composed = l.gather_off + l.gather_bytes;
     const size_t fused = l.fused_off + l.fused_bytes;
     l.total = composed > fused ? composed : fused;
     return l;
@@ -105,6 +110,7 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
                     p->H, p->I, qk);
     if (!p->A_base || !p->D_base || !p->expert_offsets || !p->gate_ptrs || !p->up_ptrs || !p->down_ptrs)
         return fail(LSG_ERR_INVALID, "gguf_moe_ffn: null A/D/expert_offsets/weight pointer arrays");
+    if (p->perm && p->top_k < 1) return fail(LSG_ERR_INVALID, "gguf_moe_ffn: top_k must be >= 1 with a permutation");
     const int T = total_tokens, E = p->num_experts, H = p->H, I = p->I;
     const FfnLayout l = ffn_layout(T, H, I, E);
     if (!workspace || workspace_bytes < l.total)
@@ -126,12 +132,23 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
         if (rc != LSG_OK) return rc;
         return tc_fused_moe_ffn(p->type, T, E, H, I, p->A_base, p->gate_ptrs, p->up_ptrs, p->down_ptrs, offs,
                                 p->D_base, p->out_dtype, tile_expert, tile_mstart, t_max, tile_m,
-                                base + l.fused_off, l.fused_bytes, s);
+                                base + l.fused_off, l.fused_bytes, s, p->perm, p->perm ? p->top_k : 1);
+    }
+
+    const void* rows = p->A_base;
+    if (p->perm) {
+        if (l.gather_bytes == 0)
+            return fail(LSG_ERR_UNSUPPORTED,
+                        "gguf_moe_ffn: a permutation with this type and batch needs the rows gathered by the caller "
+                        "(lsg_moe_permute)");
+        int rc = lsg_moe_permute(p->A_base, p->perm, T, p->top_k, H, base + l.gather_off, stream);
+        if (rc != LSG_OK) return rc;
+        rows = base + l.gather_off;
     }
 
     lsg_gguf_grouped_gemm_params g = {};
     g.type = p->type; g.strategy = LSG_GGUF_STRATEGY_INT; g.num_experts = E;
-    g.N = I; g.K = H; g.A_base = p->A_base; g.expert_offsets = offs; g.out_dtype = LSG_DTYPE_BF16;
+    g.N = I; g.K = H; g.A_base = rows; g.expert_offsets = offs; g.out_dtype = LSG_DTYPE_BF16;
     g.D_base = base + l.g_off; g.B_ptrs = p->gate_ptrs;
     int rc = lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
     if (rc != LSG_OK) return rc;

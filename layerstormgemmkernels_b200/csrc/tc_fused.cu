@@ -27,7 +27,10 @@
 //               writes its 32 fp16 values as 16 packed columns of its lane
 // Tensor memory (512 columns): the accumulators in columns 0..255 (two of NT <= 128 columns,
 // alternating so the epilogue overlaps the next tile, or one of 256), the weight ring in
-// columns 256..511 (8 stages x 32 columns).  A stage is "full" after nine arrivals (eight
+// columns 256..511 (8 stages x 32 columns).  Expert batches whose experts hold a little more
+// than 256 rows take token tiles of 384 rows instead (one accumulator in columns 0..383, two
+// MMAs per K step, the ring in the last 128 columns): a second, nearly empty 256-row tile
+// would repeat the whole weight decoding for a handful of rows.  A stage is "full" after nine arrivals (eight
 // decoder warps + the TMA transaction); tcgen05.commit releases it.  All waits are
 // time-limited; a time-out ends every role and is reported in the status word.
 //
@@ -69,7 +72,9 @@ struct FusedArgs {
     int ldc;
     int out_dtype;
     int K, N, M;
-    int nt;                       // token rows per tile: 32, 64, 128 or 256
+    int nt;                       // token rows per tile: 32, 64, 128, 256 or 384
+    int box_rows;                 // rows of one TMA box of the token tile (nt, or 128 when nt = 384)
+    int a_col_base;               // first tensor-memory column of the weight ring (256, or 384 when nt = 384)
     int n_wtiles;                 // ceil(N / 128)
     int t_tiles;                  // dense: ceil(M / nt); grouped: capacity of the tile map
     const int* tile_expert;
@@ -435,7 +440,8 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                         break;
                     }
                     mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(stage_bytes));
-                    tma_load_2d(smem + ring.s * stage_bytes, &tmX, kb * BK, im.mstart, &full[ring.s]);
+                    for (int r0 = 0; r0 < a.nt; r0 += a.box_rows)
+                        tma_load_2d(smem + ring.s * stage_bytes + r0 * 128, &tmX, kb * BK, im.mstart + r0, &full[ring.s]);
                     ring.advance();
                 }
             }
@@ -462,17 +468,24 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             // N of the instruction follows the token rows that are really in the tile (a multiple
             // of 16): the ragged last tile of an expert costs tensor time for its rows only
             const int live = min(a.nt, im.mend - im.mstart);
-            const uint32_t idesc = idesc_f16(WM, max(16, (live + 15) & ~15));
+            const int live16 = max(16, (live + 15) & ~15);
+            const int n1 = min(256, live16), n2 = live16 - n1;   // second instruction: rows 256.. of a 384-row tile
+            const uint32_t idesc = idesc_f16(WM, n1);
+            const uint32_t idesc2 = idesc_f16(WM, max(16, n2));
             for (int kb = kb0; kb < kb1; ++kb) {
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint));
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t xdesc = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes));
-                const uint32_t a_tmem = tmem_base + kAColBase + ring.s * kAColsPerStage;
+                const uint64_t xdesc2 = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes + 256 * 128));
+                const uint32_t a_tmem = tmem_base + a.a_col_base + ring.s * kAColsPerStage;
                 if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
+                    for (int k = 0; k < BK / 16; ++k) {
                         tc_mma_f16_ta(d_tmem, a_tmem + 8 * k, xdesc + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+                        if (n2 > 0)
+                            tc_mma_f16_ta(d_tmem + 256, a_tmem + 8 * k, xdesc2 + 2 * k, idesc2, (kb != kb0 || k != 0) ? 1u : 0u);
+                    }
                     tc_commit(&empty[ring.s]);
                 }
                 __syncwarp();
@@ -499,7 +512,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         DecCtx ctx;
         ctx.full = full;
         ctx.empty = empty;
-        ctx.tmem_a = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kAColBase;
+        ctx.tmem_a = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a.a_col_base;
         ctx.status = a.status;
         ctx.hint = hint;
         Ring ring = {0, 0u, a.stages};
@@ -680,7 +693,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 __global__ void __launch_bounds__(256)
 x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks,
               unsigned int* __restrict__ counters, int n_counters, const int32_t* __restrict__ live_rows,
-              int blocks_per_row) {
+              int blocks_per_row, const int32_t* __restrict__ perm, int top_k) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
@@ -690,7 +703,15 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, lon
     if (live_rows) n_blocks = min(n_blocks, static_cast<long long>(*live_rows) * blocks_per_row);
     const bool live = task < n_blocks * 4;
     const long long tk = live ? task : 0;
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
+    // With a permutation the rows are gathered on the way in: row i of the output is token
+    // perm[i] / top_k of x (the permute pass of a MoE layer folded into this kernel).
+    long long src = tk;
+    if (perm) {
+        const int vpr = blocks_per_row * 4;   // 16-byte vectors per row
+        const long long row = tk / vpr;
+        src = static_cast<long long>(perm[row] / top_k) * vpr + (tk - row * vpr);
+    }
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + src);
     float v[8];
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -831,7 +852,7 @@ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 bool staged_decoder(int type) { return type == LSG_GGUF_Q4_K; }
 
 struct Plan {
-    int nt, stages, raw_depth, raw_bytes, t_tiles, n_wtiles, ksplit, kb_per_split;
+    int nt, box_rows, a_col_base, stages, raw_depth, raw_bytes, t_tiles, n_wtiles, ksplit, kb_per_split;
     size_t x_bytes, partial_bytes, counter_bytes;
     size_t total() const { return x_bytes + partial_bytes + counter_bytes; }
 };
@@ -852,6 +873,10 @@ Plan make_plan(long long rows, int nt, int t_tiles, int N, int K, bool allow_spl
     p.raw_depth = staged ? 8 : 0;
     p.raw_bytes = staged ? p.raw_depth * kRawSlotBytes + kHdrRingBytes : 0;
     p.stages = (224 * 1024 - p.raw_bytes) / stage_bytes;
+    p.box_rows = nt > 256 ? 128 : nt;
+    p.a_col_base = nt > 256 ? 384 : kAColBase;
+    const int ring_stages = (kTmemCols - p.a_col_base) / kAColsPerStage;
+    if (p.stages > ring_stages) p.stages = ring_stages;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
     p.t_tiles = t_tiles;
     p.n_wtiles = (N + WM - 1) / WM;
@@ -940,9 +965,23 @@ size_t tc_fused_dense_scratch_bytes(int M, int N, int K) {
     return make_plan(M, nt, (M + nt - 1) / nt, N, K, true, false).total();
 }
 
+// Token rows per tile of a grouped call, from the average rows per expert.  Routed batches
+// scatter around their mean (a few standard deviations of a multinomial), so the tile is
+// chosen with a fifth of headroom: an expert that holds a few rows more than its tile pays
+// the whole weight decoding a second time for those few rows.  Averages beyond 320 rows take
+// 256-row tiles (several per expert).
 int tc_fused_grouped_tile_m(long long T, int E) {
-    const int nt = pick_nt(E > 0 ? (T + E - 1) / E : T);
-    return nt < 64 ? 64 : nt;  // the workspace reserves a tile map for tiles of 64 rows or more
+    static const int force = [] {
+        const char* e = getenv("LSG_TC_FUSED_TILE_M");
+        return e ? atoi(e) : 0;
+    }();
+    if (force == 64 || force == 128 || force == 256 || force == 384) return force;
+    const long long avg = E > 0 ? (T + E - 1) / E : T;
+    if (avg * 6 <= 64 * 5) return 64;      // the workspace reserves a tile map for tiles of 64 rows or more
+    if (avg * 6 <= 128 * 5) return 128;
+    if (avg * 6 <= 256 * 5) return 256;
+    if (avg * 6 <= 384 * 5) return 384;
+    return 256;
 }
 
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K) {
@@ -973,7 +1012,7 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((tasks + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
                                n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters,
-                               static_cast<const int32_t*>(nullptr), 0));
+                               static_cast<const int32_t*>(nullptr), 0, static_cast<const int32_t*>(nullptr), 1));
     CUtensorMap tmX;
     int rc = make_map(&tmX, x16, M, K, nt);
     if (rc != LSG_OK) return rc;
@@ -985,7 +1024,7 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
         a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off;
     }
     a.K = K; a.N = N; a.M = M;
-    a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.nt = nt; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
     a.status = device_status_word();
@@ -1034,7 +1073,7 @@ int tc_fused_dense_bf16(int type, int M, int N, int K, const void* A_bf16, const
     a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
     a.C = C; a.ldc = ldc; a.out_dtype = out_dtype;
     a.K = K; a.N = N; a.M = M;
-    a.nt = nt; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages;
+    a.nt = nt; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages;
     a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
@@ -1059,16 +1098,17 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
     const long long nb = static_cast<long long>(T) * (K / 32);
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, K / 32));
+                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, K / 32,
+                               static_cast<const int32_t*>(nullptr), 1));
     CUtensorMap tmX;
-    int rc = make_map(&tmX, x16, T, K, tile_m);
+    int rc = make_map(&tmX, x16, T, K, p.box_rows);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.B_ptrs = B_ptrs;
     a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
     a.C = D; a.ldc = N; a.out_dtype = out_dtype;
     a.K = K; a.N = N; a.M = T;
-    a.nt = tile_m; a.n_wtiles = p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.nt = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
     a.status = device_status_word();
@@ -1088,7 +1128,7 @@ size_t tc_fused_moe_ffn_scratch_bytes(long long T, int H, int I) {
 int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, const void* const* gate_ptrs,
                      const void* const* up_ptrs, const void* const* down_ptrs, const int32_t* expert_offsets,
                      void* D, int out_dtype, const int* tile_expert, const int* tile_mstart, int t_max, int tile_m,
-                     void* scratch, size_t scratch_bytes, cudaStream_t s) {
+                     void* scratch, size_t scratch_bytes, cudaStream_t s, const int32_t* perm, int top_k) {
     if (T == 0) return LSG_OK;
     const size_t need = tc_fused_moe_ffn_scratch_bytes(T, H, I);
     if (!scratch || scratch_bytes < need)
@@ -1105,17 +1145,17 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     long long nb = static_cast<long long>(T) * (H / 32);
     LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, H / 32));
+                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, H / 32, perm, top_k));
     CUtensorMap tmX;
-    int rc = make_map(&tmX, x16, T, H, tile_m);
-    if (rc != LSG_OK) return rc;
     Plan p = make_plan(T, tile_m, t_max, I, H, false, staged);
+    int rc = make_map(&tmX, x16, T, H, p.box_rows);
+    if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.B_ptrs = gate_ptrs; a.B_ptrs2 = up_ptrs; a.split_wt = p.n_wtiles; a.col2_off = I;
     a.row_bytes = static_cast<long long>(H / qk) * qb;
     a.C = gu; a.ldc = 2 * I; a.out_dtype = LSG_DTYPE_BF16;
     a.K = H; a.N = I; a.M = T;
-    a.nt = tile_m; a.n_wtiles = 2 * p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages;
+    a.nt = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = 2 * p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages;
     a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
@@ -1128,15 +1168,15 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     LSG_CUDA_TRY(launch_kernel(swiglu_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s,
                                true, static_cast<const __nv_bfloat16*>(gu), act16, nb, I, expert_offsets + E));
     CUtensorMap tmA;
-    rc = make_map(&tmA, act16, T, I, tile_m);
-    if (rc != LSG_OK) return rc;
     p = make_plan(T, tile_m, t_max, H, I, false, staged);
+    rc = make_map(&tmA, act16, T, I, p.box_rows);
+    if (rc != LSG_OK) return rc;
     FusedArgs b = {};
     b.B_ptrs = down_ptrs;
     b.row_bytes = static_cast<long long>(I / qk) * qb;
     b.C = D; b.ldc = H; b.out_dtype = out_dtype;
     b.K = I; b.N = H; b.M = T;
-    b.nt = tile_m; b.n_wtiles = p.n_wtiles; b.t_tiles = t_max; b.stages = p.stages;
+    b.nt = tile_m; b.box_rows = p.box_rows; b.a_col_base = p.a_col_base; b.n_wtiles = p.n_wtiles; b.t_tiles = t_max; b.stages = p.stages;
     b.raw_depth = p.raw_depth; b.raw_bytes = p.raw_bytes;
     b.ksplit = 1; b.kb_per_split = p.kb_per_split;
     b.tile_expert = tile_expert; b.tile_mstart = tile_mstart; b.expert_offsets = expert_offsets;

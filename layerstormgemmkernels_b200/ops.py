@@ -415,12 +415,17 @@ def gguf_grouped_gemm(A_base, expert_offsets, b_ptrs, type, strategy, N, K, forc
     return D
 
 
-def gguf_moe_ffn(A_base, expert_offsets, gate_ptrs, up_ptrs, down_ptrs, type, H, I, out_dtype=torch.bfloat16):
+def gguf_moe_ffn(A_base, expert_offsets, gate_ptrs, up_ptrs, down_ptrs, type, H, I, out_dtype=torch.bfloat16,
+                 perm=None, top_k=1):
     """Expert feed-forward block over rows grouped by expert, one call:
     down( silu(gate(x)) * up(x) ) with gate/up packed [I, H] and down packed [H, I] per expert
     (`*_ptrs`: CUDA int64 tensors of device pointers).  The same numbers as three
     gguf_grouped_gemm calls (Int strategy) with the activation computed in fp32 and stored as
-    bf16 in between.  An addition to the reference's operator set."""
+    bf16 in between.  An addition to the reference's operator set.
+
+    With `perm` (int32, as moe_permutation returns it) A_base is the UNPERMUTED token matrix
+    [num_tokens, H] and row i of the block is token perm[i] // top_k: the permute pass of the
+    layer is folded into the call."""
     _require(A_base.is_cuda and A_base.dtype == torch.bfloat16 and A_base.dim() == 2 and A_base.is_contiguous(),
              "gguf_moe_ffn: A_base must be contiguous BF16 [T, H] on CUDA")
     _require(A_base.size(1) == H, "gguf_moe_ffn: A_base.size(1) != H")
@@ -432,12 +437,18 @@ def gguf_moe_ffn(A_base, expert_offsets, gate_ptrs, up_ptrs, down_ptrs, type, H,
                  f"gguf_moe_ffn: {name} must be int64 (device pointers) on CUDA, one per expert")
     _require(expert_offsets.numel() == E + 1, "gguf_moe_ffn: expert_offsets must be [num_experts+1]")
     T = A_base.size(0)
+    if perm is not None:
+        _require(perm.is_cuda and perm.dtype == torch.int32 and perm.dim() == 1 and perm.is_contiguous()
+                 and int(top_k) >= 1 and perm.numel() == T * int(top_k),
+                 "gguf_moe_ffn: perm must be contiguous int32 [num_tokens * top_k] on CUDA")
+        T = perm.numel()
     D = torch.empty((T, H), dtype=out_dtype, device=A_base.device)
     p = capi.GgufMoeFfnParams(
         type=int(type), num_experts=E, H=int(H), I=int(I), A_base=A_base.data_ptr(), D_base=D.data_ptr(),
         expert_offsets=expert_offsets.data_ptr(), gate_ptrs=gate_ptrs.data_ptr(), up_ptrs=up_ptrs.data_ptr(),
         down_ptrs=down_ptrs.data_ptr(),
-        out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
+        out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16,
+        perm=perm.data_ptr() if perm is not None else None, top_k=int(top_k))
     ws_bytes = _lib.lsg_gguf_moe_ffn_workspace_bytes(T, int(H), int(I), E)
     ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=A_base.device)
     capi.check(_lib.lsg_gguf_moe_ffn(ctypes.byref(p), T, _ptr(ws), ws_bytes, _stream()))

@@ -159,6 +159,24 @@ def ref_lib():
     return _ref
 
 
+REF_GROUPED_LIB_PATH = os.path.join(_HERE, "_ref", "libref_grouped.so")
+_ref_grouped = None
+
+
+def ref_grouped_lib():
+    """ctypes handle of oracle/_ref/libref_grouped.so (the reference's grouped GGUF launchers,
+    its routing-metadata kernels, its mma.sync prefill GEMM and its FP8 weight quantizer), or
+    None when it has not been built (it needs CuTe headers, see oracle/Makefile)."""
+    global _ref_grouped
+    if _ref_grouped is None and os.path.exists(REF_GROUPED_LIB_PATH):
+        try:
+            _ref_grouped = ctypes.CDLL(REF_GROUPED_LIB_PATH)
+            _ref_grouped.ref_gguf_grouped_gemm_workspace_bytes.restype = ctypes.c_size_t
+        except OSError:
+            _ref_grouped = None
+    return _ref_grouped
+
+
 # ---------------------------------------------------------------------------
 # FP8 / NVFP4 activation quantizers
 # ---------------------------------------------------------------------------

@@ -120,6 +120,9 @@ def test_moe_layer_128_experts_top8_sampled_vs_oracle(ops, moe_weights, tokens):
     offs, perm, inv = ops.moe_permutation(idx, E_MOE)
     rows = ops.moe_permute(h_dev, perm, K_MOE)
     y = ops.gguf_moe_ffn(rows, offs, gate_p, up_p, down_p, T["Q4_K"], H_MOE, I_MOE)
+    # the same block with the gather folded in must give the same bits
+    y_fused = ops.gguf_moe_ffn(h_dev, offs, gate_p, up_p, down_p, T["Q4_K"], H_MOE, I_MOE, perm=perm, top_k=K_MOE)
+    assert torch.equal(y, y_fused)
     out = ops.moe_unpermute(y, inv, w).float().cpu().numpy()
     # routing oracle: the torch definition
     p = torch.softmax(logits.float(), -1)
