@@ -92,7 +92,18 @@ struct FusedArgs {
     int n_out;                    //   element is stored into each of them (GEMM + all-gather)
     int col_off;                  // column offset of this call's N columns inside the output rows
     unsigned int* status;
+#ifdef LSG_TCF_EXP
+    int dbg;
+#endif
 };
+// Knock-out switches for timing experiments, only in builds with -DLSG_TCF_EXP (the shipped
+// library has none): environment variable LSG_TCF_EXP = sum of 1 (no epilogue stores), 2 (no
+// token-tile loads), 4 (no weight decoding), 8 (no epilogue at all).  Results are garbage then.
+#ifdef LSG_TCF_EXP
+#define TCF_DBG(a, bit) (((a).dbg & (bit)) != 0)
+#else
+#define TCF_DBG(a, bit) false
+#endif
 
 // True in exactly one lane of the (converged) warp.
 __device__ __forceinline__ bool elect_one() {
@@ -439,6 +450,11 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                         *abort_flag = 1;
                         break;
                     }
+                    if (TCF_DBG(a, 2)) {
+                        mbar_arrive(&full[ring.s]);
+                        ring.advance();
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(stage_bytes));
                     for (int r0 = 0; r0 < a.nt; r0 += a.box_rows)
                         tma_load_2d(smem + ring.s * stage_bytes + r0 * 128, &tmX, kb * BK, im.mstart + r0, &full[ring.s]);
@@ -531,7 +547,17 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             bool ok;
             const bool aligned16 =
                 ((reinterpret_cast<uintptr_t>(base) | static_cast<uintptr_t>(a.row_bytes)) & 15) == 0;
-            if (T == LSG_GGUF_Q4_K && a.raw_depth > 0 && row != nullptr && aligned16) {
+            if (TCF_DBG(a, 4)) {
+                ok = true;
+                for (int kb = kb0; kb < kb1 && ok; ++kb) {
+                    if (ring.lap > 0)
+                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status,
+                                                                       kDevWaitEmpty, hint));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[ring.s]);
+                    ring.advance();
+                }
+            } else if (T == LSG_GGUF_Q4_K && a.raw_depth > 0 && row != nullptr && aligned16) {
                 if (a.raw_depth == 8)
                     ok = decode_rows_q4k<8>(ctx, ring, row, kb0, kb1, half, raw, dec_tid);
                 else
@@ -568,9 +594,10 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 #pragma unroll 1
                 for (int c = 0; c < a.nt; c += 32) {
                     if (im.mstart + c >= im.mend) break;  // warp-uniform: no token rows left in this tile
+                    if (TCF_DBG(a, 8)) break;
                     uint32_t v[32];
                     tmem_ld32(t_lane + c, v);
-                    if (n_ok) {
+                    if (n_ok && !TCF_DBG(a, 1)) {
                         const int rows = min(32, im.mend - (im.mstart + c));
                         if (a.row_scale) {
 #pragma unroll
@@ -1028,6 +1055,9 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
     a.status = device_status_word();
+#ifdef LSG_TCF_EXP
+    a.dbg = getenv("LSG_TCF_EXP") ? atoi(getenv("LSG_TCF_EXP")) : 0;
+#endif
     return launch_fused(type, tmX, a, s);
 }
 
@@ -1079,6 +1109,9 @@ int tc_fused_dense_bf16(int type, int M, int N, int K, const void* A_bf16, const
     a.partial = partial; a.counters = counters;
     a.row_scale = row_scale;
     a.status = device_status_word();
+#ifdef LSG_TCF_EXP
+    a.dbg = getenv("LSG_TCF_EXP") ? atoi(getenv("LSG_TCF_EXP")) : 0;
+#endif
     return launch_fused(type, tmX, a, s);
 }
 
@@ -1112,6 +1145,9 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
     a.status = device_status_word();
+#ifdef LSG_TCF_EXP
+    a.dbg = getenv("LSG_TCF_EXP") ? atoi(getenv("LSG_TCF_EXP")) : 0;
+#endif
     return launch_fused(type, tmX, a, s);
 }
 
@@ -1160,6 +1196,9 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
     a.status = device_status_word();
+#ifdef LSG_TCF_EXP
+    a.dbg = getenv("LSG_TCF_EXP") ? atoi(getenv("LSG_TCF_EXP")) : 0;
+#endif
     rc = launch_fused(type, tmX, a, s);
     if (rc != LSG_OK) return rc;
 
@@ -1181,6 +1220,9 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     b.ksplit = 1; b.kb_per_split = p.kb_per_split;
     b.tile_expert = tile_expert; b.tile_mstart = tile_mstart; b.expert_offsets = expert_offsets;
     b.status = device_status_word();
+#ifdef LSG_TCF_EXP
+    b.dbg = getenv("LSG_TCF_EXP") ? atoi(getenv("LSG_TCF_EXP")) : 0;
+#endif
     return launch_fused(type, tmA, b, s);
 }
 
