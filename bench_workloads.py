@@ -8,6 +8,7 @@ the current stream, max over ranks.  Nothing here touches the CPU oracle except 
 `cpu_*` functions at the end, which are the bounded CPU baselines that sit beside the GPU
 numbers (rank 0, one GPU).
 """
+import ctypes
 import json
 import os
 import sys
@@ -79,7 +80,7 @@ def moe_expert_weights(dev, e0, e1, distinct=8):
     return base, sets, ptrs
 
 
-def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
+def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunks=1):
     from layerstormgemmkernels_b200 import capi, ops, distributed as D
     E, k, H, I = MOE["E"], MOE["k"], MOE["H"], MOE["I"]
     world, rank, dev = ctx.world, ctx.rank, ctx.dev
@@ -103,7 +104,13 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
         ep_mode = ep
         if ep == "peer":
             try:
-                exchange = D.EpPeerExchange.make(E, k, H, T)
+                # chunks > 1: halves of the tokens on side streams, one half's row exchange under the
+                # other half's expert GEMMs.  Measured slower on this layer (each half repeats the
+                # decoding of every expert's weights), so one exchange is the default.
+                if chunks > 1 and T % chunks == 0 and T // chunks >= 64:
+                    exchange = D.EpPeerPipeline.make(E, k, H, T, chunks=chunks)
+                else:
+                    exchange = D.EpPeerExchange.make(E, k, H, T)
             except Exception as exc:   # noqa: BLE001 - the optional path falls back
                 if rank == 0:
                     print(f"peer-memory exchange unavailable ({type(exc).__name__}: {exc}); using NCCL all-to-all",
@@ -179,7 +186,9 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True):
                                "route, permute, gate/up/down grouped GEMMs, SwiGLU, combine",
                    "tokens": T_total, "tokens_per_gpu": T,
                    "launch": "one CUDA graph per layer" if graphed else "eager (the NCCL exchange reads split sizes on the host)",
-                   "parallelism": (f"ep{world}, rows exchanged by peer-memory stores, library flag barrier"
+                   "parallelism": (f"ep{world}, rows exchanged by peer-memory stores"
+                                   + (f" in {exchange.chunks} pipelined halves" if hasattr(exchange, "chunks") else "")
+                                   + ", library flag barrier"
                                    if ep_mode == "peer" and exchange is not None
                                    else f"ep{world}, NCCL all-to-all" if world > 1 else "single"),
                    "l2_defeat": "339 MB of expert weights (per rank set) exceed the 126 MB L2"},
@@ -378,14 +387,28 @@ def run_quant(ctx, steps, warmup):
 
     cell("dynamic_fp8_quant", lambda: ops.dynamic_fp8_quant(rot()), M * K * 2 + M * K + M * (K // 128) * 4)
     cell("quantize_q8_1", lambda: ops.quantize_q8_1(rot()), M * K * 2 + M * (K // 32) * 36)
-    cell("bf16_to_nvfp4_grouped", lambda: ops.bf16_to_nvfp4_grouped(rot(), offs), M * K * 2 + M * K // 2 + M * K // 16)
+    # NVFP4 grouped: through the C ABI with caller-owned outputs.  The Python operator mirrors the
+    # reference binding, which copies the offsets to the host on every call to size the scale buffer.
+    from layerstormgemmkernels_b200 import capi
+    packed = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    scales = torch.zeros((M * (K // 16),), dtype=torch.uint8, device=dev)
+    sf_offs = torch.tensor([0, M], dtype=torch.int32, device=dev)
+
+    def nvfp4_call():
+        x = rot()
+        p = capi.Nvfp4GroupedQuantParams(input=x.data_ptr(), up=None, output_packed=packed.data_ptr(),
+                                         output_scales=scales.data_ptr(), expert_offsets=offs.data_ptr(),
+                                         sf_offsets=sf_offs.data_ptr(), total_tokens=M, num_experts=1, K=K,
+                                         input_scales=None)
+        capi.check(capi.lib.lsg_bf16_to_nvfp4_grouped(ctypes.byref(p), torch.cuda.current_stream().cuda_stream))
+    cell("bf16_to_nvfp4_grouped", nvfp4_call, M * K * 2 + M * K // 2 + M * K // 16)
     best = cells["dynamic_fp8_quant"]
     return {
         "metric": "fp8_quant_gbps", "value": best["gbps"], "unit": "GB/s", "n_gpus": ctx.world, "steps": steps,
         "warmup": warmup, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 -> e4m3 / int8 / e2m1", "data": "synthetic",
         "config": {"workload": "activation quantizers on a 4096x4096 bf16 tensor (dynamic FP8 headline; Q8_1 and "
-                               "NVFP4 grouped in `cells`), output allocation included as the operator does it",
+                               "NVFP4 grouped in `cells`), output allocation included for the first two as the operator does it, caller-owned outputs for the third",
                    "l2_defeat": "calls rotate over six input tensors (201 MB)"},
         "roofline": {"bound": "hbm", "achieved": best["gbps"], "peak": pk.hbm, "unit": "GB/s",
                      "frac": best["gbps"] / pk.hbm, "peak_kind": pk.kind, "traffic": None},

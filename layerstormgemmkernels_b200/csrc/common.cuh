@@ -58,6 +58,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// Height of the token tiles of an expert with m rows when its ceil(m / tile_m) tiles share the
+// rows evenly: m / tiles rounded up to 16 (never more than tile_m, a multiple of 16).  The tile
+// map builder and the kernels that consume balanced maps both use this.
+__host__ __device__ __forceinline__ int balanced_tile_rows(int m, int tile_m) {
+    const int tiles = (m + tile_m - 1) / tile_m;
+    if (tiles <= 1) return tile_m;
+    return (((m + tiles - 1) / tiles) + 15) & ~15;
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
                  : "memory");

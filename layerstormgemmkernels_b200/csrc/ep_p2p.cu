@@ -126,56 +126,107 @@ ep_plan_kernel(const int32_t* __restrict__ tab, int rank, int world, int E, int 
     }
 }
 
+// Rows per CTA of the two copy kernels.  Two rows and at most 32 registers per thread, so that a
+// copy CTA fits on an SM next to a resident 448-thread, 128-register GEMM CTA (57,344 + 8,192 =
+// the whole register file) and an exchange on a second stream can run under the expert GEMMs.
+constexpr int kEpRows = 2;
+
+// Index of the last segment whose start is <= i, for nondecreasing starts[0..n): the number of
+// starts that are <= i, minus one, counted by the whole CTA (one or a few loads per thread and
+// one reduction) instead of a binary search per thread.  Uniform over the CTA.
+__device__ __forceinline__ int segment_of(const int32_t* __restrict__ starts, int n, int i, int* s_count) {
+    if (threadIdx.x == 0) *s_count = 0;
+    __syncthreads();
+    int c = 0;
+    for (int t = threadIdx.x; t < n; t += blockDim.x) c += (__ldg(starts + t) <= i) ? 1 : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if ((threadIdx.x & 31) == 0 && c) atomicAdd(s_count, c);
+    __syncthreads();
+    return max(*s_count - 1, 0);
+}
+
 // Sorted row i (expert e, j-th row of e) -> row send_base[e] + j of rank e / per.
-// One thread per 16-byte vector.
-__global__ void __launch_bounds__(256)
+// A CTA copies kEpRows consecutive sorted rows: the expert of the first one is counted once,
+// the following rows walk on from it; every thread has kEpRows independent 16-byte loads in
+// flight before the stores into the destination GPUs' receive buffers.
+__global__ void __launch_bounds__(256, 8)
 ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm,
                     const int32_t* __restrict__ offs, const int32_t* __restrict__ send_base, int P, int top_k,
                     int vpr, int E, int per, uint4* const* __restrict__ recv, int capacity,
                     uint4* __restrict__ back_local) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (idx >= static_cast<long long>(P) * vpr) return;
-    const int i = static_cast<int>(idx / vpr), v = static_cast<int>(idx - static_cast<long long>(i) * vpr);
-    int lo = 0, hi = E - 1;   // last expert whose first row is <= i and that owns row i
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (offs[mid] <= i) lo = mid;
-        else hi = mid - 1;
+    __shared__ int s_count;
+    const int i0 = blockIdx.x * kEpRows;
+    int e = segment_of(offs, E, i0, &s_count);   // last expert whose first row is <= i0
+    int token[kEpRows], row[kEpRows], dst[kEpRows];
+#pragma unroll
+    for (int j = 0; j < kEpRows; ++j) {
+        const int i = i0 + j;
+        token[j] = -1;
+        row[j] = 0;
+        dst[j] = 0;
+        if (i < P) {
+            while (e + 1 < E && __ldg(offs + e + 1) <= i) ++e;
+            row[j] = __ldg(send_base + e) + (i - __ldg(offs + e));
+            dst[j] = e / per;
+            token[j] = __ldg(perm + i) / top_k;
+        }
     }
-    const int e = lo;
-    const int row = send_base[e] + (i - offs[e]);
-    if (row >= capacity) {
-        // no room at the destination: nothing comes back for this row, so its slot of this
-        // rank's return buffer is cleared instead of keeping the previous layer's contents
-        if (back_local) back_local[static_cast<size_t>(i) * vpr + v] = make_uint4(0, 0, 0, 0);
-        return;
+    for (int v = threadIdx.x; v < vpr; v += blockDim.x) {
+        uint4 val[kEpRows];
+#pragma unroll
+        for (int j = 0; j < kEpRows; ++j)
+            val[j] = (token[j] >= 0 && row[j] < capacity) ? __ldg(hidden + static_cast<size_t>(token[j]) * vpr + v)
+                                                          : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < kEpRows; ++j) {
+            if (token[j] < 0) continue;
+            if (row[j] < capacity) {
+                recv[dst[j]][static_cast<size_t>(row[j]) * vpr + v] = val[j];
+            } else if (back_local) {
+                // no room at the destination: nothing comes back for this row, so its slot of this
+                // rank's return buffer is cleared instead of keeping the previous layer's contents
+                back_local[static_cast<size_t>(i0 + j) * vpr + v] = val[j];
+            }
+        }
     }
-    const int token = perm[i] / top_k;
-    recv[e / per][static_cast<size_t>(row) * vpr + v] = __ldg(hidden + static_cast<size_t>(token) * vpr + v);
 }
 
 // Received row r of block (el, s) -> row ret_base[block] + j of source s's return buffer.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 8)
 ep_return_rows_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ dst_start,
                       const int32_t* __restrict__ ret_base, const int32_t* __restrict__ info, int world, int B,
                       int vpr, int capacity, uint4* const* __restrict__ back) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    const int rows = min(info[0], capacity);
-    if (idx >= static_cast<long long>(rows) * vpr) return;
-    const int r = static_cast<int>(idx / vpr), v = static_cast<int>(idx - static_cast<long long>(r) * vpr);
-    int lo = 0, hi = B - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (dst_start[mid] <= r) lo = mid;
-        else hi = mid - 1;
+    __shared__ int s_count;
+    const int rows = min(__ldg(info), capacity);
+    const int r0 = blockIdx.x * kEpRows;
+    if (r0 >= rows) return;   // uniform over the CTA
+    int b = segment_of(dst_start, B, r0, &s_count);
+    int row[kEpRows], dst[kEpRows];
+#pragma unroll
+    for (int j = 0; j < kEpRows; ++j) {
+        const int r = r0 + j;
+        row[j] = -1;
+        dst[j] = 0;
+        if (r < rows) {
+            while (b + 1 < B && __ldg(dst_start + b + 1) <= r) ++b;
+            row[j] = __ldg(ret_base + b) + (r - __ldg(dst_start + b));
+            dst[j] = b % world;
+        }
     }
-    const int s = lo % world;
-    const int row = ret_base[lo] + (r - dst_start[lo]);
-    back[s][static_cast<size_t>(row) * vpr + v] = __ldg(y + static_cast<size_t>(r) * vpr + v);
+    for (int v = threadIdx.x; v < vpr; v += blockDim.x) {
+        uint4 val[kEpRows];
+#pragma unroll
+        for (int j = 0; j < kEpRows; ++j)
+            val[j] = row[j] >= 0 ? __ldg(y + static_cast<size_t>(r0 + j) * vpr + v) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int j = 0; j < kEpRows; ++j)
+            if (row[j] >= 0) back[dst[j]][static_cast<size_t>(row[j]) * vpr + v] = val[j];
+    }
 }
 
 // Cross-GPU barrier on the stream, owned by this library: every rank holds a flag array
@@ -276,8 +327,8 @@ extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, co
     if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(hidden_bf16) & 15))
         return fail(LSG_ERR_ALIGNMENT, "ep_send_rows: H must be a multiple of 8 and buffers 16-byte aligned");
     const int vpr = H / 8;
-    const long long total = static_cast<long long>(num_pairs) * vpr;
-    LSG_CUDA_TRY(launch_kernel(ep_send_rows_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+    const int threads = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
+    LSG_CUDA_TRY(launch_kernel(ep_send_rows_kernel, dim3(static_cast<unsigned>((num_pairs + kEpRows - 1) / kEpRows)), dim3(threads), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(hidden_bf16), perm,
                                expert_offsets, send_base, num_pairs, top_k, vpr, num_experts, num_experts / world,
                                reinterpret_cast<uint4* const*>(recv_buf_ptrs), capacity,
@@ -296,8 +347,8 @@ extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, 
     if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15))
         return fail(LSG_ERR_ALIGNMENT, "ep_return_rows: H must be a multiple of 8 and buffers 16-byte aligned");
     const int vpr = H / 8;
-    const long long total = static_cast<long long>(capacity) * vpr;
-    LSG_CUDA_TRY(launch_kernel(ep_return_rows_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
+    const int threads = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
+    LSG_CUDA_TRY(launch_kernel(ep_return_rows_kernel, dim3(static_cast<unsigned>((capacity + kEpRows - 1) / kEpRows)), dim3(threads), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(y_bf16), dst_start,
                                ret_base, info, world, world * experts_per_rank, vpr, capacity,
                                reinterpret_cast<uint4* const*>(back_buf_ptrs)));

@@ -106,7 +106,7 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
         const int t_max = (T + tile_m - 1) / tile_m + p->num_experts;
         int* tile_mstart = tile_expert + t_max;  // t_max(tile_m >= 64) <= t_max(64): fits the reserved map
         rc = build_mmq_tile_map(static_cast<const int32_t*>(p->expert_offsets), p->num_experts, tile_m,
-                                t_max, tile_expert, tile_mstart, s, T);
+                                t_max, tile_expert, tile_mstart, s, T, true);
         if (rc != LSG_OK) return rc;
         return tc_fused_grouped(p->type, T, p->num_experts, p->N, p->K, p->A_base, p->B_ptrs,
                                 static_cast<const int32_t*>(p->expert_offsets), p->D_base, p->out_dtype,

@@ -19,8 +19,10 @@ int build_active_expert_list(const int32_t* offs, int E, int cap, int* active, c
 // `rows` bounds every offset read from the device: offsets that run past the caller's row
 // count (an expert-parallel receive buffer that overflowed) can then never index past it.
 // The default leaves the offsets as they are, which is the reference's behaviour.
+// balanced: tiles of an expert share its rows evenly (balanced_tile_rows) instead of full
+// tiles plus a remainder; only for consumers that derive the tile height the same way.
 int build_mmq_tile_map(const int32_t* offs, int E, int tile_m, int T_max, int* tile_expert,
-                       int* tile_mstart, cudaStream_t s, int rows = 0x7fffffff);
+                       int* tile_mstart, cudaStream_t s, int rows = 0x7fffffff, bool balanced = false);
 int build_segment_list(const int32_t* offs, const void* const* B_ptrs, int E, int max_rows,
                        int max_segments, int* seg, cudaStream_t s, int rows = 0x7fffffff);
 

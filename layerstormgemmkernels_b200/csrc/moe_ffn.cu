@@ -128,7 +128,7 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
         const int t_max = (T + tile_m - 1) / tile_m + E;
         int* tile_expert = reinterpret_cast<int*>(base + l.map_off);
         int* tile_mstart = tile_expert + t_max;
-        int rc = build_mmq_tile_map(offs, E, tile_m, t_max, tile_expert, tile_mstart, s, T);
+        int rc = build_mmq_tile_map(offs, E, tile_m, t_max, tile_expert, tile_mstart, s, T, true);
         if (rc != LSG_OK) return rc;
         return tc_fused_moe_ffn(p->type, T, E, H, I, p->A_base, p->gate_ptrs, p->up_ptrs, p->down_ptrs, offs,
                                 p->D_base, p->out_dtype, tile_expert, tile_mstart, t_max, tile_m,

@@ -16,7 +16,8 @@ namespace {
 
 constexpr int kMaxTopK = 16;
 
-// One warp per token.  E <= 1024.
+// One warp per token, PER experts per lane (E <= 32 * PER <= 1024).
+template <int PER>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int32_t* __restrict__ topk_idx,
                  float* __restrict__ topk_w) {
@@ -26,7 +27,6 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int32_t*
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= T) return;
     const float* row = logits + static_cast<size_t>(t) * E;
-    constexpr int PER = 32;  // up to 1024 experts
     float v[PER];
     float mx = -INFINITY;
 #pragma unroll
@@ -102,7 +102,8 @@ moe_chunk_hist_kernel(const int32_t* __restrict__ idx, int P, int E, int32_t* __
         if (e >= 0 && e < E) atomicAdd(&h[e], 1);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += kChunk) hist[static_cast<size_t>(blockIdx.x) * E + e] = h[e];
+    // laid out [expert][chunk]: the scan below reads consecutive chunks of one expert
+    for (int e = threadIdx.x; e < E; e += kChunk) hist[static_cast<size_t>(e) * gridDim.x + blockIdx.x] = h[e];
 }
 
 // One CTA of 1024 threads (E <= 1024).  Phase 1: warp w scans the chunk histograms of experts
@@ -118,10 +119,24 @@ moe_chunk_scan_kernel(int32_t* __restrict__ hist, int n_chunks, int E, int32_t* 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int e = warp; e < E; e += 32) {
         int carry = 0;
+        // up to 128 chunks are fetched before the first scan step: the loads of an expert's row
+        // are contiguous and independent, only the carry is sequential
+        int pre[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = j * 32 + lane;
+            pre[j] = c < n_chunks ? hist[static_cast<size_t>(e) * n_chunks + c] : 0;
+        }
         for (int c0 = 0; c0 < n_chunks; c0 += 32) {
             const int c = c0 + lane;
-            const size_t at = static_cast<size_t>(c) * E + e;
-            const int v = c < n_chunks ? hist[at] : 0;
+            const size_t at = static_cast<size_t>(e) * n_chunks + c;
+            int v;
+            if (c0 < 128) {
+                const int j = c0 >> 5;
+                v = j == 0 ? pre[0] : (j == 1 ? pre[1] : (j == 2 ? pre[2] : pre[3]));
+            } else {
+                v = c < n_chunks ? hist[at] : 0;
+            }
             int incl = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -179,7 +194,7 @@ moe_place_kernel(const int32_t* __restrict__ idx, int P, int E, const int32_t* _
     if (e >= 0) {
         int before = 0;
         for (int w = 0; w < warp; ++w) before += whist[w * E + e];
-        const int row = offsets[e] + chunk_base[static_cast<size_t>(blockIdx.x) * E + e] + before + rank;
+        const int row = offsets[e] + chunk_base[static_cast<size_t>(e) * gridDim.x + blockIdx.x] + before + rank;
         perm[row] = i;
         inv[i] = row;
     }
@@ -302,7 +317,17 @@ extern "C" int lsg_moe_route(const float* logits, int num_tokens, int num_expert
     if (num_experts < 1 || num_experts > 1024 || top_k < 1 || top_k > kMaxTopK || top_k > num_experts)
         return fail(LSG_ERR_INVALID, "moe_route: need 1 <= top_k <= min(16, E) and E <= 1024 (E=%d, k=%d)",
                     num_experts, top_k);
-    LSG_CUDA_TRY(launch_kernel(moe_route_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0,
+    const dim3 rg((num_tokens + 7) / 8), rb(256);
+    if (num_experts <= 128)
+        LSG_CUDA_TRY(launch_kernel(moe_route_kernel<4>, rg, rb, 0,
+                               static_cast<cudaStream_t>(stream), true, logits, num_tokens, num_experts,
+                               top_k, topk_idx, topk_weights));
+    else if (num_experts <= 256)
+        LSG_CUDA_TRY(launch_kernel(moe_route_kernel<8>, rg, rb, 0,
+                               static_cast<cudaStream_t>(stream), true, logits, num_tokens, num_experts,
+                               top_k, topk_idx, topk_weights));
+    else
+        LSG_CUDA_TRY(launch_kernel(moe_route_kernel<32>, rg, rb, 0,
                                static_cast<cudaStream_t>(stream), true, logits, num_tokens, num_experts,
                                top_k, topk_idx, topk_weights));
     return LSG_OK;

@@ -62,26 +62,29 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
                            const float* __restrict__ input_scales, int T, int E, int K) {
     pdl_launch_dependents();
     pdl_wait_prior();
-    __shared__ int s_info[3];  // expert start, sf base (in groups), expert id
     const int row = blockIdx.y;
     const int gpr = K >> 4;
-    if (threadIdx.x == 0) {
-        if (expert_offsets == nullptr) {   // single problem
-            s_info[0] = 0;
-            s_info[1] = 0;
-            s_info[2] = 0;
+    // The row's expert is the number of experts that end at or before it.  With at most one
+    // expert per thread that is one load per thread and one counting barrier; a binary search
+    // by one thread (seven dependent loads with the CTA waiting) only for more experts.
+    int e = 0, e_start = 0, sf_base = 0;
+    if (expert_offsets != nullptr) {
+        if (E <= static_cast<int>(blockDim.x)) {
+            const int t = threadIdx.x;
+            e = __syncthreads_count(t < E && __ldg(expert_offsets + t + 1) <= row);
         } else {
-            const int e = expert_of_row(expert_offsets, E, row);
-            s_info[0] = expert_offsets[e];
-            s_info[1] = sf_offsets[e];
-            s_info[2] = e;
+            __shared__ int s_e;
+            if (threadIdx.x == 0) s_e = expert_of_row(expert_offsets, E, row);
+            __syncthreads();
+            e = s_e;
         }
+        e = min(e, E - 1);
+        e_start = __ldg(expert_offsets + e);
+        sf_base = __ldg(sf_offsets + e);
     }
-    __syncthreads();
     const int g = blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= gpr) return;
-    const int e = s_info[2];
-    const int local_row = row - s_info[0];
+    const int local_row = row - e_start;
     float is = 1.0f;
     if (input_scales) {
         const float v = input_scales[e];
@@ -125,7 +128,7 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
     float srepr = static_cast<float>(f8);
     srepr = fmaxf(srepr, 1e-12f);
     const int groups_padded4 = (gpr + 3) & ~3;
-    scales[static_cast<size_t>(s_info[1]) * gpr + sf_offset_sm1xx(local_row, g, groups_padded4)] =
+    scales[static_cast<size_t>(sf_base) * gpr + sf_offset_sm1xx(local_row, g, groups_padded4)] =
         static_cast<uint8_t>(sbits);
 
     const float inv = 1.0f / (srepr * is);

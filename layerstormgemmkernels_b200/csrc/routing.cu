@@ -39,19 +39,22 @@ __global__ void active_expert_list_kernel(const int32_t* __restrict__ offs, int 
 
 // `rows` bounds every offset (callers whose offsets come from another GPU's counts pass the
 // row capacity of their buffers; INT_MAX leaves the offsets as they are).
+// balanced: an expert's tiles share its rows evenly (height = rows / tiles, rounded up to 16)
+// instead of full tiles followed by a remainder; the consumer derives the same height.
 __global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int tile_m, int T_max, int rows,
-                                    int* __restrict__ tile_expert, int* __restrict__ tile_mstart) {
+                                    int balanced, int* __restrict__ tile_expert, int* __restrict__ tile_mstart) {
     pdl_launch_dependents();
     pdl_wait_prior();
     const int lane = threadIdx.x & 31;
     int t0 = 0;  // tiles emitted so far (warp-uniform)
     for (int base = 0; base < E; base += 32) {
         const int e = base + lane;
-        int off = 0, nt = 0;
+        int off = 0, nt = 0, height = tile_m;
         if (e < E) {
             off = min(offs[e], rows);
             const int m = min(offs[e + 1], rows) - off;
             nt = m > 0 ? (m + tile_m - 1) / tile_m : 0;
+            if (balanced && nt > 0) height = balanced_tile_rows(m, tile_m);
         }
         // exclusive prefix sum of nt over the warp
         int incl = nt;
@@ -65,7 +68,7 @@ __global__ void mmq_tile_map_kernel(const int32_t* __restrict__ offs, int E, int
             const int t = first + i;
             if (t < T_max) {
                 tile_expert[t] = e;
-                tile_mstart[t] = off + i * tile_m;
+                tile_mstart[t] = off + i * height;
             }
         }
         t0 += __shfl_sync(0xffffffffu, incl, 31);
@@ -124,10 +127,10 @@ int build_active_expert_list(const int32_t* offs, int E, int cap, int* active, c
 }
 
 int build_mmq_tile_map(const int32_t* offs, int E, int tile_m, int T_max, int* tile_expert,
-                       int* tile_mstart, cudaStream_t s, int rows) {
+                       int* tile_mstart, cudaStream_t s, int rows, bool balanced) {
     if (T_max <= 0) return LSG_OK;
     LSG_CUDA_TRY(launch_kernel(mmq_tile_map_kernel, dim3(1), dim3(32), 0, s, true, offs, E, tile_m,
-                               T_max, rows, tile_expert, tile_mstart));
+                               T_max, rows, balanced ? 1 : 0, tile_expert, tile_mstart));
     return LSG_OK;
 }
 

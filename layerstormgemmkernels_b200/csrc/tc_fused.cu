@@ -210,6 +210,9 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
             // never past the rows the caller holds, whatever the offsets say
             it.mstart = min(a.tile_mstart[it.tt], a.M);
             it.mend = min(a.expert_offsets[e + 1], a.M);
+            // balanced tile maps: the expert's tiles share its rows evenly
+            const int m = it.mend - min(a.expert_offsets[e], a.M);
+            it.mend = min(it.mend, it.mstart + balanced_tile_rows(m, a.nt));
         }
     }
     return it;
@@ -716,117 +719,121 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 // ---------------------------------------------------------------------------
 // Activation preparation: bf16 -> fp16 of the Q8_1 round trip (d_h * rn(x / d), the values
 // the integer kernels multiply by), plus zeroing of the split-K tile counters.
+//
+// SWIGLU = false: x[rows, K].  With a permutation the rows are gathered on the way in: row i
+// of the output is token perm[i] / top_k of x (the permute pass of a MoE layer folded in).
+// SWIGLU = true: x = gu[rows, 2K] holds gate | up; per element
+//   act = bf16( silu(g) * u )  with silu(g) = g / (1 + exp(-g)) in fp32
+// (what a caller computing the activation in fp32 and storing bf16 gets), then the round trip.
+//
+// Four lanes per 32-value block, eight values (one 16-byte vector) each.  The thread block is
+// (vectors of a row, rows); every thread handles RB rows, so RB (2 RB with SwiGLU) independent
+// loads are in flight per thread and no index needs a division.  Grouped callers may hold
+// fewer rows than the buffer they pass: the row count then lives on the device (live_rows).
 // ---------------------------------------------------------------------------
+template <int RB, bool SWIGLU>
 __global__ void __launch_bounds__(256)
-x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, long long n_blocks,
+x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int rows, int vpr,
               unsigned int* __restrict__ counters, int n_counters, const int32_t* __restrict__ live_rows,
-              int blocks_per_row, const int32_t* __restrict__ perm, int top_k) {
+              const int32_t* __restrict__ perm, int top_k) {
+    const unsigned lanes = __activemask();   // a block of K/8 x rows threads may end in a partial warp
     pdl_launch_dependents();
     pdl_wait_prior();
-    const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (counters && task < n_counters) counters[task] = 0;
-    // grouped callers may hold fewer rows than the buffer they pass: the row count then lives
-    // on the device (the last entry of the expert offsets) and the rest is skipped
-    if (live_rows) n_blocks = min(n_blocks, static_cast<long long>(*live_rows) * blocks_per_row);
-    const bool live = task < n_blocks * 4;
-    const long long tk = live ? task : 0;
-    // With a permutation the rows are gathered on the way in: row i of the output is token
-    // perm[i] / top_k of x (the permute pass of a MoE layer folded into this kernel).
-    long long src = tk;
-    if (perm) {
-        const int vpr = blocks_per_row * 4;   // 16-byte vectors per row
-        const long long row = tk / vpr;
-        src = static_cast<long long>(perm[row] / top_k) * vpr + (tk - row * vpr);
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    if (counters) {
+        const int nthreads = blockDim.x * blockDim.y;
+        const long long stride = static_cast<long long>(gridDim.x) * gridDim.y * nthreads;
+        for (long long i = (static_cast<long long>(blockIdx.y) * gridDim.x + blockIdx.x) * nthreads + ty * blockDim.x + tx;
+             i < n_counters; i += stride)
+            counters[i] = 0;
     }
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + src);
-    float v[8];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const int live = live_rows ? min(rows, __ldg(live_rows)) : rows;
+    const int v = blockIdx.y * blockDim.x + tx;
+    const int rbase = blockIdx.x * (blockDim.y * RB) + ty;
+    const int ld_in = SWIGLU ? 2 * vpr : vpr;
+    const uint4* xin = reinterpret_cast<const uint4*>(x);
+    uint4 g[RB], u[RB];
+    bool ok[RB];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (!live) return;
-    const float d = amax / 127.0f;
-    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-    const float dh = __half2float(__float2half(d));
-    uint32_t p[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float r[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const float t = v[2 * i + hh] * rcp;
-            int k = __float2int_rn(t);
-            // same integer as rn(fl(x / d)): the product with the reciprocal only differs
-            // next to a half-integer, and there the true quotient decides
-            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + hh] / d);
-            r[hh] = dh * static_cast<float>(k);
+    for (int j = 0; j < RB; ++j) {
+        const int r = rbase + j * blockDim.y;
+        ok[j] = v < vpr && r < live;
+        g[j] = make_uint4(0, 0, 0, 0);
+        u[j] = make_uint4(0, 0, 0, 0);
+        if (ok[j]) {
+            const int sr = perm ? __ldg(perm + r) / top_k : r;
+            const uint4* src = xin + static_cast<size_t>(sr) * ld_in + v;
+            g[j] = __ldg(src);
+            if (SWIGLU) u[j] = __ldg(src + vpr);
         }
-        p[i] = pack_h2(r[0], r[1]);
     }
-    reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
+#pragma unroll
+    for (int j = 0; j < RB; ++j) {
+        const uint32_t gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w}, uw[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+        float val[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float a = __uint_as_float(hh ? (gw[i] & 0xFFFF0000u) : (gw[i] << 16));
+                if (SWIGLU) {
+                    const float b = __uint_as_float(hh ? (uw[i] & 0xFFFF0000u) : (uw[i] << 16));
+                    val[2 * i + hh] = __bfloat162float(__float2bfloat16_rn((a / (1.0f + expf(-a))) * b));
+                } else {
+                    val[2 * i + hh] = a;
+                }
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(val[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(lanes, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(lanes, amax, 2));
+        const float d = amax / 127.0f;
+        const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+        const float dh = __half2float(__float2half(d));
+        uint32_t pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float r2[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float t = val[2 * i + hh] * rcp;
+                int k = __float2int_rn(t);
+                // same integer as rn(fl(x / d)): the product with the reciprocal only differs
+                // next to a half-integer, and there the true quotient decides
+                if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(val[2 * i + hh] / d);
+                r2[hh] = dh * static_cast<float>(k);
+            }
+            pk[i] = pack_h2(r2[0], r2[1]);
+        }
+        if (ok[j]) {
+            const int r = rbase + j * blockDim.y;
+            reinterpret_cast<uint4*>(out)[static_cast<size_t>(r) * vpr + v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+    }
 }
 
-// SwiGLU between the two halves of an expert feed-forward block, fused with the preparation
-// of the second GEMM's activation: gu[T, 2I] bf16 holds gate | up; per element
-//   act = bf16( silu(g) * u )  with silu(g) = g / (1 + exp(-g)) in fp32
-// (what a caller computing the activation in fp32 and storing bf16 gets), then the Q8_1 round
-// trip of act over 32-value blocks along I, as fp16.  Four lanes per block, eight values each.
-__global__ void __launch_bounds__(256)
-swiglu_prep_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ out, long long n_blocks, int I,
-                   const int32_t* __restrict__ live_rows) {
-    pdl_launch_dependents();
-    pdl_wait_prior();
-    const long long task = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
-    if (live_rows) n_blocks = min(n_blocks, static_cast<long long>(*live_rows) * (I / 32));
-    const bool live = task < n_blocks * 4;
-    const long long tk = live ? task : 0;
-    const int per_row = I / 8;
-    const long long row = tk / per_row;
-    const int c8 = static_cast<int>(tk - row * per_row);
-    const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gu + row * 2 * I + c8 * 8));
-    const uint4 uraw = __ldg(reinterpret_cast<const uint4*>(gu + row * 2 * I + I + c8 * 8));
-    const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w}, uw[4] = {uraw.x, uraw.y, uraw.z, uraw.w};
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const float g = __uint_as_float(hh ? (gw[i] & 0xFFFF0000u) : (gw[i] << 16));
-            const float u = __uint_as_float(hh ? (uw[i] & 0xFFFF0000u) : (uw[i] << 16));
-            const float a = (g / (1.0f + expf(-g))) * u;
-            v[2 * i + hh] = __bfloat162float(__float2bfloat16_rn(a));
-        }
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    if (!live) return;
-    const float d = amax / 127.0f;
-    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-    const float dh = __half2float(__float2half(d));
-    uint32_t p[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float r[2];
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            const float t = v[2 * i + hh] * rcp;
-            int k = __float2int_rn(t);
-            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + hh] / d);
-            r[hh] = dh * static_cast<float>(k);
-        }
-        p[i] = pack_h2(r[0], r[1]);
-    }
-    reinterpret_cast<uint4*>(out)[tk] = make_uint4(p[0], p[1], p[2], p[3]);
+// rows x K values (K a multiple of 32).  The block is (min(K/8, 256) vectors, 256 / that rows).
+template <bool SWIGLU>
+int launch_x_prep(const __nv_bfloat16* x, __half* out, long long rows, int K, unsigned int* counters, int n_counters,
+                  const int32_t* live_rows, const int32_t* perm, int top_k, cudaStream_t s) {
+    if (rows <= 0 || rows > 0x7fffffffll) return rows == 0 ? LSG_OK : fail(LSG_ERR_UNSUPPORTED, "activation preparation: too many rows");
+    const int vpr = K / 8;
+    const int bx = vpr < 256 ? vpr : 256;
+    const int by = 256 / bx > 0 ? 256 / bx : 1;
+    const int gy = (vpr + bx - 1) / bx;
+    // four rows per thread once there are enough rows to fill the GPU that way
+    const bool rb4 = rows >= 4ll * by * 2 * sm_count();
+    const int rows_per_block = by * (rb4 ? 4 : 1);
+    const unsigned gx = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+    if (rb4)
+        LSG_CUDA_TRY(launch_kernel(x_prep_kernel<4, SWIGLU>, dim3(gx, gy), dim3(bx, by), 0, s, true, x, out,
+                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k));
+    else
+        LSG_CUDA_TRY(launch_kernel(x_prep_kernel<1, SWIGLU>, dim3(gx, gy), dim3(bx, by), 0, s, true, x, out,
+                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k));
+    return LSG_OK;
 }
 
 // bf16 activation rows -> fp16 scaled by a power of two per row: the row's largest magnitude
@@ -1004,11 +1011,13 @@ int tc_fused_grouped_tile_m(long long T, int E) {
     }();
     if (force == 64 || force == 128 || force == 256 || force == 384) return force;
     const long long avg = E > 0 ? (T + E - 1) / E : T;
+    // Tiles are balanced per expert (routing.cu), so the tile height only caps how many rows
+    // share one pass over an expert's weights; the 5/6 margin keeps most experts of a routed
+    // batch in one tile of the chosen height.
     if (avg * 6 <= 64 * 5) return 64;      // the workspace reserves a tile map for tiles of 64 rows or more
     if (avg * 6 <= 128 * 5) return 128;
     if (avg * 6 <= 256 * 5) return 256;
-    if (avg * 6 <= 384 * 5) return 384;
-    return 256;
+    return 384;
 }
 
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K) {
@@ -1033,15 +1042,12 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
     float* partial = reinterpret_cast<float*>(wsb + p.x_bytes);
     unsigned int* counters = reinterpret_cast<unsigned int*>(wsb + p.x_bytes + p.partial_bytes);
     const int n_counters = p.ksplit > 1 ? p.t_tiles * p.n_wtiles * 4 : 0;
-    const long long nb = static_cast<long long>(M) * (K / 32);
-    long long tasks = nb * 4;
-    if (tasks < n_counters) tasks = n_counters;
-    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((tasks + 255) / 256)), dim3(256), 0, s, true,
-                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters,
-                               static_cast<const int32_t*>(nullptr), 0, static_cast<const int32_t*>(nullptr), 1));
+    int rc = launch_x_prep<false>(static_cast<const __nv_bfloat16*>(A_bf16), x16, M, K,
+                                  n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters, nullptr,
+                                  nullptr, 1, s);
+    if (rc != LSG_OK) return rc;
     CUtensorMap tmX;
-    int rc = make_map(&tmX, x16, M, K, nt);
+    rc = make_map(&tmX, x16, M, K, nt);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.W = static_cast<const uint8_t*>(W);
@@ -1128,13 +1134,11 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
         return fail(LSG_ERR_WORKSPACE, "gguf grouped mmq: scratch too small (have %zu, need %zu)",
                     scratch ? scratch_bytes : size_t(0), p.total());
     __half* x16 = static_cast<__half*>(scratch);
-    const long long nb = static_cast<long long>(T) * (K / 32);
-    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
-                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, K / 32,
-                               static_cast<const int32_t*>(nullptr), 1));
+    int rc = launch_x_prep<false>(static_cast<const __nv_bfloat16*>(A_bf16), x16, T, K, nullptr, 0, expert_offsets + E,
+                                  nullptr, 1, s);
+    if (rc != LSG_OK) return rc;
     CUtensorMap tmX;
-    int rc = make_map(&tmX, x16, T, K, p.box_rows);
+    rc = make_map(&tmX, x16, T, K, p.box_rows);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.B_ptrs = B_ptrs;
@@ -1178,13 +1182,12 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     const int qk = gguf_block_values(type), qb = gguf_block_bytes(type);
 
     // gate | up
-    long long nb = static_cast<long long>(T) * (H / 32);
-    LSG_CUDA_TRY(launch_kernel(x_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s, true,
-                               static_cast<const __nv_bfloat16*>(A_bf16), x16, nb,
-                               static_cast<unsigned int*>(nullptr), 0, expert_offsets + E, H / 32, perm, top_k));
+    int rc = launch_x_prep<false>(static_cast<const __nv_bfloat16*>(A_bf16), x16, T, H, nullptr, 0, expert_offsets + E,
+                                  perm, top_k, s);
+    if (rc != LSG_OK) return rc;
     CUtensorMap tmX;
     Plan p = make_plan(T, tile_m, t_max, I, H, false, staged);
-    int rc = make_map(&tmX, x16, T, H, p.box_rows);
+    rc = make_map(&tmX, x16, T, H, p.box_rows);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.B_ptrs = gate_ptrs; a.B_ptrs2 = up_ptrs; a.split_wt = p.n_wtiles; a.col2_off = I;
@@ -1203,9 +1206,8 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     if (rc != LSG_OK) return rc;
 
     // SwiGLU + preparation, then down
-    nb = static_cast<long long>(T) * (I / 32);
-    LSG_CUDA_TRY(launch_kernel(swiglu_prep_kernel, dim3(static_cast<unsigned>((nb * 4 + 255) / 256)), dim3(256), 0, s,
-                               true, static_cast<const __nv_bfloat16*>(gu), act16, nb, I, expert_offsets + E));
+    rc = launch_x_prep<true>(gu, act16, T, I, nullptr, 0, expert_offsets + E, nullptr, 1, s);
+    if (rc != LSG_OK) return rc;
     CUtensorMap tmA;
     p = make_plan(T, tile_m, t_max, H, I, false, staged);
     rc = make_map(&tmA, act16, T, I, p.box_rows);

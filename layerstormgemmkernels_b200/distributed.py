@@ -229,7 +229,10 @@ class EpPeerExchange:
         if not (logits.is_cuda and logits.dim() == 2 and tuple(logits.shape) == (hidden.shape[0], self.E)):
             raise ValueError(f"EpPeerExchange: logits must be a CUDA tensor [{hidden.shape[0]}, {self.E}]")
 
-    def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
+    # A layer in three phases, so that a caller can interleave two exchanges (EpPeerPipeline):
+    # dispatch (route, sort, publish, barrier, plan, send, barrier), experts, finish (return
+    # rows, barrier, combine).  layer() runs them back to back on the current stream.
+    def dispatch(self, hidden, logits, route, permutation):
         from . import capi
         lib = capi.lib
         st = torch.cuda.current_stream().cuda_stream
@@ -239,7 +242,7 @@ class EpPeerExchange:
         offs, perm, inv = permutation(idx, self.E)
         counts, counts_ptrs = self.b["counts"]
         recv, recv_ptrs = self.b["recv"]
-        back, back_ptrs = self.b["back"]
+        back, _ = self.b["back"]
         capi.check(lib.lsg_ep_publish_counts(p(offs), self.E, self.rank, self.world, p(counts_ptrs), st))
         self.barrier()
         capi.check(lib.lsg_ep_plan(p(counts), self.rank, self.world, self.E, self.cap, p(self.send_base),
@@ -247,11 +250,25 @@ class EpPeerExchange:
         capi.check(lib.lsg_ep_send_rows(p(hidden), p(perm), p(offs), p(self.send_base), self.P, self.k, self.H,
                                         self.E, self.world, p(recv_ptrs), self.cap, p(back), st))
         self.barrier()
-        y = expert_ffn(recv, self.local_offsets)
-        capi.check(lib.lsg_ep_return_rows(p(y), p(self.dst_start), p(self.ret_base), p(self.info), self.world,
-                                          self.per, y.shape[1], self.cap, p(back_ptrs), st))
+        return (offs, perm, inv, w)      # offs and perm stay referenced until the layer is done
+
+    def experts(self, expert_ffn):
+        return expert_ffn(self.b["recv"][0], self.local_offsets)
+
+    def finish(self, y, state, unpermute):
+        from . import capi
+        st = torch.cuda.current_stream().cuda_stream
+        p = lambda t: t.data_ptr()
+        back, back_ptrs = self.b["back"]
+        capi.check(capi.lib.lsg_ep_return_rows(p(y), p(self.dst_start), p(self.ret_base), p(self.info), self.world,
+                                               self.per, y.shape[1], self.cap, p(back_ptrs), st))
         self.barrier()
-        return unpermute(back, inv, w)
+        return unpermute(back, state[2], state[3])
+
+    def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
+        state = self.dispatch(hidden, logits, route, permutation)
+        y = self.experts(expert_ffn)
+        return self.finish(y, state, unpermute)
 
     def overflowed(self):
         """True if some rank's receive buffer was too small in the last layer (synchronizes).
@@ -259,6 +276,73 @@ class EpPeerExchange:
         a caller that checks the status after a run needs no extra call; rows that did not fit
         contributed zeros."""
         return bool(self.info[1].item())
+
+
+class EpPeerPipeline:
+    """An expert-parallel layer as `chunks` EpPeerExchange halves on side streams, staggered so
+    that the row exchange of one half runs under the expert GEMMs of the other:
+
+        stream 0:  dispatch 0 | experts 0             | finish 0
+        stream 1:             | dispatch 1 | experts 1            | finish 1
+
+    (dispatch 1 starts when dispatch 0 is done, experts 1 when experts 0 is done.)  Every half has
+    its own symmetric buffers and barrier flags, so the halves never wait for each other across
+    GPUs; the copy kernels are small enough to be resident next to the GEMM's CTAs.  Results are
+    those of one EpPeerExchange per half: each token's output depends on its own row only.
+    The whole layer can be captured into one CUDA graph (the side streams fork from and join the
+    capturing stream)."""
+
+    def __init__(self, exchanges):
+        self.ex = exchanges
+        self.chunks = len(exchanges)
+        self.streams = [torch.cuda.Stream() for _ in exchanges]
+        self.tokens = sum(e.P // e.k for e in exchanges)
+
+    @staticmethod
+    def make(num_experts, top_k, H, tokens_per_rank, chunks=2, capacity_factor=1.5, group=None):
+        if tokens_per_rank % chunks != 0:
+            raise ValueError(f"EpPeerPipeline: {tokens_per_rank} tokens per rank do not split into {chunks} chunks")
+        return EpPeerPipeline([EpPeerExchange.make(num_experts, top_k, H, tokens_per_rank // chunks,
+                                                   capacity_factor, group) for _ in range(chunks)])
+
+    def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
+        n = self.chunks
+        if hidden.shape[0] != self.tokens:
+            raise ValueError(f"EpPeerPipeline: built for {self.tokens} tokens per rank, got {hidden.shape[0]}")
+        per = self.tokens // n
+        hs = [hidden[c * per:(c + 1) * per] for c in range(n)]
+        ls = [logits[c * per:(c + 1) * per].contiguous() for c in range(n)]
+        for c in range(n):     # every rank-local check before anything waits for a peer
+            self.ex[c].check_inputs(hs[c], ls[c])
+        cur = torch.cuda.current_stream()
+        states, ys, outs = [None] * n, [None] * n, [None] * n
+        ev_a = [torch.cuda.Event() for _ in range(n)]
+        ev_b = [torch.cuda.Event() for _ in range(n)]
+        for c in range(n):
+            st = self.streams[c]
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                if c > 0:
+                    st.wait_event(ev_a[c - 1])
+                states[c] = self.ex[c].dispatch(hs[c], ls[c], route, permutation)
+                ev_a[c].record(st)
+        for c in range(n):
+            st = self.streams[c]
+            with torch.cuda.stream(st):
+                if c > 0:
+                    st.wait_event(ev_b[c - 1])
+                ys[c] = self.ex[c].experts(expert_ffn)
+                ev_b[c].record(st)
+        for c in range(n):
+            with torch.cuda.stream(self.streams[c]):
+                outs[c] = self.ex[c].finish(ys[c], states[c], unpermute)
+        for c in range(n):
+            cur.wait_stream(self.streams[c])
+            outs[c].record_stream(cur)
+        return torch.cat(outs, 0)
+
+    def overflowed(self):
+        return any(e.overflowed() for e in self.ex)
 
 
 def column_slab(rank, world, N, align=128):

@@ -1,6 +1,7 @@
 """Worker of tests/test_gpu_ep_peer.py: one rank of a 2-GPU (or N-GPU) expert-parallel MoE
-layer.  Runs the layer once with the NCCL all-to-all exchange and three times with the
-peer-memory exchange and prints whether the outputs are identical."""
+layer.  Runs the layer once with the NCCL all-to-all exchange, three times with the
+peer-memory exchange, and as two pipelined halves (eagerly and from a CUDA graph), and prints
+whether the outputs are identical."""
 import os
 import sys
 
@@ -38,6 +39,20 @@ def main():
     torch.cuda.synchronize()
     print(f"EP_PEER rank {rank} equal={torch.equal(out, ref)} overflow={ex.overflowed()} "
           f"status={capi.device_status()}", flush=True)
+    # the same layer as two pipelined halves on side streams, eagerly and replayed from a CUDA graph
+    pipe = D.EpPeerPipeline.make(E, k, H, T, chunks=2, capacity_factor=2.5)
+    for _ in range(2):
+        out2 = pipe.layer(hidden, logits, ffn, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out3 = pipe.layer(hidden, logits, ffn, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    print(f"EP_PIPE rank {rank} equal={torch.equal(out2, ref)} graph_equal={torch.equal(out3, ref)} "
+          f"overflow={pipe.overflowed()} status={capi.device_status()}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

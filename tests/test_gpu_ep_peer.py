@@ -28,6 +28,11 @@ def test_peer_exchange_equals_nccl_exchange_on_two_gpus():
     assert len(lines) == 2, r.stdout[-2000:]
     for ln in lines:
         assert "equal=True" in ln and "overflow=False" in ln and ln.endswith("status=0"), ln
+    # the pipelined form (two halves on side streams), eager and graph-replayed
+    pipes = re.findall(r"EP_PIPE rank \d+ equal=\w+ graph_equal=\w+ overflow=\w+ status=\d+", r.stdout)
+    assert len(pipes) == 2, r.stdout[-2000:] + r.stderr[-2000:]
+    for ln in pipes:
+        assert " equal=True" in ln and "graph_equal=True" in ln and "overflow=False" in ln and ln.endswith("status=0"), ln
 
 
 @pytest.mark.timeout(300)
