@@ -13,6 +13,9 @@
 #include "smxx/quant/dynamic_fp8_quant.h"
 #include "smxx/quant/bf16_to_nvfp4_grouped.h"
 #include "smxx/quant/silu_mul_to_nvfp4_grouped.h"
+#include "smxx/quant/bf16_to_nvfp4.h"
+#include "smxx/quant/reformat_scales.h"
+#include "smxx/quant/nvfp4_dequant_bf16.h"
 
 namespace lc = layerstorm::compute;
 
@@ -92,6 +95,41 @@ REF_API int ref_silu_mul_to_nvfp4_grouped(const void* gate, const void* up, void
     p.input_scales = input_scales;
     try {
         lc::launch_silu_mul_to_nvfp4_grouped(p, stream);
+    } catch (const std::exception&) { return -1; }
+    return static_cast<int>(cudaGetLastError());
+}
+
+REF_API int ref_bf16_to_nvfp4(const void* in, void* packed, void* scales, int M, int N, int K, void* stream) {
+    lc::Bf16ToNvfp4Params p{};
+    p.input = static_cast<const __nv_bfloat16*>(in);
+    p.output_packed = static_cast<uint8_t*>(packed);
+    p.output_scales = static_cast<uint8_t*>(scales);
+    p.M = M; p.N = N; p.K = K;
+    try {
+        lc::launch_bf16_to_nvfp4(p, static_cast<cudaStream_t>(stream));
+    } catch (const std::exception&) { return -1; }
+    return static_cast<int>(cudaGetLastError());
+}
+
+REF_API int ref_reformat_scales(const float* src, void* dst, int rows, int groups_per_row, int M, int N, int K,
+                                int is_scale_a, void* stream) {
+    lc::ReformatScalesParams p{};
+    p.src_scales = src;
+    p.dst_scales = static_cast<uint8_t*>(dst);
+    p.rows = rows; p.groups_per_row = groups_per_row; p.M = M; p.N = N; p.K = K;
+    p.is_scale_a = is_scale_a != 0;
+    try {
+        lc::launch_reformat_scales(p, static_cast<cudaStream_t>(stream));
+    } catch (const std::exception&) { return -1; }
+    return static_cast<int>(cudaGetLastError());
+}
+
+REF_API int ref_nvfp4_dequant_bf16(const void* packed, const void* scales, float weight_scale_2, void* out, int N,
+                                   int K, void* stream) {
+    lc::Nvfp4DequantBf16Params p{};
+    p.N = N; p.K = K; p.input = packed; p.scales = scales; p.weight_scale_2 = weight_scale_2; p.output = out;
+    try {
+        lc::launch_nvfp4_dequant_bf16(p, stream);
     } catch (const std::exception&) { return -1; }
     return static_cast<int>(cudaGetLastError());
 }

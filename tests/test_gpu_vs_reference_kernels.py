@@ -89,3 +89,57 @@ def test_dequant_gemm_vs_reference_kernel(ref, ops, name):
         scale = want.float().abs().max().item()
         assert (got.float() - want.float()).abs().max().item() <= 2.0 ** -7 * scale
         assert (got == want).float().mean().item() > 0.97
+
+
+# ---------------------------------------------------------------------------
+# Single-problem NVFP4 operators (csrc/smxx/quant/bf16_to_nvfp4.cu, reformat_scales.cu,
+# nvfp4_dequant_bf16.cu of the reference): bytes must be equal.
+# ---------------------------------------------------------------------------
+def _need(ref, name):
+    if not hasattr(ref, name):
+        pytest.skip(f"oracle/_ref/libref_gguf.so was built without {name}: rebuild it (make -C oracle ref)")
+    return getattr(ref, name)
+
+
+@pytest.mark.parametrize("M,K", [(1, 64), (7, 256), (130, 1024), (257, 4096)])
+def test_bf16_to_nvfp4_bytes_equal_reference_kernel(ref, ops, M, K):
+    fn = _need(ref, "ref_bf16_to_nvfp4")
+    g = torch.Generator().manual_seed(M * 7 + K)
+    x = (torch.randn(M, K, generator=g) * torch.exp(torch.randn(M, 1, generator=g))).to(torch.bfloat16).cuda()
+    x[0, :16] = 0                                   # an all-zero group
+    packed, scales = ops.bf16_to_nvfp4(x)
+    want_p = torch.zeros_like(packed)
+    want_s = torch.zeros_like(scales)
+    assert fn(_p(x), _p(want_p), _p(want_s), M, 128, K, _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed, want_p)
+    assert torch.equal(scales, want_s)
+
+
+@pytest.mark.parametrize("N,K", [(1, 64), (96, 256), (128, 1024), (300, 2048)])
+def test_reformat_scales_bytes_equal_reference_kernel(ref, ops, N, K):
+    fn = _need(ref, "ref_reformat_scales")
+    g = torch.Generator().manual_seed(N + K)
+    src = (torch.rand(N, K // 16, generator=g) * 500.0 - 5.0).cuda()      # below 0 and above 480 included
+    src[0, 0] = 2.0 ** -10                                                  # rounds to zero or the smallest code
+    got = ops.nvfp4_gemm_preprocess(src, N, K)
+    want = torch.zeros_like(got)
+    assert fn(ctypes.c_void_p(src.data_ptr()), _p(want), N, K // 16, 1, N, K, 0, _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("N,K", [(1, 64), (33, 512), (256, 4096)])
+def test_nvfp4_dequant_bf16_equal_reference_kernel(ref, ops, N, K):
+    fn = _need(ref, "ref_nvfp4_dequant_bf16")
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                   ctypes.c_void_p]
+    g = torch.Generator().manual_seed(N * 3 + K)
+    packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g).cuda()
+    # scale bytes over the whole finite ue4m3 range (no NaN code 0x7F / 0xFF)
+    sc = torch.randint(0, 0x7F, (N, K // 16), dtype=torch.uint8, generator=g).cuda()
+    got = ops.nvfp4_dequant_bf16(packed, sc, 0.37)
+    want = torch.zeros_like(got)
+    assert fn(_p(packed), _p(sc), 0.37, _p(want), N, K, _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
