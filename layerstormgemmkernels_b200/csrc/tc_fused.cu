@@ -28,8 +28,8 @@
 // Tensor memory (512 columns): the accumulators in columns 0..255 (two of NT <= 128 columns,
 // alternating so the epilogue overlaps the next tile, or one of 256), the weight ring in
 // columns 256..511 (8 stages x 32 columns).  Expert batches whose experts hold a little more
-// than 256 rows take token tiles of 384 rows instead (one accumulator in columns 0..383, two
-// MMAs per K step, the ring in the last 128 columns): a second, nearly empty 256-row tile
+// than 256 rows take token tiles of 320 or 384 rows instead (one accumulator in columns 0..nt-1,
+// two MMAs per K step, the ring in the columns after it): a second, nearly empty 256-row tile
 // would repeat the whole weight decoding for a handful of rows.  A stage is "full" after nine arrivals (eight
 // decoder warps + the TMA transaction); tcgen05.commit releases it.  All waits are
 // time-limited; a time-out ends every role and is reported in the status word.
@@ -60,6 +60,8 @@ constexpr int kAColsPerStage = BK / 2;      // 64 fp16 of a row = 32 packed colu
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kRawSlotBytes = kDecThreads * 16;     // 16 packed bytes per decoder thread and K block (Q4_K)
 constexpr int kHdrRingBytes = 4 * kDecThreads * 16; // block headers of four consecutive 256-value blocks, per thread
+constexpr int kTabTiles = 340;                      // grouped calls: tile table copied to shared memory (expert, first row, end row)
+constexpr int kTabBytes = kTabTiles * 12 + 16;
 
 struct FusedArgs {
     const uint8_t* W;             // dense: packed rows
@@ -72,9 +74,9 @@ struct FusedArgs {
     int ldc;
     int out_dtype;
     int K, N, M;
-    int nt;                       // token rows per tile: 32, 64, 128, 256 or 384
-    int box_rows;                 // rows of one TMA box of the token tile (nt, or 128 when nt = 384)
-    int a_col_base;               // first tensor-memory column of the weight ring (256, or 384 when nt = 384)
+    int nt;                       // token rows per tile: 32, 64, 128, 256, 320 or 384
+    int box_rows;                 // rows of one TMA box of the token tile (nt, or 64 above 256)
+    int a_col_base;               // first tensor-memory column of the weight ring (256, or nt above 256)
     int n_wtiles;                 // ceil(N / 128)
     int t_tiles;                  // dense: ceil(M / nt); grouped: capacity of the tile map
     const int* tile_expert;
@@ -95,6 +97,9 @@ struct FusedArgs {
 #ifdef LSG_TCF_EXP
     int dbg;
 #endif
+#ifdef LSG_TCF_TRACE
+    unsigned long long* trace;   // [grid][16] cycle sums per role
+#endif
 };
 // Knock-out switches for timing experiments, only in builds with -DLSG_TCF_EXP (the shipped
 // library has none): environment variable LSG_TCF_EXP = sum of 1 (no epilogue stores), 2 (no
@@ -103,6 +108,29 @@ struct FusedArgs {
 #define TCF_DBG(a, bit) (((a).dbg & (bit)) != 0)
 #else
 #define TCF_DBG(a, bit) false
+#endif
+
+// Where the roles spend their time, only in builds with -DLSG_TCF_TRACE: cycles summed per CTA
+// into trace[blockIdx.x * 16 + slot] by one lane of each role.  Slots: 0 MMA waits for a full
+// stage, 1 MMA waits for a free accumulator, 2 MMA role total, 3 decoder (warp 6) waits for a
+// free stage, 4 decoder total, 5 TMA waits for a free stage, 6 TMA total, 7 epilogue (warp 0)
+// waits for the accumulator, 8 epilogue total, 9 items, 10 K blocks.
+#ifdef LSG_TCF_TRACE
+#define TCF_T0() const long long tcf_t0 = clock64()
+#define TCF_ADD(slot, expr)                                                                                  \
+    do {                                                                                                     \
+        if (a.trace) a.trace[blockIdx.x * 16 + (slot)] += static_cast<unsigned long long>(expr);           \
+    } while (0)
+#define TCF_TIMED(slot, lanecond, stmt)                                                                      \
+    do {                                                                                                     \
+        const long long tcf_a = clock64();                                                                   \
+        stmt;                                                                                                \
+        if (lanecond) TCF_ADD(slot, clock64() - tcf_a);                                                      \
+    } while (0)
+#else
+#define TCF_T0()
+#define TCF_ADD(slot, expr)
+#define TCF_TIMED(slot, lanecond, stmt) stmt
 #endif
 
 // True in exactly one lane of the (converged) warp.
@@ -192,7 +220,7 @@ struct Item {
     bool live;
 };
 
-__device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
+__device__ __forceinline__ Item decode_item(const FusedArgs& a, int w, const int* tab) {
     Item it;
     it.wt = w % a.n_wtiles;
     const int rest = w / a.n_wtiles;
@@ -203,6 +231,13 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int w) {
     it.mend = a.M;
     it.live = true;
     if (a.tile_expert) {
+        if (tab) {   // the CTA's copy of the tile map: no dependent global loads per item
+            it.expert = tab[3 * it.tt];
+            it.mstart = tab[3 * it.tt + 1];
+            it.mend = tab[3 * it.tt + 2];
+            it.live = it.expert >= 0;
+            return it;
+        }
         const int e = a.tile_expert[it.tt];
         it.expert = e;
         it.live = e >= 0;
@@ -239,15 +274,24 @@ struct DecCtx {
     uint32_t tmem_a;        // tensor-memory address of column kAColBase in this warp's lane quadrant
     unsigned int* status;
     uint32_t hint;
+#ifdef LSG_TCF_TRACE
+    unsigned long long* wait_cycles;   // where this thread sums its waits for a free stage (or null)
+#endif
 };
 
 // Waits until the stage is free, stores 2 x 8 packed columns of this thread's lane (column
 // offsets c0 and c1 inside the stage), and arrives on the stage's "full" barrier.
 __device__ __forceinline__ bool publish_stage(const DecCtx& c, Ring& ring, const uint32_t* lo, uint32_t c0,
                                               const uint32_t* hi, uint32_t c1) {
+#ifdef LSG_TCF_TRACE
+    const long long tw = clock64();
+#endif
     if (ring.lap > 0 &&
         !__all_sync(0xffffffffu, mbar_wait_bounded(&c.empty[ring.s], (ring.lap - 1) & 1, c.status, kDevWaitEmpty, c.hint)))
         return false;
+#ifdef LSG_TCF_TRACE
+    if (c.wait_cycles) *c.wait_cycles += static_cast<unsigned long long>(clock64() - tw);
+#endif
     tc_fence_after();  // the MMAs that last read this stage are ordered before the stores
     const uint32_t col = c.tmem_a + static_cast<uint32_t>(ring.s * kAColsPerStage);
     tmem_st8(col + c0, lo);
@@ -403,7 +447,8 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stage_bytes = a.nt * 128;              // one (64 x NT) fp16 token tile
     uint8_t* raw = smem + a.stages * stage_bytes;   // packed-weight ring of the staged decoders
-    uint64_t* full = reinterpret_cast<uint64_t*>(raw + a.raw_bytes);
+    int* tab_mem = reinterpret_cast<int*>(raw + a.raw_bytes);   // kTabBytes
+    uint64_t* full = reinterpret_cast<uint64_t*>(raw + a.raw_bytes + kTabBytes);
     uint64_t* empty = full + kMaxStages;
     uint64_t* acc_full = empty + kMaxStages;  // [2]
     uint64_t* acc_empty = acc_full + 2;       // [2]
@@ -434,6 +479,28 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 
     pdl_wait_prior();  // x16, the tile map and the zeroed counters come from earlier kernels
 
+    // Grouped calls: every role looks every item's tile up, and three dependent global loads per
+    // look-up sit in front of each item's first copy, decode and MMA.  The tile map is small, so
+    // the CTA resolves it once into shared memory.
+    const int* tab = nullptr;
+    if (a.tile_expert && a.t_tiles <= kTabTiles) {
+        for (int t = threadIdx.x; t < a.t_tiles; t += kFusedThreads) {
+            const int e = a.tile_expert[t];
+            int ms = 0, me = 0;
+            if (e >= 0) {
+                ms = min(a.tile_mstart[t], a.M);
+                me = min(a.expert_offsets[e + 1], a.M);
+                const int m = me - min(a.expert_offsets[e], a.M);
+                me = min(me, ms + balanced_tile_rows(m, a.nt));
+            }
+            tab_mem[3 * t] = e;
+            tab_mem[3 * t + 1] = ms;
+            tab_mem[3 * t + 2] = me;
+        }
+        __syncthreads();
+        tab = tab_mem;
+    }
+
     const int kblocks_all = (a.K + BK - 1) / BK;
     const int total = a.t_tiles * a.ksplit * a.n_wtiles;
     const uint32_t hint = 2000u;  // suspend-time hint of the barrier waits, ns
@@ -441,15 +508,19 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
     if (warp == 4) {
         // ------------------------------ TMA producer (x16 tiles) ------------------
         if (lane == 0) {
+            TCF_T0();
             Ring ring = {0, 0u, a.stages};
             for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
-                const Item im = decode_item(a, w);
+                const Item im = decode_item(a, w, tab);
                 if (!im.live) continue;
                 const int kb0 = im.ks * a.kb_per_split;
                 const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
+                const int live_rows = min(a.nt, im.mend - im.mstart);
+                const int live_boxes = max(1, (live_rows + a.box_rows - 1) / a.box_rows);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (ring.lap > 0 &&
-                        !mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint)) {
+                    bool freed = true;
+                    TCF_TIMED(5, true, if (ring.lap > 0) freed = mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint));
+                    if (!freed) {
                         *abort_flag = 1;
                         break;
                     }
@@ -458,52 +529,57 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                         ring.advance();
                         continue;
                     }
-                    mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(stage_bytes));
-                    for (int r0 = 0; r0 < a.nt; r0 += a.box_rows)
+                    // only the boxes that hold live token rows: the rest of the stage is never read,
+                    // and every byte copied takes shared-memory bandwidth from the MMA's operand reads
+                    mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(live_boxes * a.box_rows * 128));
+                    for (int r0 = 0; r0 < live_boxes * a.box_rows; r0 += a.box_rows)
                         tma_load_2d(smem + ring.s * stage_bytes + r0 * 128, &tmX, kb * BK, im.mstart + r0, &full[ring.s]);
                     ring.advance();
                 }
             }
+            TCF_ADD(6, clock64() - tcf_t0);
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
         // The whole warp walks the loop so that descriptors and addresses stay warp-uniform
         // values; one elected lane issues the tensor-core instructions.
+        TCF_T0();
         Ring ring = {0, 0u, a.stages};
         int tile_i = 0, ab = 0;
         uint32_t acc_lap = 0;  // how often the accumulator set has been cycled through
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
-            const Item im = decode_item(a, w);
+            const Item im = decode_item(a, w, tab);
             if (!im.live) continue;
             const int kb0 = im.ks * a.kb_per_split;
             const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
-            if (acc_lap > 0)
-                ok = __all_sync(0xffffffffu,
-                                mbar_wait_bounded(&acc_empty[ab], (acc_lap - 1) & 1, a.status, kDevWaitTmem, hint));
+            TCF_TIMED(1, lane == 0, if (acc_lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], (acc_lap - 1) & 1, a.status, kDevWaitTmem, hint)));
             if (!ok) break;
+            if (lane == 0) { TCF_ADD(9, 1); TCF_ADD(10, kb1 - kb0); }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + ab * a.nt;
             // N of the instruction follows the token rows that are really in the tile (a multiple
             // of 16): the ragged last tile of an expert costs tensor time for its rows only
             const int live = min(a.nt, im.mend - im.mstart);
             const int live16 = max(16, (live + 15) & ~15);
-            const int n1 = min(256, live16), n2 = live16 - n1;   // second instruction: rows 256.. of a 384-row tile
+            // more than 256 rows take two instructions per K step; split evenly (a short second
+            // instruction would cost its issue time, not its tensor time)
+            const int n1 = live16 <= 256 ? live16 : ((live16 >> 1) + 15) & ~15, n2 = live16 - n1;
             const uint32_t idesc = idesc_f16(WM, n1);
             const uint32_t idesc2 = idesc_f16(WM, max(16, n2));
             for (int kb = kb0; kb < kb1; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint));
+                TCF_TIMED(0, lane == 0, ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint)));
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t xdesc = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes));
-                const uint64_t xdesc2 = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes + 256 * 128));
+                const uint64_t xdesc2 = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes + n1 * 128));
                 const uint32_t a_tmem = tmem_base + a.a_col_base + ring.s * kAColsPerStage;
                 if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         tc_mma_f16_ta(d_tmem, a_tmem + 8 * k, xdesc + 2 * k, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
                         if (n2 > 0)
-                            tc_mma_f16_ta(d_tmem + 256, a_tmem + 8 * k, xdesc2 + 2 * k, idesc2, (kb != kb0 || k != 0) ? 1u : 0u);
+                            tc_mma_f16_ta(d_tmem + n1, a_tmem + 8 * k, xdesc2 + 2 * k, idesc2, (kb != kb0 || k != 0) ? 1u : 0u);
                     }
                     tc_commit(&empty[ring.s]);
                 }
@@ -520,6 +596,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             }
         }
         if (!ok) *abort_flag = 1;
+        if (lane == 0) TCF_ADD(2, clock64() - tcf_t0);
     } else if (warp >= 6) {
         // ------------------------------ weight decoders ---------------------------
         // warp -> lane quadrant (a warp may only touch tensor-memory lanes 32 * (warp % 4) ..),
@@ -534,9 +611,13 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         ctx.tmem_a = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a.a_col_base;
         ctx.status = a.status;
         ctx.hint = hint;
+#ifdef LSG_TCF_TRACE
+        ctx.wait_cycles = (a.trace && warp == 6 && lane == 0) ? a.trace + blockIdx.x * 16 + 3 : nullptr;
+#endif
+        TCF_T0();
         Ring ring = {0, 0u, a.stages};
         for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
-            const Item im = decode_item(a, w);
+            const Item im = decode_item(a, w, tab);
             if (!im.live) continue;
             const int kb0 = im.ks * a.kb_per_split;
             const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
@@ -573,15 +654,17 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 break;
             }
         }
+        if (warp == 6 && lane == 0) TCF_ADD(4, clock64() - tcf_t0);
     } else {
         // ------------------------------ epilogue (warps 0-3) ----------------------
+        TCF_T0();
         int tile_i = 0, ab = 0;
         uint32_t acc_lap = 0;
         for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
-            const Item im = decode_item(a, w);
+            const Item im = decode_item(a, w, tab);
             if (!im.live) continue;
-            const bool landed = __all_sync(
-                0xffffffffu, mbar_wait_bounded(&acc_full[ab], acc_lap & 1, a.status, kDevWaitMma, hint));
+            bool landed = false;
+            TCF_TIMED(7, warp == 0 && lane == 0, landed = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[ab], acc_lap & 1, a.status, kDevWaitMma, hint)));
             if (!landed) {
                 *abort_flag = 1;
                 break;
@@ -600,7 +683,21 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                     if (TCF_DBG(a, 8)) break;
                     uint32_t v[32];
                     tmem_ld32(t_lane + c, v);
-                    if (n_ok && !TCF_DBG(a, 1)) {
+                    if (n_ok && a.n_out == 0 && !a.row_scale && a.out_dtype == LSG_DTYPE_BF16 && !TCF_DBG(a, 1)) {
+                        // the common case on its own: one conversion and one 2-byte store per token row
+                        const int rows = min(32, im.mend - (im.mstart + c));
+                        uint16_t* dst = static_cast<uint16_t*>(a.C) + static_cast<size_t>(im.mstart + c) * a.ldc + n;
+                        if (rows == 32) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                dst[static_cast<size_t>(i) * a.ldc] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(v[i])));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (i < rows)
+                                    dst[static_cast<size_t>(i) * a.ldc] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(v[i])));
+                        }
+                    } else if (n_ok && !TCF_DBG(a, 1)) {
                         const int rows = min(32, im.mend - (im.mstart + c));
                         if (a.row_scale) {
 #pragma unroll
@@ -706,6 +803,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 ++acc_lap;
             }
         }
+        if (warp == 0 && lane == 0) TCF_ADD(8, clock64() - tcf_t0);
     }
 
     tc_fence_before();
@@ -881,6 +979,11 @@ x_rows_to_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ o
     }
 }
 
+#ifdef LSG_TCF_TRACE
+unsigned long long* g_tcf_trace = nullptr;   // [launch slot][148][16]
+int g_tcf_trace_slots = 0, g_tcf_trace_launch = 0;
+#endif
+
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 bool staged_decoder(int type) { return type == LSG_GGUF_Q4_K; }
@@ -906,9 +1009,9 @@ Plan make_plan(long long rows, int nt, int t_tiles, int N, int K, bool allow_spl
     // packed-weight ring of the staged decoders, 8 K blocks deep
     p.raw_depth = staged ? 8 : 0;
     p.raw_bytes = staged ? p.raw_depth * kRawSlotBytes + kHdrRingBytes : 0;
-    p.stages = (224 * 1024 - p.raw_bytes) / stage_bytes;
-    p.box_rows = nt > 256 ? 128 : nt;
-    p.a_col_base = nt > 256 ? 384 : kAColBase;
+    p.stages = (224 * 1024 - p.raw_bytes - kTabBytes) / stage_bytes;
+    p.box_rows = nt > 256 ? 64 : nt;   // taller tiles: boxes of 64 rows, of which only those with live rows are copied
+    p.a_col_base = nt > 256 ? nt : kAColBase;
     const int ring_stages = (kTmemCols - p.a_col_base) / kAColsPerStage;
     if (p.stages > ring_stages) p.stages = ring_stages;
     if (p.stages > kMaxStages) p.stages = kMaxStages;
@@ -944,7 +1047,7 @@ int launch_fused_t(const CUtensorMap& tmX, const FusedArgs& a, cudaStream_t s) {
     static bool configured[64] = {};
     int dev = 0;
     LSG_CUDA_TRY(cudaGetDevice(&dev));
-    const int smem = a.stages * a.nt * 128 + a.raw_bytes + 1024 + 512;
+    const int smem = a.stages * a.nt * 128 + a.raw_bytes + kTabBytes + 1024 + 512;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
         LSG_CUDA_TRY(cudaFuncSetAttribute(tc_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           227 * 1024));
@@ -954,7 +1057,15 @@ int launch_fused_t(const CUtensorMap& tmX, const FusedArgs& a, cudaStream_t s) {
     int grid = sm_count();
     if (grid > items) grid = static_cast<int>(items);
     if (grid < 1) grid = 1;
+#ifdef LSG_TCF_TRACE
+    FusedArgs at = a;
+    at.trace = g_tcf_trace && g_tcf_trace_slots > 0
+                   ? g_tcf_trace + static_cast<size_t>(g_tcf_trace_launch++ % g_tcf_trace_slots) * 148 * 16
+                   : nullptr;
+    LSG_CUDA_TRY(launch_kernel(tc_fused_kernel<T>, dim3(grid), dim3(kFusedThreads), smem, s, true, tmX, at));
+#else
     LSG_CUDA_TRY(launch_kernel(tc_fused_kernel<T>, dim3(grid), dim3(kFusedThreads), smem, s, true, tmX, a));
+#endif
     return LSG_OK;
 }
 
@@ -1009,7 +1120,7 @@ int tc_fused_grouped_tile_m(long long T, int E) {
         const char* e = getenv("LSG_TC_FUSED_TILE_M");
         return e ? atoi(e) : 0;
     }();
-    if (force == 64 || force == 128 || force == 256 || force == 384) return force;
+    if (force == 64 || force == 128 || force == 256 || force == 320 || force == 384) return force;
     const long long avg = E > 0 ? (T + E - 1) / E : T;
     // Tiles are balanced per expert (routing.cu), so the tile height only caps how many rows
     // share one pass over an expert's weights; the 5/6 margin keeps most experts of a routed
@@ -1017,7 +1128,11 @@ int tc_fused_grouped_tile_m(long long T, int E) {
     if (avg * 6 <= 64 * 5) return 64;      // the workspace reserves a tile map for tiles of 64 rows or more
     if (avg * 6 <= 128 * 5) return 128;
     if (avg * 6 <= 256 * 5) return 256;
-    return 384;
+    // above 256 rows the accumulator is single and the stages are large: 320-row tiles keep four
+    // stages in shared memory (384-row tiles three), so 384 only where it saves a second tile
+    if (avg * 6 <= 320 * 5) return 320;
+    if (avg * 6 <= 384 * 5) return 384;
+    return 320;
 }
 
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K) {
@@ -1235,3 +1350,13 @@ extern "C" int lsg_mmq_set_weight_path(int mode) {
     lsg::g_mode_override = mode < 0 ? -1 : mode;
     return LSG_OK;
 }
+
+#ifdef LSG_TCF_TRACE
+// Trace builds only: buf holds slots x 148 x 16 zeroed 64-bit counters; launch k sums into slot k % slots.
+extern "C" __attribute__((visibility("default"))) int lsg_tc_fused_set_trace(void* buf, int slots) {
+    lsg::g_tcf_trace = static_cast<unsigned long long*>(buf);
+    lsg::g_tcf_trace_slots = slots;
+    lsg::g_tcf_trace_launch = 0;
+    return LSG_OK;
+}
+#endif
