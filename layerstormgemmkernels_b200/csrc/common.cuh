@@ -67,6 +67,19 @@ __host__ __device__ __forceinline__ int balanced_tile_rows(int m, int tile_m) {
     return (((m + tiles - 1) / tiles) + 15) & ~15;
 }
 
+// True in exactly one lane of a converged warp (all 32 lanes must call it).
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
                  : "memory");

@@ -427,34 +427,39 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         // Weights are constants of the model, so this does not wait for the
         // previous kernel in the stream.
         // ------------------------------------------------------------------
-        if (lane == 0) {
-            const uint64_t policy = l2_policy_evict_first();
-            const uintptr_t w_base = reinterpret_cast<uintptr_t>(Wm);
-            const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(Nm) * a.row_bytes) & ~uintptr_t(15);
-            int s = 0;
-            uint32_t lap = 0;  // ring position of slab i: stage s, lap = i / stages
-            for (int i = 0; i < n_slabs; ++i, s = (s + 1 == a.stages) ? 0 : s + 1, lap += (s == 0)) {
-                if (lap > 0 && !mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, 2000u, a.wait_limit))
-                    break;
-                // Failure-path test hook: this slab is never loaded nor published, so its
-                // consumers run into their wait limit, report and return.
-                if (i == a.drop_slab && blockIdx.x == 0) break;
-                const int r0 = row_begin + i * a.slab_rows;
-                const int r1 = min(r0 + a.slab_rows, row_end);
-                const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
-                const uintptr_t src_e = w_base + static_cast<uintptr_t>(r1) * a.row_bytes;
-                const uintptr_t cp_b = src_b & ~uintptr_t(15);
-                uintptr_t cp_e = (src_e + 15) & ~uintptr_t(15);
-                uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
-                if (cp_e > w_end_al) {
-                    // Last rows of the matrix end off a 16-byte boundary: the
-                    // bulk copy stops at the last whole 16 bytes and the
-                    // remainder is moved with byte loads.
-                    cp_e = w_end_al > cp_b ? w_end_al : cp_b;
+        // The whole warp walks the loop with the same values in every lane and one elected
+        // lane issues the copy: bulk copies and barrier operations take their operands from
+        // warp-uniform registers, and inside a one-lane branch each of them costs several
+        // times what it costs in converged code.
+        const uint64_t policy = l2_policy_evict_first();
+        const uintptr_t w_base = reinterpret_cast<uintptr_t>(Wm);
+        const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(Nm) * a.row_bytes) & ~uintptr_t(15);
+        int s = 0;
+        uint32_t lap = 0;  // ring position of slab i: stage s, lap = i / stages
+        for (int i = 0; i < n_slabs; ++i, s = (s + 1 == a.stages) ? 0 : s + 1, lap += (s == 0)) {
+            if (lap > 0 &&
+                !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, 2000u, a.wait_limit)))
+                break;
+            // Failure-path test hook: this slab is never loaded nor published, so its
+            // consumers run into their wait limit, report and return.
+            if (i == a.drop_slab && blockIdx.x == 0) break;
+            const int r0 = row_begin + i * a.slab_rows;
+            const int r1 = min(r0 + a.slab_rows, row_end);
+            const uintptr_t src_b = w_base + static_cast<uintptr_t>(r0) * a.row_bytes;
+            const uintptr_t src_e = w_base + static_cast<uintptr_t>(r1) * a.row_bytes;
+            const uintptr_t cp_b = src_b & ~uintptr_t(15);
+            uintptr_t cp_e = (src_e + 15) & ~uintptr_t(15);
+            uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
+            const bool ragged = cp_e > w_end_al;
+            if (ragged) cp_e = w_end_al > cp_b ? w_end_al : cp_b;
+            const uint32_t bytes = static_cast<uint32_t>(cp_e - cp_b);
+            if (elect_one_lane()) {
+                if (ragged) {
+                    // Last rows of the matrix end off a 16-byte boundary: the bulk copy stops at
+                    // the last whole 16 bytes and the remainder is moved with byte loads.
                     for (uintptr_t p = cp_e; p < src_e; ++p)
                         dst[p - cp_b] = *reinterpret_cast<const uint8_t*>(p);
                 }
-                const uint32_t bytes = static_cast<uint32_t>(cp_e - cp_b);
                 slab_in_stage[s] = i;  // published before the arrive below (release)
                 if (i == 0) LSG_TRACE(1);
                 if (i == n_slabs - 1) LSG_TRACE(2);
@@ -465,6 +470,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
                     mbar_arrive(&full[s]);
                 }
             }
+            __syncwarp();
         }
         return;
     }

@@ -143,9 +143,13 @@ nvfp4_mma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
     if (warp == 4) {
         // ------------------------------ producer ------------------------------
-        if (lane == 0) {
-            int it = 0;
-            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+        // The whole warp walks the loop, one elected lane issues the four copies of a stage
+        // (see the MMA issuer for why).
+        {
+            int s = 0;
+            uint32_t lap = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
                 const int t = w % a.m_tiles, j = w / a.m_tiles;
                 int mstart = t * FM;
                 long long brow0 = static_cast<long long>(j) * FN;
@@ -160,58 +164,64 @@ nvfp4_mma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     sfa_tile = a.sfa + (static_cast<long long>(a.sf_offsets[e]) + 128ll * local_tile) * gpr;
                     sfb_tile += static_cast<long long>(e) * a.sfb_expert_bytes;
                 }
-                for (int kt = 0; kt < ktiles; ++kt, ++it) {
-                    const int s = it % kFStages;
-                    if (it >= kFStages &&
-                        !mbar_wait_bounded(&empty[s], ((it / kFStages) - 1) & 1, a.status, kDevWaitEmpty)) {
-                        *abort_flag = 1;
-                        break;
-                    }
+                for (int kt = 0; kt < ktiles; ++kt) {
+                    if (lap > 0)
+                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty));
+                    if (!ok) break;
                     const int atoms = min(4, (a.K - kt * 256) >> 6);   // 64-value K blocks in this tile
                     uint8_t* sA = smem + s * kFStageBytes;
                     uint8_t* sB = sA + kFABytes;
                     uint8_t* sSA = sB + kFBBytes;
                     uint8_t* sSB = sSA + kFSfBytes;
-                    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(kFABytes + kFBBytes + 2 * atoms * 512));
-                    tma_load_2d(sA, &tmA, kt * FKB, mstart, &full[s]);
-                    tma_load_2d(sB, &tmB, kt * FKB, static_cast<int>(brow0), &full[s]);
-                    bulk_g2s(sSA, sfa_tile + static_cast<long long>(kt) * 2048, static_cast<uint32_t>(atoms * 512), &full[s]);
-                    bulk_g2s(sSB, sfb_tile + static_cast<long long>(kt) * 2048, static_cast<uint32_t>(atoms * 512), &full[s]);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(kFABytes + kFBBytes + 2 * atoms * 512));
+                        tma_load_2d(sA, &tmA, kt * FKB, mstart, &full[s]);
+                        tma_load_2d(sB, &tmB, kt * FKB, static_cast<int>(brow0), &full[s]);
+                        bulk_g2s(sSA, sfa_tile + static_cast<long long>(kt) * 2048, static_cast<uint32_t>(atoms * 512), &full[s]);
+                        bulk_g2s(sSB, sfb_tile + static_cast<long long>(kt) * 2048, static_cast<uint32_t>(atoms * 512), &full[s]);
+                    }
+                    __syncwarp();
+                    if (++s == kFStages) {
+                        s = 0;
+                        ++lap;
+                    }
                 }
             }
+            if (!ok) *abort_flag = 1;
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = idesc_nvf4(FM, FN);
-            int it = 0, tile_i = 0;
-            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
-                const int t = w % a.m_tiles;
-                if (a.tile_expert && a.tile_expert[t] < 0) continue;
-                const int ab = tile_i & 1;
-                if (tile_i >= 2 &&
-                    !mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status, kDevWaitTmem)) {
-                    *abort_flag = 1;
-                    break;
-                }
+        // The whole warp walks the loop and one elected lane issues: in converged code the
+        // descriptors and addresses are warp-uniform values, and an issue costs about 20 cycles;
+        // the same instructions inside a one-lane branch measured about 60 cycles each, which
+        // with eight scale copies and four MMAs per stage was three times the tensor time.
+        constexpr uint32_t idesc = idesc_nvf4(FM, FN);
+        int s = 0, tile_i = 0;
+        uint32_t lap = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
+            const int t = w % a.m_tiles;
+            if (a.tile_expert && a.tile_expert[t] < 0) continue;
+            const int ab = tile_i & 1;
+            if (tile_i >= 2)
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status, kDevWaitTmem));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + ab * FN;
+            for (int kt = 0; kt < ktiles; ++kt) {
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[s], lap & 1, a.status, kDevWaitFull));
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * FN;
-                for (int kt = 0; kt < ktiles; ++kt, ++it) {
-                    const int s = it % kFStages;
-                    if (!mbar_wait_bounded(&full[s], (it / kFStages) & 1, a.status, kDevWaitFull)) {
-                        *abort_flag = 1;
-                        break;
-                    }
-                    tc_fence_after();
-                    const int atoms = min(4, (a.K - kt * 256) >> 6);
-                    const uint32_t sA = smem_u32(smem + s * kFStageBytes);
-                    const uint32_t sSA = sA + kFABytes + kFBBytes, sSB = sSA + kFSfBytes;
+                const int atoms = min(4, (a.K - kt * 256) >> 6);
+                const uint32_t sA = smem_u32(smem + s * kFStageBytes);
+                const uint32_t sSA = sA + kFABytes + kFBBytes, sSB = sSA + kFSfBytes;
+                const uint64_t adesc = smem_desc_sw128(sA);
+                const uint64_t bdesc = smem_desc_sw128(sA + kFABytes);
+                if (elect_one()) {
                     for (int k = 0; k < atoms; ++k) {
                         tc_cp_sf(tmem_base + kFSfaCol + 4 * k, smem_desc_sf_atom(sSA + 512 * k));
                         tc_cp_sf(tmem_base + kFSfbCol + 4 * k, smem_desc_sf_atom(sSB + 512 * k));
                     }
-                    const uint64_t adesc = smem_desc_sw128(sA);
-                    const uint64_t bdesc = smem_desc_sw128(sA + kFABytes);
                     for (int k = 0; k < atoms; ++k) {
                         // 64 values = 32 bytes further along K inside the swizzle atom
                         tc_mma_nvf4(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, tmem_base + kFSfaCol + 4 * k,
@@ -219,11 +229,18 @@ nvfp4_mma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                     tc_commit(&empty[s]);
                 }
-                if (*abort_flag) break;
-                tc_commit(&acc_full[ab]);
-                ++tile_i;
+                __syncwarp();
+                if (++s == kFStages) {
+                    s = 0;
+                    ++lap;
+                }
             }
+            if (!ok) break;
+            if (elect_one()) tc_commit(&acc_full[ab]);
+            __syncwarp();
+            ++tile_i;
         }
+        if (!ok) *abort_flag = 1;
     } else {
         // ------------------------------ epilogue (warps 0-3) ------------------------------
         int tile_i = 0;

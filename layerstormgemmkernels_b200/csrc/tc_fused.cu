@@ -133,18 +133,6 @@ struct FusedArgs {
 #define TCF_TIMED(slot, lanecond, stmt) stmt
 #endif
 
-// True in exactly one lane of the (converged) warp.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "elect.sync _|p, 0xffffffff;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(pred));
-    return pred != 0;
-}
 // Eight 32-bit columns of this thread's tensor-memory lane (the warp's lane quadrant).
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
@@ -507,10 +495,12 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
 
     if (warp == 4) {
         // ------------------------------ TMA producer (x16 tiles) ------------------
-        if (lane == 0) {
+        // The whole warp walks the loop, one elected lane issues the copies (see the MMA issuer).
+        {
             TCF_T0();
             Ring ring = {0, 0u, a.stages};
-            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
                 const Item im = decode_item(a, w, tab);
                 if (!im.live) continue;
                 const int kb0 = im.ks * a.kb_per_split;
@@ -518,26 +508,25 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 const int live_rows = min(a.nt, im.mend - im.mstart);
                 const int live_boxes = max(1, (live_rows + a.box_rows - 1) / a.box_rows);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    bool freed = true;
-                    TCF_TIMED(5, true, if (ring.lap > 0) freed = mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint));
-                    if (!freed) {
-                        *abort_flag = 1;
-                        break;
+                    TCF_TIMED(5, lane == 0, if (ring.lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint)));
+                    if (!ok) break;
+                    if (elect_one()) {
+                        if (TCF_DBG(a, 2)) {
+                            mbar_arrive(&full[ring.s]);
+                        } else {
+                            // only the boxes that hold live token rows: the rest of the stage is never read,
+                            // and every byte copied takes shared-memory bandwidth from the MMA's operand reads
+                            mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(live_boxes * a.box_rows * 128));
+                            for (int r0 = 0; r0 < live_boxes * a.box_rows; r0 += a.box_rows)
+                                tma_load_2d(smem + ring.s * stage_bytes + r0 * 128, &tmX, kb * BK, im.mstart + r0, &full[ring.s]);
+                        }
                     }
-                    if (TCF_DBG(a, 2)) {
-                        mbar_arrive(&full[ring.s]);
-                        ring.advance();
-                        continue;
-                    }
-                    // only the boxes that hold live token rows: the rest of the stage is never read,
-                    // and every byte copied takes shared-memory bandwidth from the MMA's operand reads
-                    mbar_arrive_expect_tx(&full[ring.s], static_cast<uint32_t>(live_boxes * a.box_rows * 128));
-                    for (int r0 = 0; r0 < live_boxes * a.box_rows; r0 += a.box_rows)
-                        tma_load_2d(smem + ring.s * stage_bytes + r0 * 128, &tmX, kb * BK, im.mstart + r0, &full[ring.s]);
+                    __syncwarp();
                     ring.advance();
                 }
             }
-            TCF_ADD(6, clock64() - tcf_t0);
+            if (!ok) *abort_flag = 1;
+            if (lane == 0) TCF_ADD(6, clock64() - tcf_t0);
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------

@@ -144,30 +144,30 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = idesc_f16(BM, BN);
-            int it = 0, tile_i = 0;
-            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
-                const int t = w % a.m_tiles;
-                if (a.tile_expert && a.tile_expert[t] < 0) continue;
-                const int ab = tile_i & 1;
-                if (tile_i >= 2 &&
-                    !mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status, kDevWaitTmem)) {
-                    *abort_flag = 1;
-                    break;
-                }
+        // The whole warp walks the loop and one elected lane issues: descriptors and addresses
+        // are then warp-uniform values (an issue inside a one-lane branch costs about three
+        // times as long).
+        constexpr uint32_t idesc = idesc_f16(BM, BN);
+        int s = 0, tile_i = 0;
+        uint32_t lap = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
+            const int t = w % a.m_tiles;
+            if (a.tile_expert && a.tile_expert[t] < 0) continue;
+            const int ab = tile_i & 1;
+            if (tile_i >= 2)
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], ((tile_i >> 1) - 1) & 1, a.status, kDevWaitTmem));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + ab * BN;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[s], lap & 1, a.status, kDevWaitFull));
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * BN;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait_bounded(&full[s], (it / kStages) & 1, a.status, kDevWaitFull)) {
-                        *abort_flag = 1;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t sA = smem_u32(smem + s * kStageBytes);
-                    const uint64_t adesc = smem_desc_sw128(sA);
-                    const uint64_t bdesc = smem_desc_sw128(sA + kABytes);
+                const uint32_t sA = smem_u32(smem + s * kStageBytes);
+                const uint64_t adesc = smem_desc_sw128(sA);
+                const uint64_t bdesc = smem_desc_sw128(sA + kABytes);
+                if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k) {
                         // 16 fp16 = 32 bytes further along K inside the swizzle atom: +2 in
@@ -176,11 +176,18 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                     tc_commit(&empty[s]);  // the stage is free once these MMAs have read it
                 }
-                if (*abort_flag) break;
-                tc_commit(&acc_full[ab]);  // accumulator complete
-                ++tile_i;
+                __syncwarp();
+                if (++s == kStages) {
+                    s = 0;
+                    ++lap;
+                }
             }
+            if (!ok) break;
+            if (elect_one()) tc_commit(&acc_full[ab]);  // accumulator complete
+            __syncwarp();
+            ++tile_i;
         }
+        if (!ok) *abort_flag = 1;
     } else {
         // ------------------------------ epilogue (warps 0-3) ----------------------
         int tile_i = 0;
