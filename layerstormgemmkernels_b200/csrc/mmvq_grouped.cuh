@@ -102,38 +102,44 @@ __global__ void __launch_bounds__(512, 1) mmvq_grouped_kernel(const GroupedArgs 
     const int n_slabs = *n_slabs_sh;
 
     if (is_producer) {
-        if (lane == 0) {
-            const uint64_t policy = l2_policy_evict_first();
-            for (int i = 0; i < n_slabs; ++i) {
-                const int s = i % a.stages;
-                if (i >= a.stages) {
-                    const uint32_t parity = ((i / a.stages) - 1) & 1;
-                    if (*abort_flag || !mbar_wait_bounded(&empty[s], parity, a.status, kDevWaitEmpty)) {
-                        *abort_flag = 1;
-                        break;
-                    }
+        // The whole warp walks the loop with the same values in every lane; one elected lane
+        // issues the copy (bulk copies and barrier operations take warp-uniform operands and
+        // cost several times as much inside a one-lane branch).
+        const uint64_t policy = l2_policy_evict_first();
+        int s = 0;
+        uint32_t lap = 0;
+        for (int i = 0; i < n_slabs; ++i) {
+            if (lap > 0) {
+                const bool ok = __all_sync(0xffffffffu, !*abort_flag && mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty));
+                if (!ok) {
+                    *abort_flag = 1;
+                    break;
                 }
-                const int sg = slab_tab[3 * i], n0 = slab_tab[3 * i + 1], rows = slab_tab[3 * i + 2];
-                const int e = a.seg[1 + 3 * sg];
-                const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.B_ptrs[e]);
-                const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(a.N) * a.row_bytes) & ~uintptr_t(15);
-                const uintptr_t src_b = w_base + static_cast<uintptr_t>(n0) * a.row_bytes;
-                const uintptr_t src_e = src_b + static_cast<uintptr_t>(rows) * a.row_bytes;
-                uintptr_t cp_b = src_b & ~uintptr_t(15);
-                uintptr_t cp_e = (src_e + 15) & ~uintptr_t(15);
-                uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
-                if ((w_base & 15) != 0) {
+            }
+            const int sg = slab_tab[3 * i], n0 = slab_tab[3 * i + 1], rows = slab_tab[3 * i + 2];
+            const int e = a.seg[1 + 3 * sg];
+            const uintptr_t w_base = reinterpret_cast<uintptr_t>(a.B_ptrs[e]);
+            const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(a.N) * a.row_bytes) & ~uintptr_t(15);
+            const uintptr_t src_b = w_base + static_cast<uintptr_t>(n0) * a.row_bytes;
+            const uintptr_t src_e = src_b + static_cast<uintptr_t>(rows) * a.row_bytes;
+            uintptr_t cp_b = src_b & ~uintptr_t(15);
+            uintptr_t cp_e = (src_e + 15) & ~uintptr_t(15);
+            uint8_t* dst = ring + static_cast<size_t>(s) * a.stage_bytes;
+            const bool unaligned = (w_base & 15) != 0;
+            const bool ragged = !unaligned && cp_e > w_end_al;
+            if (unaligned) cp_e = cp_b;
+            else if (ragged) cp_e = w_end_al > cp_b ? w_end_al : cp_b;
+            const uint32_t bytes = static_cast<uint32_t>(cp_e - cp_b);
+            if (elect_one_lane()) {
+                if (unaligned) {
                     // Weights must be 16-byte aligned for bulk copies; fall back to byte
                     // loads for such an expert rather than read before its buffer.
                     for (uintptr_t p = src_b; p < src_e; ++p)
                         dst[(p - src_b) + (src_b & 15)] = *reinterpret_cast<const uint8_t*>(p);
-                    cp_e = cp_b;
-                } else if (cp_e > w_end_al) {
-                    cp_e = w_end_al > cp_b ? w_end_al : cp_b;
+                } else if (ragged) {
                     for (uintptr_t p = cp_e; p < src_e; ++p)
                         dst[p - cp_b] = *reinterpret_cast<const uint8_t*>(p);
                 }
-                const uint32_t bytes = static_cast<uint32_t>(cp_e - cp_b);
                 slab_in_stage[s] = i;
                 if (bytes > 0) {
                     mbar_arrive_expect_tx(&full[s], bytes);
@@ -141,6 +147,11 @@ __global__ void __launch_bounds__(512, 1) mmvq_grouped_kernel(const GroupedArgs 
                 } else {
                     mbar_arrive(&full[s]);
                 }
+            }
+            __syncwarp();
+            if (++s == a.stages) {
+                s = 0;
+                ++lap;
             }
         }
         return;

@@ -116,9 +116,12 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            int it = 0;
-            for (int w = blockIdx.x; w < total && !*abort_flag; w += gridDim.x) {
+        // The whole warp walks the loop, one elected lane issues the copies (see the MMA issuer).
+        {
+            int s = 0;
+            uint32_t lap = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok && !*abort_flag; w += gridDim.x) {
                 const int t = w % a.m_tiles, j = w / a.m_tiles;
                 int mstart = t * BM, brow0 = j * BN;
                 if (a.tile_expert) {
@@ -127,20 +130,25 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     mstart = a.tile_mstart[t];
                     brow0 = e * a.N + j * BN;
                 }
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % kStages;
-                    if (it >= kStages &&
-                        !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1, a.status, kDevWaitEmpty)) {
-                        *abort_flag = 1;
-                        break;
-                    }
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (lap > 0)
+                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty));
+                    if (!ok) break;
                     uint8_t* sA = smem + s * kStageBytes;
                     uint8_t* sB = sA + kABytes;
-                    mbar_arrive_expect_tx(&full[s], kStageBytes);
-                    tma_load_2d(sA, &tmA, kb * BK, mstart, &full[s]);
-                    tma_load_2d(sB, &tmB, kb * BK, brow0, &full[s]);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(&full[s], kStageBytes);
+                        tma_load_2d(sA, &tmA, kb * BK, mstart, &full[s]);
+                        tma_load_2d(sB, &tmB, kb * BK, brow0, &full[s]);
+                    }
+                    __syncwarp();
+                    if (++s == kStages) {
+                        s = 0;
+                        ++lap;
+                    }
                 }
             }
+            if (!ok) *abort_flag = 1;
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
