@@ -251,7 +251,13 @@ def run_prefill(ctx, M, steps, warmup, ep="peer", w_full=None, check=True):
     equal = None
     if world > 1 and check and fused_gather is not None:
         a = step().clone()
-        b = D.column_split_gather(ops.gguf_mmq(A, slab, t, n1 - n0, K))
+        # the same GEMM route with one local output (above 2048 rows the gather entry keeps the
+        # prepared-operand kernel, whose results differ from the fused kernel's by fp16 rounding
+        # of the weights), then NCCL's all-gather
+        local = torch.empty((M, n1 - n0), dtype=torch.bfloat16, device=dev)
+        ops.gguf_mmq_gather(A, slab, t, n1 - n0, K, torch.tensor([local.data_ptr()], dtype=torch.int64, device=dev),
+                            n1 - n0, 0)
+        b = D.column_split_gather(local)
         ok = torch.tensor([1 if torch.equal(a, b) else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         equal = bool(ok.item())
@@ -276,7 +282,7 @@ def run_prefill(ctx, M, steps, warmup, ep="peer", w_full=None, check=True):
                      "traffic": None},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
-        "gpu_launches": steps * (3 if M > 2048 else 2),
+        "gpu_launches": steps * (3 if (M > 2048 and fused_gather is not None) else 2),
     }
     if equal is not None:
         line["equal_to_nccl_gather"] = equal

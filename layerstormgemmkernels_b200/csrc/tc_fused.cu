@@ -75,6 +75,7 @@ struct FusedArgs {
     int out_dtype;
     int K, N, M;
     int nt;                       // token rows per tile: 32, 64, 128, 256, 320 or 384
+    int tile_rows;                // dense: rows per token tile (M shared evenly among its tiles, <= nt)
     int box_rows;                 // rows of one TMA box of the token tile (nt, or 64 above 256)
     int a_col_base;               // first tensor-memory column of the weight ring (256, or nt above 256)
     int n_wtiles;                 // ceil(N / 128)
@@ -215,8 +216,8 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int w, const int
     it.ks = rest % a.ksplit;
     it.tt = rest / a.ksplit;
     it.expert = -1;
-    it.mstart = it.tt * a.nt;
-    it.mend = a.M;
+    it.mstart = it.tt * a.tile_rows;
+    it.mend = min(a.M, it.mstart + a.tile_rows);
     it.live = true;
     if (a.tile_expert) {
         if (tab) {   // the CTA's copy of the tile map: no dependent global loads per item
@@ -984,10 +985,27 @@ struct Plan {
 };
 
 int pick_nt(long long rows_per_problem) {
+    static const int force = [] {
+        const char* e = getenv("LSG_TC_FUSED_DENSE_NT");
+        return e ? atoi(e) : 0;
+    }();
+    if (force == 32 || force == 64 || force == 128 || force == 256 || force == 320 || force == 384) return force;
     if (rows_per_problem <= 32) return 32;
     if (rows_per_problem <= 64) return 64;
     if (rows_per_problem <= 128) return 128;
-    return 256;
+    // Every token tile repeats the decoding of the weights, so above 256 rows the height that
+    // needs the fewest tiles wins; at equal count the lower one (more stages in shared memory).
+    // Measured on 14336 x 4096 Q4_K: M = 4096 0.474 ms with 256-row tiles, 0.399 ms with 384.
+    int best = 256;
+    long long best_tiles = (rows_per_problem + 255) / 256;
+    for (int nt : {320, 384}) {
+        const long long tiles = (rows_per_problem + nt - 1) / nt;
+        if (tiles < best_tiles) {
+            best = nt;
+            best_tiles = tiles;
+        }
+    }
+    return best;
 }
 
 // rows: token rows of the whole call; t_tiles: dense tile count or the tile map's capacity.
@@ -1151,7 +1169,7 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
                                   nullptr, 1, s);
     if (rc != LSG_OK) return rc;
     CUtensorMap tmX;
-    rc = make_map(&tmX, x16, M, K, nt);
+    rc = make_map(&tmX, x16, M, K, p.box_rows);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.W = static_cast<const uint8_t*>(W);
@@ -1161,7 +1179,7 @@ int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void
         a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off;
     }
     a.K = K; a.N = N; a.M = M;
-    a.nt = nt; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.nt = nt; a.tile_rows = balanced_tile_rows(M, nt); a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
     a.status = device_status_word();
@@ -1206,14 +1224,14 @@ int tc_fused_dense_bf16(int type, int M, int N, int K, const void* A_bf16, const
                                static_cast<const __nv_bfloat16*>(A_bf16), x16, row_scale, M, K,
                                n_counters ? counters : static_cast<unsigned int*>(nullptr), n_counters));
     CUtensorMap tmX;
-    int rc = make_map(&tmX, x16, M, K, nt);
+    int rc = make_map(&tmX, x16, M, K, p.box_rows);
     if (rc != LSG_OK) return rc;
     FusedArgs a = {};
     a.W = static_cast<const uint8_t*>(W);
     a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
     a.C = C; a.ldc = ldc; a.out_dtype = out_dtype;
     a.K = K; a.N = N; a.M = M;
-    a.nt = nt; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages;
+    a.nt = nt; a.tile_rows = balanced_tile_rows(M, nt); a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = p.t_tiles; a.stages = p.stages;
     a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = p.ksplit; a.kb_per_split = p.kb_per_split;
     a.partial = partial; a.counters = counters;
@@ -1249,7 +1267,7 @@ int tc_fused_grouped(int type, int T, int E, int N, int K, const void* A_bf16, c
     a.row_bytes = static_cast<long long>(K / gguf_block_values(type)) * gguf_block_bytes(type);
     a.C = D; a.ldc = N; a.out_dtype = out_dtype;
     a.K = K; a.N = N; a.M = T;
-    a.nt = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
+    a.nt = tile_m; a.tile_rows = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages; a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
     a.status = device_status_word();
@@ -1298,7 +1316,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     a.row_bytes = static_cast<long long>(H / qk) * qb;
     a.C = gu; a.ldc = 2 * I; a.out_dtype = LSG_DTYPE_BF16;
     a.K = H; a.N = I; a.M = T;
-    a.nt = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = 2 * p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages;
+    a.nt = tile_m; a.tile_rows = tile_m; a.box_rows = p.box_rows; a.a_col_base = p.a_col_base; a.n_wtiles = 2 * p.n_wtiles; a.t_tiles = t_max; a.stages = p.stages;
     a.raw_depth = p.raw_depth; a.raw_bytes = p.raw_bytes;
     a.ksplit = 1; a.kb_per_split = p.kb_per_split;
     a.tile_expert = tile_expert; a.tile_mstart = tile_mstart; a.expert_offsets = expert_offsets;
@@ -1321,7 +1339,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     b.row_bytes = static_cast<long long>(I / qk) * qb;
     b.C = D; b.ldc = H; b.out_dtype = out_dtype;
     b.K = I; b.N = H; b.M = T;
-    b.nt = tile_m; b.box_rows = p.box_rows; b.a_col_base = p.a_col_base; b.n_wtiles = p.n_wtiles; b.t_tiles = t_max; b.stages = p.stages;
+    b.nt = tile_m; b.tile_rows = tile_m; b.box_rows = p.box_rows; b.a_col_base = p.a_col_base; b.n_wtiles = p.n_wtiles; b.t_tiles = t_max; b.stages = p.stages;
     b.raw_depth = p.raw_depth; b.raw_bytes = p.raw_bytes;
     b.ksplit = 1; b.kb_per_split = p.kb_per_split;
     b.tile_expert = tile_expert; b.tile_mstart = tile_mstart; b.expert_offsets = expert_offsets;

@@ -494,10 +494,12 @@ size_t mmq_scratch_bytes(long long rows, int K, int E, int N) {
 int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
               size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs) {
     if (M == 0 || N == 0) return LSG_OK;
-    // Decoding inside the GEMM repeats the decode once per 256-token tile; past a few tiles
-    // one expansion pass plus the plain fp16 GEMM is cheaper (measured cross-over near
-    // M = 4096 for 14336 x 4096 Q4_K), unless every type is forced through the fused kernel.
-    if (tc_fused_available(type) && (M <= 2048 || tc_fused_forced()))
+    // Weights decoded inside the GEMM wherever that kernel has a decoder for the type: it reads
+    // the packed weights once per token tile (up to 384 rows) and measured faster than one
+    // expansion pass plus the plain fp16 GEMM at every M (14336 x 4096 Q4_K, M = 4096: 0.399 ms
+    // against 0.489 ms).  The all-gather epilogue for large M stays with the prepared-operand
+    // kernel, whose epilogue stores whole 128-byte segments into the peers.
+    if (tc_fused_available(type) && (M <= 2048 || outs == nullptr || tc_fused_forced()))
         return tc_fused_dense(type, M, N, K, A, W, C, outs ? outs->ldc : N, out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16,
                               ws, ws_bytes, s, outs);
     if (K % 8 != 0) return fail(LSG_ERR_UNSUPPORTED, "gguf_mmq: K must be a multiple of 8");
