@@ -550,7 +550,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         }
         // Every stage collects one arrival per group, real or past the end.
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
+        if (elect_one_lane()) mbar_arrive(&empty[s]);
 #ifdef LSG_MMVQ_TRACE
         if (lane == 0) {
             LSG_TRACE_CLK(tc2);

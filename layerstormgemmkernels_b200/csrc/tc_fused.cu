@@ -288,7 +288,7 @@ __device__ __forceinline__ bool publish_stage(const DecCtx& c, Ring& ring, const
     tmem_st_wait();
     tc_fence_before();
     __syncwarp();
-    if ((threadIdx.x & 31) == 0) mbar_arrive(&c.full[ring.s]);
+    if (elect_one()) mbar_arrive(&c.full[ring.s]);
     ring.advance();
     return true;
 }
