@@ -407,15 +407,16 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
 
     const int n_slabs = (row_end - row_begin + a.slab_rows - 1) / a.slab_rows;
 
-    if (tid == 0) {
-        LSG_TRACE(0);
-        for (int s = 0; s < a.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], groups_per_slab);  // one arrival per row group
+    // One lane per stage initialises its two barriers (a loop in a single thread would issue
+    // them one after the other at the very start of every launch).
+    if (tid == 0) LSG_TRACE(0);
+    if (tid < kMmvqMaxStages) {
+        if (tid < a.stages) {
+            mbar_init(&full[tid], 1);
+            mbar_init(&empty[tid], groups_per_slab);  // one arrival per row group
         }
-        *next_group = 0;
-        for (int s = 0; s < kMmvqMaxStages; ++s) slab_in_stage[s] = -1;
-
+        slab_in_stage[tid] = -1;
+        if (tid == 0) *next_group = 0;
         mbar_fence_init();
     }
     __syncthreads();
