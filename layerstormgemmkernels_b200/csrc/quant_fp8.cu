@@ -39,7 +39,9 @@ dynamic_fp8_quant_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restri
     const long long total = static_cast<long long>(M) * blocks_per_row;
     const bool live = gblk < total;
     const long long blk = live ? gblk : 0;
-    const int row = static_cast<int>(blk / blocks_per_row);
+    // a 64-bit division costs about a hundred instructions; block counts fit 32 bits in practice
+    const int row = total <= 0x7fffffffLL ? static_cast<int>(static_cast<unsigned>(blk) / static_cast<unsigned>(blocks_per_row))
+                                          : static_cast<int>(blk / blocks_per_row);
     const int bc = static_cast<int>(blk - static_cast<long long>(row) * blocks_per_row);
     const int col0 = bc * kFp8Block + hl * 8;
     const size_t base = static_cast<size_t>(row) * K + col0;

@@ -30,50 +30,62 @@ __device__ __forceinline__ int q8_round(float x, float d, float rcp) {
 // (offsets 16, 8, 4, 2, 1 over lanes = elements): element pairs (i, i+16), then
 // (i, i+8), (i, i+4), (i, i+2), (i, i+1).  With eight values per lane the first two
 // levels are lane exchanges (lane+2, lane+1) and the last three are in-register.
+// U vectors per thread, kQuantThreads apart (so that a warp's loads stay contiguous): all U loads
+// are in flight before the first result is needed.  Large tensors take U = 4.
+template <int U>
 __global__ void __launch_bounds__(kQuantThreads)
 quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y,
                      long long n_blocks) {
     pdl_launch_dependents();
     pdl_wait_prior();  // x may be the output of the previous kernel in the stream
-    const long long task = static_cast<long long>(blockIdx.x) * kQuantThreads + threadIdx.x;
-    const bool live = task < n_blocks * 4;
-    const long long tk = live ? task : 0;
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x) + tk);
-    float v[8];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const long long task0 = static_cast<long long>(blockIdx.x) * (kQuantThreads * U) + threadIdx.x;
+    uint4 raw[U];
+    bool live[U];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    for (int u = 0; u < U; ++u) {
+        const long long task = task0 + u * kQuantThreads;
+        live[u] = task < n_blocks * 4;
+        raw[u] = __ldg(reinterpret_cast<const uint4*>(x) + (live[u] ? task : 0));
     }
-    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    // butterfly-ordered sum
-    float s[8];
+    for (int u = 0; u < U; ++u) {
+        const long long tk = live[u] ? task0 + u * kQuantThreads : 0;
+        float v[8];
+        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i] = v[i] + __shfl_xor_sync(0xffffffffu, v[i], 2);   // (i, i+16)
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+        float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i] = s[i] + __shfl_xor_sync(0xffffffffu, s[i], 1);   // (i, i+8)
-    const float c0 = s[0] + s[4], c1 = s[1] + s[5], c2 = s[2] + s[6], c3 = s[3] + s[7];  // (i, i+4)
-    const float sum = (c0 + c2) + (c1 + c3);                                             // (i, i+2), (i, i+1)
-    if (!live) return;
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        // butterfly-ordered sum
+        float s[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = v[i] + __shfl_xor_sync(0xffffffffu, v[i], 2);   // (i, i+16)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = s[i] + __shfl_xor_sync(0xffffffffu, s[i], 1);   // (i, i+8)
+        const float c0 = s[0] + s[4], c1 = s[1] + s[5], c2 = s[2] + s[6], c3 = s[3] + s[7];  // (i, i+4)
+        const float sum = (c0 + c2) + (c1 + c3);                                             // (i, i+2), (i, i+1)
+        if (!live[u]) continue;
 
-    const float d = amax / 127.0f;
-    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-    uint32_t q[8];
+        const float d = amax / 127.0f;
+        const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+        uint32_t q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = static_cast<uint32_t>(q8_round(v[i], d, rcp)) & 0xFFu;
-    const long long blk = tk >> 2;
-    const int part = static_cast<int>(tk & 3);
-    uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
-    out[1 + 2 * part] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
-    out[2 + 2 * part] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
-    if (part == 0) {
-        const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
-        out[0] = *reinterpret_cast<const uint32_t*>(&ds);
+        for (int i = 0; i < 8; ++i) q[i] = static_cast<uint32_t>(q8_round(v[i], d, rcp)) & 0xFFu;
+        const long long blk = tk >> 2;
+        const int part = static_cast<int>(tk & 3);
+        uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
+        out[1 + 2 * part] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+        out[2 + 2 * part] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+        if (part == 0) {
+            const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
+            out[0] = *reinterpret_cast<const uint32_t*>(&ds);
+        }
     }
 }
 
@@ -88,12 +100,19 @@ int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t
     if (!x_bf16 || !q8_1_out) return fail(LSG_ERR_INVALID, "quantize_q8_1: null pointer");
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(q8_1_out) & 3))
         return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1: input must be 16-byte and output 4-byte aligned");
-    const long long grid = (n_blocks * 4 + kQuantThreads - 1) / kQuantThreads;
+    const long long tasks = n_blocks * 4;
+    const bool big = tasks >= 8ll * kQuantThreads * 4 * sm_count();   // enough CTAs left at four vectors per thread
+    const int per_cta = kQuantThreads * (big ? 4 : 1);
+    const long long grid = (tasks + per_cta - 1) / per_cta;
     if (grid > 0x7fffffffLL) return fail(LSG_ERR_INVALID, "quantize_q8_1: too many blocks");
-    LSG_CUDA_TRY(launch_kernel(quantize_q8_1_kernel, dim3(static_cast<unsigned>(grid)),
-                               dim3(kQuantThreads), 0, stream, pdl,
-                               static_cast<const __nv_bfloat16*>(x_bf16),
-                               static_cast<uint8_t*>(q8_1_out), n_blocks));
+    if (big)
+        LSG_CUDA_TRY(launch_kernel(quantize_q8_1_kernel<4>, dim3(static_cast<unsigned>(grid)), dim3(kQuantThreads), 0,
+                                   stream, pdl, static_cast<const __nv_bfloat16*>(x_bf16),
+                                   static_cast<uint8_t*>(q8_1_out), n_blocks));
+    else
+        LSG_CUDA_TRY(launch_kernel(quantize_q8_1_kernel<1>, dim3(static_cast<unsigned>(grid)), dim3(kQuantThreads), 0,
+                                   stream, pdl, static_cast<const __nv_bfloat16*>(x_bf16),
+                                   static_cast<uint8_t*>(q8_1_out), n_blocks));
     return LSG_OK;
 }
 
