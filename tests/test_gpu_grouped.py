@@ -268,3 +268,30 @@ def test_mmq_prefill_config_shape_sampled(ops):
     cols = np.r_[0:8, 7000:7008, N - 8:N]
     ref = oracle.mmvq(T["Q4_K"], oracle.quantize_q8_1(bits_of(A)[rows]), W[cols], K)
     assert np.abs(got[np.ix_(rows, cols)] - ref).max() <= TOL_TC * np.abs(ref).max()
+
+
+def test_grouped_many_experts_takes_the_global_tile_lookup(ops):
+    """More token tiles than the fused kernel's shared-memory tile table holds (340): 400 experts with
+    9..40 rows each take 64-row tiles, one or more per expert, and every role then resolves its
+    tiles from global memory.  Same results as the oracle; balanced tiles (33..40 rows stay one
+    tile, nothing is split unevenly) and empty experts included."""
+    E, K, N = 400, 256, 128
+    counts = [0 if e % 50 == 7 else 9 + (e * 7) % 32 for e in range(E)]
+    A, off, ptrs, dev_w, host_w, offs = build_group("Q4_K", counts, N, K, seed=900)
+    ref = oracle_grouped("Q4_K", A, host_w, offs, K)
+    out = ops.gguf_grouped_gemm(A, off, ptrs, T["Q4_K"], S_INT, N, K, F_MMQ, out_dtype=torch.float32)
+    check(out.cpu().numpy(), ref, TOL_TC)
+
+
+@pytest.mark.parametrize("rows", [257, 320, 321, 384, 385, 700])
+def test_grouped_tall_and_balanced_tiles(ops, rows):
+    """Experts around the tile heights of the fused kernel: one 320- or 384-row tile, two evenly
+    shared tiles just above it, and several tiles for a large expert, next to a small and an empty one."""
+    K, N = 512, 256
+    counts = [rows, 0, 5, rows - 1]
+    A, off, ptrs, dev_w, host_w, offs = build_group("Q4_K", counts, N, K, seed=rows)
+    ref = oracle_grouped("Q4_K", A, host_w, offs, K)
+    out = ops.gguf_grouped_gemm(A, off, ptrs, T["Q4_K"], S_INT, N, K, F_MMQ, out_dtype=torch.float32)
+    check(out.cpu().numpy(), ref, TOL_TC)
+    again = ops.gguf_grouped_gemm(A, off, ptrs, T["Q4_K"], S_INT, N, K, F_MMQ, out_dtype=torch.float32)
+    assert torch.equal(out, again)
