@@ -80,6 +80,17 @@ __device__ __forceinline__ bool elect_one_lane() {
     return pred != 0;
 }
 
+// rn(fl(x / d)) as a float, for |x / d| <= 127, without a division per element: x * fl(1/d) is
+// within 2.3e-5 of fl(x/d), so rounding it gives the same integer unless it lies within 1e-4 of
+// a half-integer (t - rint(t) is exact in fp32 at this magnitude); only then, for about one
+// value in 5000, is the true quotient formed.  Five instructions on the common path.
+__device__ __forceinline__ float q8_round_f(float x, float d, float rcp) {
+    const float t = x * rcp;
+    float k = rintf(t);
+    if (fabsf(t - k) > 0.4999f) k = rintf(x / d);
+    return k;
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
                  : "memory");

@@ -224,9 +224,7 @@ __device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bflo
             int sum16 = 0;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float t = x[i] * rcp;
-                int k = __float2int_rn(t);
-                if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x[i] / d);
+                const int k = static_cast<int>(q8_round_f(x[i], d, rcp));
                 q[i] = k;
                 sum16 += k;
             }

@@ -15,14 +15,8 @@ namespace {
 
 constexpr int kQuantThreads = 256;
 
-// q = rn(fl(x / d)) without a division per element: x * fl(1/d) is within 2.3e-5 of
-// fl(x/d) for |x/d| <= 127, so rounding it gives the same integer unless it lies within
-// 1e-4 of a half-integer; only then is the true quotient formed.
 __device__ __forceinline__ int q8_round(float x, float d, float rcp) {
-    const float t = x * rcp;
-    int k = __float2int_rn(t);
-    if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(x / d);
-    return k;
+    return static_cast<int>(q8_round_f(x, d, rcp));
 }
 
 // Four lanes per 32-value block, eight consecutive values (one 16-byte load) per lane.

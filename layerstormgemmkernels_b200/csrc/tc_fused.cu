@@ -836,6 +836,7 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int
             counters[i] = 0;
     }
     const int live = live_rows ? min(rows, __ldg(live_rows)) : rows;
+    if (static_cast<int>(blockIdx.x * (blockDim.y * RB)) >= live) return;   // the whole block lies past the live rows
     const int v = blockIdx.y * blockDim.x + tx;
     const int rbase = blockIdx.x * (blockDim.y * RB) + ty;
     const int ld_in = SWIGLU ? 2 * vpr : vpr;
@@ -886,12 +887,9 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int
             float r2[2];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                const float t = val[2 * i + hh] * rcp;
-                int k = __float2int_rn(t);
                 // same integer as rn(fl(x / d)): the product with the reciprocal only differs
                 // next to a half-integer, and there the true quotient decides
-                if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(val[2 * i + hh] / d);
-                r2[hh] = dh * static_cast<float>(k);
+                r2[hh] = dh * q8_round_f(val[2 * i + hh], d, rcp);
             }
             pk[i] = pack_h2(r2[0], r2[1]);
         }

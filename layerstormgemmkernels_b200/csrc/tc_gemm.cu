@@ -417,11 +417,7 @@ x_q8_1_roundtrip_f16_kernel(const __nv_bfloat16* __restrict__ x, __half* __restr
         float r[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const float t = v[2 * i + h] * rcp;
-            int k = __float2int_rn(t);
-            // same integer as rn(fl(x / d)): see quantize_q8_1_kernel
-            if (fabsf(fabsf(t - static_cast<float>(k)) - 0.5f) < 1e-4f) k = __float2int_rn(v[2 * i + h] / d);
-            r[h] = dh * static_cast<float>(k);
+            r[h] = dh * q8_round_f(v[2 * i + h], d, rcp);   // same integer as rn(fl(x / d))
         }
         const __half2 hv = __floats2half2_rn(r[0], r[1]);
         p[i] = *reinterpret_cast<const uint32_t*>(&hv);
