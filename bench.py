@@ -372,6 +372,7 @@ def main():
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="several GPUs: exchange rows by peer-memory stores or by NCCL collectives")
     ap.add_argument("--weak", action="store_true", help="moe: --tokens is per GPU (weak scaling)")
+    ap.add_argument("--ep-groups", type=int, default=1, help="moe on several GPUs: groups of local experts pipelined on side streams (1: none)")
     ap.add_argument("--ep-chunks", type=int, default=1, help="moe on several GPUs: pipelined token halves of the peer exchange (1: none)")
     ap.add_argument("--shape", default="Q4_K,14336,4096,1,8", help="shape mode: TYPE,N,K,M[,COPIES]")
     ap.add_argument("--calls", type=int, default=12, help="shape mode: calls issued before timing")
@@ -422,7 +423,7 @@ def main():
         sampler = ClockSampler(local_rank)
         sampler.start()
         if args.workload == "moe":
-            line = W.run_moe(ctx, args.tokens, sec_steps, sec_warm, weak=args.weak, ep=args.ep, chunks=args.ep_chunks)
+            line = W.run_moe(ctx, args.tokens, sec_steps, sec_warm, weak=args.weak, ep=args.ep, chunks=args.ep_chunks, groups=args.ep_groups)
             if world == 1 and not args.no_cpu_baseline:
                 line["cpu_baseline"] = W.cpu_moe()
         elif args.workload == "prefill":

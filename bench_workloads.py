@@ -80,7 +80,7 @@ def moe_expert_weights(dev, e0, e1, distinct=8):
     return base, sets, ptrs
 
 
-def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunks=1):
+def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunks=1, groups=1):
     from layerstormgemmkernels_b200 import capi, ops, distributed as D
     E, k, H, I = MOE["E"], MOE["k"], MOE["H"], MOE["I"]
     world, rank, dev = ctx.world, ctx.rank, ctx.dev
@@ -96,8 +96,11 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunk
     logits = torch.randn(T, E, generator=gg).to(dev)
     hidden_host, logits_host = hidden.cpu().pin_memory(), logits.cpu().pin_memory()
 
-    def ffn(rows, offs):
-        return ops.gguf_moe_ffn(rows, offs, gate_p, up_p, down_p, t, H, I)
+    def ffn(rows, offs, lo=None, hi=None):
+        if lo is None:
+            return ops.gguf_moe_ffn(rows, offs, gate_p, up_p, down_p, t, H, I)
+        # one group of this rank's experts (EpPeerGroups): slices of the pointer arrays
+        return ops.gguf_moe_ffn(rows, offs, gate_p[lo:hi], up_p[lo:hi], down_p[lo:hi], t, H, I)
 
     exchange, ep_mode = None, "single"
     if world > 1:
@@ -109,6 +112,12 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunk
                 # decoding of every expert's weights), so one exchange is the default.
                 if chunks > 1 and T % chunks == 0 and T // chunks >= 64:
                     exchange = D.EpPeerPipeline.make(E, k, H, T, chunks=chunks)
+                elif groups > 1 and (e1 - e0) >= groups and T * k // E > 8:
+                    # groups of local experts on side streams: one group's rows travel while the
+                    # other group's expert GEMMs run.  Also measured slower here (two GPUs, weak:
+                    # 0.870 ms in two groups, 1.059 in four, 0.787 plain): every group is four more
+                    # launches of persistent kernels over half as many items
+                    exchange = D.EpPeerGroups.make(E, k, H, T, groups=groups)
                 else:
                     exchange = D.EpPeerExchange.make(E, k, H, T)
             except Exception as exc:   # noqa: BLE001 - the optional path falls back
@@ -187,7 +196,9 @@ def run_moe(ctx, tokens, steps, warmup, weak=False, ep="peer", check=True, chunk
                    "tokens": T_total, "tokens_per_gpu": T,
                    "launch": "one CUDA graph per layer" if graphed else "eager (the NCCL exchange reads split sizes on the host)",
                    "parallelism": (f"ep{world}, rows exchanged by peer-memory stores"
-                                   + (f" in {exchange.chunks} pipelined halves" if hasattr(exchange, "chunks") else "")
+                                   + (f" in {exchange.chunks} pipelined "
+                                      + ("expert groups" if isinstance(exchange, D.EpPeerGroups) else "token chunks")
+                                      if hasattr(exchange, "chunks") else "")
                                    + ", library flag barrier"
                                    if ep_mode == "peer" and exchange is not None
                                    else f"ep{world}, NCCL all-to-all" if world > 1 else "single"),

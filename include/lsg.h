@@ -589,6 +589,21 @@ LSG_API int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const
 LSG_API int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
                                const int32_t* info, int world, int experts_per_rank, int H, int capacity,
                                void* const* back_buf_ptrs, void* stream);
+/* The same two steps for one group of each rank's local experts, [local_expert_lo, local_expert_hi)
+ * in the rank-local numbering: send_rows_group sends only the rows routed to those experts of
+ * every rank (they are contiguous in the receive layout, rows local_offsets[lo] ..
+ * local_offsets[hi]), return_rows_group returns only those rows of `y_bf16` (local_offsets as
+ * written by lsg_ep_plan).  A caller can then exchange one group's rows while the expert GEMMs
+ * of another group run on a second stream (distributed.EpPeerGroups); each group's steps need
+ * their own barrier flags.  No counterpart in the reference. */
+LSG_API int lsg_ep_send_rows_group(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
+                                   const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts,
+                                   int world, void* const* recv_buf_ptrs, int capacity, void* back_local,
+                                   int local_expert_lo, int local_expert_hi, void* stream);
+LSG_API int lsg_ep_return_rows_group(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
+                                     const int32_t* info, int world, int experts_per_rank, int H, int capacity,
+                                     void* const* back_buf_ptrs, const int32_t* local_offsets, int local_expert_lo,
+                                     int local_expert_hi, void* stream);
 
 /* Barrier over the ranks of the exchange, on the stream, with a time limit.  flag_ptrs is a
  * DEVICE array of `world` device pointers, entry p = rank p's flag array uint32 [world + 1]

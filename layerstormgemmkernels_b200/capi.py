@@ -163,6 +163,8 @@ def _load():
         "lsg_ep_plan": (ci, [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp]),
         "lsg_ep_send_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp, vp]),
         "lsg_ep_return_rows": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, vp]),
+        "lsg_ep_send_rows_group": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp, ci, ci, vp]),
+        "lsg_ep_return_rows_group": (ci, [vp, vp, vp, vp, ci, ci, ci, ci, vp, vp, ci, ci, vp]),
         "lsg_moe_permutation_scratch_ints": (ctypes.c_longlong, [ci, ci, ci]),
         "lsg_moe_permutation": (ci, [vp, ci, ci, ci, vp, vp, vp, vp, vp]),
         "lsg_moe_permute": (ci, [vp, vp, ci, ci, ci, vp, vp]),

@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(256, 8)
 ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm,
                     const int32_t* __restrict__ offs, const int32_t* __restrict__ send_base, int P, int top_k,
                     int vpr, int E, int per, uint4* const* __restrict__ recv, int capacity,
-                    uint4* __restrict__ back_local) {
+                    uint4* __restrict__ back_local, int le_lo, int le_hi) {
     pdl_launch_dependents();
     pdl_wait_prior();
     __shared__ int s_count;
@@ -169,9 +169,12 @@ ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict_
         dst[j] = 0;
         if (i < P) {
             while (e + 1 < E && __ldg(offs + e + 1) <= i) ++e;
-            row[j] = __ldg(send_base + e) + (i - __ldg(offs + e));
             dst[j] = e / per;
-            token[j] = __ldg(perm + i) / top_k;
+            const int le = e - dst[j] * per;   // the expert's index on its rank: only the group [le_lo, le_hi) travels
+            if (le >= le_lo && le < le_hi) {
+                row[j] = __ldg(send_base + e) + (i - __ldg(offs + e));
+                token[j] = __ldg(perm + i) / top_k;
+            }
         }
     }
     for (int v = threadIdx.x; v < vpr; v += blockDim.x) {
@@ -198,12 +201,18 @@ ep_send_rows_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict_
 __global__ void __launch_bounds__(256, 8)
 ep_return_rows_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ dst_start,
                       const int32_t* __restrict__ ret_base, const int32_t* __restrict__ info, int world, int B,
-                      int vpr, int capacity, uint4* const* __restrict__ back) {
+                      int vpr, int capacity, uint4* const* __restrict__ back,
+                      const int32_t* __restrict__ local_offsets, int le_lo, int le_hi) {
     pdl_launch_dependents();
     pdl_wait_prior();
     __shared__ int s_count;
-    const int rows = min(__ldg(info), capacity);
-    const int r0 = blockIdx.x * kEpRows;
+    int rows = min(__ldg(info), capacity);
+    int first = 0;
+    if (local_offsets) {   // only the rows of the local experts [le_lo, le_hi)
+        first = min(__ldg(local_offsets + le_lo), rows);
+        rows = min(__ldg(local_offsets + le_hi), rows);
+    }
+    const int r0 = first + blockIdx.x * kEpRows;
     if (r0 >= rows) return;   // uniform over the CTA
     int b = segment_of(dst_start, B, r0, &s_count);
     int row[kEpRows], dst[kEpRows];
@@ -316,14 +325,17 @@ extern "C" int lsg_ep_plan(const int32_t* counts_table, int rank, int world, int
     return LSG_OK;
 }
 
-extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
-                                const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
-                                void* const* recv_buf_ptrs, int capacity, void* back_local, void* stream) {
+extern "C" int lsg_ep_send_rows_group(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
+                                      const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts,
+                                      int world, void* const* recv_buf_ptrs, int capacity, void* back_local,
+                                      int local_expert_lo, int local_expert_hi, void* stream) {
     int rc = check_world("ep_send_rows", num_experts, world);
     if (rc != LSG_OK) return rc;
     if (num_pairs <= 0) return LSG_OK;
     if (!hidden_bf16 || !perm || !expert_offsets || !send_base || !recv_buf_ptrs || top_k < 1)
         return fail(LSG_ERR_INVALID, "ep_send_rows: null pointer or bad top_k");
+    if (local_expert_lo < 0 || local_expert_hi > num_experts / world || local_expert_lo > local_expert_hi)
+        return fail(LSG_ERR_INVALID, "ep_send_rows: bad local expert range [%d, %d)", local_expert_lo, local_expert_hi);
     if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(hidden_bf16) & 15))
         return fail(LSG_ERR_ALIGNMENT, "ep_send_rows: H must be a multiple of 8 and buffers 16-byte aligned");
     const int vpr = H / 8;
@@ -332,18 +344,28 @@ extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, co
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(hidden_bf16), perm,
                                expert_offsets, send_base, num_pairs, top_k, vpr, num_experts, num_experts / world,
                                reinterpret_cast<uint4* const*>(recv_buf_ptrs), capacity,
-                               static_cast<uint4*>(back_local)));
+                               static_cast<uint4*>(back_local), local_expert_lo, local_expert_hi));
     return LSG_OK;
 }
 
-extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
-                                  const int32_t* info, int world, int experts_per_rank, int H, int capacity,
-                                  void* const* back_buf_ptrs, void* stream) {
+extern "C" int lsg_ep_send_rows(const void* hidden_bf16, const int32_t* perm, const int32_t* expert_offsets,
+                                const int32_t* send_base, int num_pairs, int top_k, int H, int num_experts, int world,
+                                void* const* recv_buf_ptrs, int capacity, void* back_local, void* stream) {
+    return lsg_ep_send_rows_group(hidden_bf16, perm, expert_offsets, send_base, num_pairs, top_k, H, num_experts, world,
+                                  recv_buf_ptrs, capacity, back_local, 0, world > 0 ? num_experts / world : 0, stream);
+}
+
+extern "C" int lsg_ep_return_rows_group(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
+                                        const int32_t* info, int world, int experts_per_rank, int H, int capacity,
+                                        void* const* back_buf_ptrs, const int32_t* local_offsets, int local_expert_lo,
+                                        int local_expert_hi, void* stream) {
     if (world < 1 || experts_per_rank < 1 || world * experts_per_rank > 1024)
         return fail(LSG_ERR_INVALID, "ep_return_rows: need 1 <= world * experts_per_rank <= 1024");
     if (capacity <= 0) return LSG_OK;
     if (!y_bf16 || !dst_start || !ret_base || !info || !back_buf_ptrs)
         return fail(LSG_ERR_INVALID, "ep_return_rows: null pointer");
+    if (local_offsets && (local_expert_lo < 0 || local_expert_hi > experts_per_rank || local_expert_lo > local_expert_hi))
+        return fail(LSG_ERR_INVALID, "ep_return_rows: bad local expert range [%d, %d)", local_expert_lo, local_expert_hi);
     if (H % 8 != 0 || (reinterpret_cast<uintptr_t>(y_bf16) & 15))
         return fail(LSG_ERR_ALIGNMENT, "ep_return_rows: H must be a multiple of 8 and buffers 16-byte aligned");
     const int vpr = H / 8;
@@ -351,8 +373,16 @@ extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, 
     LSG_CUDA_TRY(launch_kernel(ep_return_rows_kernel, dim3(static_cast<unsigned>((capacity + kEpRows - 1) / kEpRows)), dim3(threads), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(y_bf16), dst_start,
                                ret_base, info, world, world * experts_per_rank, vpr, capacity,
-                               reinterpret_cast<uint4* const*>(back_buf_ptrs)));
+                               reinterpret_cast<uint4* const*>(back_buf_ptrs), local_offsets, local_expert_lo,
+                               local_expert_hi));
     return LSG_OK;
+}
+
+extern "C" int lsg_ep_return_rows(const void* y_bf16, const int32_t* dst_start, const int32_t* ret_base,
+                                  const int32_t* info, int world, int experts_per_rank, int H, int capacity,
+                                  void* const* back_buf_ptrs, void* stream) {
+    return lsg_ep_return_rows_group(y_bf16, dst_start, ret_base, info, world, experts_per_rank, H, capacity,
+                                    back_buf_ptrs, nullptr, 0, experts_per_rank, stream);
 }
 
 extern "C" int lsg_ep_barrier(void* const* flag_ptrs, int rank, int world, int mode, void* stream) {

@@ -823,7 +823,7 @@ template <int RB, bool SWIGLU>
 __global__ void __launch_bounds__(256)
 x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int rows, int vpr,
               unsigned int* __restrict__ counters, int n_counters, const int32_t* __restrict__ live_rows,
-              const int32_t* __restrict__ perm, int top_k) {
+              const int32_t* __restrict__ perm, int top_k, const int32_t* __restrict__ first_row) {
     const unsigned lanes = __activemask();   // a block of K/8 x rows threads may end in a partial warp
     pdl_launch_dependents();
     pdl_wait_prior();
@@ -837,6 +837,8 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int
     }
     const int live = live_rows ? min(rows, __ldg(live_rows)) : rows;
     if (static_cast<int>(blockIdx.x * (blockDim.y * RB)) >= live) return;   // the whole block lies past the live rows
+    // ... or before the first row any expert of this call owns (a call on a group of experts)
+    if (first_row && static_cast<int>((blockIdx.x + 1) * (blockDim.y * RB)) <= __ldg(first_row)) return;
     const int v = blockIdx.y * blockDim.x + tx;
     const int rbase = blockIdx.x * (blockDim.y * RB) + ty;
     const int ld_in = SWIGLU ? 2 * vpr : vpr;
@@ -903,7 +905,8 @@ x_prep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ out, int
 // rows x K values (K a multiple of 32).  The block is (min(K/8, 256) vectors, 256 / that rows).
 template <bool SWIGLU>
 int launch_x_prep(const __nv_bfloat16* x, __half* out, long long rows, int K, unsigned int* counters, int n_counters,
-                  const int32_t* live_rows, const int32_t* perm, int top_k, cudaStream_t s) {
+                  const int32_t* live_rows, const int32_t* perm, int top_k, cudaStream_t s,
+                  const int32_t* first_row = nullptr) {
     if (rows <= 0 || rows > 0x7fffffffll) return rows == 0 ? LSG_OK : fail(LSG_ERR_UNSUPPORTED, "activation preparation: too many rows");
     const int vpr = K / 8;
     const int bx = vpr < 256 ? vpr : 256;
@@ -915,10 +918,10 @@ int launch_x_prep(const __nv_bfloat16* x, __half* out, long long rows, int K, un
     const unsigned gx = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
     if (rb4)
         LSG_CUDA_TRY(launch_kernel(x_prep_kernel<4, SWIGLU>, dim3(gx, gy), dim3(bx, by), 0, s, true, x, out,
-                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k));
+                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k, first_row));
     else
         LSG_CUDA_TRY(launch_kernel(x_prep_kernel<1, SWIGLU>, dim3(gx, gy), dim3(bx, by), 0, s, true, x, out,
-                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k));
+                                   static_cast<int>(rows), vpr, counters, n_counters, live_rows, perm, top_k, first_row));
     return LSG_OK;
 }
 
@@ -1303,7 +1306,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
 
     // gate | up
     int rc = launch_x_prep<false>(static_cast<const __nv_bfloat16*>(A_bf16), x16, T, H, nullptr, 0, expert_offsets + E,
-                                  perm, top_k, s);
+                                  perm, top_k, s, expert_offsets);
     if (rc != LSG_OK) return rc;
     CUtensorMap tmX;
     Plan p = make_plan(T, tile_m, t_max, I, H, false, staged);
@@ -1326,7 +1329,7 @@ int tc_fused_moe_ffn(int type, int T, int E, int H, int I, const void* A_bf16, c
     if (rc != LSG_OK) return rc;
 
     // SwiGLU + preparation, then down
-    rc = launch_x_prep<true>(gu, act16, T, I, nullptr, 0, expert_offsets + E, nullptr, 1, s);
+    rc = launch_x_prep<true>(gu, act16, T, I, nullptr, 0, expert_offsets + E, nullptr, 1, s, expert_offsets);
     if (rc != LSG_OK) return rc;
     CUtensorMap tmA;
     p = make_plan(T, tile_m, t_max, H, I, false, staged);

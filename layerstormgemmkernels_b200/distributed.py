@@ -345,6 +345,93 @@ class EpPeerPipeline:
         return any(e.overflowed() for e in self.ex)
 
 
+class EpPeerGroups:
+    """The peer-memory exchange with each rank's local experts in `groups` groups, staggered on
+    side streams so that one group's rows travel while another group's expert GEMMs run:
+
+        main:      route, sort, publish counts | barrier | plan
+        stream 0:  send group 0 | barrier | experts 0                 | return 0 | barrier
+        stream 1:               send group 1 | barrier | experts 1               | return 1 | barrier
+        main:      combine
+
+    (send g starts when send g-1 is done, experts g when experts g-1 are done.)  Unlike a split by
+    tokens (EpPeerPipeline) every expert's weights are still decoded once per layer: the receive
+    layout is grouped by local expert, so a group's rows are one contiguous range.  Every group
+    has its own barrier flags.  `expert_ffn(rows, offsets, lo, hi)` runs local experts [lo, hi):
+    `offsets` is the slice local_offsets[lo : hi + 1] (absolute rows of `rows`)."""
+
+    def __init__(self, exchange, groups, group=None):
+        self.ex = exchange
+        per = exchange.per
+        self.groups = max(1, min(groups, per))
+        self.bounds = [per * g // self.groups for g in range(self.groups + 1)]
+        self.bars = [FlagBarrier(group) for _ in range(self.groups)]
+        self.streams = [torch.cuda.Stream() for _ in range(self.groups)]
+        self.chunks = self.groups        # for callers that report how the layer is pipelined
+
+    @staticmethod
+    def make(num_experts, top_k, H, tokens_per_rank, groups=2, capacity_factor=1.5, group=None):
+        return EpPeerGroups(EpPeerExchange.make(num_experts, top_k, H, tokens_per_rank, capacity_factor, group),
+                            groups, group)
+
+    def layer(self, hidden, logits, expert_ffn, route, permutation, unpermute):
+        from . import capi
+        lib, ex = capi.lib, self.ex
+        p = lambda t: t.data_ptr()
+        ex.check_inputs(hidden, logits)
+        cur = torch.cuda.current_stream()
+        st = cur.cuda_stream
+        idx, w = route(logits, ex.k)
+        offs, perm, inv = permutation(idx, ex.E)
+        counts, counts_ptrs = ex.b["counts"]
+        recv, recv_ptrs = ex.b["recv"]
+        back, back_ptrs = ex.b["back"]
+        capi.check(lib.lsg_ep_publish_counts(p(offs), ex.E, ex.rank, ex.world, p(counts_ptrs), st))
+        ex.barrier()
+        capi.check(lib.lsg_ep_plan(p(counts), ex.rank, ex.world, ex.E, ex.cap, p(ex.send_base), p(ex.local_offsets),
+                                   p(ex.dst_start), p(ex.ret_base), p(ex.info), st))
+        n = self.groups
+        ev_a = [torch.cuda.Event() for _ in range(n)]
+        ev_b = [torch.cuda.Event() for _ in range(n)]
+        ys = [None] * n
+        for g in range(n):
+            s = self.streams[g]
+            s.wait_stream(cur)
+            lo, hi = self.bounds[g], self.bounds[g + 1]
+            with torch.cuda.stream(s):
+                if g > 0:
+                    s.wait_event(ev_a[g - 1])
+                capi.check(lib.lsg_ep_send_rows_group(p(hidden), p(perm), p(offs), p(ex.send_base), ex.P, ex.k, ex.H,
+                                                      ex.E, ex.world, p(recv_ptrs), ex.cap, p(back), lo, hi,
+                                                      s.cuda_stream))
+                self.bars[g]()
+                ev_a[g].record(s)
+        for g in range(n):
+            s = self.streams[g]
+            lo, hi = self.bounds[g], self.bounds[g + 1]
+            with torch.cuda.stream(s):
+                if g > 0:
+                    s.wait_event(ev_b[g - 1])
+                ys[g] = expert_ffn(recv, ex.local_offsets[lo:hi + 1], lo, hi)
+                ev_b[g].record(s)
+        for g in range(n):
+            s = self.streams[g]
+            lo, hi = self.bounds[g], self.bounds[g + 1]
+            with torch.cuda.stream(s):
+                y = ys[g]
+                capi.check(lib.lsg_ep_return_rows_group(p(y), p(ex.dst_start), p(ex.ret_base), p(ex.info), ex.world,
+                                                        ex.per, y.shape[1], ex.cap, p(back_ptrs), p(ex.local_offsets),
+                                                        lo, hi, s.cuda_stream))
+                self.bars[g]()
+        for g in range(n):
+            cur.wait_stream(self.streams[g])
+            ys[g].record_stream(cur)
+        return unpermute(back, inv, w)
+
+    def overflowed(self):
+        return self.ex.overflowed()
+
+
 def column_slab(rank, world, N, align=128):
     """Output columns [n0, n1) owned by `rank`: contiguous, multiples of `align`."""
     if N % (world * align) != 0:

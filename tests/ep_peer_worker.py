@@ -1,6 +1,7 @@
 """Worker of tests/test_gpu_ep_peer.py: one rank of a 2-GPU (or N-GPU) expert-parallel MoE
 layer.  Runs the layer once with the NCCL all-to-all exchange, three times with the
-peer-memory exchange, and as two pipelined halves (eagerly and from a CUDA graph), and prints
+peer-memory exchange, as two pipelined token halves and as two pipelined expert groups
+(each eagerly and from a CUDA graph), and prints
 whether the outputs are identical."""
 import os
 import sys
@@ -53,6 +54,22 @@ def main():
     torch.cuda.synchronize()
     print(f"EP_PIPE rank {rank} equal={torch.equal(out2, ref)} graph_equal={torch.equal(out3, ref)} "
           f"overflow={pipe.overflowed()} status={capi.device_status()}", flush=True)
+    # local experts in two groups on side streams (one group's rows travel under the other's GEMMs)
+    def ffn_group(rows, offs, lo, hi):
+        return ops.gguf_moe_ffn(rows, offs, gp[lo:hi], up[lo:hi], dp[lo:hi], t, H, I)
+    grp = D.EpPeerGroups.make(E, k, H, T, groups=2, capacity_factor=2.5)
+    for _ in range(2):
+        out4 = grp.layer(hidden, logits, ffn_group, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        out5 = grp.layer(hidden, logits, ffn_group, ops.moe_route, ops.moe_permutation, ops.moe_unpermute)
+    for _ in range(2):
+        graph2.replay()
+    torch.cuda.synchronize()
+    print(f"EP_GROUPS rank {rank} equal={torch.equal(out4, ref)} graph_equal={torch.equal(out5, ref)} "
+          f"overflow={grp.overflowed()} status={capi.device_status()}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

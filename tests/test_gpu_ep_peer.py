@@ -33,6 +33,11 @@ def test_peer_exchange_equals_nccl_exchange_on_two_gpus():
     assert len(pipes) == 2, r.stdout[-2000:] + r.stderr[-2000:]
     for ln in pipes:
         assert " equal=True" in ln and "graph_equal=True" in ln and "overflow=False" in ln and ln.endswith("status=0"), ln
+    # local experts in two groups on side streams
+    groups = re.findall(r"EP_GROUPS rank \d+ equal=\w+ graph_equal=\w+ overflow=\w+ status=\d+", r.stdout)
+    assert len(groups) == 2, r.stdout[-2000:] + r.stderr[-2000:]
+    for ln in groups:
+        assert " equal=True" in ln and "graph_equal=True" in ln and "overflow=False" in ln and ln.endswith("status=0"), ln
 
 
 @pytest.mark.timeout(300)
