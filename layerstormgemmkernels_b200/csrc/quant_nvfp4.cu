@@ -64,6 +64,22 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
     pdl_wait_prior();
     const int row = blockIdx.y;
     const int gpr = K >> 4;
+    // The group's values are fetched first: their addresses need nothing of the expert look-up
+    // below, whose dependent loads would otherwise sit in front of them in every CTA.
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool in_row = g < gpr;
+    const size_t base = static_cast<size_t>(row) * K + static_cast<size_t>(in_row ? g : 0) * 16;
+    uint4 ra = make_uint4(0, 0, 0, 0), rb = ra, ua = ra, ub = ra;
+    if (in_row) {
+        const uint4* p = reinterpret_cast<const uint4*>(in + base);
+        ra = __ldg(p);
+        rb = __ldg(p + 1);
+        if (SWIGLU) {
+            const uint4* q = reinterpret_cast<const uint4*>(up + base);
+            ua = __ldg(q);
+            ub = __ldg(q + 1);
+        }
+    }
     // The row's expert is the number of experts that end at or before it.  With at most one
     // expert per thread that is one load per thread and one counting barrier; a binary search
     // by one thread (seven dependent loads with the CTA waiting) only for more experts.
@@ -82,8 +98,7 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
         e_start = __ldg(expert_offsets + e);
         sf_base = __ldg(sf_offsets + e);
     }
-    const int g = blockIdx.x * blockDim.x + threadIdx.x;
-    if (g >= gpr) return;
+    if (!in_row) return;
     const int local_row = row - e_start;
     float is = 1.0f;
     if (input_scales) {
@@ -91,12 +106,9 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
         if (v > 0.0f) is = v;
     }
 
-    const size_t base = static_cast<size_t>(row) * K + static_cast<size_t>(g) * 16;
     float x[16];
     {
-        const uint4* p = reinterpret_cast<const uint4*>(in + base);
-        const uint4 a = __ldg(p), b = __ldg(p + 1);
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint32_t w[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             x[2 * i] = __uint_as_float(w[i] << 16);
@@ -104,9 +116,7 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
         }
     }
     if (SWIGLU) {
-        const uint4* p = reinterpret_cast<const uint4*>(up + base);
-        const uint4 a = __ldg(p), b = __ldg(p + 1);
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint32_t w[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float u0 = __uint_as_float(w[i] << 16), u1 = __uint_as_float(w[i] & 0xFFFF0000u);
