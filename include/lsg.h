@@ -187,8 +187,10 @@ LSG_API int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace, s
 /* n projections in one call, executed in order, each as lsg_gguf_mmvq_host would.
  * Entries naming the same A, M and K as an earlier entry reuse its Q8_1 image (the q, k
  * and v projections of one hidden state quantize it once), and consecutive ones share a
- * launch as in lsg_gguf_mmvq_batch.  All activations must be in
- * place when the call is made and no C may overlap an A of the batch.  n <= 64.
+ * launch as in lsg_gguf_mmvq_batch.  All activations must be in place when the call is made:
+ * up to eight distinct ones are quantized by a single launch up front.  (A batch in which a C
+ * overlaps the A of a later entry is still executed in order, with a quantizer launch in
+ * front of each group of projections.)  n <= 64.
  * Workspace: lsg_gguf_mmvq_host_batch_workspace_bytes(p, n), 256-byte aligned. */
 LSG_API size_t lsg_gguf_mmvq_host_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
 LSG_API int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,

@@ -8,6 +8,9 @@ namespace lsg {
 
 int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t stream,
                   bool pdl);
+// Up to eight tensors quantized by one launch (same bytes as quantize_q8_1 on each).
+int quantize_q8_1_batch(int n, const void* const* x_bf16, void* const* q8_1_out, const int* M, const int* K,
+                        cudaStream_t stream, bool pdl);
 int check_gemm_params(const char* op, const lsg_gguf_mmvq_params* p);
 int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void* C, int ldc,
               int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16 = nullptr);

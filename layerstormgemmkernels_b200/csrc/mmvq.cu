@@ -421,6 +421,51 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
         return fail(LSG_ERR_ALIGNMENT, "gguf_mmvq_host: workspace must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint8_t* base = static_cast<uint8_t*>(workspace);
+    // Every input is there when the call is made, so the distinct activations are quantized by
+    // ONE launch up front (their reads over PCIe overlap) instead of one quantizer launch in
+    // front of each group of projections: a layer of seven projections is five dependent
+    // launches instead of eight.  More than eight distinct inputs fall back to one launch each.
+    bool quantized_up_front = false;
+    {
+        const void* xs[8];
+        void* qs[8];
+        int Ms[8], Ks[8];
+        int cnt = 0;
+        bool fits = true;
+        // not when a projection reads what an earlier one of the batch writes
+        for (int j = 1; j < n && fits; ++j) {
+            const uintptr_t a0 = reinterpret_cast<uintptr_t>(p[j].A);
+            const uintptr_t a1 = a0 + static_cast<size_t>(p[j].M) * p[j].K * 2;
+            for (int i = 0; i < j; ++i) {
+                const uintptr_t c0 = reinterpret_cast<uintptr_t>(p[i].C);
+                const uintptr_t c1 = c0 + static_cast<size_t>(p[i].M) * p[i].N * (p[i].out_dtype == LSG_DTYPE_F32 ? 4 : 2);
+                if (a0 < c1 && c0 < a1) fits = false;
+            }
+        }
+        for (int i = 0; i < n && fits; ++i) {
+            if (p[i].M == 0 || p[i].N == 0 || slot[i].first != i) continue;
+            if (cnt == 8) {
+                fits = false;
+                break;
+            }
+            const void* a_src = mapped_alias(p[i].A);
+            if (!a_src) {
+                const size_t a_bytes = static_cast<size_t>(p[i].M) * p[i].K * 2;
+                LSG_CUDA_TRY(cudaMemcpyAsync(base + slot[i].a_off, p[i].A, a_bytes, cudaMemcpyHostToDevice, s));
+                a_src = base + slot[i].a_off;
+            }
+            xs[cnt] = a_src;
+            qs[cnt] = base + slot[i].q_off;
+            Ms[cnt] = p[i].M;
+            Ks[cnt] = p[i].K;
+            ++cnt;
+        }
+        if (fits && cnt > 1) {
+            const int rc = quantize_q8_1_batch(cnt, xs, qs, Ms, Ks, s, true);
+            if (rc != LSG_OK) return rc;
+            quantized_up_front = true;
+        }
+    }
     for (int i = 0; i < n;) {
         const lsg_gguf_mmvq_params& e = p[i];
         const int run = joinable_run(p, i, n);
@@ -432,7 +477,7 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
         const size_t a_bytes = static_cast<size_t>(e.M) * e.K * 2;
         uint8_t* q_dev = base + slot[i].q_off;
         int rc;
-        if (slot[i].first == i) {
+        if (slot[i].first == i && !quantized_up_front) {
             const void* a_src = mapped_alias(e.A);
             if (!a_src) {
                 LSG_CUDA_TRY(cudaMemcpyAsync(base + slot[i].a_off, e.A, a_bytes, cudaMemcpyHostToDevice, s));

@@ -14,6 +14,7 @@ namespace lsg {
 namespace {
 
 constexpr int kQuantThreads = 256;
+constexpr int kQ8BatchMax = 8;
 
 __device__ __forceinline__ int q8_round(float x, float d, float rcp) {
     return static_cast<int>(q8_round_f(x, d, rcp));
@@ -27,12 +28,9 @@ __device__ __forceinline__ int q8_round(float x, float d, float rcp) {
 // U vectors per thread, kQuantThreads apart (so that a warp's loads stay contiguous): all U loads
 // are in flight before the first result is needed.  Large tensors take U = 4.
 template <int U>
-__global__ void __launch_bounds__(kQuantThreads)
-quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y,
-                     long long n_blocks) {
-    pdl_launch_dependents();
-    pdl_wait_prior();  // x may be the output of the previous kernel in the stream
-    const long long task0 = static_cast<long long>(blockIdx.x) * (kQuantThreads * U) + threadIdx.x;
+__device__ __forceinline__ void quantize_q8_1_body(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y,
+                                                   long long n_blocks, long long cta) {
+    const long long task0 = cta * (kQuantThreads * U) + threadIdx.x;
     uint4 raw[U];
     bool live[U];
 #pragma unroll
@@ -83,7 +81,59 @@ quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ 
     }
 }
 
+template <int U>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, long long n_blocks) {
+    pdl_launch_dependents();
+    pdl_wait_prior();  // x may be the output of the previous kernel in the stream
+    quantize_q8_1_body<U>(x, y, n_blocks, blockIdx.x);
+}
+
+// Several tensors in one launch (the distinct activations of a batch of projections whose inputs
+// are all there when the call is made): CTAs [cta_end[t-1], cta_end[t]) quantize tensor t.
+struct Q8BatchArgs {
+    const __nv_bfloat16* x[kQ8BatchMax];
+    uint8_t* y[kQ8BatchMax];
+    long long n_blocks[kQ8BatchMax];
+    int cta_end[kQ8BatchMax];
+    int n;
+};
+
+__global__ void __launch_bounds__(kQuantThreads) quantize_q8_1_batch_kernel(const Q8BatchArgs a) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    int t = 0;
+    while (t + 1 < a.n && static_cast<int>(blockIdx.x) >= a.cta_end[t]) ++t;
+    const int first = t > 0 ? a.cta_end[t - 1] : 0;
+    quantize_q8_1_body<1>(a.x[t], a.y[t], a.n_blocks[t], static_cast<long long>(blockIdx.x) - first);
+}
+
 }  // namespace
+
+int quantize_q8_1_batch(int n, const void* const* x_bf16, void* const* q8_1_out, const int* M, const int* K,
+                        cudaStream_t stream, bool pdl) {
+    if (n <= 0) return LSG_OK;
+    if (n > kQ8BatchMax) return fail(LSG_ERR_INVALID, "quantize_q8_1_batch: at most %d tensors, got %d", kQ8BatchMax, n);
+    Q8BatchArgs a = {};
+    long long ctas = 0;
+    for (int i = 0; i < n; ++i) {
+        if (M[i] <= 0 || K[i] <= 0 || K[i] % 32 != 0)
+            return fail(LSG_ERR_INVALID, "quantize_q8_1_batch: bad shape of tensor %d (M=%d, K=%d)", i, M[i], K[i]);
+        if (!x_bf16[i] || !q8_1_out[i]) return fail(LSG_ERR_INVALID, "quantize_q8_1_batch: null pointer");
+        if ((reinterpret_cast<uintptr_t>(x_bf16[i]) & 15) || (reinterpret_cast<uintptr_t>(q8_1_out[i]) & 3))
+            return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1_batch: input must be 16-byte and output 4-byte aligned");
+        a.x[i] = static_cast<const __nv_bfloat16*>(x_bf16[i]);
+        a.y[i] = static_cast<uint8_t*>(q8_1_out[i]);
+        a.n_blocks[i] = static_cast<long long>(M[i]) * (K[i] / 32);
+        ctas += (a.n_blocks[i] * 4 + kQuantThreads - 1) / kQuantThreads;
+        if (ctas > 0x7fffffffLL) return fail(LSG_ERR_INVALID, "quantize_q8_1_batch: too many blocks");
+        a.cta_end[i] = static_cast<int>(ctas);
+    }
+    a.n = n;
+    LSG_CUDA_TRY(launch_kernel(quantize_q8_1_batch_kernel, dim3(static_cast<unsigned>(ctas)), dim3(kQuantThreads), 0,
+                               stream, pdl, a));
+    return LSG_OK;
+}
 
 int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t stream,
                   bool pdl) {

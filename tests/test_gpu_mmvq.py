@@ -190,6 +190,37 @@ def test_mmvq_host_batch_shares_quantized_activations(ops):
         ops.HostMmvqBatch(items, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
 
 
+def test_mmvq_host_batch_chained_projection_reads_the_earlier_result(ops):
+    """A projection whose input is the host buffer an earlier projection of the same batch writes:
+    the batch must not quantize that input up front with the others."""
+    from layerstormgemmkernels_b200 import capi
+    import ctypes
+    K0, N0, N1 = 512, 256, 96          # y0 = x W0^T (bf16 [1, 256]), y1 = y0 W1^T
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(1, K0, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    x2 = (torch.randn(1, K0, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    W0 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N0, K0, seed=1)).cuda()
+    W1 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N1, N0, seed=2)).cuda()
+    W2 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N1, K0, seed=3)).cuda()
+    y0 = torch.zeros((1, N0), dtype=torch.bfloat16).pin_memory()
+    y1 = torch.zeros((1, N1), dtype=torch.bfloat16).pin_memory()
+    y2 = torch.zeros((1, N1), dtype=torch.bfloat16).pin_memory()
+    arr = (capi.GgufMmvqParams * 3)()
+    t = T["Q4_K"]
+    arr[0] = capi.GgufMmvqParams(M=1, N=N0, K=K0, A=x.data_ptr(), B=W0.data_ptr(), C=y0.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[1] = capi.GgufMmvqParams(M=1, N=N1, K=N0, A=y0.data_ptr(), B=W1.data_ptr(), C=y1.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[2] = capi.GgufMmvqParams(M=1, N=N1, K=K0, A=x2.data_ptr(), B=W2.data_ptr(), C=y2.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    need = capi.lib.lsg_gguf_mmvq_host_batch_workspace_bytes(arr, 3)
+    ws = torch.empty((need,), dtype=torch.uint8, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    capi.check(capi.lib.lsg_gguf_mmvq_host_batch(arr, 3, ctypes.c_void_p(ws.data_ptr()), need, st))
+    torch.cuda.synchronize()
+    r0 = ops.gguf_mmvq(x.cuda(), W0, t, N0, K0)
+    assert torch.equal(y0, r0.cpu())
+    assert torch.equal(y1, ops.gguf_mmvq(r0, W1, t, N1, N0).cpu())
+    assert torch.equal(y2, ops.gguf_mmvq(x2.cuda(), W2, t, N1, K0).cpu())
+
+
 @pytest.mark.parametrize("name,M,K,Ns", [
     ("Q4_K", 1, 4096, (4096, 1024, 1024)),       # q, k, v
     ("Q4_K", 1, 4096, (14336, 14336)),           # gate, up
