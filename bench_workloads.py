@@ -284,7 +284,9 @@ def run_prefill(ctx, M, steps, warmup, ep="peer", w_full=None, check=True):
         "data": "synthetic",
         "config": {"workload": f"Q4_K 14336x4096 prefill GEMM, M={M}, Q8_1 activations",
                    "parallelism": ("single" if world == 1 else
-                                   f"column-split x{world}, all-gather fused into the GEMM epilogue (peer stores)"
+                                   f"column-split x{world}, all-gather fused into the GEMM epilogue ("
+                                   + ("multimem stores into the NVLink multicast object" if getattr(fused_gather, "multicast_ptr", 0)
+                                      else "peer stores") + ")"
                                    if fused_gather is not None else f"column-split x{world} + NCCL all-gather"),
                    "l2_defeat": "weights 33 MB + activations + outputs (117 MB at M=4096) exceed L2 at M=4096; "
                                 "at M=512 the operands fit L2 and the number is an L2-resident one"},

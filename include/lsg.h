@@ -243,6 +243,14 @@ LSG_API int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace, s
  * No counterpart in the reference (it has no multi-GPU code). */
 LSG_API int lsg_gguf_mmq_gather(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
                                 int col_offset, void* workspace, size_t workspace_bytes, void* stream);
+/* The same with an NVLink multicast address of the output (the address under which a store
+ * reaches the [M, ldc] matrix of EVERY rank, e.g. the multicast pointer of a symmetric-memory
+ * allocation; NULL = lsg_gguf_mmq_gather).  Above 2048 rows the epilogue then issues one
+ * multimem.st per 16 bytes instead of n_out peer stores, so a rank sends its slab once and the
+ * switch replicates it.  C_ptrs is still required (smaller calls use it). */
+LSG_API int lsg_gguf_mmq_gather_mc(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
+                                   int col_offset, void* multicast_ptr, void* workspace, size_t workspace_bytes,
+                                   void* stream);
 
 /* How the tensor-core GEMMs (lsg_gguf_mmq and the grouped GEMM's tensor-core route) obtain
  * their fp16 weights, process-wide:

@@ -128,6 +128,7 @@ def _load():
         "lsg_mmvq_set_tuning": (ci, [ci, ci, ci, ci, ci]),
         "lsg_mmq_set_weight_path": (ci, [ci]),
         "lsg_gguf_mmq_gather": (ci, [ctypes.POINTER(GgufMmvqParams), vp, ci, ci, ci, vp, sz, vp]),
+        "lsg_gguf_mmq_gather_mc": (ci, [ctypes.POINTER(GgufMmvqParams), vp, ci, ci, ci, vp, vp, sz, vp]),
         "lsg_gguf_gemm_bf16_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_gemm_bf16": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_dynamic_fp8_quant": (ci, [ctypes.POINTER(DynamicFp8QuantParams), vp]),

@@ -38,6 +38,8 @@ struct MmqOutputs {
     int n_out;
     int ldc;
     int col_off;
+    void* mc_ptr;          // optional: NVLink multicast address of the same [M, ldc] output on every rank
+                           // (one multimem store reaches all of them instead of n_out peer stores)
 };
 int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void* C, int out_f32, void* ws,
               size_t ws_bytes, cudaStream_t s, const MmqOutputs* outs = nullptr);

@@ -58,6 +58,7 @@ struct TcArgs {
     float alpha_host;         // output scale known on the host (used when alphas is null and it is not 1)
     void* const* C_ptrs;      // optional: n_out output matrices (this GPU's and its peers'), every tile is
     int n_out;                //   stored into each of them at column offset col_off (GEMM + all-gather)
+    void* mc;                 // optional multicast address of those matrices: one multimem.st per 16 bytes
     int col_off;
     int K;
     int N;                    // columns of one problem (per expert)
@@ -269,8 +270,18 @@ tc_gemm_f16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         const int grow = mstart + warp * 32 + rr;
                         if (grow < mend) {
                             const size_t o = static_cast<size_t>(grow) * a.ldc + a.col_off + n0 + c + q * 8;
-                            for (int po = 0; po < a.n_out; ++po)
-                                *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.C_ptrs[po]) + o) = v;
+                            if (a.mc) {
+                                // one store into the NVLink multicast object: the switch replicates it
+                                // to every rank's copy of the output, this one included
+                                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                                                 static_cast<uint16_t*>(a.mc) + o),
+                                             "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                                             "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                                             : "memory");
+                            } else {
+                                for (int po = 0; po < a.n_out; ++po)
+                                    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.C_ptrs[po]) + o) = v;
+                            }
                         }
                     }
                 }
@@ -519,7 +530,7 @@ int mmq_dense(int type, int M, int N, int K, const void* A, const void* W, void*
     a.alpha_host = 1.0f;
     a.C = C; a.ldc = N; a.out_f32 = out_f32 ? LSG_DTYPE_F32 : LSG_DTYPE_BF16; a.K = K; a.N = N;
     if (outs) {
-        a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off; a.ldc = outs->ldc;
+        a.C_ptrs = outs->C_ptrs; a.n_out = outs->n_out; a.col_off = outs->col_off; a.ldc = outs->ldc; a.mc = outs->mc_ptr;
     }
     a.n_tiles = (N + BN - 1) / BN;
     a.m_tiles = (M + BM - 1) / BM;
@@ -622,15 +633,23 @@ extern "C" int lsg_gguf_gemm_bf16(const lsg_gguf_mmvq_params* p, void* workspace
                                workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int lsg_gguf_mmq_gather(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
-                                   int col_offset, void* workspace, size_t workspace_bytes, void* stream) {
+extern "C" int lsg_gguf_mmq_gather_mc(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
+                                      int col_offset, void* multicast_ptr, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
     int rc = check_gemm_params("gguf_mmq_gather", p);
     if (rc != LSG_OK) return rc;
     if (p->M == 0 || p->N == 0) return LSG_OK;
     if (!p->A || !p->B || !C_ptrs) return fail(LSG_ERR_INVALID, "gguf_mmq_gather: null pointer");
     if (n_out < 1 || n_out > 64 || col_offset < 0 || ldc < col_offset + p->N)
         return fail(LSG_ERR_INVALID, "gguf_mmq_gather: need 1 <= n_out <= 64 and col_offset + N <= ldc");
-    MmqOutputs outs = {C_ptrs, n_out, ldc, col_offset};
+    if (reinterpret_cast<uintptr_t>(multicast_ptr) & 15)
+        return fail(LSG_ERR_ALIGNMENT, "gguf_mmq_gather: the multicast address must be 16-byte aligned");
+    MmqOutputs outs = {C_ptrs, n_out, ldc, col_offset, multicast_ptr};
     return mmq_dense(p->type, p->M, p->N, p->K, p->A, p->B, nullptr, p->out_dtype == LSG_DTYPE_F32, workspace,
                      workspace_bytes, static_cast<cudaStream_t>(stream), &outs);
+}
+
+extern "C" int lsg_gguf_mmq_gather(const lsg_gguf_mmvq_params* p, void* const* C_ptrs, int n_out, int ldc,
+                                   int col_offset, void* workspace, size_t workspace_bytes, void* stream) {
+    return lsg_gguf_mmq_gather_mc(p, C_ptrs, n_out, ldc, col_offset, nullptr, workspace, workspace_bytes, stream);
 }

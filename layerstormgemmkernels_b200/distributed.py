@@ -15,6 +15,8 @@ them), and through peer memory (EpPeerExchange, ColumnSplitPeer: the kernels sto
 into the other GPUs' buffers, separated by the library's own time-limited flag barrier).
 Decode mat-vec and the quantizers do not shard ("replicas only").
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -447,7 +449,7 @@ class ColumnSplitPeer:
     following tiles); one barrier afterwards and every rank holds the whole product.  The
     outputs are torch symmetric-memory allocations."""
 
-    def __init__(self, M, N, dtype=torch.bfloat16, group=None):
+    def __init__(self, M, N, dtype=torch.bfloat16, group=None, multicast=True):
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
@@ -456,6 +458,18 @@ class ColumnSplitPeer:
         self.out = symm.empty((M, N), dtype=dtype, device=dev)
         self._h = symm.rendezvous(self.out, group)
         self.ptrs = torch.tensor([int(p) for p in self._h.buffer_ptrs], dtype=torch.int64, device=dev)
+        # NVLink multicast address of the output, where the fabric offers one: a rank then sends its
+        # slab once (multimem.st) and the switch replicates it, instead of one store per peer.
+        # Measured equal to plain peer stores at 4 and 8 GPUs (0.245 / 0.237 ms against 0.247 /
+        # 0.236 ms at M = 4096: every rank still receives (G-1)/G of the product), so it is off
+        # unless asked for.
+        self.multicast_ptr = 0
+        mode = os.environ.get("LSG_GATHER_MULTICAST", "0")     # 0: never, 1: with three or more ranks, 2: always
+        if multicast and mode != "0" and (self.world > 2 or mode == "2"):
+            try:
+                self.multicast_ptr = int(getattr(self._h, "multicast_ptr", 0) or 0)
+            except Exception:   # noqa: BLE001 - older handles have no such attribute
+                self.multicast_ptr = 0
         self.barrier = FlagBarrier(group)
 
     def gemm(self, A, slab, type, K):
@@ -464,7 +478,8 @@ class ColumnSplitPeer:
         from . import ops
         n0, n1 = column_slab(self.rank, self.world, self.N)
         self.barrier()   # every rank is done reading the previous product
-        ops.gguf_mmq_gather(A, slab, type, n1 - n0, K, self.ptrs, self.N, n0, out_dtype=self.out.dtype)
+        ops.gguf_mmq_gather(A, slab, type, n1 - n0, K, self.ptrs, self.N, n0, out_dtype=self.out.dtype,
+                            multicast_ptr=self.multicast_ptr)
         self.barrier()   # every slab has landed everywhere
         return self.out
 

@@ -490,10 +490,12 @@ def gguf_mmq(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
     return C
 
 
-def gguf_mmq_gather(A, B_slab, type, n_local, K, out_ptrs, ldc, col_offset, out_dtype=torch.bfloat16):
+def gguf_mmq_gather(A, B_slab, type, n_local, K, out_ptrs, ldc, col_offset, out_dtype=torch.bfloat16,
+                    multicast_ptr=0):
     """gguf_mmq on a column slab of the weight, every output tile stored into each matrix of
     `out_ptrs` (CUDA int64 tensor of device pointers to [M, ldc] matrices of `out_dtype`, this
-    GPU's and its peers') at column offset `col_offset`."""
+    GPU's and its peers') at column offset `col_offset`.  `multicast_ptr`: optional NVLink
+    multicast address of those matrices (one store reaches every rank)."""
     _require(A.is_cuda and A.dtype == torch.bfloat16 and A.dim() == 2 and A.is_contiguous(),
              "gguf_mmq_gather: A must be contiguous BF16 [M, K] on CUDA")
     _require(out_ptrs.is_cuda and out_ptrs.dtype == torch.int64, "gguf_mmq_gather: out_ptrs must be int64 on CUDA")
@@ -503,8 +505,9 @@ def gguf_mmq_gather(A, B_slab, type, n_local, K, out_ptrs, ldc, col_offset, out_
     p = capi.GgufMmvqParams(M=M, N=int(n_local), K=int(K), A=A.data_ptr(), B=B_slab.data_ptr(), C=None,
                             type=int(type),
                             out_dtype=capi.DTYPE_F32 if out_dtype == torch.float32 else capi.DTYPE_BF16)
-    capi.check(_lib.lsg_gguf_mmq_gather(ctypes.byref(p), _ptr(out_ptrs), out_ptrs.numel(), int(ldc), int(col_offset),
-                                        _ptr(ws), ws_bytes, _stream()))
+    capi.check(_lib.lsg_gguf_mmq_gather_mc(ctypes.byref(p), _ptr(out_ptrs), out_ptrs.numel(), int(ldc),
+                                           int(col_offset), ctypes.c_void_p(int(multicast_ptr) or None),
+                                           _ptr(ws), ws_bytes, _stream()))
 
 
 def gguf_gemm_bf16(A, B_packed, type, N, K, out_dtype=torch.bfloat16):
