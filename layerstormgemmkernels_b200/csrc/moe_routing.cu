@@ -233,6 +233,51 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restric
     reinterpret_cast<__nv_bfloat162*>(out + static_cast<size_t>(t) * H)[c] = __floats2bfloat162_rn(a0, a1);
 }
 
+// The same for H a multiple of 8 and 16-byte aligned rows: one token per blockIdx.x, one 16-byte
+// vector (eight columns) per thread and slot, the k slot rows of a vector in flight together;
+// same sum order (slots ascending, fmaf in fp32), hence the same bits.
+template <int KMAX>
+__global__ void __launch_bounds__(256)
+moe_combine_vec_kernel(const uint4* __restrict__ y, const int32_t* __restrict__ inv, const float* __restrict__ w,
+                       int k, int vpr, uint4* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int t = blockIdx.x;
+    for (int v = threadIdx.x; v < vpr; v += blockDim.x) {
+        uint4 r[KMAX];
+        float ws[KMAX];
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) {
+            if (s < k) {
+                const int row = __ldg(inv + static_cast<size_t>(t) * k + s);
+                ws[s] = __ldg(w + static_cast<size_t>(t) * k + s);
+                r[s] = __ldg(y + static_cast<size_t>(row) * vpr + v);
+            }
+        }
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+#pragma unroll
+        for (int s = 0; s < KMAX; ++s) {
+            if (s < k) {
+                const uint32_t q[4] = {r[s].x, r[s].y, r[s].z, r[s].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[2 * i] = fmaf(ws[s], __uint_as_float(q[i] << 16), acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(ws[s], __uint_as_float(q[i] & 0xFFFF0000u), acc[2 * i + 1]);
+                }
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            o[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        out[static_cast<size_t>(t) * vpr + v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // Expert-parallel receive side: rows arrive grouped by (source rank, local expert); the
 // grouped GEMM wants them grouped by (local expert, source rank).  counts[s * per + e] = rows
 // from source s for local expert e.  One CTA: exclusive scans of the block sizes in both
@@ -381,6 +426,14 @@ extern "C" int lsg_moe_unpermute(const void* y_bf16, const int32_t* inv_perm, co
     if (num_tokens <= 0) return LSG_OK;
     if (!y_bf16 || !inv_perm || !topk_weights || !out_bf16) return fail(LSG_ERR_INVALID, "moe_unpermute: null pointer");
     if (H % 2 != 0) return fail(LSG_ERR_INVALID, "moe_unpermute: H must be even");
+    if (H % 8 == 0 && top_k <= 8 && ((reinterpret_cast<uintptr_t>(y_bf16) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0) {
+        const int vpr = H / 8;
+        const int threads = vpr >= 256 ? 256 : ((vpr + 31) / 32) * 32;
+        LSG_CUDA_TRY(launch_kernel(moe_combine_vec_kernel<8>, dim3(static_cast<unsigned>(num_tokens)), dim3(threads), 0,
+                                   static_cast<cudaStream_t>(stream), true, static_cast<const uint4*>(y_bf16), inv_perm,
+                                   topk_weights, top_k, vpr, static_cast<uint4*>(out_bf16)));
+        return LSG_OK;
+    }
     const long long total = static_cast<long long>(num_tokens) * (H / 2);
     LSG_CUDA_TRY(launch_kernel(moe_combine_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0,
                                static_cast<cudaStream_t>(stream), true, static_cast<const __nv_bfloat16*>(y_bf16),
