@@ -351,6 +351,16 @@ typedef struct lsg_gguf_moe_ffn_params {
 LSG_API size_t lsg_gguf_moe_ffn_workspace_bytes(int total_tokens, int H, int I, int num_experts);
 LSG_API int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_tokens, void* workspace,
                              size_t workspace_bytes, void* stream);
+/* Average rows per expert (total_tokens / num_experts, rounded down) up to which
+ * lsg_gguf_moe_ffn composes the block from the grouped mat-vec kernels, whose results are
+ * bit-identical to the reference's; above it the tensor-core kernels run (equal within the
+ * tolerance of a GEMM with fp32 accumulation in another order).  Default 8, the batch at which
+ * the reference leaves its mat-vec kernels (gguf_grouped_int.cu:918-919), or the environment
+ * variable LSG_MOE_MATVEC_ROWS; -1 sends every batch to the tensor cores, which is faster from
+ * about two rows per expert (128 experts of 2048 x 768, 64 / 128 tokens top-8: 0.33 -> 0.27 ms
+ * and 0.47 -> 0.27 ms per layer).  Returns the previous value.  Process-wide, not synchronized
+ * with calls in flight on other threads. */
+LSG_API int lsg_gguf_moe_ffn_set_matvec_rows(int rows);
 
 /* Ascending list of the experts that have rows, padded with -1 to `cap` entries.
  * Replaces build_active_expert_list, gguf_grouped_int.cu:156-187. */

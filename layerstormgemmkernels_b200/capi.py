@@ -148,6 +148,7 @@ def _load():
         "lsg_nvfp4_gemm": (ci, [ctypes.POINTER(Nvfp4GemmParams), vp, sz, vp]),
         "lsg_gguf_moe_ffn_workspace_bytes": (sz, [ci, ci, ci, ci]),
         "lsg_gguf_moe_ffn": (ci, [ctypes.POINTER(GgufMoeFfnParams), ci, vp, sz, vp]),
+        "lsg_gguf_moe_ffn_set_matvec_rows": (ci, [ci]),
         "lsg_build_active_expert_list": (ci, [vp, ci, ci, vp, vp]),
         "lsg_build_mmq_tile_map": (ci, [vp, ci, ci, ci, vp, vp, vp]),
         "lsg_gguf_grouped_gemm_workspace_bytes_ex": (sz, [ci, ci, ci, ci]),

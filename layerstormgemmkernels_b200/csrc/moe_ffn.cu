@@ -14,6 +14,9 @@
 //     GEMM's operand, one tile map for both launches;
 //   * otherwise (types without an in-kernel decoder, or few rows per expert) the three
 //     grouped GEMMs of this library back to back with a SwiGLU kernel in between.
+#include <atomic>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "formats.cuh"
 #include "host.h"
@@ -47,6 +50,15 @@ silu_mul_bf16_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, u
         o[j] = *reinterpret_cast<const uint32_t*>(&r);
     }
     out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Average rows per expert up to which the block is composed from the grouped mat-vec kernels.
+std::atomic<int>& matvec_rows() {
+    static std::atomic<int> rows([] {
+        const char* e = getenv("LSG_MOE_MATVEC_ROWS");
+        return e ? atoi(e) : 8;
+    }());
+    return rows;
 }
 
 struct FfnLayout {
@@ -95,6 +107,10 @@ extern "C" size_t lsg_gguf_moe_ffn_workspace_bytes(int total_tokens, int H, int 
     return ffn_layout(total_tokens, H, I, num_experts).total;
 }
 
+extern "C" int lsg_gguf_moe_ffn_set_matvec_rows(int rows) {
+    return matvec_rows().exchange(rows, std::memory_order_relaxed);
+}
+
 extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_tokens, void* workspace,
                                 size_t workspace_bytes, void* stream) {
     if (!p) return fail(LSG_ERR_INVALID, "gguf_moe_ffn: null params");
@@ -123,7 +139,8 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
     const int32_t* offs = static_cast<const int32_t*>(p->expert_offsets);
 
     // the reference's rule for leaving the mat-vec kernels: more than 8 rows per expert on average
-    if (tc_fused_available(p->type) && T / E > 8) {
+    // (lsg_gguf_moe_ffn_set_matvec_rows moves the threshold)
+    if (tc_fused_available(p->type) && T / E > matvec_rows().load(std::memory_order_relaxed)) {
         const int tile_m = tc_fused_grouped_tile_m(T, E);
         const int t_max = (T + tile_m - 1) / tile_m + E;
         int* tile_expert = reinterpret_cast<int*>(base + l.map_off);

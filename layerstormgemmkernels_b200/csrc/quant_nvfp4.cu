@@ -8,7 +8,8 @@
 // bf16_to_nvfp4_grouped_detail.cuh:30-92:
 //   scale      = max(amax / (6 * is), 2^-9), stored as ue4m3 (clamped to [0, 480], RN)
 //   code(v)    = sign | #{thresholds .25 .75 1.25 1.75 2.5 3.5 5 that |v| reaches},
-//                v = x * (1 / (ue4m3(scale) * is))       (ties go up in magnitude)
+//                v = x * (1 / (ue4m3(scale) * is))       (ties go up in magnitude; formed here
+//                by the hardware converter on a value that cannot tie, see e2m1_untie)
 //   SwiGLU     = bf16( (g * (0.5 * tanhf(0.5 g) + 0.5)) * u ) before quantization
 // One thread per 16-value group (two 16-byte loads, one 8-byte store); a CTA covers up to
 // 256 consecutive groups of one row and resolves the row's expert once.
@@ -30,11 +31,38 @@ __device__ __forceinline__ int sf_offset_sm1xx(int row, int g, int groups_padded
     return atom * 512 + (r & 31) * 16 + (r >> 5) * 4 + (g & 3);
 }
 
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-    const float a = fabsf(v);
-    const uint32_t mag = (a >= 0.25f) + (a >= 0.75f) + (a >= 1.25f) + (a >= 1.75f) +
-                         (a >= 2.5f) + (a >= 3.5f) + (a >= 5.0f);
-    return mag | ((v < 0.0f) ? 8u : 0u);
+// The reference's code of a value is sign | #{thresholds .25 .75 1.25 1.75 2.5 3.5 5 that |v|
+// reaches}: round to the nearest e2m1 magnitude with every tie going up.  The converter of the
+// hardware rounds ties to even, so it is given a value that is never a tie: the lowest mantissa
+// bit is set first.  A threshold (even bit pattern) then lies just above itself and goes up; the
+// float just below a threshold already has that bit set and stays below; no other value can
+// cross a threshold by one unit in the last place.  Three inputs need care: -0.0 and NaN, which
+// the reference maps to code 0 (none of its comparisons holds), and infinities, whose bit
+// pattern with the low bit set would be a NaN (clamped to +-8 first: the converter saturates
+// to 6, code 7, like the comparisons).
+__device__ __forceinline__ float e2m1_untie(float v) {
+    const bool some = fabsf(v) > 0.0f;                       // false for +-0 and NaN
+    const float c = fminf(fmaxf(v, -8.0f), 8.0f);
+    return some ? __uint_as_float(__float_as_uint(c) | 1u) : 0.0f;
+}
+
+// Eight values -> eight 4-bit codes, value i in bits 4i..4i+3.
+__device__ __forceinline__ uint32_t e2m1_codes8(const float* v, float inv) {
+    float t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = e2m1_untie(v[i] * inv);
+    uint32_t r;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n"
+        "}"
+        : "=r"(r)
+        : "f"(t[0]), "f"(t[1]), "f"(t[2]), "f"(t[3]), "f"(t[4]), "f"(t[5]), "f"(t[6]), "f"(t[7]));
+    return r;
 }
 
 __device__ __forceinline__ float swiglu(float g, float u) {
@@ -142,11 +170,7 @@ nvfp4_grouped_quant_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bflo
         static_cast<uint8_t>(sbits);
 
     const float inv = 1.0f / (srepr * is);
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) lo |= e2m1_code(x[i] * inv) << (4 * i);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) hi |= e2m1_code(x[8 + i] * inv) << (4 * i);
+    const uint32_t lo = e2m1_codes8(x, inv), hi = e2m1_codes8(x + 8, inv);
     *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * (K >> 1) + static_cast<size_t>(g) * 8) =
         make_uint2(lo, hi);
 }

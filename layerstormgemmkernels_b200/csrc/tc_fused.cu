@@ -117,21 +117,25 @@ struct FusedArgs {
 // free stage, 4 decoder total, 5 TMA waits for a free stage, 6 TMA total, 7 epilogue (warp 0)
 // waits for the accumulator, 8 epilogue total, 9 items, 10 K blocks.
 #ifdef LSG_TCF_TRACE
-#define TCF_T0() const long long tcf_t0 = clock64()
+#define TCF_T0() const long long tcf_t0 = clock64(); long long tcf_w0 = 0, tcf_w1 = 0, tcf_n0 = 0, tcf_n1 = 0
 #define TCF_ADD(slot, expr)                                                                                  \
     do {                                                                                                     \
         if (a.trace) a.trace[blockIdx.x * 16 + (slot)] += static_cast<unsigned long long>(expr);           \
     } while (0)
-#define TCF_TIMED(slot, lanecond, stmt)                                                                      \
+// every lane times the statement and sums in a register (no divergence, no memory traffic inside
+// the loops); one lane adds the sums to the trace when its role ends
+#define TCF_TIMED(which, stmt)                                                                               \
     do {                                                                                                     \
         const long long tcf_a = clock64();                                                                   \
         stmt;                                                                                                \
-        if (lanecond) TCF_ADD(slot, clock64() - tcf_a);                                                      \
+        tcf_w##which += clock64() - tcf_a;                                                                   \
     } while (0)
+#define TCF_COUNT(which, n) tcf_n##which += (n)
 #else
 #define TCF_T0()
 #define TCF_ADD(slot, expr)
-#define TCF_TIMED(slot, lanecond, stmt) stmt
+#define TCF_TIMED(which, stmt) stmt
+#define TCF_COUNT(which, n)
 #endif
 
 // Eight 32-bit columns of this thread's tensor-memory lane (the warp's lane quadrant).
@@ -264,7 +268,7 @@ struct DecCtx {
     unsigned int* status;
     uint32_t hint;
 #ifdef LSG_TCF_TRACE
-    unsigned long long* wait_cycles;   // where this thread sums its waits for a free stage (or null)
+    mutable long long waited;          // cycles this thread waited for a free stage
 #endif
 };
 
@@ -279,7 +283,7 @@ __device__ __forceinline__ bool publish_stage(const DecCtx& c, Ring& ring, const
         !__all_sync(0xffffffffu, mbar_wait_bounded(&c.empty[ring.s], (ring.lap - 1) & 1, c.status, kDevWaitEmpty, c.hint)))
         return false;
 #ifdef LSG_TCF_TRACE
-    if (c.wait_cycles) *c.wait_cycles += static_cast<unsigned long long>(clock64() - tw);
+    c.waited += clock64() - tw;
 #endif
     tc_fence_after();  // the MMAs that last read this stage are ordered before the stores
     const uint32_t col = c.tmem_a + static_cast<uint32_t>(ring.s * kAColsPerStage);
@@ -509,7 +513,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 const int live_rows = min(a.nt, im.mend - im.mstart);
                 const int live_boxes = max(1, (live_rows + a.box_rows - 1) / a.box_rows);
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    TCF_TIMED(5, lane == 0, if (ring.lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint)));
+                    TCF_TIMED(0, if (ring.lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&empty[ring.s], (ring.lap - 1) & 1, a.status, kDevWaitEmpty, hint)));
                     if (!ok) break;
                     if (elect_one()) {
                         if (TCF_DBG(a, 2)) {
@@ -527,7 +531,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 }
             }
             if (!ok) *abort_flag = 1;
-            if (lane == 0) TCF_ADD(6, clock64() - tcf_t0);
+            if (lane == 0) { TCF_ADD(5, tcf_w0); TCF_ADD(6, clock64() - tcf_t0); }
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
@@ -543,9 +547,9 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             if (!im.live) continue;
             const int kb0 = im.ks * a.kb_per_split;
             const int kb1 = min(kblocks_all, kb0 + a.kb_per_split);
-            TCF_TIMED(1, lane == 0, if (acc_lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], (acc_lap - 1) & 1, a.status, kDevWaitTmem, hint)));
+            TCF_TIMED(1, if (acc_lap > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_empty[ab], (acc_lap - 1) & 1, a.status, kDevWaitTmem, hint)));
             if (!ok) break;
-            if (lane == 0) { TCF_ADD(9, 1); TCF_ADD(10, kb1 - kb0); }
+            TCF_COUNT(0, 1); TCF_COUNT(1, kb1 - kb0);
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + ab * a.nt;
             // N of the instruction follows the token rows that are really in the tile (a multiple
@@ -558,7 +562,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             const uint32_t idesc = idesc_f16(WM, n1);
             const uint32_t idesc2 = idesc_f16(WM, max(16, n2));
             for (int kb = kb0; kb < kb1; ++kb) {
-                TCF_TIMED(0, lane == 0, ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint)));
+                TCF_TIMED(0, ok = __all_sync(0xffffffffu, mbar_wait_bounded(&full[ring.s], ring.lap & 1, a.status, kDevWaitFull, hint)));
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t xdesc = smem_desc_sw128(smem_u32(smem + ring.s * stage_bytes));
@@ -586,7 +590,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             }
         }
         if (!ok) *abort_flag = 1;
-        if (lane == 0) TCF_ADD(2, clock64() - tcf_t0);
+        if (lane == 0) { TCF_ADD(0, tcf_w0); TCF_ADD(1, tcf_w1); TCF_ADD(9, tcf_n0); TCF_ADD(10, tcf_n1); TCF_ADD(2, clock64() - tcf_t0); }
     } else if (warp >= 6) {
         // ------------------------------ weight decoders ---------------------------
         // warp -> lane quadrant (a warp may only touch tensor-memory lanes 32 * (warp % 4) ..),
@@ -602,7 +606,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
         ctx.status = a.status;
         ctx.hint = hint;
 #ifdef LSG_TCF_TRACE
-        ctx.wait_cycles = (a.trace && warp == 6 && lane == 0) ? a.trace + blockIdx.x * 16 + 3 : nullptr;
+        ctx.waited = 0;
 #endif
         TCF_T0();
         Ring ring = {0, 0u, a.stages};
@@ -644,7 +648,9 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 break;
             }
         }
-        if (warp == 6 && lane == 0) TCF_ADD(4, clock64() - tcf_t0);
+#ifdef LSG_TCF_TRACE
+        if (warp == 6 && lane == 0) { TCF_ADD(3, ctx.waited); TCF_ADD(4, clock64() - tcf_t0); }
+#endif
     } else {
         // ------------------------------ epilogue (warps 0-3) ----------------------
         TCF_T0();
@@ -654,7 +660,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
             const Item im = decode_item(a, w, tab);
             if (!im.live) continue;
             bool landed = false;
-            TCF_TIMED(7, warp == 0 && lane == 0, landed = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[ab], acc_lap & 1, a.status, kDevWaitMma, hint)));
+            TCF_TIMED(0, landed = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_full[ab], acc_lap & 1, a.status, kDevWaitMma, hint)));
             if (!landed) {
                 *abort_flag = 1;
                 break;
@@ -793,7 +799,7 @@ tc_fused_kernel(const __grid_constant__ CUtensorMap tmX, const FusedArgs a) {
                 ++acc_lap;
             }
         }
-        if (warp == 0 && lane == 0) TCF_ADD(8, clock64() - tcf_t0);
+        if (warp == 0 && lane == 0) { TCF_ADD(7, tcf_w0); TCF_ADD(8, clock64() - tcf_t0); }
     }
 
     tc_fence_before();

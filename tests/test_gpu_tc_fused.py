@@ -195,6 +195,30 @@ def test_moe_ffn_equals_three_grouped_gemms(ops, name, counts):
     assert (got[live] - ref[live]).abs().max().item() <= (TOL_TC + 2.0 ** -8) * scale
 
 
+def test_moe_ffn_matvec_threshold(ops):
+    """lsg_gguf_moe_ffn_set_matvec_rows: with the threshold at -1 a batch of a few rows per expert
+    runs on the tensor cores (tolerance against the mat-vec composition), and the default route
+    is back, bit for bit, once the old value is restored."""
+    from layerstormgemmkernels_b200 import capi
+    H, I = 512, 256
+    A, offs, ws, gp, up, dp = _ffn_case("Q4_K", [2, 1, 0, 3, 5, 0, 1, 4], H, I, seed=13)
+    t = T["Q4_K"]
+    base = ops.gguf_moe_ffn(A, offs, gp, up, dp, t, H, I, out_dtype=torch.float32)
+    old = capi.lib.lsg_gguf_moe_ffn_set_matvec_rows(-1)
+    try:
+        assert old == 8
+        tc = ops.gguf_moe_ffn(A, offs, gp, up, dp, t, H, I, out_dtype=torch.float32)
+    finally:
+        assert capi.lib.lsg_gguf_moe_ffn_set_matvec_rows(old) == -1
+    again = ops.gguf_moe_ffn(A, offs, gp, up, dp, t, H, I, out_dtype=torch.float32)
+    assert torch.equal(base, again)
+    assert not torch.equal(base, tc)   # another route really ran
+    # the two routes quantize the activation of the down projection from values that differ in
+    # the last bf16 bit here and there; an int8 step of a block is 1/127 of its largest value
+    scale = base.abs().max().item()
+    assert (tc - base).abs().max().item() <= (TOL_TC + 2.0 ** -6) * scale
+
+
 def test_moe_ffn_vs_oracle_small(ops):
     """End to end against the CPU oracle: Q8_1 mat-vec oracle for each projection, activation
     in fp32 with bf16 rounding in between."""
