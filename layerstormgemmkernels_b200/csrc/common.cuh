@@ -80,15 +80,62 @@ __device__ __forceinline__ bool elect_one_lane() {
     return pred != 0;
 }
 
-// rn(fl(x / d)) as a float, for |x / d| <= 127, without a division per element: x * fl(1/d) is
-// within 2.3e-5 of fl(x/d), so rounding it gives the same integer unless it lies within 1e-4 of
-// a half-integer (t - rint(t) is exact in fp32 at this magnitude); only then, for about one
-// value in 5000, is the true quotient formed.  Five instructions on the common path.
+// rn(fl(x / d)) as a float, for |x / d| <= 127, without a division per element.  t = x * fl(1/d)
+// corrected once by its exact remainder, fma(fma(-t, d, x), fl(1/d), t), is the correctly
+// rounded quotient when fl(1/d) is the correctly rounded reciprocal and nothing under- or
+// overflows (the last step of the usual division sequence); four instructions and no branch.
+// A test for "x * fl(1/d) is near a half-integer" would not do: with bf16 inputs x / d is an
+// exact half-integer for one value in 250, and a warp would take the division for one value
+// in eight.  Scales outside [1e-28, 1e30] (all-zero and infinite blocks among them, rcp = 0
+// for the former) keep the older form.
 __device__ __forceinline__ float q8_round_f(float x, float d, float rcp) {
     const float t = x * rcp;
+    if (d >= 1e-28f && d <= 1e30f) return rintf(fmaf(fmaf(-t, d, x), rcp, t));
     float k = rintf(t);
     if (fabsf(t - k) > 0.4999f) k = rintf(x / d);
     return k;
+}
+
+// max(a, b) that is NaN when either operand is.
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
+// Eight values of one Q8_1 block at once -> their int8 codes, values 0-3 in w0 and 4-7 in w1.
+// Same integers as q8_round_f, i.e. rn(fl(x / d)).  With bf16 inputs x / d is an exact
+// half-integer for one value in 250, so a test for "near a tie" sends most warps into the
+// division; instead the quotient itself is formed exactly: t = x * fl(1/d) corrected once by
+// its exact remainder, fma(fma(-t, d, x), fl(1/d), t), is the correctly rounded x / d when
+// fl(1/d) is the correctly rounded reciprocal (the final step of the usual division
+// sequence), as long as nothing under- or overflows.  It is rounded to an integer by adding
+// 1.5 * 2^23; the low mantissa byte of that sum is the integer in two's complement, so no
+// conversion instruction is needed.  Blocks whose scale is outside [1e-28, 1e30] (zero and
+// infinite blocks among them) and groups with a NaN take the plain path.
+__device__ __forceinline__ void q8_round8(const float* x, float d, float rcp, uint32_t& w0, uint32_t& w1) {
+    const float magic = 12582912.0f;
+    float km[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float t = x[i] * rcp;
+        km[i] = fmaf(fmaf(-t, d, x[i]), rcp, t) + magic;
+    }
+    const float m = max_nan(max_nan(max_nan(km[0], km[1]), max_nan(km[2], km[3])),
+                            max_nan(max_nan(km[4], km[5]), max_nan(km[6], km[7])));
+    const bool redo = !(d >= 1e-28f && d <= 1e30f) || m != m;
+    if (redo) {
+        uint32_t q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = static_cast<uint32_t>(static_cast<int>(q8_round_f(x[i], d, rcp))) & 0xFFu;
+        w0 = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
+        w1 = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+        return;
+    }
+    const uint32_t b[8] = {__float_as_uint(km[0]), __float_as_uint(km[1]), __float_as_uint(km[2]), __float_as_uint(km[3]),
+                           __float_as_uint(km[4]), __float_as_uint(km[5]), __float_as_uint(km[6]), __float_as_uint(km[7])};
+    w0 = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    w1 = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

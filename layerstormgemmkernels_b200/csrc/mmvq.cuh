@@ -215,26 +215,19 @@ __device__ __forceinline__ void build_x_image_bf16(uint8_t* img, const __nv_bflo
             for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             const float d = amax / 127.0f;
-            // q = rn(fl(x / d)) as the reference computes it, without sixteen IEEE divisions:
-            // x * fl(1/d) is within 2.3e-5 of fl(x/d) for |x/d| <= 127, so rounding it gives
-            // the same integer unless it lies within 1e-4 of a half-integer; only then
-            // (about one value in 5000) is the true quotient formed.
+            // q = rn(fl(x / d)) as the reference computes it, without sixteen IEEE divisions
+            // (q8_round8: the quotient from the reciprocal and one exact remainder step)
             const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-            int q[16];
-            int sum16 = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int k = static_cast<int>(q8_round_f(x[i], d, rcp));
-                q[i] = k;
-                sum16 += k;
-            }
+            uint4 packed;
+            q8_round8(x, d, rcp, packed.x, packed.y);
+            q8_round8(x + 8, d, rcp, packed.z, packed.w);
+            // sum of the sixteen int8 codes: four byte-wise dot products with ones
+            const int sum16 = __dp4a(static_cast<int>(packed.x), 0x01010101,
+                              __dp4a(static_cast<int>(packed.y), 0x01010101,
+                              __dp4a(static_cast<int>(packed.z), 0x01010101,
+                              __dp4a(static_cast<int>(packed.w), 0x01010101, 0))));
             const int sum32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 1);
             if (!live) continue;
-            uint4 packed;
-            packed.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
-            packed.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
-            packed.z = (q[8] & 0xFF) | ((q[9] & 0xFF) << 8) | ((q[10] & 0xFF) << 16) | ((q[11] & 0xFF) << 24);
-            packed.w = (q[12] & 0xFF) | ((q[13] & 0xFF) << 8) | ((q[14] & 0xFF) << 16) | ((q[15] & 0xFF) << 24);
             const float dh = __half2float(__float2half(d));  // the mat-vec sees the fp16-rounded scale
             const int half = task & 1;
             const int b = task >> 1;

@@ -4,10 +4,13 @@
 // (csrc/smxx/quant/dynamic_fp8_quant.cu:38-112): scale = amax / 448 (1.0 when the block
 // is all zero), values multiplied by the fp32 reciprocal 1.0f / scale (reciprocal, then
 // multiply), clamped to +-448 and converted with round-to-nearest-even, saturating.  The
-// maximum does not depend on the order it is taken in, so the thread layout is free:
-// here sixteen lanes own one 128-column block (eight values = one 16-byte load each, one
-// 8-byte store), two blocks per warp, instead of a 256-thread CTA with half its threads
-// idle and the input read twice.
+// maximum does not depend on the order it is taken in, so the thread layout is free.
+// The kernel is bound by instruction issue, not by memory, unless the per-block work (index
+// arithmetic, two IEEE divisions, the reduction) is spread over many values per lane: four
+// lanes own one 128-column block, each four 16-byte pieces of it (piece l, l+4, l+8, l+12, so
+// that the four lanes' loads of one step cover 64 contiguous bytes), eight blocks per warp.
+// Rows that are not a multiple of eight values long, or unaligned tensors, take the older
+// layout (sixteen lanes per block, scalar loads).
 #include "common.cuh"
 #include "host.h"
 
@@ -94,6 +97,67 @@ dynamic_fp8_quant_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restri
     }
 }
 
+// Four lanes per block, 32 values per lane.  K % 8 == 0, 16-byte aligned input, 8-byte aligned output.
+__global__ void __launch_bounds__(kFp8Warps * 32)
+dynamic_fp8_quant_wide_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict__ out,
+                              float* __restrict__ scales, int M, int K, int blocks_per_row, int m_major) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int lane = threadIdx.x & 31;
+    const int ql = lane & 3;
+    const long long gblk = (static_cast<long long>(blockIdx.x) * kFp8Warps + (threadIdx.x >> 5)) * 8 + (lane >> 2);
+    const long long total = static_cast<long long>(M) * blocks_per_row;
+    const bool live = gblk < total;
+    const long long blk = live ? gblk : 0;
+    const int row = total <= 0x7fffffffLL ? static_cast<int>(static_cast<unsigned>(blk) / static_cast<unsigned>(blocks_per_row))
+                                          : static_cast<int>(blk / blocks_per_row);
+    const int bc = static_cast<int>(blk - static_cast<long long>(row) * blocks_per_row);
+    const int col0 = bc * kFp8Block + ql * 8;           // piece j starts at col0 + 32 j
+    const size_t base = static_cast<size_t>(row) * K + col0;
+
+    uint4 raw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        raw[j] = (col0 + 32 * j < K) ? __ldg(reinterpret_cast<const uint4*>(in + base + 32 * j)) : make_uint4(0, 0, 0, 0);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[8 * j + 2 * i] = __uint_as_float(w[i] << 16);
+            v[8 * j + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live) return;
+
+    const float scale = (amax > 0.0f) ? (amax / 448.0f) : 1.0f;
+    const float inv = 1.0f / scale;
+    if (ql == 0) {
+        const size_t si = m_major ? (static_cast<size_t>(bc) * M + row)
+                                  : (static_cast<size_t>(row) * blocks_per_row + bc);
+        scales[si] = scale;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (col0 + 32 * j >= K) break;
+        // the lower clamp also turns a NaN into -448 as the reference's fmaxf/fminf pair does;
+        // the upper clamp is the converter's saturation
+        float s[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] = fmaxf(v[8 * j + i] * inv, -448.0f);
+        uint2 o;
+        o.x = pack_e4m3x4(s[0], s[1], s[2], s[3]);
+        o.y = pack_e4m3x4(s[4], s[5], s[6], s[7]);
+        *reinterpret_cast<uint2*>(out + base + 32 * j) = o;
+    }
+}
+
 }  // namespace
 
 }  // namespace lsg
@@ -117,7 +181,8 @@ extern "C" int lsg_dynamic_fp8_quant(const lsg_dynamic_fp8_quant_params* p, void
     auto out = static_cast<uint8_t*>(p->output);
     auto sc = static_cast<float*>(p->scales);
     if (vec)
-        LSG_CUDA_TRY(launch_kernel(dynamic_fp8_quant_kernel<true>, dim3(static_cast<unsigned>(grid)),
+        LSG_CUDA_TRY(launch_kernel(dynamic_fp8_quant_wide_kernel,
+                                   dim3(static_cast<unsigned>((total + kFp8Warps * 8 - 1) / (kFp8Warps * 8))),
                                    dim3(kFp8Warps * 32), 0, s, true, in, out, sc, M, K, bpr,
                                    p->m_major_scales ? 1 : 0));
     else

@@ -16,10 +16,6 @@ namespace {
 constexpr int kQuantThreads = 256;
 constexpr int kQ8BatchMax = 8;
 
-__device__ __forceinline__ int q8_round(float x, float d, float rcp) {
-    return static_cast<int>(q8_round_f(x, d, rcp));
-}
-
 // Four lanes per 32-value block, eight consecutive values (one 16-byte load) per lane.
 // The block sum is formed in exactly the order of the reference's xor butterfly
 // (offsets 16, 8, 4, 2, 1 over lanes = elements): element pairs (i, i+16), then
@@ -66,14 +62,13 @@ __device__ __forceinline__ void quantize_q8_1_body(const __nv_bfloat16* __restri
 
         const float d = amax / 127.0f;
         const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-        uint32_t q[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = static_cast<uint32_t>(q8_round(v[i], d, rcp)) & 0xFFu;
+        uint32_t w0, w1;
+        q8_round8(v, d, rcp, w0, w1);
         const long long blk = tk >> 2;
         const int part = static_cast<int>(tk & 3);
         uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
-        out[1 + 2 * part] = q[0] | (q[1] << 8) | (q[2] << 16) | (q[3] << 24);
-        out[2 + 2 * part] = q[4] | (q[5] << 8) | (q[6] << 16) | (q[7] << 24);
+        out[1 + 2 * part] = w0;
+        out[2 + 2 * part] = w1;
         if (part == 0) {
             const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
             out[0] = *reinterpret_cast<const uint32_t*>(&ds);
@@ -87,6 +82,60 @@ quantize_q8_1_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ 
     pdl_launch_dependents();
     pdl_wait_prior();  // x may be the output of the previous kernel in the stream
     quantize_q8_1_body<U>(x, y, n_blocks, blockIdx.x);
+}
+
+// Large tensors: one lane per block.  With four lanes per block the kernel is bound by
+// instruction issue (eighteen shuffles and two IEEE divisions per eight values); a lane that
+// holds all 32 values of a block needs no shuffle, forms the sum in the same butterfly order in
+// registers and divides once per 32 values.  The CTA's 256 blocks (9216 contiguous bytes) go
+// through shared memory so that the stores are coalesced 4-byte words.
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_q8_1_wide_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y, long long n_blocks) {
+    __shared__ uint32_t stage[kQuantThreads * 9];
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const long long blk0 = static_cast<long long>(blockIdx.x) * kQuantThreads;
+    const long long blk = blk0 + threadIdx.x;
+    const bool live = blk < n_blocks;
+    const uint4* src = reinterpret_cast<const uint4*>(x) + (live ? blk : 0) * 4;
+    uint4 raw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) raw[j] = __ldg(src + j);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[8 * j + 2 * i] = __uint_as_float(w[i] << 16);
+            v[8 * j + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    // the xor butterfly over 32 lanes, in registers: (i, i+16), (i, i+8), (i, i+4), (i, i+2), (i, i+1)
+    float a[16], b[8], c[4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) a[i] = v[i] + v[i + 16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] = a[i] + a[i + 8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = b[i] + b[i + 4];
+    const float sum = (c[0] + c[2]) + (c[1] + c[3]);
+
+    const float d = amax / 127.0f;
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    uint32_t* out = stage + threadIdx.x * 9;
+    const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
+    out[0] = *reinterpret_cast<const uint32_t*>(&ds);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) q8_round8(v + 8 * k, d, rcp, out[1 + 2 * k], out[2 + 2 * k]);
+    __syncthreads();
+    const long long left = n_blocks - blk0;
+    const int words = static_cast<int>(left < kQuantThreads ? left : kQuantThreads) * 9;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(y + blk0 * kQ8_1Bytes);
+    for (int i = threadIdx.x; i < words; i += kQuantThreads) dst[i] = stage[i];
 }
 
 // Several tensors in one launch (the distinct activations of a batch of projections whose inputs
@@ -144,6 +193,14 @@ int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t
     if (!x_bf16 || !q8_1_out) return fail(LSG_ERR_INVALID, "quantize_q8_1: null pointer");
     if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(q8_1_out) & 3))
         return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1: input must be 16-byte and output 4-byte aligned");
+    if (n_blocks >= 2ll * kQuantThreads * sm_count()) {
+        const long long ctas = (n_blocks + kQuantThreads - 1) / kQuantThreads;
+        if (ctas > 0x7fffffffLL) return fail(LSG_ERR_INVALID, "quantize_q8_1: too many blocks");
+        LSG_CUDA_TRY(launch_kernel(quantize_q8_1_wide_kernel, dim3(static_cast<unsigned>(ctas)), dim3(kQuantThreads), 0,
+                                   stream, pdl, static_cast<const __nv_bfloat16*>(x_bf16),
+                                   static_cast<uint8_t*>(q8_1_out), n_blocks));
+        return LSG_OK;
+    }
     const long long tasks = n_blocks * 4;
     const bool big = tasks >= 8ll * kQuantThreads * 4 * sm_count();   // enough CTAs left at four vectors per thread
     const int per_cta = kQuantThreads * (big ? 4 : 1);

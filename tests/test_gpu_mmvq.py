@@ -34,7 +34,7 @@ def rel_err(got, ref):
     return np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30)
 
 
-@pytest.mark.parametrize("M,K", [(1, 32), (1, 4096), (3, 512), (8, 14336), (17, 256), (64, 2048)])
+@pytest.mark.parametrize("M,K", [(1, 32), (1, 4096), (3, 512), (8, 14336), (17, 256), (64, 2048), (611, 4096)])
 def test_q8_1_quantizer_bit_exact(ops, M, K):
     g = torch.Generator().manual_seed(M * 1000 + K)
     x = torch.randn(M, K, generator=g)

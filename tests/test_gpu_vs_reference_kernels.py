@@ -38,7 +38,7 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-@pytest.mark.parametrize("M,K", [(1, 4096), (5, 512), (8, 14336), (33, 2048)])
+@pytest.mark.parametrize("M,K", [(1, 4096), (5, 512), (8, 14336), (33, 2048), (611, 4096)])   # the last: one lane per block, ragged last CTA
 def test_q8_1_bit_exact_vs_reference_kernel(ref, ops, M, K):
     x = torch.randn(M, K, generator=torch.Generator().manual_seed(K + M))
     x[0, :32] = 0
@@ -143,3 +143,54 @@ def test_nvfp4_dequant_bf16_equal_reference_kernel(ref, ops, N, K):
     assert fn(_p(packed), _p(sc), 0.37, _p(want), N, K, _stream()) == 0
     torch.cuda.synchronize()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def _special_rows(M, K, seed):
+    """Random rows with values placed exactly on, one float below and one float above every
+    e2m1 / e4m3 rounding boundary the quantizers divide by powers of two into, plus zeros of
+    both signs, infinities and a NaN."""
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(seed)) * 2
+    x[0, :16] = 0.0
+    x[0, 3] = -0.0
+    x[1, 5] = float("inf")
+    x[2, 7] = float("-inf")
+    x[3, 9] = float("nan")
+    # a group whose largest value is 6 * 2^k has an exact scale; the other values of the group
+    # then land exactly on the thresholds after the division
+    ties = torch.tensor([6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, 0.5])
+    for r, k in ((4, 0), (5, 3), (6, -2)):
+        x[r, 16:32] = ties * 2.0 ** k
+    return x.to(torch.bfloat16).cuda()
+
+
+def test_nvfp4_grouped_special_values_equal_reference_kernel(ref, ops):
+    """Ties on every e2m1 threshold (the reference sends them up in magnitude), zeros of both
+    signs, infinities and NaN: the bytes of the reference's kernels."""
+    K, offs = 256, [0, 5, 5, 12]
+    T, E = offs[-1], len(offs) - 1
+    xb = _special_rows(T, K, seed=5)
+    offs_t = torch.tensor(offs, dtype=torch.int32, device="cuda")
+    packed, scales, sf = ops.bf16_to_nvfp4_grouped(xb, offs_t, None)
+    wp, wsc = torch.zeros_like(packed), torch.zeros_like(scales)
+    assert ref.ref_bf16_to_nvfp4_grouped(_p(xb), _p(wp), _p(wsc), _p(offs_t), _p(sf), T, E, K, None, _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed, wp) and torch.equal(scales, wsc)
+    up = _special_rows(T, K, seed=6)
+    packed, scales, sf = ops.silu_mul_to_nvfp4_grouped(xb, up, offs_t, None)
+    wp, wsc = torch.zeros_like(packed), torch.zeros_like(scales)
+    assert ref.ref_silu_mul_to_nvfp4_grouped(_p(xb), _p(up), _p(wp), _p(wsc), _p(offs_t), _p(sf), T, E, K, None,
+                                             _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed, wp) and torch.equal(scales, wsc)
+
+
+@pytest.mark.parametrize("M,K", [(12, 256), (12, 200)])
+def test_dynamic_fp8_special_values_equal_reference_kernel(ref, ops, M, K):
+    xb = _special_rows(M, K, seed=7)
+    out, sc = ops.dynamic_fp8_quant(xb, False)
+    want = torch.zeros((M, K), dtype=torch.uint8, device="cuda")
+    wsc = torch.zeros_like(sc)
+    assert ref.ref_dynamic_fp8_quant(_p(xb), _p(want), _p(wsc), M, K, 0, _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.uint8), want)
+    assert torch.equal(sc.view(torch.int32), wsc.view(torch.int32))   # bit patterns: a NaN scale equals itself
