@@ -219,8 +219,11 @@ def workload_config(args):
             "shapes": {n: [N, K] for n, N, K in LAYER},
             "l2_defeat": "steps walk over layer copies totalling more than 2.5x the 126 MB L2",
             "launch": "one CUDA graph over all layer copies (a decoder's layers back to back), each layer one "
-                      "lsg_gguf_mmvq_batch call: (q,k,v), o, (gate,up), down as four dependent mat-vec launches, "
-                      "activations quantized inside them (or by a quantizer launch above 16384 values)",
+                      "lsg_gguf_mmvq_batch call over the seven projections, which have four distinct inputs and "
+                      "no dependency on each other inside the call: the library runs the six K = 4096 projections "
+                      "as one launch and down as a second one that does not wait for the first; activations "
+                      "quantized inside the launches (above 16384 values: a quantizer launch per input, one "
+                      "launch per input, each waiting for the one before)",
             "parallelism": "replicas only"}
 
 
@@ -253,13 +256,20 @@ class DecodeLayerBench:
         self.args = [self._params(w) for w in self.layers]
         need = capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(self.args[0], len(layer))
         self.ws = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
+        # launches of one lsg_gguf_mmvq_batch call, as the library forms them: consecutive
+        # projections of one K share a launch (up to six) when they read the same activations or,
+        # with the quantizer inside the kernel (M * K <= 16384), independent ones
         joined = []
         for name, _, K in layer:
-            if not joined or joined[-1][0] != group[name] or joined[-1][2] >= 4:
-                joined.append([group[name], K, 0])
-            joined[-1][2] += 1
+            fused = M * K <= 16384
+            if (joined and joined[-1][1] == K and joined[-1][2] < 6
+                    and (joined[-1][0] == group[name] or (fused and joined[-1][3]))):
+                joined[-1][2] += 1
+                joined[-1][0] = group[name]
+            else:
+                joined.append([group[name], K, 1, fused])
         self.n_matvec = len(joined)
-        self.launches_per_step = sum(1 if M * K <= 16384 else 2 for _, K, _ in joined)
+        self.launches_per_step = sum(1 if f else 2 for _, _, _, f in joined)
 
     def _params(self, weights):
         capi = self.capi

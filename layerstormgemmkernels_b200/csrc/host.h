@@ -13,7 +13,7 @@ int quantize_q8_1_batch(int n, const void* const* x_bf16, void* const* q8_1_out,
                         cudaStream_t stream, bool pdl);
 int check_gemm_params(const char* op, const lsg_gguf_mmvq_params* p);
 int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void* C, int ldc,
-              int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16 = nullptr);
+              int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16 = nullptr, int dep_mode = 0);
 bool fused_quant_ok(int M, int K, const void* A);
 int dequant_gemm(int type, int M, int N, int K, const void* A, const void* W, void* C, int ldc,
                  int out_f32, cudaStream_t stream);

@@ -97,7 +97,7 @@ int check_gemm_params(const char* op, const lsg_gguf_mmvq_params* p) {
 // xq: Q8_1 blocks of all M rows.  ldc: output row stride.  Rows are processed
 // in batches that fit the shared-memory activation image.
 int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void* C, int ldc,
-              int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16) {
+              int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16, int dep_mode) {
     if (M == 0 || N == 0) return LSG_OK;
     if (K == 0) return fail(LSG_ERR_INVALID, "gguf_mmvq: K must be positive");
     if (!W || (!xq && !A_bf16) || !C) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
@@ -125,6 +125,7 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
         a.K = K;
         a.ldc = ldc;
         a.out_f32 = out_f32;
+        a.dep_mode = (pdl && m0 == 0) ? dep_mode : 0;   // later row batches are fully serialized launches
         const int rc = dispatch_launch(type, a, stream, pdl && m0 == 0);
         if (rc != LSG_OK) return rc;
     }
@@ -134,9 +135,10 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
 // The same activations against n <= 4 weight matrices of one type and K, as one launch
 // per batch of rows.  Matrix j writes C[j], [M][N[j]] row-major.
 int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* const* C, const int* N,
-                     const void* xq, int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16) {
-    if (n < 1 || n > 1 + kMmvqMaxExtra) return fail(LSG_ERR_INVALID, "gguf_mmvq: 1..4 matrices per joined launch");
-    if (n == 1) return mmvq_q8_1(type, M, N[0], K, W[0], xq, C[0], N[0], out_f32, stream, pdl, A_bf16);
+                     const void* xq, int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16, int dep_mode = 0,
+                     const void* const* A_each = nullptr) {
+    if (n < 1 || n > 1 + kMmvqMaxExtra) return fail(LSG_ERR_INVALID, "gguf_mmvq: 1..6 matrices per joined launch");
+    if (n == 1) return mmvq_q8_1(type, M, N[0], K, W[0], xq, C[0], N[0], out_f32, stream, pdl, A_bf16, dep_mode);
     if (M == 0) return LSG_OK;
     if (K == 0) return fail(LSG_ERR_INVALID, "gguf_mmvq: K must be positive");
     if (!xq && !A_bf16) return fail(LSG_ERR_INVALID, "gguf_mmvq: null pointer");
@@ -172,7 +174,10 @@ int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* 
             a.Wx[j - 1] = static_cast<const uint8_t*>(W[j]);
             a.Cx[j - 1] = static_cast<uint8_t*>(C[j]) + static_cast<size_t>(m0) * N[j] * c_elem;
             a.Nx[j - 1] = N[j];
+            if (A_each && A_each[j] && A_each[j] != A_bf16)
+                a.Ax[j - 1] = static_cast<const __nv_bfloat16*>(A_each[j]) + static_cast<size_t>(m0) * K;
         }
+        a.dep_mode = (pdl && m0 == 0) ? dep_mode : 0;
         const int rc = dispatch_launch(type, a, stream, pdl && m0 == 0);
         if (rc != LSG_OK) return rc;
     }
@@ -265,16 +270,62 @@ store_to_host_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
 namespace lsg {
 namespace {
 
+// Byte ranges of an entry's activations and result.
+struct Span {
+    uintptr_t b, e;
+    bool meets(const Span& o) const { return b < o.e && o.b < e; }
+};
+Span a_span(const lsg_gguf_mmvq_params& q) {
+    const uintptr_t b = reinterpret_cast<uintptr_t>(q.A);
+    return {b, b + static_cast<uintptr_t>(q.M) * q.K * 2};
+}
+Span c_span(const lsg_gguf_mmvq_params& q) {
+    const uintptr_t b = reinterpret_cast<uintptr_t>(q.C);
+    return {b, b + static_cast<uintptr_t>(q.M) * q.N * (q.out_dtype == LSG_DTYPE_F32 ? 4 : 2)};
+}
+
+// True when entries [i, i + run) read nothing an earlier entry writes and write nothing an
+// earlier entry reads or writes.
+bool independent_of_earlier(const lsg_gguf_mmvq_params* p, int i, int run) {
+    for (int j = i; j < i + run; ++j) {
+        const Span a = a_span(p[j]), c = c_span(p[j]);
+        for (int k = 0; k < i; ++k) {
+            if (p[k].M == 0 || p[k].N == 0) continue;
+            const Span ak = a_span(p[k]), ck = c_span(p[k]);
+            if (a.meets(ck) || c.meets(ck) || c.meets(ak)) return false;
+        }
+    }
+    return true;
+}
+
+// LSG_MMVQ_BATCH_OVERLAP=0 keeps every launch of a batch waiting for the one in front of it.
+bool batch_overlap_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("LSG_MMVQ_BATCH_OVERLAP");
+        return !e || atoi(e) != 0;
+    }();
+    return on;
+}
+
 // Entries [i, i + run) of a batch that can share one launch: same activations, type, K,
 // batch rows and output type, at most four, every N >= 1.
-int joinable_run(const lsg_gguf_mmvq_params* p, int i, int n) {
+int joinable_run(const lsg_gguf_mmvq_params* p, int i, int n, bool distinct_a = false) {
     int run = 1;
     if (p[i].M < 1 || p[i].N < 1) return 1;
     while (i + run < n && run < 1 + kMmvqMaxExtra) {
         const lsg_gguf_mmvq_params& a = p[i];
         const lsg_gguf_mmvq_params& b = p[i + run];
-        if (b.A != a.A || b.M != a.M || b.K != a.K || b.type != a.type || b.out_dtype != a.out_dtype || b.N < 1)
-            break;
+        if (b.M != a.M || b.K != a.K || b.type != a.type || b.out_dtype != a.out_dtype || b.N < 1) break;
+        if (b.A != a.A) {
+            // Activations of its own: the entry may share the launch when both take the
+            // quantizer inside the kernel and it shares no buffer with the entries already in
+            // the run (they are computed at the same time).
+            if (!distinct_a || !fused_quant_ok(a.M, a.K, a.A) || !fused_quant_ok(b.M, b.K, b.A)) break;
+            bool apart = true;
+            const Span ab = a_span(b), cb = c_span(b);
+            for (int k = i; k < i + run && apart; ++k) apart = !ab.meets(c_span(p[k])) && !cb.meets(c_span(p[k])) && !cb.meets(a_span(p[k]));
+            if (!apart) break;
+        }
         ++run;
     }
     return run;
@@ -305,25 +356,47 @@ extern "C" int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* w
         return fail(LSG_ERR_WORKSPACE, "gguf_mmvq_batch: workspace too small (have %zu, need %zu)",
                     workspace ? workspace_bytes : size_t(0), need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Launches that neither read what an earlier entry of the batch writes nor write what an
+    // earlier entry reads or writes need not wait for the launch in front of them: only the
+    // first launch waits for the work in front of the batch (and releases the next launch only
+    // after that wait).  Needs the first launch to be a mat-vec with the quantizer inside.
+    bool relaxed = false;
+    {
+        int first = 0;
+        while (first < n && (p[first].M == 0 || p[first].N == 0)) ++first;
+        relaxed = first < n && fused_quant_ok(p[first].M, p[first].K, p[first].A) && batch_overlap_enabled();
+    }
+    bool launched = false;
     for (int i = 0; i < n;) {
-        const int run = joinable_run(p, i, n);
+        const int run = joinable_run(p, i, n, batch_overlap_enabled());
         const lsg_gguf_mmvq_params& e = p[i];
         if (e.M == 0 || e.N == 0) {
             i += run;
             continue;
         }
+        int dep_mode = 0;
+        if (relaxed) {
+            if (!launched) {
+                dep_mode = 1;
+            } else if (fused_quant_ok(e.M, e.K, e.A) && independent_of_earlier(p, i, run)) {
+                dep_mode = 2;
+            }
+        }
+        launched = true;
         const void* W[1 + kMmvqMaxExtra];
+        const void* A[1 + kMmvqMaxExtra];
         void* C[1 + kMmvqMaxExtra];
         int N[1 + kMmvqMaxExtra];
         for (int j = 0; j < run; ++j) {
             W[j] = p[i + j].B;
+            A[j] = p[i + j].A;
             C[j] = p[i + j].C;
             N[j] = p[i + j].N;
         }
         const int out_f32 = e.out_dtype == LSG_DTYPE_F32;
         int rc;
         if (fused_quant_ok(e.M, e.K, e.A)) {
-            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, nullptr, out_f32, s, true, e.A);
+            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, nullptr, out_f32, s, true, e.A, dep_mode, A);
         } else {
             rc = quantize_q8_1(e.A, workspace, e.M, e.K, s, true);
             if (rc != LSG_OK) return rc;

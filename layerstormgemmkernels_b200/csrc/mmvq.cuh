@@ -30,7 +30,7 @@
 namespace lsg {
 
 constexpr int kMmvqMaxStages = 8;
-constexpr int kMmvqMaxExtra = 3;
+constexpr int kMmvqMaxExtra = 5;
 
 struct MmvqArgs {
     const uint8_t* W;         // packed weight, 16-byte aligned
@@ -50,6 +50,16 @@ struct MmvqArgs {
     int cons_warps;           // consumer warps per CTA (block = 32 * (cons_warps + 1))
     long long wait_limit;     // limit of every device-side wait, SM cycles (lsg_set_wait_limit_cycles)
     int drop_slab;            // failure-path test hook: CTA 0's producer never loads this slab (-1: none)
+    // How the launch is ordered against the kernel in front of it in the stream (programmatic
+    // dependent launch).  0: the kernel after this one may be scheduled at once, the activations
+    // are read after the kernel in front has completed.  1 (first launch of a batch whose later
+    // launches are of kind 2): the same wait, but the kernel after this one is released only
+    // after the wait, so that nothing behind this launch runs before the work in front of the
+    // batch has completed.  2 (a launch of a batch that reads and writes nothing an earlier
+    // launch of the batch writes or reads): no wait before the activations are read - CTAs
+    // start on the SMs the previous launch has left while its last CTAs still stream - and
+    // the wait is made before the CTA exits, so that launches still complete in stream order.
+    int dep_mode;
 #ifdef LSG_MMVQ_TRACE
     unsigned long long* trace;  // [grid][16] nanosecond timestamps of the phases of each CTA
 #endif
@@ -60,12 +70,14 @@ struct MmvqArgs {
     int gps;                  // row groups per slab
     uint32_t gps_magic;       // ceil(2^32 / gps), 0 when gps == 1
     uint32_t stages_magic;    // ceil(2^32 / stages), 0 when stages == 1
-    // Joined launch: up to three further weight matrices with the same type, K and
-    // activations (the q, k, v or the gate, up projections of one input).  Matrix j owns
+    // Joined launch: up to five further weight matrices with the same type, K and batch rows
+    // (the q, k, v or the gate, up projections of one input; with activations of their own,
+    // Ax[j], any projections of that shape that do not depend on each other).  Matrix j owns
     // the CTAs from cta0x[j] up to the next matrix's first CTA; its output is [M][Nx[j]].
     // For joined launches rows_q / rows_r describe matrix 0 over its cta0x[0] CTAs.
     int n_extra;
     const uint8_t* Wx[kMmvqMaxExtra];
+    const __nv_bfloat16* Ax[kMmvqMaxExtra];   // bf16 activations of matrix j (null: those of matrix 0)
     void* Cx[kMmvqMaxExtra];
     int Nx[kMmvqMaxExtra];
     int cta0x[kMmvqMaxExtra];
@@ -367,6 +379,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     uint64_t* empty = full + kMmvqMaxStages;
     int* next_group = reinterpret_cast<int*>(empty + kMmvqMaxStages);
     volatile int* slab_in_stage = next_group + 1;  // which slab each stage was last loaded with
+    volatile int* released = slab_in_stage + kMmvqMaxStages;  // dep_mode 1: the consumers have passed their wait
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -377,6 +390,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     // The matrix this CTA works on (joined launches) and its contiguous row range there.
     int bx = static_cast<int>(blockIdx.x);
     const uint8_t* Wm = a.W;
+    const __nv_bfloat16* Am = a.A;
     void* Cm = a.C;
     int Nm = a.N, ldcm = a.ldc, rows_q = a.rows_q, rows_r = a.rows_r;
     if (a.n_extra > 0) {
@@ -385,6 +399,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         for (int j = 0; j < kMmvqMaxExtra; ++j)
             if (j < a.n_extra && b >= a.cta0x[j]) {
                 Wm = a.Wx[j];
+                if (a.Ax[j]) Am = a.Ax[j];
                 Cm = a.Cx[j];
                 Nm = ldcm = a.Nx[j];
                 rows_q = a.rows_qx[j];
@@ -410,8 +425,9 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         if (tid == 0) *next_group = 0;
         mbar_fence_init();
     }
+    if (tid == 0) *released = 0;
     __syncthreads();
-    pdl_launch_dependents();
+    if (a.dep_mode != 1) pdl_launch_dependents();
 
     if (is_producer) {
         // ------------------------------------------------------------------
@@ -428,7 +444,12 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
         const uintptr_t w_end_al = (w_base + static_cast<uintptr_t>(Nm) * a.row_bytes) & ~uintptr_t(15);
         int s = 0;
         uint32_t lap = 0;  // ring position of slab i: stage s, lap = i / stages
+        bool trigger_due = a.dep_mode == 1;   // this warp releases the next kernel too, once the consumers have
         for (int i = 0; i < n_slabs; ++i, s = (s + 1 == a.stages) ? 0 : s + 1, lap += (s == 0)) {
+            if (trigger_due && *released) {
+                pdl_launch_dependents();
+                trigger_due = false;
+            }
             if (lap > 0 &&
                 !__all_sync(0xffffffffu, mbar_wait_bounded(&empty[s], (lap - 1) & 1, a.status, kDevWaitEmpty, 2000u, a.wait_limit)))
                 break;
@@ -464,6 +485,12 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
             }
             __syncwarp();
         }
+        if (trigger_due) {
+            // all slabs issued before the consumers were released: wait for them (bounded), then release
+            const long long t0 = sm_clock();
+            while (!*released && sm_clock() - t0 <= a.wait_limit) __nanosleep(64);
+            pdl_launch_dependents();
+        }
         return;
     }
 
@@ -471,9 +498,13 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     // Consumers
     // ----------------------------------------------------------------------
     const int n_cons = n_cons_warps * 32;
-    pdl_wait_prior();  // activations (and the output buffer) belong to the stream order
+    if (a.dep_mode != 2) pdl_wait_prior();  // activations (and the output buffer) belong to the stream order
+    if (a.dep_mode == 1) {
+        pdl_launch_dependents();
+        if (tid == 0) *released = 1;
+    }
     if (tid == 0) LSG_TRACE(3);
-    if (a.A) build_x_image_bf16<T>(x_img, a.A, a.M, a.K, tid, n_cons);
+    if (a.A) build_x_image_bf16<T>(x_img, Am, a.M, a.K, tid, n_cons);
     else build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
     asm volatile("bar.sync 1, %0;" ::"r"(n_cons) : "memory");
     if (tid == 0) LSG_TRACE(4);
@@ -553,6 +584,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
 #endif
     }
     if (lane == 0) LSG_TRACE_MAX(7);
+    if (a.dep_mode == 2) pdl_wait_prior();
 }
 
 #endif  // __CUDACC__

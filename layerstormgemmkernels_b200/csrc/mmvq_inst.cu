@@ -71,13 +71,13 @@ int MMVQ_FN(launch)(MmvqArgs a, const MmvqTune& tn_in, cudaStream_t stream, bool
     MmvqTune tn = tn_in;
     // Joined launches: geometry follows the rows of all matrices together.
     const int n_prob = 1 + a.n_extra;
-    int n_rows[1 + kMmvqMaxExtra] = {a.N, 0, 0, 0};
+    int n_rows[1 + kMmvqMaxExtra] = {a.N};
     int n_total = a.N;
     for (int j = 0; j < a.n_extra; ++j) {
         n_rows[1 + j] = a.Nx[j];
         n_total += a.Nx[j];
     }
-    int ctas_of[1 + kMmvqMaxExtra] = {0, 0, 0, 0};
+    int ctas_of[1 + kMmvqMaxExtra] = {};
     {
         static const int small_kb = [] {
             const char* e = getenv("LSG_MMVQ_SMALL_KB");

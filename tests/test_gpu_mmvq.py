@@ -221,6 +221,98 @@ def test_mmvq_host_batch_chained_projection_reads_the_earlier_result(ops):
     assert torch.equal(y2, ops.gguf_mmvq(x2.cuda(), W2, t, N1, K0).cpu())
 
 
+@pytest.mark.parametrize("name,M", [("Q4_K", 1), ("Q4_K", 3), ("Q6_K", 2)])
+def test_mmvq_batch_distinct_inputs_share_a_launch(ops, name, M):
+    """A decoder layer's seven projections (scaled down) with their four distinct inputs in one
+    lsg_gguf_mmvq_batch call: the six projections of one K run as one launch although they read
+    three different activation rows; bits of the separate calls."""
+    from layerstormgemmkernels_b200 import capi
+    import ctypes
+    t = T[name]
+    K, KD = 1024, 3584
+    shapes = [("x", 1024, K), ("x", 256, K), ("x", 256, K), ("att", 1024, K), ("h", 3584, K), ("h", 3584, K), ("act", 1024, KD)]
+    g = torch.Generator().manual_seed(31 + M)
+    xin = {}
+    for grp, _, k in shapes:
+        if grp not in xin:
+            xin[grp] = (torch.randn(M, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    Ws = [torch.from_numpy(Q.random_gguf_weight(name, N, k, seed=7 + i)).cuda() for i, (_, N, k) in enumerate(shapes)]
+    outs = [torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") for _, N, _ in shapes]
+    P = capi.GgufMmvqParams
+    arr = (P * len(shapes))()
+    for i, (grp, N, k) in enumerate(shapes):
+        arr[i] = P(M=M, N=N, K=k, A=xin[grp].data_ptr(), B=Ws[i].data_ptr(), C=outs[i].data_ptr(), type=t,
+                   out_dtype=capi.DTYPE_BF16)
+    need = max(256, capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, len(shapes)))
+    ws = torch.empty((need,), dtype=torch.uint8, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        capi.check(capi.lib.lsg_gguf_mmvq_batch(arr, len(shapes), ctypes.c_void_p(ws.data_ptr()), need, st))
+    torch.cuda.synchronize()
+    for i, (grp, N, k) in enumerate(shapes):
+        assert torch.equal(outs[i], ops.gguf_mmvq(xin[grp], Ws[i], t, N, k)), (i, grp)
+    assert capi.device_status() == 0
+
+
+def test_mmvq_batch_independent_launches_overlap_dependent_ones_wait(ops):
+    """lsg_gguf_mmvq_batch lets a launch start before the one in front of it has finished when it
+    shares no buffer with the earlier entries; an entry that reads an earlier result (or writes
+    an earlier entry's buffer) must still wait.  Five launches, mixed, large enough to take a few
+    microseconds each, replayed back to back from a CUDA graph with changing inputs: every result
+    equals the separate calls'."""
+    from layerstormgemmkernels_b200 import capi
+    import ctypes
+    t = T["Q4_K"]
+    K0, N0, N1, N2 = 4096, 4096, 2048, 1024
+    W0 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N0, K0, seed=1)).cuda()     # y0 = x W0^T
+    W1 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N1, N0, seed=2)).cuda()     # y1 = y0 W1^T   (reads y0)
+    W2 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=3)).cuda()     # y2 = x2 W2^T   (independent)
+    W3 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, N1, seed=4)).cuda()     # y3 = y1 W3^T   (reads y1)
+    W4 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=5)).cuda()     # y2 = x W4^T    (rewrites y2)
+    x = torch.zeros((1, K0), dtype=torch.bfloat16, device="cuda")
+    x2 = torch.zeros((1, K0), dtype=torch.bfloat16, device="cuda")
+    y0 = torch.zeros((1, N0), dtype=torch.bfloat16, device="cuda")
+    y1 = torch.zeros((1, N1), dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")
+    y3 = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")
+    keep = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")   # y2 of entry 2, copied out before entry 4 rewrites it
+    P = capi.GgufMmvqParams
+    arr = (P * 5)()
+    arr[0] = P(M=1, N=N0, K=K0, A=x.data_ptr(), B=W0.data_ptr(), C=y0.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[1] = P(M=1, N=N1, K=N0, A=y0.data_ptr(), B=W1.data_ptr(), C=y1.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[2] = P(M=1, N=N2, K=K0, A=x2.data_ptr(), B=W2.data_ptr(), C=y2.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[3] = P(M=1, N=N2, K=N1, A=y1.data_ptr(), B=W3.data_ptr(), C=y3.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    arr[4] = P(M=1, N=N2, K=K0, A=x.data_ptr(), B=W4.data_ptr(), C=y2.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
+    need = max(256, capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, 5))
+    ws = torch.empty((need,), dtype=torch.uint8, device="cuda")
+
+    def batch():
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        capi.check(capi.lib.lsg_gguf_mmvq_batch(arr, 5, ctypes.c_void_p(ws.data_ptr()), need, st))
+
+    g = torch.Generator().manual_seed(9)
+    xs = [(torch.randn(1, K0, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(6)]
+    batch()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph):
+            batch()
+    for it in range(6):
+        x.copy_(xs[it])
+        x2.copy_(xs[(it + 1) % 6])
+        for _ in range(3):      # back-to-back replays: the next batch's first launch follows the last one directly
+            graph.replay()
+        torch.cuda.synchronize()
+        r0 = ops.gguf_mmvq(xs[it], W0, t, N0, K0)
+        r1 = ops.gguf_mmvq(r0, W1, t, N1, N0)
+        assert torch.equal(y0, r0) and torch.equal(y1, r1)
+        assert torch.equal(y3, ops.gguf_mmvq(r1, W3, t, N2, N1))
+        assert torch.equal(y2, ops.gguf_mmvq(xs[it], W4, t, N2, K0))
+    assert capi.device_status() == 0
+
+
 @pytest.mark.parametrize("name,M,K,Ns", [
     ("Q4_K", 1, 4096, (4096, 1024, 1024)),       # q, k, v
     ("Q4_K", 1, 4096, (14336, 14336)),           # gate, up
