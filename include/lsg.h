@@ -158,14 +158,24 @@ LSG_API int lsg_gguf_mmvq_q8_1(const lsg_gguf_mmvq_params* p, const void* xq, vo
 #define LSG_NOALLOC_MAX_Q8_1_BYTES 147456
 LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
 
-/* n projections in one call, executed in order, each as lsg_gguf_mmvq would.
- * Consecutive entries with the same A, M, K, type and out_dtype (q, k and v of one
- * hidden state; gate and up of one MLP input) run as ONE launch, up to four matrices
- * per launch, their CTAs divided in proportion to the rows: one prologue, one
- * activation image and one pipeline fill instead of several.  Results are the bits of
- * the separate calls.  Workspace: lsg_gguf_mmvq_batch_workspace_bytes(p, n) (the
- * largest Q8_1 image of the batch).  The reference launches one kernel per projection
- * (launch_gguf_mmvq, csrc/sm120/gemm/gguf/gguf_mmvq.cu:130-152). */
+/* n projections in one call, with the results of executing them in order, each as
+ * lsg_gguf_mmvq would.  Consecutive entries with the same M, K, type and out_dtype run as ONE
+ * launch, up to six matrices per launch, their CTAs divided in proportion to the rows (one
+ * prologue, one activation image per CTA and one pipeline fill instead of several): entries
+ * with the same A (q, k and v of one hidden state; gate and up of one MLP input) always, and,
+ * when the activations are quantized inside the mat-vec (M * K <= 16384), entries with
+ * activations of their own as long as none of them reads or writes a buffer another entry of
+ * the launch writes (byte ranges of A and C are compared).  A launch that shares no buffer
+ * with the earlier entries of the call does not wait for the launch in front of it: its CTAs
+ * start on the SMs that launch has left while its last CTAs still stream (only the first
+ * launch of the call waits for the work in front of the call, and it releases the next launch
+ * after that wait; the others wait before they exit, so the call still completes in stream
+ * order).  An entry that reads an earlier entry's result, or writes a buffer an earlier entry
+ * uses, waits as before.  LSG_MMVQ_BATCH_OVERLAP=0 in the environment switches both off.
+ * Results are the bits of the separate calls.  Workspace:
+ * lsg_gguf_mmvq_batch_workspace_bytes(p, n) (the largest Q8_1 image of the batch).  The
+ * reference launches one kernel per projection (launch_gguf_mmvq,
+ * csrc/sm120/gemm/gguf/gguf_mmvq.cu:130-152). */
 LSG_API size_t lsg_gguf_mmvq_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
 LSG_API int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
                         size_t workspace_bytes, void* stream);
@@ -188,9 +198,12 @@ LSG_API int lsg_gguf_mmvq_host(const lsg_gguf_mmvq_params* p, void* workspace, s
  * Entries naming the same A, M and K as an earlier entry reuse its Q8_1 image (the q, k
  * and v projections of one hidden state quantize it once), and consecutive ones share a
  * launch as in lsg_gguf_mmvq_batch.  All activations must be in place when the call is made:
- * up to eight distinct ones are quantized by a single launch up front.  (A batch in which a C
- * overlaps the A of a later entry is still executed in order, with a quantizer launch in
- * front of each group of projections.)  n <= 64.
+ * up to eight distinct ones are quantized by a single launch up front.  When, in addition,
+ * every result goes straight to its page-locked buffer (M <= 4) and no entry's buffers meet
+ * another's, entries of one shape share a launch whatever their input and the launches do not
+ * wait for each other, as in lsg_gguf_mmvq_batch: a layer of seven projections is three
+ * launches.  (A batch in which a C overlaps the A of a later entry is still executed in
+ * order, with a quantizer launch in front of each group of projections.)  n <= 64.
  * Workspace: lsg_gguf_mmvq_host_batch_workspace_bytes(p, n), 256-byte aligned. */
 LSG_API size_t lsg_gguf_mmvq_host_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
 LSG_API int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,

@@ -136,7 +136,7 @@ int mmvq_q8_1(int type, int M, int N, int K, const void* W, const void* xq, void
 // per batch of rows.  Matrix j writes C[j], [M][N[j]] row-major.
 int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* const* C, const int* N,
                      const void* xq, int out_f32, cudaStream_t stream, bool pdl, const void* A_bf16, int dep_mode = 0,
-                     const void* const* A_each = nullptr) {
+                     const void* const* A_each = nullptr, const void* const* xq_each = nullptr) {
     if (n < 1 || n > 1 + kMmvqMaxExtra) return fail(LSG_ERR_INVALID, "gguf_mmvq: 1..6 matrices per joined launch");
     if (n == 1) return mmvq_q8_1(type, M, N[0], K, W[0], xq, C[0], N[0], out_f32, stream, pdl, A_bf16, dep_mode);
     if (M == 0) return LSG_OK;
@@ -174,8 +174,10 @@ int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* 
             a.Wx[j - 1] = static_cast<const uint8_t*>(W[j]);
             a.Cx[j - 1] = static_cast<uint8_t*>(C[j]) + static_cast<size_t>(m0) * N[j] * c_elem;
             a.Nx[j - 1] = N[j];
-            if (A_each && A_each[j] && A_each[j] != A_bf16)
-                a.Ax[j - 1] = static_cast<const __nv_bfloat16*>(A_each[j]) + static_cast<size_t>(m0) * K;
+            if (A_bf16)
+                a.Ax[j - 1] = static_cast<const __nv_bfloat16*>(A_each && A_each[j] ? A_each[j] : A_bf16) + static_cast<size_t>(m0) * K;
+            else
+                a.xqx[j - 1] = static_cast<const uint8_t*>(xq_each && xq_each[j] ? xq_each[j] : xq) + static_cast<size_t>(m0) * xq_row;
         }
         a.dep_mode = (pdl && m0 == 0) ? dep_mode : 0;
         const int rc = dispatch_launch(type, a, stream, pdl && m0 == 0);
@@ -539,9 +541,30 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
             quantized_up_front = true;
         }
     }
+    // With every input quantized up front, every result written straight to its page-locked
+    // buffer and no buffer shared between entries, the projections do not depend on each other:
+    // those of one shape share a launch whatever their input, and a launch does not wait for
+    // the one in front of it (the first waits for the quantizer and only then releases the next).
+    bool apart = quantized_up_front && batch_overlap_enabled();
+    for (int i = 0; i < n && apart; ++i) {
+        if (p[i].M == 0 || p[i].N == 0) continue;
+        if (p[i].M > 4 || !mapped_alias(p[i].C)) apart = false;
+        for (int k = 0; k < i && apart; ++k) {
+            if (p[k].M == 0 || p[k].N == 0) continue;
+            if (c_span(p[i]).meets(c_span(p[k])) || c_span(p[i]).meets(a_span(p[k])) || a_span(p[i]).meets(c_span(p[k])))
+                apart = false;
+        }
+    }
+    bool launched = false;
     for (int i = 0; i < n;) {
         const lsg_gguf_mmvq_params& e = p[i];
-        const int run = joinable_run(p, i, n);
+        int run = joinable_run(p, i, n);
+        if (apart && e.M > 0 && e.N > 0) {
+            run = 1;
+            while (i + run < n && run < 1 + kMmvqMaxExtra && p[i + run].M == e.M && p[i + run].K == e.K &&
+                   p[i + run].type == e.type && p[i + run].out_dtype == e.out_dtype && p[i + run].N >= 1)
+                ++run;
+        }
         if (e.M == 0 || e.N == 0) {
             i += run;
             continue;
@@ -562,16 +585,20 @@ extern "C" int lsg_gguf_mmvq_host_batch(const lsg_gguf_mmvq_params* p, int n, vo
         // The projections of this input that can share a launch; each writes either the
         // host buffer's alias or its rows of the workspace.
         const void* W[1 + kMmvqMaxExtra];
+        const void* XQ[1 + kMmvqMaxExtra];
         void* C[1 + kMmvqMaxExtra];
         void* c_map[1 + kMmvqMaxExtra];
         int N[1 + kMmvqMaxExtra];
         for (int j = 0; j < run; ++j) {
             c_map[j] = mapped_alias(p[i + j].C);
             W[j] = p[i + j].B;
+            XQ[j] = base + slot[i + j].q_off;
             N[j] = p[i + j].N;
             C[j] = (c_map[j] && e.M <= 4) ? c_map[j] : static_cast<void*>(base + slot[i + j].c_off);
         }
-        rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, q_dev, out_f32, s, true, nullptr);
+        const int dep_mode = apart ? (launched ? 2 : 1) : 0;
+        launched = true;
+        rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, q_dev, out_f32, s, true, nullptr, dep_mode, nullptr, XQ);
         if (rc != LSG_OK) return rc;
         for (int j = 0; j < run; ++j) {
             if (C[j] == c_map[j]) continue;

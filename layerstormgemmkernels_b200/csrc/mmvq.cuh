@@ -77,7 +77,8 @@ struct MmvqArgs {
     // For joined launches rows_q / rows_r describe matrix 0 over its cta0x[0] CTAs.
     int n_extra;
     const uint8_t* Wx[kMmvqMaxExtra];
-    const __nv_bfloat16* Ax[kMmvqMaxExtra];   // bf16 activations of matrix j (null: those of matrix 0)
+    const __nv_bfloat16* Ax[kMmvqMaxExtra];   // bf16 activations of matrix j (set when A is)
+    const uint8_t* xqx[kMmvqMaxExtra];        // Q8_1 blocks of matrix j (set when A is null)
     void* Cx[kMmvqMaxExtra];
     int Nx[kMmvqMaxExtra];
     int cta0x[kMmvqMaxExtra];
@@ -391,21 +392,25 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     int bx = static_cast<int>(blockIdx.x);
     const uint8_t* Wm = a.W;
     const __nv_bfloat16* Am = a.A;
+    const uint8_t* xqm = a.xq;
     void* Cm = a.C;
     int Nm = a.N, ldcm = a.ldc, rows_q = a.rows_q, rows_r = a.rows_r;
     if (a.n_extra > 0) {
         const int b = static_cast<int>(blockIdx.x);
+        int jm = -1;
 #pragma unroll
         for (int j = 0; j < kMmvqMaxExtra; ++j)
-            if (j < a.n_extra && b >= a.cta0x[j]) {
-                Wm = a.Wx[j];
-                if (a.Ax[j]) Am = a.Ax[j];
-                Cm = a.Cx[j];
-                Nm = ldcm = a.Nx[j];
-                rows_q = a.rows_qx[j];
-                rows_r = a.rows_rx[j];
-                bx = b - a.cta0x[j];
-            }
+            if (j < a.n_extra && b >= a.cta0x[j]) jm = j;
+        if (jm >= 0) {
+            Wm = a.Wx[jm];
+            Am = a.Ax[jm];
+            xqm = a.xqx[jm];
+            Cm = a.Cx[jm];
+            Nm = ldcm = a.Nx[jm];
+            rows_q = a.rows_qx[jm];
+            rows_r = a.rows_rx[jm];
+            bx = b - a.cta0x[jm];
+        }
     }
     const int row_begin = bx * rows_q + min(bx, rows_r);
     const int row_end = row_begin + rows_q + (bx < rows_r ? 1 : 0);
@@ -505,7 +510,7 @@ __global__ void __launch_bounds__(512, 1) mmvq_kernel(const MmvqArgs a) {
     }
     if (tid == 0) LSG_TRACE(3);
     if (a.A) build_x_image_bf16<T>(x_img, Am, a.M, a.K, tid, n_cons);
-    else build_x_image<T>(x_img, a.xq, a.M, a.K, tid, n_cons);
+    else build_x_image<T>(x_img, xqm, a.M, a.K, tid, n_cons);
     asm volatile("bar.sync 1, %0;" ::"r"(n_cons) : "memory");
     if (tid == 0) LSG_TRACE(4);
 

@@ -230,7 +230,8 @@ def test_mmvq_batch_distinct_inputs_share_a_launch(ops, name, M):
     import ctypes
     t = T[name]
     K, KD = 1024, 3584
-    shapes = [("x", 1024, K), ("x", 256, K), ("x", 256, K), ("att", 1024, K), ("h", 3584, K), ("h", 3584, K), ("act", 1024, KD)]
+    # ("x" comes back after "att": the launch's matrices name their inputs one by one)
+    shapes = [("x", 1024, K), ("x", 256, K), ("att", 1024, K), ("x", 256, K), ("h", 3584, K), ("h", 3584, K), ("act", 1024, KD)]
     g = torch.Generator().manual_seed(31 + M)
     xin = {}
     for grp, _, k in shapes:
