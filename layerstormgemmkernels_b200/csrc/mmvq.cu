@@ -361,16 +361,26 @@ extern "C" int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* w
     // Launches that neither read what an earlier entry of the batch writes nor write what an
     // earlier entry reads or writes need not wait for the launch in front of them: only the
     // first launch waits for the work in front of the batch (and releases the next launch only
-    // after that wait).  Needs the first launch to be a mat-vec with the quantizer inside.
+    // after that wait).  Needs the first launch to be a mat-vec with the quantizer inside and
+    // at least one later launch of that kind.
+    const bool overlap = batch_overlap_enabled();
     bool relaxed = false;
-    {
-        int first = 0;
-        while (first < n && (p[first].M == 0 || p[first].N == 0)) ++first;
-        relaxed = first < n && fused_quant_ok(p[first].M, p[first].K, p[first].A) && batch_overlap_enabled();
+    if (overlap) {
+        bool first = true, first_fused = false;
+        for (int i = 0; i < n;) {
+            const int run = joinable_run(p, i, n, true);
+            if (p[i].M > 0 && p[i].N > 0) {
+                const bool fused = fused_quant_ok(p[i].M, p[i].K, p[i].A);
+                if (first) first_fused = fused;
+                else if (first_fused && fused && independent_of_earlier(p, i, run)) relaxed = true;
+                first = false;
+            }
+            i += run;
+        }
     }
     bool launched = false;
     for (int i = 0; i < n;) {
-        const int run = joinable_run(p, i, n, batch_overlap_enabled());
+        const int run = joinable_run(p, i, n, overlap);
         const lsg_gguf_mmvq_params& e = p[i];
         if (e.M == 0 || e.N == 0) {
             i += run;
@@ -378,11 +388,8 @@ extern "C" int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* w
         }
         int dep_mode = 0;
         if (relaxed) {
-            if (!launched) {
-                dep_mode = 1;
-            } else if (fused_quant_ok(e.M, e.K, e.A) && independent_of_earlier(p, i, run)) {
-                dep_mode = 2;
-            }
+            if (!launched) dep_mode = 1;
+            else if (fused_quant_ok(e.M, e.K, e.A) && independent_of_earlier(p, i, run)) dep_mode = 2;
         }
         launched = true;
         const void* W[1 + kMmvqMaxExtra];
