@@ -222,7 +222,7 @@ def workload_config(args):
                       "lsg_gguf_mmvq_batch call over the seven projections, which have four distinct inputs and "
                       "no dependency on each other inside the call: the library runs the six K = 4096 projections "
                       "as one launch and down as a second one that does not wait for the first; activations "
-                      "quantized inside the launches (above 16384 values: a quantizer launch per input, one "
+                      "quantized inside the launches (above 32768 values: a quantizer launch per input, one "
                       "launch per input, each waiting for the one before)",
             "parallelism": "replicas only"}
 
@@ -258,10 +258,10 @@ class DecodeLayerBench:
         self.ws = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
         # launches of one lsg_gguf_mmvq_batch call, as the library forms them: consecutive
         # projections of one K share a launch (up to six) when they read the same activations or,
-        # with the quantizer inside the kernel (M * K <= 16384), independent ones
+        # with the quantizer inside the kernel (M * K <= 32768), independent ones
         joined = []
         for name, _, K in layer:
-            fused = M * K <= 16384
+            fused = M * K <= 32768
             if (joined and joined[-1][1] == K and joined[-1][2] < 6
                     and (joined[-1][0] == group[name] or (fused and joined[-1][3]))):
                 joined[-1][2] += 1

@@ -163,7 +163,7 @@ LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
  * launch, up to six matrices per launch, their CTAs divided in proportion to the rows (one
  * prologue, one activation image per CTA and one pipeline fill instead of several): entries
  * with the same A (q, k and v of one hidden state; gate and up of one MLP input) always, and,
- * when the activations are quantized inside the mat-vec (M * K <= 16384), entries with
+ * when the activations are quantized inside the mat-vec (M * K <= 32768), entries with
  * activations of their own as long as none of them reads or writes a buffer another entry of
  * the launch writes (byte ranges of A and C are compared).  A launch that shares no buffer
  * with the earlier entries of the call does not wait for the launch in front of it: its CTAs

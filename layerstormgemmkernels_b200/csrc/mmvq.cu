@@ -189,7 +189,7 @@ int mmvq_q8_1_joined(int type, int M, int K, int n, const void* const* W, void* 
 bool fused_quant_ok(int M, int K, const void* A) {
     static const long long limit = [] {
         const char* e = getenv("LSG_MMVQ_FUSED_QUANT_MAX");
-        return e ? atoll(e) : 16384LL;
+        return e ? atoll(e) : 32768LL;
     }();
     return A && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && static_cast<long long>(M) * K <= limit;
 }
