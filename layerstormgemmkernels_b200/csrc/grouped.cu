@@ -75,6 +75,37 @@ int check_common(const lsg_gguf_grouped_gemm_params* p) {
     return LSG_OK;
 }
 
+// The grouped mat-vec over a device-built segment list: activations quantized into the
+// workspace (skipped when `xq_ready`: the call in front, with the same A_base, K and workspace,
+// left them there), segments from the offsets, one launch.
+int grouped_matvec_tail(const lsg_gguf_grouped_gemm_params* p, int T, uint8_t* base, const WsLayout& w,
+                        cudaStream_t s, bool xq_ready) {
+    int rc = LSG_OK;
+    if (!xq_ready) {
+        rc = quantize_q8_1(p->A_base, base, T, p->K, s, true);
+        if (rc != LSG_OK) return rc;
+    }
+    int* seg = reinterpret_cast<int*>(base + w.seg_off);
+    const MmvqTune tn = mmvq_tuning();
+    const int max_rows = grouped_max_rows(p->type, p->K, tn);
+    rc = build_segment_list(static_cast<const int32_t*>(p->expert_offsets), p->B_ptrs, p->num_experts,
+                            max_rows, w.max_segments, seg, s, T);
+    if (rc != LSG_OK) return rc;
+    GroupedArgs a = {};
+    a.xq = base;
+    a.B_ptrs = p->B_ptrs;
+    a.seg = seg;
+    a.D = p->D_base;
+    a.status = device_status_word();
+    a.N = p->N;
+    a.K = p->K;
+    a.out_f32 = p->out_dtype == LSG_DTYPE_F32;
+    // upper bound of live segments: each expert contributes ceil(M_e / max_rows) <= 1 + M_e / max_rows
+    long long bound = static_cast<long long>(p->num_experts < T ? p->num_experts : T) + T / max_rows;
+    if (bound > w.max_segments) bound = w.max_segments;
+    return grouped_dispatch(p->type, a, tn, static_cast<int>(bound), s);
+}
+
 // Device-routed integer path.
 int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, int force,
                 cudaStream_t s) {
@@ -125,31 +156,7 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
                            p->out_dtype == LSG_DTYPE_F32, tile_expert, tile_mstart, t_max,
                            base + w.total, ws_bytes - w.total, s);
     }
-    rc = quantize_q8_1(p->A_base, base, T, p->K, s, true);
-    if (rc != LSG_OK) return rc;
-    int* active = reinterpret_cast<int*>(base + w.active_off);
-    int* seg = reinterpret_cast<int*>(base + w.seg_off);
-    rc = build_active_expert_list(static_cast<const int32_t*>(p->expert_offsets), p->num_experts, w.cap,
-                                  active, s);
-    if (rc != LSG_OK) return rc;
-    const MmvqTune tn = mmvq_tuning();
-    const int max_rows = grouped_max_rows(p->type, p->K, tn);
-    rc = build_segment_list(static_cast<const int32_t*>(p->expert_offsets), p->B_ptrs, p->num_experts,
-                            max_rows, w.max_segments, seg, s, T);
-    if (rc != LSG_OK) return rc;
-    GroupedArgs a = {};
-    a.xq = base;
-    a.B_ptrs = p->B_ptrs;
-    a.seg = seg;
-    a.D = p->D_base;
-    a.status = device_status_word();
-    a.N = p->N;
-    a.K = p->K;
-    a.out_f32 = p->out_dtype == LSG_DTYPE_F32;
-    // upper bound of live segments: each expert contributes ceil(M_e / max_rows) <= 1 + M_e / max_rows
-    long long bound = static_cast<long long>(p->num_experts < T ? p->num_experts : T) + T / max_rows;
-    if (bound > w.max_segments) bound = w.max_segments;
-    return grouped_dispatch(p->type, a, tn, static_cast<int>(bound), s);
+    return grouped_matvec_tail(p, T, base, w, s, false);
 }
 
 // Host per-expert loop: the golden of both strategies and the Dequant implementation.
@@ -197,6 +204,25 @@ int grouped_hostloop(const lsg_gguf_grouped_gemm_params* p, void* ws, size_t ws_
 }
 
 }  // namespace
+
+// The mat-vec route of lsg_gguf_grouped_gemm for a caller inside the library that runs several
+// projections of the same rows through the same workspace (gate and up of an expert block):
+// `xq_ready` skips the activation quantizer of the second one.
+int grouped_gemm_matvec(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, cudaStream_t s,
+                        bool xq_ready) {
+    int rc = check_common(p);
+    if (rc != LSG_OK) return rc;
+    if (p->num_experts <= 0 || T <= 0) return LSG_OK;
+    if (p->K % 32 != 0 || p->K % gguf_block_values(p->type) != 0)
+        return fail(LSG_ERR_INVALID, "GGUF grouped int: K must be divisible by %d", gguf_block_values(p->type));
+    if (!ws) return fail(LSG_ERR_WORKSPACE, "GGUF grouped int: workspace required");
+    if (!p->A_base || !p->D_base || !p->expert_offsets || !p->B_ptrs)
+        return fail(LSG_ERR_INVALID, "GGUF grouped GEMM: null A/D/expert_offsets/B_ptrs");
+    const WsLayout w = ws_layout(T, p->K, p->num_experts);
+    if (ws_bytes < w.total)
+        return fail(LSG_ERR_WORKSPACE, "GGUF grouped int: workspace too small (have %zu, need %zu)", ws_bytes, w.total);
+    return grouped_matvec_tail(p, T, static_cast<uint8_t*>(ws), w, s, xq_ready);
+}
 
 }  // namespace lsg
 

@@ -63,6 +63,8 @@ int nvfp4_mma(const void* A, long long a_rows, const void* B, long long b_rows, 
 bool tc_fused_available(int type);
 bool tc_fused_forced();   // weight path 2: every call takes the fused kernel
 size_t tc_fused_dense_scratch_bytes(int M, int N, int K);
+int grouped_gemm_matvec(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, cudaStream_t s,
+                        bool xq_ready);
 int tc_fused_grouped_tile_m(long long T, int E);
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K);
 int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,

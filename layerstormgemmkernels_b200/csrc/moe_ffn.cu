@@ -167,10 +167,15 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
     g.type = p->type; g.strategy = LSG_GGUF_STRATEGY_INT; g.num_experts = E;
     g.N = I; g.K = H; g.A_base = rows; g.expert_offsets = offs; g.out_dtype = LSG_DTYPE_BF16;
     g.D_base = base + l.g_off; g.B_ptrs = p->gate_ptrs;
-    int rc = lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
+    // few rows per expert: both projections take the grouped mat-vec, and up reads the Q8_1
+    // blocks gate's quantizer left in the workspace
+    const bool matvec = T / E <= 8;
+    int rc = matvec ? grouped_gemm_matvec(&g, T, base + l.grouped_off, l.grouped_bytes, s, false)
+                    : lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
     if (rc != LSG_OK) return rc;
     g.D_base = base + l.u_off; g.B_ptrs = p->up_ptrs;
-    rc = lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
+    rc = matvec ? grouped_gemm_matvec(&g, T, base + l.grouped_off, l.grouped_bytes, s, true)
+                : lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);
     if (rc != LSG_OK) return rc;
     const long long n_vec = static_cast<long long>(T) * I / 8;
     LSG_CUDA_TRY(launch_kernel(silu_mul_bf16_kernel, dim3(static_cast<unsigned>((n_vec + 255) / 256)), dim3(256), 0, s,
