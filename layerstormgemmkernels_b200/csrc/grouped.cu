@@ -76,8 +76,10 @@ int check_common(const lsg_gguf_grouped_gemm_params* p) {
 }
 
 // The grouped mat-vec over a device-built segment list: activations quantized into the
-// workspace (skipped when `xq_ready`: the call in front, with the same A_base, K and workspace,
-// left them there), segments from the offsets, one launch.
+// workspace and segments built from the offsets (both skipped when `xq_ready`: the call in
+// front, with the same A_base, K, offsets and workspace, left them there, and it skipped the
+// same experts - the caller guarantees that an expert has a weight here when it had one there),
+// then one launch.
 int grouped_matvec_tail(const lsg_gguf_grouped_gemm_params* p, int T, uint8_t* base, const WsLayout& w,
                         cudaStream_t s, bool xq_ready) {
     int rc = LSG_OK;
@@ -88,9 +90,11 @@ int grouped_matvec_tail(const lsg_gguf_grouped_gemm_params* p, int T, uint8_t* b
     int* seg = reinterpret_cast<int*>(base + w.seg_off);
     const MmvqTune tn = mmvq_tuning();
     const int max_rows = grouped_max_rows(p->type, p->K, tn);
-    rc = build_segment_list(static_cast<const int32_t*>(p->expert_offsets), p->B_ptrs, p->num_experts,
-                            max_rows, w.max_segments, seg, s, T);
-    if (rc != LSG_OK) return rc;
+    if (!xq_ready) {
+        rc = build_segment_list(static_cast<const int32_t*>(p->expert_offsets), p->B_ptrs, p->num_experts,
+                                max_rows, w.max_segments, seg, s, T);
+        if (rc != LSG_OK) return rc;
+    }
     GroupedArgs a = {};
     a.xq = base;
     a.B_ptrs = p->B_ptrs;
@@ -207,7 +211,8 @@ int grouped_hostloop(const lsg_gguf_grouped_gemm_params* p, void* ws, size_t ws_
 
 // The mat-vec route of lsg_gguf_grouped_gemm for a caller inside the library that runs several
 // projections of the same rows through the same workspace (gate and up of an expert block):
-// `xq_ready` skips the activation quantizer of the second one.
+// `xq_ready` skips the activation quantizer and the segment list of the second one (every expert
+// with rows has all its weights there: lsg_gguf_moe_ffn's contract).
 int grouped_gemm_matvec(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, cudaStream_t s,
                         bool xq_ready) {
     int rc = check_common(p);

@@ -168,7 +168,7 @@ extern "C" int lsg_gguf_moe_ffn(const lsg_gguf_moe_ffn_params* p, int total_toke
     g.N = I; g.K = H; g.A_base = rows; g.expert_offsets = offs; g.out_dtype = LSG_DTYPE_BF16;
     g.D_base = base + l.g_off; g.B_ptrs = p->gate_ptrs;
     // few rows per expert: both projections take the grouped mat-vec, and up reads the Q8_1
-    // blocks gate's quantizer left in the workspace
+    // blocks and the segment list gate's call left in the workspace
     const bool matvec = T / E <= 8;
     int rc = matvec ? grouped_gemm_matvec(&g, T, base + l.grouped_off, l.grouped_bytes, s, false)
                     : lsg_gguf_grouped_gemm(&g, T, base + l.grouped_off, l.grouped_bytes, LSG_GGUF_FORCE_AUTO, stream);

@@ -200,6 +200,69 @@ moe_place_kernel(const int32_t* __restrict__ idx, int P, int E, const int32_t* _
     }
 }
 
+// The three steps above in one CTA, for P <= 1024 pairs (decode-sized batches, where three
+// dependent launches cost more than the work): thread i owns pair i; per-warp histograms in
+// shared memory ([warps][E], the caller checks that they fit), their sum over the warps per
+// expert, the exclusive scan over the experts, then each pair's row.
+__global__ void __launch_bounds__(1024)
+moe_permutation_small_kernel(const int32_t* __restrict__ idx, int P, int E, int32_t* __restrict__ offsets,
+                             int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    extern __shared__ int whist[];  // [n_warps][E]
+    __shared__ int totals[1024];
+    __shared__ int wsum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_warps = (P + 31) >> 5;
+    for (int j = tid; j < n_warps * E; j += 1024) whist[j] = 0;
+    __syncthreads();
+    int e = tid < P ? idx[tid] : -1;
+    if (e >= E) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) whist[warp * E + e] = __popc(same);
+    __syncthreads();
+    // thread x: total of expert x, and the warps' counts turned into exclusive prefixes
+    int total = 0;
+    if (tid < E) {
+        for (int w = 0; w < n_warps; ++w) {
+            const int v = whist[w * E + tid];
+            whist[w * E + tid] = total;
+            total += v;
+        }
+    }
+    int incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = wsum[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        wsum[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const int before = warp > 0 ? wsum[warp - 1] : 0;
+    if (tid < E) {
+        totals[tid] = before + incl - total;
+        offsets[tid] = before + incl - total;
+    }
+    if (tid == E - 1) offsets[E] = before + incl;
+    __syncthreads();
+    if (e >= 0) {
+        const int row = totals[e] + whist[warp * E + e] + rank;
+        perm[row] = tid;
+        inv[tid] = row;
+    }
+}
+
 // out[row, :] = hidden[perm[row] / k, :]   (bf16 rows, 16-byte vectors)
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const uint4* __restrict__ hidden, const int32_t* __restrict__ perm, int k, int rows,
@@ -394,6 +457,12 @@ extern "C" int lsg_moe_permutation(const int32_t* topk_idx, int num_tokens, int 
     if (P > 0 && (!topk_idx || !perm || !inv_perm)) return fail(LSG_ERR_INVALID, "moe_permutation: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (num_experts > 1024) return fail(LSG_ERR_INVALID, "moe_permutation: at most 1024 experts (E=%d)", num_experts);
+    if (P > 0 && P <= 1024 && static_cast<long long>((P + 31) / 32) * num_experts <= 10240) {
+        LSG_CUDA_TRY(launch_kernel(moe_permutation_small_kernel, dim3(1), dim3(1024),
+                                   static_cast<size_t>((P + 31) / 32) * num_experts * sizeof(int), s, true, topk_idx,
+                                   P, num_experts, expert_offsets, perm, inv_perm));
+        return LSG_OK;
+    }
     const int n_chunks = P > 0 ? (P + kChunk - 1) / kChunk : 1;
     LSG_CUDA_TRY(launch_kernel(moe_chunk_hist_kernel, dim3(n_chunks), dim3(kChunk), 0, s, true, topk_idx, P,
                                num_experts, counts_scratch));

@@ -29,7 +29,8 @@ def oracle_permutation(idx, E):
     return offs, perm, inv
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 128, 8), (64, 128, 8), (4096, 128, 8), (4096, 8, 2), (33, 60, 4), (5, 4, 4)])
+@pytest.mark.parametrize("T,E,k", [(1, 128, 8), (64, 128, 8), (4096, 128, 8), (4096, 8, 2), (33, 60, 4), (5, 4, 4),
+                                   (128, 128, 8), (129, 128, 8), (32, 1024, 8)])   # 1024 pairs: last one-CTA case
 def test_route_permute_combine(ops, T, E, k):
     g = torch.Generator().manual_seed(T + E)
     logits = torch.randn(T, E, generator=g)
