@@ -96,6 +96,19 @@ __device__ __forceinline__ float q8_round_f(float x, float d, float rcp) {
     return k;
 }
 
+// Two packed bf16 values: bf16( silu(g) * u ), silu(g) = g / (1 + exp(-g)) in fp32.
+__device__ __forceinline__ uint32_t silu_mul_bf16x2(uint32_t gw, uint32_t uw) {
+    float a[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float gv = __uint_as_float(h ? (gw & 0xFFFF0000u) : (gw << 16));
+        const float uv = __uint_as_float(h ? (uw & 0xFFFF0000u) : (uw << 16));
+        a[h] = (gv / (1.0f + expf(-gv))) * uv;
+    }
+    const __nv_bfloat162 r = __floats2bfloat162_rn(a[0], a[1]);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // max(a, b) that is NaN when either operand is.
 __device__ __forceinline__ float max_nan(float a, float b) {
     float d;

@@ -76,12 +76,12 @@ int check_common(const lsg_gguf_grouped_gemm_params* p) {
 }
 
 // The grouped mat-vec over a device-built segment list: activations quantized into the
-// workspace and segments built from the offsets (both skipped when `xq_ready`: the call in
-// front, with the same A_base, K, offsets and workspace, left them there, and it skipped the
-// same experts - the caller guarantees that an expert has a weight here when it had one there),
-// then one launch.
+// workspace (skipped when `xq_ready`: the caller, or the call in front with the same A_base, K
+// and workspace, left them there) and segments built from the offsets (skipped when
+// `seg_ready`: the call in front had the same offsets and K and skipped the same experts - the
+// caller guarantees that an expert has a weight here when it had one there), then one launch.
 int grouped_matvec_tail(const lsg_gguf_grouped_gemm_params* p, int T, uint8_t* base, const WsLayout& w,
-                        cudaStream_t s, bool xq_ready) {
+                        cudaStream_t s, bool xq_ready, bool seg_ready) {
     int rc = LSG_OK;
     if (!xq_ready) {
         rc = quantize_q8_1(p->A_base, base, T, p->K, s, true);
@@ -90,7 +90,7 @@ int grouped_matvec_tail(const lsg_gguf_grouped_gemm_params* p, int T, uint8_t* b
     int* seg = reinterpret_cast<int*>(base + w.seg_off);
     const MmvqTune tn = mmvq_tuning();
     const int max_rows = grouped_max_rows(p->type, p->K, tn);
-    if (!xq_ready) {
+    if (!seg_ready) {
         rc = build_segment_list(static_cast<const int32_t*>(p->expert_offsets), p->B_ptrs, p->num_experts,
                                 max_rows, w.max_segments, seg, s, T);
         if (rc != LSG_OK) return rc;
@@ -160,7 +160,7 @@ int grouped_int(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t w
                            p->out_dtype == LSG_DTYPE_F32, tile_expert, tile_mstart, t_max,
                            base + w.total, ws_bytes - w.total, s);
     }
-    return grouped_matvec_tail(p, T, base, w, s, false);
+    return grouped_matvec_tail(p, T, base, w, s, false, false);
 }
 
 // Host per-expert loop: the golden of both strategies and the Dequant implementation.
@@ -211,22 +211,23 @@ int grouped_hostloop(const lsg_gguf_grouped_gemm_params* p, void* ws, size_t ws_
 
 // The mat-vec route of lsg_gguf_grouped_gemm for a caller inside the library that runs several
 // projections of the same rows through the same workspace (gate and up of an expert block):
-// `xq_ready` skips the activation quantizer and the segment list of the second one (every expert
-// with rows has all its weights there: lsg_gguf_moe_ffn's contract).
+// `xq_ready` skips the activation quantizer (the Q8_1 blocks of all T rows are at the start of
+// the workspace already) and `seg_ready` the segment list (every expert with rows has all its
+// weights: lsg_gguf_moe_ffn's contract).  A_base may be null with `xq_ready`.
 int grouped_gemm_matvec(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, cudaStream_t s,
-                        bool xq_ready) {
+                        bool xq_ready, bool seg_ready) {
     int rc = check_common(p);
     if (rc != LSG_OK) return rc;
     if (p->num_experts <= 0 || T <= 0) return LSG_OK;
     if (p->K % 32 != 0 || p->K % gguf_block_values(p->type) != 0)
         return fail(LSG_ERR_INVALID, "GGUF grouped int: K must be divisible by %d", gguf_block_values(p->type));
     if (!ws) return fail(LSG_ERR_WORKSPACE, "GGUF grouped int: workspace required");
-    if (!p->A_base || !p->D_base || !p->expert_offsets || !p->B_ptrs)
+    if ((!p->A_base && !xq_ready) || !p->D_base || !p->expert_offsets || !p->B_ptrs)
         return fail(LSG_ERR_INVALID, "GGUF grouped GEMM: null A/D/expert_offsets/B_ptrs");
     const WsLayout w = ws_layout(T, p->K, p->num_experts);
     if (ws_bytes < w.total)
         return fail(LSG_ERR_WORKSPACE, "GGUF grouped int: workspace too small (have %zu, need %zu)", ws_bytes, w.total);
-    return grouped_matvec_tail(p, T, static_cast<uint8_t*>(ws), w, s, xq_ready);
+    return grouped_matvec_tail(p, T, static_cast<uint8_t*>(ws), w, s, xq_ready, seg_ready);
 }
 
 }  // namespace lsg

@@ -8,6 +8,11 @@ namespace lsg {
 
 int quantize_q8_1(const void* x_bf16, void* q8_1_out, int M, int K, cudaStream_t stream,
                   bool pdl);
+// Row r of the output = row map[r] / top_k of x (gather folded in); bf16(silu(g) * u) quantized on the way.
+int quantize_q8_1_gather(const void* x_bf16, const int32_t* map, int top_k, void* q8_1_out, int rows, int K,
+                          cudaStream_t stream, bool pdl);
+int quantize_q8_1_silu_mul(const void* g_bf16, const void* u_bf16, void* q8_1_out, int rows, int K, cudaStream_t stream,
+                           bool pdl);
 // Up to eight tensors quantized by one launch (same bytes as quantize_q8_1 on each).
 int quantize_q8_1_batch(int n, const void* const* x_bf16, void* const* q8_1_out, const int* M, const int* K,
                         cudaStream_t stream, bool pdl);
@@ -64,7 +69,7 @@ bool tc_fused_available(int type);
 bool tc_fused_forced();   // weight path 2: every call takes the fused kernel
 size_t tc_fused_dense_scratch_bytes(int M, int N, int K);
 int grouped_gemm_matvec(const lsg_gguf_grouped_gemm_params* p, int T, void* ws, size_t ws_bytes, cudaStream_t s,
-                        bool xq_ready);
+                        bool xq_ready, bool seg_ready);
 int tc_fused_grouped_tile_m(long long T, int E);
 size_t tc_fused_grouped_scratch_bytes(long long T, int E, int N, int K);
 int tc_fused_dense(int type, int M, int N, int K, const void* A_bf16, const void* W, void* C, int ldc,

@@ -23,6 +23,47 @@ constexpr int kQ8BatchMax = 8;
 // levels are lane exchanges (lane+2, lane+1) and the last three are in-register.
 // U vectors per thread, kQuantThreads apart (so that a warp's loads stay contiguous): all U loads
 // are in flight before the first result is needed.  Large tensors take U = 4.
+// One lane's share of a block: eight values (the 16 bytes `raw`) of task `tk` (block tk / 4, part
+// tk % 4).  All four lanes of a block call this together; lanes that are not `live` take part
+// in the exchanges and store nothing.
+__device__ __forceinline__ void q8_1_emit(const uint4 raw, bool live, long long tk, uint8_t* __restrict__ y) {
+    float v[8];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    // butterfly-ordered sum
+    float s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = v[i] + __shfl_xor_sync(0xffffffffu, v[i], 2);   // (i, i+16)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i] = s[i] + __shfl_xor_sync(0xffffffffu, s[i], 1);   // (i, i+8)
+    const float c0 = s[0] + s[4], c1 = s[1] + s[5], c2 = s[2] + s[6], c3 = s[3] + s[7];  // (i, i+4)
+    const float sum = (c0 + c2) + (c1 + c3);                                             // (i, i+2), (i, i+1)
+    if (!live) return;
+
+    const float d = amax / 127.0f;
+    const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
+    uint32_t w0, w1;
+    q8_round8(v, d, rcp, w0, w1);
+    const long long blk = tk >> 2;
+    const int part = static_cast<int>(tk & 3);
+    uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
+    out[1 + 2 * part] = w0;
+    out[2 + 2 * part] = w1;
+    if (part == 0) {
+        const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
+        out[0] = *reinterpret_cast<const uint32_t*>(&ds);
+    }
+}
+
 template <int U>
 __device__ __forceinline__ void quantize_q8_1_body(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ y,
                                                    long long n_blocks, long long cta) {
@@ -36,44 +77,35 @@ __device__ __forceinline__ void quantize_q8_1_body(const __nv_bfloat16* __restri
         raw[u] = __ldg(reinterpret_cast<const uint4*>(x) + (live[u] ? task : 0));
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const long long tk = live[u] ? task0 + u * kQuantThreads : 0;
-        float v[8];
-        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[2 * i] = __uint_as_float(w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-        float amax = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        // butterfly-ordered sum
-        float s[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s[i] = v[i] + __shfl_xor_sync(0xffffffffu, v[i], 2);   // (i, i+16)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s[i] = s[i] + __shfl_xor_sync(0xffffffffu, s[i], 1);   // (i, i+8)
-        const float c0 = s[0] + s[4], c1 = s[1] + s[5], c2 = s[2] + s[6], c3 = s[3] + s[7];  // (i, i+4)
-        const float sum = (c0 + c2) + (c1 + c3);                                             // (i, i+2), (i, i+1)
-        if (!live[u]) continue;
+    for (int u = 0; u < U; ++u) q8_1_emit(raw[u], live[u], live[u] ? task0 + u * kQuantThreads : 0, y);
+}
 
-        const float d = amax / 127.0f;
-        const float rcp = (amax == 0.0f) ? 0.0f : 1.0f / d;
-        uint32_t w0, w1;
-        q8_round8(v, d, rcp, w0, w1);
-        const long long blk = tk >> 2;
-        const int part = static_cast<int>(tk & 3);
-        uint32_t* out = reinterpret_cast<uint32_t*>(y + blk * kQ8_1Bytes);
-        out[1 + 2 * part] = w0;
-        out[2 + 2 * part] = w1;
-        if (part == 0) {
-            const __half2 ds = __halves2half2(__float2half(d), __float2half(sum));
-            out[0] = *reinterpret_cast<const uint32_t*>(&ds);
-        }
+// Rows taken through a row map (row r of the output is row map[r] / top_k of x: the gather of
+// an MoE layer folded into the quantizer), or formed on the way as bf16(silu(g) * u) from two
+// tensors (the activation of an expert block folded into the quantizer of its down projection).
+// Same bytes as the gather / activation kernel followed by the plain quantizer.
+template <bool SILU>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_q8_1_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x2,
+                          const int32_t* __restrict__ map, int top_k, uint8_t* __restrict__ y, int rows, int K) {
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    const int vpr = K >> 3;                                  // 16-byte vectors per row
+    const long long task = static_cast<long long>(blockIdx.x) * kQuantThreads + threadIdx.x;
+    const bool live = task < static_cast<long long>(rows) * vpr;
+    const long long tk = live ? task : 0;
+    const int row = static_cast<int>(tk / vpr), c = static_cast<int>(tk - static_cast<long long>(row) * vpr);
+    const int src = map ? map[row] / top_k : row;
+    uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(src) * K) + c);
+    if (SILU) {
+        const uint4 ur = __ldg(reinterpret_cast<const uint4*>(x2 + static_cast<size_t>(src) * K) + c);
+        const uint32_t gw[4] = {raw.x, raw.y, raw.z, raw.w}, uw[4] = {ur.x, ur.y, ur.z, ur.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = silu_mul_bf16x2(gw[j], uw[j]);
+        raw = make_uint4(o[0], o[1], o[2], o[3]);
     }
+    q8_1_emit(raw, live, tk, y);
 }
 
 template <int U>
@@ -181,6 +213,36 @@ int quantize_q8_1_batch(int n, const void* const* x_bf16, void* const* q8_1_out,
     a.n = n;
     LSG_CUDA_TRY(launch_kernel(quantize_q8_1_batch_kernel, dim3(static_cast<unsigned>(ctas)), dim3(kQuantThreads), 0,
                                stream, pdl, a));
+    return LSG_OK;
+}
+
+int quantize_q8_1_gather(const void* x_bf16, const int32_t* map, int top_k, void* q8_1_out, int rows, int K,
+                          cudaStream_t stream, bool pdl) {
+    if (rows <= 0) return LSG_OK;
+    if (K <= 0 || K % 32 != 0 || top_k < 1) return fail(LSG_ERR_INVALID, "quantize_q8_1_gather: bad shape");
+    if (!x_bf16 || !map || !q8_1_out) return fail(LSG_ERR_INVALID, "quantize_q8_1_gather: null pointer");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(q8_1_out) & 3))
+        return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1_gather: input must be 16-byte and output 4-byte aligned");
+    const long long tasks = static_cast<long long>(rows) * (K / 8);
+    LSG_CUDA_TRY(launch_kernel(quantize_q8_1_rows_kernel<false>, dim3(static_cast<unsigned>((tasks + kQuantThreads - 1) / kQuantThreads)),
+                               dim3(kQuantThreads), 0, stream, pdl, static_cast<const __nv_bfloat16*>(x_bf16),
+                               static_cast<const __nv_bfloat16*>(nullptr), map, top_k, static_cast<uint8_t*>(q8_1_out), rows, K));
+    return LSG_OK;
+}
+
+int quantize_q8_1_silu_mul(const void* g_bf16, const void* u_bf16, void* q8_1_out, int rows, int K, cudaStream_t stream,
+                           bool pdl) {
+    if (rows <= 0) return LSG_OK;
+    if (K <= 0 || K % 32 != 0) return fail(LSG_ERR_INVALID, "quantize_q8_1_silu_mul: bad shape");
+    if (!g_bf16 || !u_bf16 || !q8_1_out) return fail(LSG_ERR_INVALID, "quantize_q8_1_silu_mul: null pointer");
+    if (((reinterpret_cast<uintptr_t>(g_bf16) | reinterpret_cast<uintptr_t>(u_bf16)) & 15) ||
+        (reinterpret_cast<uintptr_t>(q8_1_out) & 3))
+        return fail(LSG_ERR_ALIGNMENT, "quantize_q8_1_silu_mul: inputs must be 16-byte and output 4-byte aligned");
+    const long long tasks = static_cast<long long>(rows) * (K / 8);
+    LSG_CUDA_TRY(launch_kernel(quantize_q8_1_rows_kernel<true>, dim3(static_cast<unsigned>((tasks + kQuantThreads - 1) / kQuantThreads)),
+                               dim3(kQuantThreads), 0, stream, pdl, static_cast<const __nv_bfloat16*>(g_bf16),
+                               static_cast<const __nv_bfloat16*>(u_bf16), static_cast<const int32_t*>(nullptr), 1,
+                               static_cast<uint8_t*>(q8_1_out), rows, K));
     return LSG_OK;
 }
 
