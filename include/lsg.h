@@ -177,6 +177,15 @@ LSG_API int lsg_gguf_mmvq_noalloc(const lsg_gguf_mmvq_params* p, void* stream);
  * reference launches one kernel per projection (launch_gguf_mmvq,
  * csrc/sm120/gemm/gguf/gguf_mmvq.cu:130-152). */
 LSG_API size_t lsg_gguf_mmvq_batch_workspace_bytes(const lsg_gguf_mmvq_params* p, int n);
+/* How lsg_gguf_mmvq_batch would run the batch, without launching anything (host arithmetic on
+ * the parameter blocks only; no device needed): returns the number of launches and, for the
+ * first `cap` of them, the first entry, the number of entries and the kind of each: 0 waits for
+ * the launch in front of it, 1 is the first launch of a batch whose later launches need not
+ * wait (it waits for the work in front of the call and releases the next launch after that),
+ * 2 does not wait for the launch in front of it; + 4 when a quantizer launch precedes the
+ * mat-vec (activations above the in-kernel quantizer's limit).  Output arrays may be null. */
+LSG_API int lsg_gguf_mmvq_batch_plan(const lsg_gguf_mmvq_params* p, int n, int* first, int* count, int* kind,
+                                     int cap);
 LSG_API int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* workspace,
                         size_t workspace_bytes, void* stream);
 

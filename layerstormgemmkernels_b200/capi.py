@@ -120,6 +120,8 @@ def _load():
         "lsg_gguf_mmvq_q8_1": (ci, [ctypes.POINTER(GgufMmvqParams), vp, vp]),
         "lsg_gguf_mmvq_batch_workspace_bytes": (sz, [ctypes.POINTER(GgufMmvqParams), ci]),
         "lsg_gguf_mmvq_batch": (ci, [ctypes.POINTER(GgufMmvqParams), ci, vp, sz, vp]),
+        "lsg_gguf_mmvq_batch_plan": (ci, [ctypes.POINTER(GgufMmvqParams), ci, ctypes.POINTER(ci), ctypes.POINTER(ci),
+                                          ctypes.POINTER(ci), ci]),
         "lsg_gguf_mmvq_host_workspace_bytes": (sz, [ci, ci, ci]),
         "lsg_gguf_mmvq_host": (ci, [ctypes.POINTER(GgufMmvqParams), vp, sz, vp]),
         "lsg_gguf_mmvq_host_batch_workspace_bytes": (sz, [ctypes.POINTER(GgufMmvqParams), ci]),

@@ -286,17 +286,22 @@ Span c_span(const lsg_gguf_mmvq_params& q) {
     return {b, b + static_cast<uintptr_t>(q.M) * q.N * (q.out_dtype == LSG_DTYPE_F32 ? 4 : 2)};
 }
 
-// True when entries [i, i + run) read nothing an earlier entry writes and write nothing an
-// earlier entry reads or writes.
-bool independent_of_earlier(const lsg_gguf_mmvq_params* p, int i, int run) {
-    for (int j = i; j < i + run; ++j) {
-        const Span a = a_span(p[j]), c = c_span(p[j]);
-        for (int k = 0; k < i; ++k) {
-            if (p[k].M == 0 || p[k].N == 0) continue;
-            const Span ak = a_span(p[k]), ck = c_span(p[k]);
-            if (a.meets(ck) || c.meets(ck) || c.meets(ak)) return false;
-        }
+// True when entry j reads nothing an entry before `limit` writes and writes nothing such an
+// entry reads or writes.
+bool entry_independent(const lsg_gguf_mmvq_params* p, int j, int limit) {
+    const Span a = a_span(p[j]), c = c_span(p[j]);
+    for (int k = 0; k < limit; ++k) {
+        if (p[k].M == 0 || p[k].N == 0) continue;
+        const Span ak = a_span(p[k]), ck = c_span(p[k]);
+        if (a.meets(ck) || c.meets(ck) || c.meets(ak)) return false;
     }
+    return true;
+}
+
+// The same for all entries [i, i + run) against the entries before i.
+bool independent_of_earlier(const lsg_gguf_mmvq_params* p, int i, int run) {
+    for (int j = i; j < i + run; ++j)
+        if (!entry_independent(p, j, i)) return false;
     return true;
 }
 
@@ -314,10 +319,14 @@ bool batch_overlap_enabled() {
 int joinable_run(const lsg_gguf_mmvq_params* p, int i, int n, bool distinct_a = false) {
     int run = 1;
     if (p[i].M < 1 || p[i].N < 1) return 1;
+    // with launches that may skip their wait, a launch holds only entries that all depend on
+    // earlier entries of the call or all do not: one dependent entry would make the others wait
+    const bool free0 = distinct_a && entry_independent(p, i, i);
     while (i + run < n && run < 1 + kMmvqMaxExtra) {
         const lsg_gguf_mmvq_params& a = p[i];
         const lsg_gguf_mmvq_params& b = p[i + run];
         if (b.M != a.M || b.K != a.K || b.type != a.type || b.out_dtype != a.out_dtype || b.N < 1) break;
+        if (distinct_a && entry_independent(p, i + run, i) != free0) break;
         if (b.A != a.A) {
             // Activations of its own: the entry may share the launch when both take the
             // quantizer inside the kernel and it shares no buffer with the entries already in
@@ -331,6 +340,51 @@ int joinable_run(const lsg_gguf_mmvq_params* p, int i, int n, bool distinct_a = 
         ++run;
     }
     return run;
+}
+
+// One launch of a batch call: entries [first, first + count), how it is ordered against the
+// launch in front of it (MmvqArgs::dep_mode; -1: the entries are empty, nothing is launched)
+// and whether the activations are quantized inside the mat-vec.
+struct BatchGroup {
+    int first, count, kind;
+    bool fused;
+};
+
+// Launches that neither read what an earlier entry of the batch writes nor write what an
+// earlier entry reads or writes need not wait for the launch in front of them: only the first
+// launch waits for the work in front of the batch (and releases the next launch only after
+// that wait).  Needs the first launch to be a mat-vec with the quantizer inside and at least
+// one later launch of that kind that is independent of the entries before it.
+bool batch_is_relaxed(const lsg_gguf_mmvq_params* p, int n) {
+    if (!batch_overlap_enabled()) return false;
+    bool first = true, first_fused = false;
+    for (int i = 0; i < n;) {
+        const int run = joinable_run(p, i, n, true);
+        if (p[i].M > 0 && p[i].N > 0) {
+            const bool fused = fused_quant_ok(p[i].M, p[i].K, p[i].A);
+            if (first) first_fused = fused;
+            else if (first_fused && fused && independent_of_earlier(p, i, run)) return true;
+            first = false;
+        }
+        i += run;
+    }
+    return false;
+}
+
+// The launch that starts at entry i.
+BatchGroup next_batch_group(const lsg_gguf_mmvq_params* p, int n, int i, bool relaxed) {
+    BatchGroup g = {i, joinable_run(p, i, n, batch_overlap_enabled()), -1, false};
+    const lsg_gguf_mmvq_params& e = p[i];
+    if (e.M == 0 || e.N == 0) return g;
+    g.fused = fused_quant_ok(e.M, e.K, e.A);
+    g.kind = 0;
+    if (relaxed) {
+        bool launched = false;
+        for (int k = 0; k < i && !launched; ++k) launched = p[k].M > 0 && p[k].N > 0;
+        if (!launched) g.kind = 1;
+        else if (g.fused && independent_of_earlier(p, i, g.count)) g.kind = 2;
+    }
+    return g;
 }
 
 }  // namespace
@@ -358,63 +412,52 @@ extern "C" int lsg_gguf_mmvq_batch(const lsg_gguf_mmvq_params* p, int n, void* w
         return fail(LSG_ERR_WORKSPACE, "gguf_mmvq_batch: workspace too small (have %zu, need %zu)",
                     workspace ? workspace_bytes : size_t(0), need);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Launches that neither read what an earlier entry of the batch writes nor write what an
-    // earlier entry reads or writes need not wait for the launch in front of them: only the
-    // first launch waits for the work in front of the batch (and releases the next launch only
-    // after that wait).  Needs the first launch to be a mat-vec with the quantizer inside and
-    // at least one later launch of that kind.
-    const bool overlap = batch_overlap_enabled();
-    bool relaxed = false;
-    if (overlap) {
-        bool first = true, first_fused = false;
-        for (int i = 0; i < n;) {
-            const int run = joinable_run(p, i, n, true);
-            if (p[i].M > 0 && p[i].N > 0) {
-                const bool fused = fused_quant_ok(p[i].M, p[i].K, p[i].A);
-                if (first) first_fused = fused;
-                else if (first_fused && fused && independent_of_earlier(p, i, run)) relaxed = true;
-                first = false;
-            }
-            i += run;
-        }
-    }
-    bool launched = false;
     for (int i = 0; i < n;) {
-        const int run = joinable_run(p, i, n, overlap);
-        const lsg_gguf_mmvq_params& e = p[i];
-        if (e.M == 0 || e.N == 0) {
-            i += run;
-            continue;
-        }
-        int dep_mode = 0;
-        if (relaxed) {
-            if (!launched) dep_mode = 1;
-            else if (fused_quant_ok(e.M, e.K, e.A) && independent_of_earlier(p, i, run)) dep_mode = 2;
-        }
-        launched = true;
+        const BatchGroup g = next_batch_group(p, n, i, batch_is_relaxed(p, n));
+        i = g.first + g.count;
+        if (g.kind < 0) continue;   // empty entries
+        const lsg_gguf_mmvq_params& e = p[g.first];
         const void* W[1 + kMmvqMaxExtra];
         const void* A[1 + kMmvqMaxExtra];
         void* C[1 + kMmvqMaxExtra];
         int N[1 + kMmvqMaxExtra];
-        for (int j = 0; j < run; ++j) {
-            W[j] = p[i + j].B;
-            A[j] = p[i + j].A;
-            C[j] = p[i + j].C;
-            N[j] = p[i + j].N;
+        for (int j = 0; j < g.count; ++j) {
+            W[j] = p[g.first + j].B;
+            A[j] = p[g.first + j].A;
+            C[j] = p[g.first + j].C;
+            N[j] = p[g.first + j].N;
         }
         const int out_f32 = e.out_dtype == LSG_DTYPE_F32;
         int rc;
-        if (fused_quant_ok(e.M, e.K, e.A)) {
-            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, nullptr, out_f32, s, true, e.A, dep_mode, A);
+        if (g.fused) {
+            rc = mmvq_q8_1_joined(e.type, e.M, e.K, g.count, W, C, N, nullptr, out_f32, s, true, e.A, g.kind, A);
         } else {
             rc = quantize_q8_1(e.A, workspace, e.M, e.K, s, true);
             if (rc != LSG_OK) return rc;
-            rc = mmvq_q8_1_joined(e.type, e.M, e.K, run, W, C, N, workspace, out_f32, s, true, nullptr);
+            rc = mmvq_q8_1_joined(e.type, e.M, e.K, g.count, W, C, N, workspace, out_f32, s, true, nullptr);
         }
         if (rc != LSG_OK) return rc;
-        i += run;
     }
     return LSG_OK;
+}
+
+extern "C" int lsg_gguf_mmvq_batch_plan(const lsg_gguf_mmvq_params* p, int n, int* first, int* count, int* kind,
+                                        int cap) {
+    if (n < 0 || (n > 0 && !p)) return fail(LSG_ERR_INVALID, "gguf_mmvq_batch_plan: null params");
+    const bool relaxed = batch_is_relaxed(p, n);
+    int groups = 0;
+    for (int i = 0; i < n;) {
+        const BatchGroup g = next_batch_group(p, n, i, relaxed);
+        i = g.first + g.count;
+        if (g.kind < 0) continue;
+        if (groups < cap) {
+            if (first) first[groups] = g.first;
+            if (count) count[groups] = g.count;
+            if (kind) kind[groups] = g.kind + (g.fused ? 0 : 4);
+        }
+        ++groups;
+    }
+    return groups;
 }
 
 namespace lsg {

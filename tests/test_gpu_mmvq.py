@@ -258,38 +258,46 @@ def test_mmvq_batch_distinct_inputs_share_a_launch(ops, name, M):
 def test_mmvq_batch_independent_launches_overlap_dependent_ones_wait(ops):
     """lsg_gguf_mmvq_batch lets a launch start before the one in front of it has finished when it
     shares no buffer with the earlier entries; an entry that reads an earlier result (or writes
-    an earlier entry's buffer) must still wait.  Five launches, mixed, large enough to take a few
-    microseconds each, replayed back to back from a CUDA graph with changing inputs: every result
-    equals the separate calls'."""
+    an earlier entry's buffer) must still wait.  Six entries in five launches of every kind (the
+    plan is checked first), large enough to take a few microseconds each, replayed back to back
+    from a CUDA graph with changing inputs: every result equals the separate calls'."""
     from layerstormgemmkernels_b200 import capi
     import ctypes
     t = T["Q4_K"]
     K0, N0, N1, N2 = 4096, 4096, 2048, 1024
-    W0 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N0, K0, seed=1)).cuda()     # y0 = x W0^T
-    W1 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N1, N0, seed=2)).cuda()     # y1 = y0 W1^T   (reads y0)
-    W2 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=3)).cuda()     # y2 = x2 W2^T   (independent)
-    W3 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, N1, seed=4)).cuda()     # y3 = y1 W3^T   (reads y1)
-    W4 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=5)).cuda()     # y2 = x W4^T    (rewrites y2)
+    W0 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N0, K0, seed=1)).cuda()     # 0: y0 = x W0^T
+    W2 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=3)).cuda()     # 1: y2 = x2 W2^T  (joins 0)
+    W1 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N1, N0, seed=2)).cuda()     # 2: y1 = y0 W1^T  (reads y0)
+    W5 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, N1, seed=6)).cuda()     # 3: y3 = x3 W5^T  (independent)
+    W3 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, N1, seed=4)).cuda()     # 4: y4 = y1 W3^T  (reads y1)
+    W4 = torch.from_numpy(Q.random_gguf_weight("Q4_K", N2, K0, seed=5)).cuda()     # 5: y2 = x W4^T   (rewrites y2)
     x = torch.zeros((1, K0), dtype=torch.bfloat16, device="cuda")
     x2 = torch.zeros((1, K0), dtype=torch.bfloat16, device="cuda")
+    x3 = torch.zeros((1, N1), dtype=torch.bfloat16, device="cuda")
     y0 = torch.zeros((1, N0), dtype=torch.bfloat16, device="cuda")
     y1 = torch.zeros((1, N1), dtype=torch.bfloat16, device="cuda")
     y2 = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")
     y3 = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")
-    keep = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")   # y2 of entry 2, copied out before entry 4 rewrites it
+    y4 = torch.zeros((1, N2), dtype=torch.bfloat16, device="cuda")
     P = capi.GgufMmvqParams
-    arr = (P * 5)()
-    arr[0] = P(M=1, N=N0, K=K0, A=x.data_ptr(), B=W0.data_ptr(), C=y0.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-    arr[1] = P(M=1, N=N1, K=N0, A=y0.data_ptr(), B=W1.data_ptr(), C=y1.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-    arr[2] = P(M=1, N=N2, K=K0, A=x2.data_ptr(), B=W2.data_ptr(), C=y2.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-    arr[3] = P(M=1, N=N2, K=N1, A=y1.data_ptr(), B=W3.data_ptr(), C=y3.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-    arr[4] = P(M=1, N=N2, K=K0, A=x.data_ptr(), B=W4.data_ptr(), C=y2.data_ptr(), type=t, out_dtype=capi.DTYPE_BF16)
-    need = max(256, capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, 5))
+    arr = (P * 6)()
+    mk = lambda N, K, A, W, C: P(M=1, N=N, K=K, A=A.data_ptr(), B=W.data_ptr(), C=C.data_ptr(), type=t,  # noqa: E731
+                                 out_dtype=capi.DTYPE_BF16)
+    arr[0] = mk(N0, K0, x, W0, y0)
+    arr[1] = mk(N2, K0, x2, W2, y2)
+    arr[2] = mk(N1, N0, y0, W1, y1)
+    arr[3] = mk(N2, N1, x3, W5, y3)
+    arr[4] = mk(N2, N1, y1, W3, y4)
+    arr[5] = mk(N2, K0, x, W4, y2)
+    f, c, k = (ctypes.c_int * 8)(), (ctypes.c_int * 8)(), (ctypes.c_int * 8)()
+    n = capi.lib.lsg_gguf_mmvq_batch_plan(arr, 6, f, c, k, 8)
+    assert [(f[i], c[i], k[i]) for i in range(n)] == [(0, 2, 1), (2, 1, 0), (3, 1, 2), (4, 1, 0), (5, 1, 0)]
+    need = max(256, capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(arr, 6))
     ws = torch.empty((need,), dtype=torch.uint8, device="cuda")
 
     def batch():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        capi.check(capi.lib.lsg_gguf_mmvq_batch(arr, 5, ctypes.c_void_p(ws.data_ptr()), need, st))
+        capi.check(capi.lib.lsg_gguf_mmvq_batch(arr, 6, ctypes.c_void_p(ws.data_ptr()), need, st))
 
     g = torch.Generator().manual_seed(9)
     xs = [(torch.randn(1, K0, generator=g) * 0.5).to(torch.bfloat16).cuda() for _ in range(6)]
@@ -303,13 +311,15 @@ def test_mmvq_batch_independent_launches_overlap_dependent_ones_wait(ops):
     for it in range(6):
         x.copy_(xs[it])
         x2.copy_(xs[(it + 1) % 6])
+        x3.copy_(xs[(it + 2) % 6][:, :N1])
         for _ in range(3):      # back-to-back replays: the next batch's first launch follows the last one directly
             graph.replay()
         torch.cuda.synchronize()
         r0 = ops.gguf_mmvq(xs[it], W0, t, N0, K0)
         r1 = ops.gguf_mmvq(r0, W1, t, N1, N0)
         assert torch.equal(y0, r0) and torch.equal(y1, r1)
-        assert torch.equal(y3, ops.gguf_mmvq(r1, W3, t, N2, N1))
+        assert torch.equal(y3, ops.gguf_mmvq(x3, W5, t, N2, N1))
+        assert torch.equal(y4, ops.gguf_mmvq(r1, W3, t, N2, N1))
         assert torch.equal(y2, ops.gguf_mmvq(xs[it], W4, t, N2, K0))
     assert capi.device_status() == 0
 
