@@ -230,6 +230,17 @@ def workload_config(args):
 # ----------------------------------------------------------------------------------------
 # The decode layer on the GPU
 # ----------------------------------------------------------------------------------------
+def planned_launches(capi, arr, n):
+    """(mat-vec launches, all kernel launches) of one lsg_gguf_mmvq_batch call over `arr[:n]`, asked
+    of lsg_gguf_mmvq_batch_plan: a mat-vec whose activations are above the in-kernel
+    quantizer's limit has a quantizer launch in front of it (kind + 4)."""
+    kind = (ctypes.c_int * max(n, 1))()
+    groups = capi.lib.lsg_gguf_mmvq_batch_plan(arr, n, None, None, kind, n)
+    if groups < 0:
+        raise RuntimeError("lsg_gguf_mmvq_batch_plan failed")
+    return groups, sum(2 if kind[i] >= 4 else 1 for i in range(groups))
+
+
 class DecodeLayerBench:
     """Device-resident layer copies, their argument blocks and graphs."""
 
@@ -256,20 +267,8 @@ class DecodeLayerBench:
         self.args = [self._params(w) for w in self.layers]
         need = capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(self.args[0], len(layer))
         self.ws = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
-        # launches of one lsg_gguf_mmvq_batch call, as the library forms them: consecutive
-        # projections of one K share a launch (up to six) when they read the same activations or,
-        # with the quantizer inside the kernel (M * K <= 32768), independent ones
-        joined = []
-        for name, _, K in layer:
-            fused = M * K <= 32768
-            if (joined and joined[-1][1] == K and joined[-1][2] < 6
-                    and (joined[-1][0] == group[name] or (fused and joined[-1][3]))):
-                joined[-1][2] += 1
-                joined[-1][0] = group[name]
-            else:
-                joined.append([group[name], K, 1, fused])
-        self.n_matvec = len(joined)
-        self.launches_per_step = sum(1 if f else 2 for _, _, _, f in joined)
+        # launches of one lsg_gguf_mmvq_batch call, as the library's own planner forms them
+        self.n_matvec, self.launches_per_step = planned_launches(capi, self.args[0], len(layer))
 
     def _params(self, weights):
         capi = self.capi

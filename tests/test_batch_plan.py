@@ -98,3 +98,16 @@ def test_environment_switch_restores_waiting_launches():
 
 def test_null_params_are_rejected():
     assert capi.lib.lsg_gguf_mmvq_batch_plan(None, 3, None, None, None, 0) < 0
+
+
+def test_bench_counts_its_launches_with_the_planner():
+    """bench.py reports gpu_launches from the library's own plan of its layer."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root)
+    import bench
+    def arr_of(entries):
+        return (P * len(entries))(*[P(M=M, N=N, K=K, A=A, B=0x1000, C=C, type=Q4_K, out_dtype=capi.DTYPE_BF16)
+                                    for (M, N, K, A, C) in entries])
+    assert bench.planned_launches(capi, arr_of(layer(1)), 7) == (2, 2)
+    assert bench.planned_launches(capi, arr_of(layer(8)), 7) == (2, 3)      # down: quantizer + mat-vec
+    assert bench.planned_launches(capi, arr_of(layer(16)), 7) == (4, 8)
