@@ -268,7 +268,19 @@ class DecodeLayerBench:
         need = capi.lib.lsg_gguf_mmvq_batch_workspace_bytes(self.args[0], len(layer))
         self.ws = torch.empty((max(need, 256),), dtype=torch.uint8, device=dev)
         # launches of one lsg_gguf_mmvq_batch call, as the library's own planner forms them
-        self.n_matvec, self.launches_per_step = planned_launches(capi, self.args[0], len(layer))
+        try:
+            self.n_matvec, self.launches_per_step = planned_launches(capi, self.args[0], len(layer))
+        except Exception:  # noqa: BLE001 - an older library without the planner: its rule restated
+            runs = []
+            for name, _, K in layer:
+                fused = M * K <= 32768
+                if runs and runs[-1][1] == K and runs[-1][2] < 6 and (runs[-1][0] == group[name] or (fused and runs[-1][3])):
+                    runs[-1][2] += 1
+                    runs[-1][0] = group[name]
+                else:
+                    runs.append([group[name], K, 1, fused])
+            self.n_matvec = len(runs)
+            self.launches_per_step = sum(1 if f else 2 for _, _, _, f in runs)
 
     def _params(self, weights):
         capi = self.capi
